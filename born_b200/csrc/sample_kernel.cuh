@@ -1,0 +1,774 @@
+// The fused row-sampling kernel: one launch does penalties -> grammar mask -> row max /
+// log-sum-exp -> top-k -> temperature -> min-p -> top-p -> inverse-CDF draw.
+//
+// Work decomposition.  A row of the [batch, vocab] logits is cut into S contiguous slices;
+// CTA (slice, row) streams its slice from HBM exactly once through a ring of kStages
+// shared-memory tiles filled by 1-D bulk copies (TMA, non-multicast) that complete on
+// mbarriers, and reads the tiles with 128-bit shared loads.  While streaming it keeps
+//   * the running maximum (NaN-propagating) and an online log-sum-exp per thread,
+//   * a candidate buffer of (rank key) entries that still can be among the k best.
+// Elements enter the buffer when they reach the current threshold tau; when the buffer
+// fills up, a radix select (shared-memory histograms, digit located with warp ballot)
+// finds the exact k-th best entry, the buffer is compacted to k and tau rises.  Since the
+// kept set of every filter is a prefix of the rank order, the k best entries of a slice are
+// all that the rest of the pipeline needs.
+// Each slice leaves a record (max, lse partial, <= k entries) in scratch memory; the last
+// CTA of a row to finish (atomic ticket, no spinning) merges the records and runs the
+// selection and the draw on exact integer masses.
+//
+// Greedy selection keeps the reference's tie rule -- the first maximum wins
+// (born: internal/nn/cross_entropy.go:241-251) -- through the rank key (value, -index).
+#pragma once
+#include <float.h>
+#include "../../include/born_sampler.h"
+#include "spec.cuh"
+
+namespace born {
+
+enum : int { kModeFull = 0, kModeLocal = 1, kModeMerge = 2 };
+
+struct RecordHdr {  // 32 bytes, precedes the entries of a slice / shard record
+    float m;        // maximum of the slice (NaN if a NaN was seen)
+    float lse_s;    // sum of 2^((z - m) * c2) over the slice
+    uint32_t count; // entries that follow
+    uint32_t flags; // bit 0: entries were dropped (more than k candidates existed)
+    uint32_t pad[4];
+};
+static_assert(sizeof(RecordHdr) == kRecordHdrBytes, "record header size");
+
+struct SampleKernelArgs {
+    const void* logits;
+    int64_t row_stride;  // elements
+    const uint32_t* mask;
+    int64_t mask_stride;  // words
+    const int32_t* history;
+    const int32_t* history_len;
+    int history_stride;
+    int B, V;
+    const born_row_params* row_params;
+    born_row_params params;
+    const float* uniforms;
+    int32_t* out_token;
+    float* out_prob;
+    float* out_lse;
+    int32_t* out_status;
+    int32_t* out_kept_ids;
+    int32_t* out_kept_count;
+    int kept_stride;
+    int mode;
+    int S;             // slices (or shards when merging) per row
+    int slice_len;     // elements per slice
+    int segment_mode;  // 1: each slice keeps its own top-k, the merge takes the union
+    int idx_offset;    // added to token indices written to records (shard offset)
+    int tma_logits, tma_mask;
+    uint8_t* records;  // record (row, slice) at row*rec_row_stride + slice*rec_slice_stride
+    int64_t rec_row_stride, rec_slice_stride;
+    uint32_t* tickets;
+    int* dev_error;
+};
+
+template <typename T>
+struct VecOf;
+template <>
+struct VecOf<float> { static constexpr int n = 4; };
+template <>
+struct VecOf<uint16_t> { static constexpr int n = 8; };
+
+// Shared-memory layout, computed identically on host and device.
+struct SmemLayout {
+    int tiles, masks, cand, search, pairs, hist, total;
+};
+__host__ __device__ inline SmemLayout smem_layout(int elem_bytes, bool has_mask, bool has_hist) {
+    SmemLayout L;
+    int off = 0;
+    L.tiles = off; off += kStages * kChunk * elem_bytes;
+    L.masks = off; off += has_mask ? kStages * (kChunk / 32) * 4 : 0;
+    L.cand = off; off += kCandCap * 8;
+    L.search = off; off += (int)((sizeof(SearchScratch) + 127) / 128 * 128);
+    L.pairs = off; off += kMaxK * 2 * 2;
+    L.hist = off; off += has_hist ? kHistCap * 8 : 0;
+    L.total = off;
+    return L;
+}
+
+struct BlockShared {  // static shared state of a CTA
+    unsigned long long bars[kStages];
+    unsigned long long tau_ck;
+    unsigned long long red64[kThreads / 32];
+    float redf[kThreads / 32];
+    float tau;
+    uint32_t maxbits;
+    int count;
+    int overflow;
+    int fail;
+    int dropped;
+    int nh;
+    int nl, nw;
+    int last;
+};
+
+struct ThreadStats {
+    float mx;   // running maximum (NaN-propagating)
+    float R;    // reference of the online log-sum-exp (z domain)
+    float nRc;  // -R * c2
+    float s;    // sum of 2^((z - R) * c2)
+};
+
+struct Ctx {  // per-CTA pointers and row constants, all block-uniform
+    uint64_t* cand;
+    SearchScratch* sc;
+    uint16_t* lslot;
+    uint16_t* wpos;
+    int32_t* hlist;
+    float* hval;
+    BlockShared* bs;
+    int k_eff;
+    int trigger;
+    float c2;
+    float delta_minp;
+    bool minp_on;
+    born_row_params rp;
+};
+
+// Keep the k best entries of cand[0..count) (exact, by rank key) and raise tau.
+__device__ void compact_to_k(Ctx& cx, int k) {
+    BlockShared& bs = *cx.bs;
+    const int tid = threadIdx.x;
+    __syncthreads();
+    int n = bs.count;
+    if (n <= k) return;
+    uint64_t* cand = cx.cand;
+    uint64_t T = block_radix_search<true, 56>(
+        n, (unsigned long long)(k - 1), [&](int i) { return cand[i]; }, [&](int) { return 1ull; }, *cx.sc);
+    if (tid == 0) { bs.nl = 0; bs.nw = 0; }
+    __syncthreads();
+    for (int i = tid; i < n; i += kThreads) {
+        uint64_t c = cand[i];
+        if (i < k) {
+            if (c < T) cx.lslot[atomicAdd(&bs.nl, 1)] = (uint16_t)i;
+        } else if (c >= T) {
+            cx.wpos[atomicAdd(&bs.nw, 1)] = (uint16_t)i;
+        }
+    }
+    __syncthreads();
+    int nl = bs.nl;
+    for (int j = tid; j < nl; j += kThreads) cand[cx.lslot[j]] = cand[cx.wpos[j]];
+    if (tid == 0) {
+        bs.count = k;
+        bs.tau_ck = T;
+        bs.tau = ck_z(T);
+        bs.dropped = 1;
+    }
+    __syncthreads();
+}
+
+// Local flag bits a thread raises for the end-of-chunk vote.
+enum : int { kFlagTrigger = 1, kFlagOverflow = 2, kFlagTimeout = 4 };
+
+__device__ __forceinline__ void try_append(Ctx& cx, float z, int idx, uint64_t tau_ck, int& lflag) {
+    uint64_t ck = make_ck(z, idx);
+    if (ck > tau_ck) {
+        int pos = atomicAdd(&cx.bs->count, 1);
+        if (pos < kCandCap) {
+            cx.cand[pos] = ck;
+            if (pos >= cx.trigger) lflag |= kFlagTrigger;
+        } else {
+            cx.bs->overflow = 1;
+            lflag |= kFlagOverflow;
+        }
+    }
+}
+
+template <bool kLse>
+__device__ __forceinline__ void stats_one(ThreadStats& st, float z, float c2) {
+    st.mx = max_nan(st.mx, z);
+    if (kLse) {
+        if (z > st.R) {
+            st.s *= ex2_approx(__fmul_rn(st.R - z, c2));
+            st.R = z;
+            st.nRc = -z * c2;
+        }
+        st.s += ex2_approx(fmaf(z, c2, st.nRc));
+    }
+}
+
+// One vector group (16 bytes) of the tile: mask, statistics, candidate test.
+template <typename T, bool kHasMask, bool kLse, bool kStats>
+__device__ __forceinline__ void process_group(Ctx& cx, ThreadStats& st, const T* tile, const uint32_t* smask, int g,
+                                              int c0, float tau, uint64_t tau_ck, int& lflag) {
+    constexpr int VEC = VecOf<T>::n;
+    float v[VEC];
+    if constexpr (VEC == 4) {
+        float4 q = reinterpret_cast<const float4*>(tile)[g];
+        v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+    } else {
+        uint4 q = reinterpret_cast<const uint4*>(tile)[g];
+        v[0] = __uint_as_float(q.x << 16); v[1] = __uint_as_float(q.x & 0xFFFF0000u);
+        v[2] = __uint_as_float(q.y << 16); v[3] = __uint_as_float(q.y & 0xFFFF0000u);
+        v[4] = __uint_as_float(q.z << 16); v[5] = __uint_as_float(q.z & 0xFFFF0000u);
+        v[6] = __uint_as_float(q.w << 16); v[7] = __uint_as_float(q.w & 0xFFFF0000u);
+    }
+    const int e = g * VEC;
+    if constexpr (kHasMask) {
+        uint32_t bits = smask[e >> 5] >> (e & 31);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[i] = ((bits >> i) & 1u) ? v[i] : -INFINITY;
+    }
+    if constexpr (kStats) {
+        float m4 = v[0];
+#pragma unroll
+        for (int i = 1; i < VEC; ++i) m4 = max_nan(m4, v[i]);
+        st.mx = max_nan(st.mx, m4);
+        if constexpr (kLse) {
+            if (m4 > st.R) {
+                st.s *= ex2_approx(__fmul_rn(st.R - m4, cx.c2));
+                st.R = m4;
+                st.nRc = -m4 * cx.c2;
+            }
+            float acc = 0.0f;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc += ex2_approx(fmaf(v[i], cx.c2, st.nRc));
+            st.s += acc;
+        }
+    }
+    bool any = false;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) any |= (v[i] >= tau);
+    if (any) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i)
+            if (v[i] >= tau) try_append(cx, v[i], c0 + e + i, tau_ck, lflag);
+    }
+}
+
+// History entries of this chunk: compute the penalised logit once per distinct token,
+// park it in hval and take the token out of the tile (-inf).
+template <typename T, bool kHasMask>
+__device__ __forceinline__ void patch_compute(Ctx& cx, T* tile, const uint32_t* smask, int c0, int nvalid, int nh) {
+    const born_row_params& rp = cx.rp;
+    const bool rep_on = (rp.repetition_penalty != 1.0f && rp.repetition_penalty != 0.0f);
+    const bool add_on = (rp.frequency_penalty != 0.0f || rp.presence_penalty != 0.0f);
+    bool wrote = false;
+    for (int i = threadIdx.x; i < nh; i += kThreads) {
+        int id = cx.hlist[i];
+        if (id < c0 || id >= c0 + nvalid) continue;
+        if (i > 0 && cx.hlist[i - 1] == id) continue;
+        int cnt = 1;
+        while (i + cnt < nh && cx.hlist[i + cnt] == id) ++cnt;
+        int off = id - c0;
+        float z;
+        if constexpr (sizeof(T) == 4) z = reinterpret_cast<float*>(tile)[off];
+        else z = bf16_bits_to_f32(reinterpret_cast<uint16_t*>(tile)[off]);
+        if (rep_on) z = (z > 0.0f) ? __fdiv_rn(z, rp.repetition_penalty) : __fmul_rn(z, rp.repetition_penalty);
+        if (add_on) {
+            float pen = __fmul_rn(rp.frequency_penalty, (float)cnt);
+            pen = __fadd_rn(pen, rp.presence_penalty);
+            z = __fsub_rn(z, pen);
+        }
+        if constexpr (kHasMask) {
+            if (!((smask[off >> 5] >> (off & 31)) & 1u)) z = -INFINITY;
+        }
+        cx.hval[i] = z;
+        if constexpr (sizeof(T) == 4) reinterpret_cast<float*>(tile)[off] = -INFINITY;
+        else reinterpret_cast<uint16_t*>(tile)[off] = 0xFF80u;
+        wrote = true;
+    }
+    if (wrote) fence_proxy_async();
+}
+
+template <bool kLse, bool kStats>
+__device__ __forceinline__ void patch_consume(Ctx& cx, ThreadStats& st, int c0, int nvalid, int nh, float tau,
+                                              uint64_t tau_ck, int& lflag) {
+    for (int i = threadIdx.x; i < nh; i += kThreads) {
+        int id = cx.hlist[i];
+        if (id < c0 || id >= c0 + nvalid) continue;
+        if (i > 0 && cx.hlist[i - 1] == id) continue;
+        float z = cx.hval[i];
+        if (kStats) stats_one<kLse>(st, z, cx.c2);
+        if (z >= tau) try_append(cx, z, id, tau_ck, lflag);
+    }
+}
+
+__device__ __forceinline__ float current_tau(const Ctx& cx) {
+    float tau = cx.bs->tau;
+    if (cx.minp_on) tau = fmaxf(tau, zkey_to_float(cx.bs->maxbits) + cx.delta_minp);
+    return tau;
+}
+
+// A whole chunk with no synchronisation inside (the common case).
+template <typename T, bool kHasMask, bool kLse>
+__device__ __forceinline__ void process_chunk_fast(Ctx& cx, ThreadStats& st, const T* tile, const uint32_t* smask,
+                                                   int c0, int nvalid, int nh, int& lflag) {
+    constexpr int VEC = VecOf<T>::n;
+    constexpr int ITER = kChunk / VEC / kThreads;
+    const float tau = current_tau(cx);
+    const uint64_t tau_ck = cx.bs->tau_ck;
+    if (nh > 0) patch_consume<kLse, true>(cx, st, c0, nvalid, nh, tau, tau_ck, lflag);
+#pragma unroll
+    for (int j = 0; j < ITER; ++j)
+        process_group<T, kHasMask, kLse, true>(cx, st, tile, smask, threadIdx.x + kThreads * j, c0, tau, tau_ck,
+                                               lflag);
+}
+
+// The same chunk in pieces small enough that the candidate buffer cannot overflow, with a
+// compaction check before every piece.  Used for the first chunk of a slice (tau is still
+// open) and to redo a chunk whose fast pass ran out of buffer.  Shared counters are read
+// between two barriers so that every thread takes the same branch.
+template <typename T, bool kHasMask, bool kLse, bool kStats>
+__device__ void process_chunk_safe(Ctx& cx, ThreadStats& st, const T* tile, const uint32_t* smask, int c0, int nvalid,
+                                   int nh) {
+    constexpr int VEC = VecOf<T>::n;
+    constexpr int ITER = kChunk / VEC / kThreads;
+    constexpr int kPiece = (kThreads / 2) * VEC;  // <= 1024 appends per piece
+    BlockShared& bs = *cx.bs;
+    int lflag = 0;
+    if (nh > 0) {
+        __syncthreads();
+        const int cnt = bs.count;
+        __syncthreads();
+        if (cnt > cx.trigger || cnt + kHistCap > kCandCap) compact_to_k(cx, cx.k_eff);
+        patch_consume<kLse, kStats>(cx, st, c0, nvalid, nh, current_tau(cx), bs.tau_ck, lflag);
+    }
+    for (int j = 0; j < ITER; ++j) {
+        for (int h = 0; h < 2; ++h) {
+            __syncthreads();
+            const int cnt = bs.count;
+            __syncthreads();
+            if (cnt > cx.trigger || cnt + kPiece > kCandCap) compact_to_k(cx, cx.k_eff);
+            if ((threadIdx.x >> 7) == h)
+                process_group<T, kHasMask, kLse, kStats>(cx, st, tile, smask, threadIdx.x + kThreads * j, c0,
+                                                         current_tau(cx), bs.tau_ck, lflag);
+        }
+    }
+    __syncthreads();
+}
+
+// In-place bitonic sort of hlist[0..n2) (n2 a power of two).
+__device__ void sort_history(int32_t* h, int n2) {
+    for (int k = 2; k <= n2; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            __syncthreads();
+            for (int i = threadIdx.x; i < n2; i += kThreads) {
+                int ixj = i ^ j;
+                if (ixj > i) {
+                    int32_t a = h[i], b = h[ixj];
+                    bool up = ((i & k) == 0);
+                    if ((a > b) == up) { h[i] = b; h[ixj] = a; }
+                }
+            }
+        }
+    }
+    __syncthreads();
+}
+
+template <typename T, bool kHasMask, bool kLse>
+__global__ void __launch_bounds__(kThreads, 2) sample_kernel(const SampleKernelArgs A) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ BlockShared bs;
+    const int tid = threadIdx.x;
+    const int row = blockIdx.y, slice = blockIdx.x;
+    const bool has_hist = A.history != nullptr;
+    const SmemLayout L = smem_layout((int)sizeof(T), kHasMask, has_hist);
+
+    Ctx cx;
+    cx.cand = reinterpret_cast<uint64_t*>(smem + L.cand);
+    cx.sc = reinterpret_cast<SearchScratch*>(smem + L.search);
+    cx.lslot = reinterpret_cast<uint16_t*>(smem + L.pairs);
+    cx.wpos = cx.lslot + kMaxK;
+    cx.hlist = reinterpret_cast<int32_t*>(smem + L.hist);
+    cx.hval = reinterpret_cast<float*>(smem + L.hist + kHistCap * 4);
+    cx.bs = &bs;
+    cx.rp = A.row_params ? A.row_params[row] : A.params;
+    const born_row_params& rp = cx.rp;
+    const bool greedy = (rp.flags & BORN_FLAG_GREEDY) || rp.temperature == 0.0f;
+    const float inv_T = greedy ? 1.0f : __fdiv_rn(1.0f, rp.temperature);
+    cx.c2 = inv_T * 1.44269504f;
+    cx.minp_on = !greedy && rp.min_p > 0.0f;
+    cx.delta_minp = cx.minp_on ? (__logf(rp.min_p) - 0.05f) * rp.temperature : 0.0f;
+    cx.k_eff = greedy ? 1 : (rp.top_k > 0 ? min(rp.top_k, kMaxK) : kMaxK);
+    cx.trigger = min(max(2 * cx.k_eff, 64), kCandCap - 512);
+
+    if (tid == 0) {
+        bs.tau = -FLT_MAX;
+        bs.tau_ck = 0;
+        bs.maxbits = zkey(-INFINITY);
+        bs.count = 0;
+        bs.overflow = 0;
+        bs.fail = 0;
+        bs.dropped = 0;
+        bs.nh = 0;
+        bs.last = 0;
+    }
+
+    float m_row = -INFINITY;  // maximum over the whole row (known after the merge)
+    float lse_sum = 0.0f;     // sum of 2^((z - m_row) * c2) over the whole row
+    int dropped = 0;
+
+    if (A.mode != kModeMerge) {
+        // ------------------------------------------------------------------ streaming pass
+        const int e_begin = slice * A.slice_len;
+        const int e_end = min(A.V, e_begin + A.slice_len);
+        const int nelem = max(0, e_end - e_begin);
+        const int nchunks = (nelem + kChunk - 1) / kChunk;
+        const T* grow = reinterpret_cast<const T*>(A.logits) + (int64_t)row * A.row_stride + e_begin;
+        const uint32_t* gmask = kHasMask ? A.mask + (int64_t)row * A.mask_stride + (e_begin >> 5) : nullptr;
+        T* tiles = reinterpret_cast<T*>(smem + L.tiles);
+        uint32_t* masks = reinterpret_cast<uint32_t*>(smem + L.masks);
+        const bool tma_l = A.tma_logits != 0, tma_m = kHasMask && A.tma_mask != 0;
+        const bool use_bar = tma_l || tma_m;
+
+        if (tid == 0) {
+            for (int s = 0; s < kStages; ++s) mbar_init(reinterpret_cast<uint64_t*>(&bs.bars[s]), 1);
+            mbar_fence_init();
+        }
+        __syncthreads();
+
+        auto issue = [&](int c) {  // thread 0 only
+            const int st = c % kStages;
+            const int n = min(kChunk, nelem - c * kChunk);
+            uint32_t bytes_l = tma_l ? (((uint32_t)n * (uint32_t)sizeof(T) + 15u) & ~15u) : 0u;
+            uint32_t bytes_m = tma_m ? ((((uint32_t)(n + 31) >> 5) * 4u + 15u) & ~15u) : 0u;
+            uint64_t* bar = reinterpret_cast<uint64_t*>(&bs.bars[st]);
+            mbar_expect_tx(bar, bytes_l + bytes_m);
+            if (tma_l) bulk_load(tiles + (size_t)st * kChunk, grow + (size_t)c * kChunk, bytes_l, bar);
+            if (tma_m) bulk_load(masks + st * (kChunk / 32), gmask + c * (kChunk / 32), bytes_m, bar);
+        };
+        if (tid == 0 && use_bar)
+            for (int c = 0; c < min(kStages, nchunks); ++c) issue(c);
+
+        // token history of this slice, sorted so that duplicates are adjacent
+        int nh = 0;
+        if (has_hist) {
+            const bool pen_on = (rp.repetition_penalty != 1.0f && rp.repetition_penalty != 0.0f) ||
+                                rp.frequency_penalty != 0.0f || rp.presence_penalty != 0.0f;
+            if (pen_on) {
+                int len = A.history_len ? A.history_len[row] : A.history_stride;
+                len = max(0, min(min(len, A.history_stride), kHistCap));
+                const int32_t* gh = A.history + (int64_t)row * A.history_stride;
+                for (int i = tid; i < len; i += kThreads) {
+                    int id = gh[i];
+                    if (id >= e_begin && id < e_end) cx.hlist[atomicAdd(&bs.nh, 1)] = id;
+                }
+                __syncthreads();
+                nh = bs.nh;
+                if (nh > 1) {
+                    int n2 = 2;
+                    while (n2 < nh) n2 <<= 1;
+                    for (int i = nh + tid; i < n2; i += kThreads) cx.hlist[i] = 0x7FFFFFFF;
+                    sort_history(cx.hlist, n2);
+                }
+            }
+        }
+
+        ThreadStats st;
+        st.mx = -INFINITY;
+        st.R = -1e30f;
+        st.nRc = 1e30f * cx.c2;
+        st.s = 0.0f;
+
+        int c_fail = -1;
+        for (int c = 0; c < nchunks; ++c) {
+            const int stg = c % kStages;
+            const uint32_t parity = (uint32_t)(c / kStages) & 1u;
+            const int c0 = e_begin + c * kChunk;
+            const int nvalid = min(kChunk, e_end - c0);
+            T* tile = tiles + (size_t)stg * kChunk;
+            uint32_t* smask = masks + stg * (kChunk / 32);
+            int lflag = 0;
+            if (use_bar) {
+                if (!mbar_wait(reinterpret_cast<uint64_t*>(&bs.bars[stg]), parity)) {
+                    bs.fail = 1;
+                    lflag |= kFlagTimeout;
+                }
+            }
+            bool need_sync = false;
+            if (!tma_l) {  // rows that are not 16-byte aligned: plain loads
+                const T* src = grow + (size_t)c * kChunk;
+                for (int i = tid; i < nvalid; i += kThreads) tile[i] = src[i];
+                need_sync = true;
+            }
+            if (kHasMask && !tma_m) {
+                const uint32_t* src = gmask + c * (kChunk / 32);
+                for (int i = tid; i < ((nvalid + 31) >> 5); i += kThreads) smask[i] = src[i];
+                need_sync = true;
+            }
+            if (nvalid < kChunk) {  // tail of the row: neutralise what lies beyond it
+                for (int i = nvalid + tid; i < kChunk; i += kThreads) {
+                    if constexpr (sizeof(T) == 4) reinterpret_cast<float*>(tile)[i] = -INFINITY;
+                    else reinterpret_cast<uint16_t*>(tile)[i] = 0xFF80u;
+                }
+                fence_proxy_async();
+                need_sync = true;
+            }
+            if (need_sync && nh > 0) __syncthreads();
+            if (nh > 0) {
+                patch_compute<T, kHasMask>(cx, tile, smask, c0, nvalid, nh);
+                need_sync = true;
+            }
+            if (need_sync) __syncthreads();
+
+            if (c == 0) {
+                process_chunk_safe<T, kHasMask, kLse, true>(cx, st, tile, smask, c0, nvalid, nh);
+            } else {
+                process_chunk_fast<T, kHasMask, kLse>(cx, st, tile, smask, c0, nvalid, nh, lflag);
+            }
+            if (cx.minp_on) {  // publish the running maximum for the min-p prune
+                float wm = st.mx;
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, d));
+                if ((tid & 31) == 0 && wm > -INFINITY) atomicMax(&bs.maxbits, zkey(wm));
+            }
+            // One barrier per chunk: it releases the tile and votes on the rare events.
+            if (__syncthreads_or(lflag)) {
+                const int ov = bs.overflow, fl = bs.fail;
+                __syncthreads();
+                if (fl) { c_fail = c; break; }
+                if (ov) {
+                    // the fast pass ran out of buffer: its appends sit at the tail of the
+                    // buffer; cut them off and redo the chunk piecewise
+                    const int ncur = min(bs.count, kCandCap);
+                    if (tid == 0) bs.nl = ncur;
+                    __syncthreads();
+                    for (int i = tid; i < ncur; i += kThreads) {
+                        int idx = ck_idx(cx.cand[i]);
+                        if (idx >= c0 && idx < c0 + kChunk) atomicMin(&bs.nl, i);
+                    }
+                    __syncthreads();
+                    if (tid == 0) { bs.count = bs.nl; bs.overflow = 0; }
+                    __syncthreads();
+                    process_chunk_safe<T, kHasMask, kLse, false>(cx, st, tile, smask, c0, nvalid, nh);
+                }
+                compact_to_k(cx, cx.k_eff);
+            }
+            if (tid == 0 && use_bar && c + kStages < nchunks) {
+                fence_proxy_async();
+                issue(c + kStages);
+            }
+        }
+        if (c_fail >= 0) {
+            // A bulk copy never arrived.  Wait (bounded) for the copies still in flight so
+            // that this CTA's shared memory is quiet before it exits, then report.
+            if (tid == 0) {
+                for (int cc = c_fail + 1; cc < min(nchunks, c_fail + kStages); ++cc)
+                    mbar_wait(reinterpret_cast<uint64_t*>(&bs.bars[cc % kStages]), (uint32_t)(cc / kStages) & 1u);
+                atomicExch(A.dev_error, 1);
+                if (A.out_status) A.out_status[row] = 100 + BORN_ERR_DEVICE_TIMEOUT;
+                if (A.out_token) A.out_token[row] = -1;
+            }
+            __syncthreads();
+            return;
+        }
+        compact_to_k(cx, cx.k_eff);
+        __syncthreads();
+
+        // slice statistics
+        float wm = st.mx;
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) wm = max_nan(wm, __shfl_xor_sync(0xffffffffu, wm, d));
+        if ((tid & 31) == 0) bs.redf[tid >> 5] = wm;
+        __syncthreads();
+        float m_slice = bs.redf[0];
+#pragma unroll
+        for (int w = 1; w < kThreads / 32; ++w) m_slice = max_nan(m_slice, bs.redf[w]);
+        __syncthreads();
+        float s_slice = 0.0f;
+        if (kLse) {
+            float v = st.s * ex2_approx(__fmul_rn(st.R - m_slice, cx.c2));
+            if (!(st.s > 0.0f)) v = 0.0f;
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+            if ((tid & 31) == 0) bs.redf[tid >> 5] = v;
+            __syncthreads();
+#pragma unroll
+            for (int w = 0; w < kThreads / 32; ++w) s_slice += bs.redf[w];
+            __syncthreads();
+        }
+
+        if (A.mode == kModeFull && A.S == 1) {
+            m_row = m_slice;
+            lse_sum = s_slice;
+            dropped = bs.dropped;
+        } else {
+            // leave the record, then take a ticket; only the last CTA of the row goes on
+            uint8_t* rec = A.records + (int64_t)row * A.rec_row_stride + (int64_t)slice * A.rec_slice_stride;
+            const int n = bs.count;
+            uint64_t* ent = reinterpret_cast<uint64_t*>(rec + kRecordHdrBytes);
+            for (int i = tid; i < n; i += kThreads) ent[i] = cx.cand[i] - (uint64_t)A.idx_offset;
+            if (tid == 0) {
+                RecordHdr h;
+                h.m = m_slice; h.lse_s = s_slice; h.count = (uint32_t)n; h.flags = (uint32_t)bs.dropped;
+                h.pad[0] = h.pad[1] = h.pad[2] = h.pad[3] = 0;
+                *reinterpret_cast<RecordHdr*>(rec) = h;
+            }
+            if (A.mode == kModeLocal) return;
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) {
+                uint32_t t = atomicAdd(&A.tickets[row], 1u);
+                bs.last = (t == (uint32_t)(A.S - 1));
+                if (bs.last) A.tickets[row] = 0;  // ready for the next launch
+            }
+            __syncthreads();
+            if (!bs.last) return;
+            __threadfence();
+        }
+    }
+
+    // ---------------------------------------------------------------------- merge records
+    if (A.mode == kModeMerge || A.S > 1) {
+        __syncthreads();
+        if (tid == 0) bs.count = 0;
+        __syncthreads();
+        m_row = -INFINITY;
+        for (int s = 0; s < A.S; ++s) {
+            const uint8_t* rec = A.records + (int64_t)row * A.rec_row_stride + (int64_t)s * A.rec_slice_stride;
+            m_row = max_nan(m_row, __ldcg(reinterpret_cast<const float*>(rec)));
+        }
+        for (int s = 0; s < A.S; ++s) {
+            const uint8_t* rec = A.records + (int64_t)row * A.rec_row_stride + (int64_t)s * A.rec_slice_stride;
+            const float ms_ = __ldcg(reinterpret_cast<const float*>(rec));
+            const float ss_ = __ldcg(reinterpret_cast<const float*>(rec) + 1);
+            const int cnt = (int)__ldcg(reinterpret_cast<const uint32_t*>(rec) + 2);
+            dropped |= (int)(__ldcg(reinterpret_cast<const uint32_t*>(rec) + 3) & 1u);
+            if (kLse && ss_ > 0.0f) lse_sum += ss_ * ex2_approx(__fmul_rn(ms_ - m_row, cx.c2));
+            if (!A.segment_mode && bs.count + cnt > kCandCap) compact_to_k(cx, cx.k_eff);
+            const int base = bs.count;
+            const unsigned long long* ent = reinterpret_cast<const unsigned long long*>(rec + kRecordHdrBytes);
+            for (int i = tid; i < cnt && base + i < kCandCap; i += kThreads) cx.cand[base + i] = __ldcg(ent + i);
+            __syncthreads();
+            if (tid == 0) bs.count = min(base + cnt, kCandCap);
+            __syncthreads();
+        }
+    }
+
+    // ------------------------------------------------------------- selection and draw
+    __syncthreads();
+    int n = bs.count;
+    int status = BORN_ROW_OK;
+    if (m_row != m_row) status = BORN_ROW_NAN;
+    else if (m_row == INFINITY) status = BORN_ROW_POS_INF;
+    else if (m_row == -INFINITY || n == 0) status = BORN_ROW_ALL_MASKED;
+    else if (!greedy && rp.top_k > kMaxK) status = BORN_ROW_OVERFLOW;
+    if (kLse && A.out_lse && tid == 0)
+        A.out_lse[row] = (status == BORN_ROW_OK) ? m_row * inv_T + __log2f(lse_sum) * 0.69314718f : NAN;
+    if (status != BORN_ROW_OK) {
+        if (tid == 0) {
+            A.out_token[row] = -1;
+            A.out_status[row] = status;
+            if (A.out_prob) A.out_prob[row] = 0.0f;
+            if (A.out_kept_count) A.out_kept_count[row] = 0;
+        }
+        return;
+    }
+    if (!A.segment_mode && n > cx.k_eff) {
+        compact_to_k(cx, cx.k_eff);
+        n = cx.k_eff;
+        dropped = 1;
+    }
+    dropped |= bs.dropped;
+    uint64_t* cand = cx.cand;
+    unsigned long long* qbuf = reinterpret_cast<unsigned long long*>(smem + L.tiles);  // tiles are idle now
+
+    if (greedy) {
+        uint64_t best = 0;
+        for (int i = tid; i < n; i += kThreads) best = max(best, cand[i]);
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) best = max(best, shfl_xor_u64(best, d));
+        if ((tid & 31) == 0) bs.red64[tid >> 5] = best;
+        __syncthreads();
+        if (tid == 0) {
+            for (int w = 1; w < kThreads / 32; ++w) best = max(best, (uint64_t)bs.red64[w]);
+            int tok = ck_idx(best);
+            A.out_token[row] = tok;
+            A.out_status[row] = BORN_ROW_OK;
+            if (A.out_prob) A.out_prob[row] = 1.0f;
+            if (A.out_kept_count) A.out_kept_count[row] = 1;
+            if (A.out_kept_ids && A.kept_stride > 0) A.out_kept_ids[(int64_t)row * A.kept_stride] = tok;
+        }
+        return;
+    }
+
+    // fixed-point masses relative to the row maximum
+    uint64_t Qa = 0;
+    if (cx.minp_on) Qa = __double2ull_ru((double)rp.min_p * 1099511627776.0);
+    uint64_t low_ck = ~0ull;
+    for (int i = tid; i < n; i += kThreads) {
+        uint64_t c = cand[i];
+        float x = scaled_shift(ck_z(c), m_row, inv_T);
+        qbuf[i] = (x < -30.0f) ? 0ull : mass_of(x);
+        low_ck = min(low_ck, c);
+    }
+    if (rp.top_k <= 0 && dropped) {
+        // survivor limit reached with top-k off: exact only if min-p cuts inside the buffer
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) low_ck = min(low_ck, shfl_xor_u64(low_ck, d));
+        __syncthreads();
+        if ((tid & 31) == 0) bs.red64[tid >> 5] = low_ck;
+        __syncthreads();
+        for (int w = 0; w < kThreads / 32; ++w) low_ck = min(low_ck, (uint64_t)bs.red64[w]);
+        float xl = scaled_shift(ck_z(low_ck), m_row, inv_T);
+        uint64_t ql = (xl < -30.0f) ? 0ull : mass_of(xl);
+        bool exact = cx.minp_on && (ql + (ql >> 18) + 4ull < Qa);
+        if (!exact) {
+            if (tid == 0) {
+                A.out_token[row] = -1;
+                A.out_status[row] = BORN_ROW_OVERFLOW;
+                if (A.out_prob) A.out_prob[row] = 0.0f;
+                if (A.out_kept_count) A.out_kept_count[row] = 0;
+            }
+            return;
+        }
+    }
+    __syncthreads();
+    if (Qa) {
+        for (int i = tid; i < n; i += kThreads)
+            if (qbuf[i] < Qa) { qbuf[i] = 0; cand[i] &= (uint64_t)kIdxMask; }
+        __syncthreads();
+    }
+    if (rp.top_p > 0.0f && rp.top_p < 1.0f) {
+        uint64_t part = 0;
+        for (int i = tid; i < n; i += kThreads) part += qbuf[i];
+        uint64_t S = block_sum_u64(part, bs.red64);
+        uint64_t Tp = __double2ull_rz(__dmul_rn((double)rp.top_p, __ull2double_rn(S)));
+        if (Tp < 1) Tp = 1;
+        uint64_t C = block_radix_search<true, 56>(
+            n, Tp - 1, [&](int i) { return cand[i]; }, [&](int i) { return qbuf[i]; }, *cx.sc);
+        for (int i = tid; i < n; i += kThreads)
+            if (cand[i] < C && ck_alive(cand[i])) { qbuf[i] = 0; cand[i] &= (uint64_t)kIdxMask; }
+        __syncthreads();
+    }
+    uint64_t part = 0;
+    for (int i = tid; i < n; i += kThreads) part += qbuf[i];
+    const uint64_t S = block_sum_u64(part, bs.red64);
+    const float u = A.uniforms ? A.uniforms[row] : 0.0f;
+    uint64_t t = __double2ull_rz(__dmul_rn((double)u, __ull2double_rn(S)));
+    if (t > S - 1) t = S - 1;
+    const uint64_t tok64 = block_radix_search<false, 24>(
+        n, t, [&](int i) { return (uint64_t)ck_idx(cand[i]); }, [&](int i) { return qbuf[i]; }, *cx.sc);
+    const int tok = (int)tok64;
+    for (int i = tid; i < n; i += kThreads) {
+        if (ck_idx(cand[i]) == tok && ck_alive(cand[i])) {
+            A.out_token[row] = tok;
+            A.out_status[row] = BORN_ROW_OK;
+            if (A.out_prob)
+                A.out_prob[row] = __double2float_rn(__ddiv_rn(__ull2double_rn(qbuf[i]), __ull2double_rn(S)));
+        }
+    }
+    if (A.out_kept_count || A.out_kept_ids) {
+        int alive = 0;
+        for (int i = tid; i < n; i += kThreads) {
+            uint64_t c = cand[i];
+            if (!ck_alive(c)) continue;
+            ++alive;
+            if (A.out_kept_ids) {
+                int rank = 0;
+                for (int j = 0; j < n; ++j) rank += (cand[j] > c) ? 1 : 0;
+                if (rank < A.kept_stride) A.out_kept_ids[(int64_t)row * A.kept_stride + rank] = ck_idx(c);
+            }
+        }
+        uint64_t tot = block_sum_u64((uint64_t)alive, bs.red64);
+        if (tid == 0 && A.out_kept_count) A.out_kept_count[row] = (int)tot;
+    }
+}
+
+}  // namespace born

@@ -1,0 +1,258 @@
+// Arithmetic and block-level primitives shared by every kernel of libborn_sampler.so.
+//
+// Everything that feeds a *decision* (which tokens are kept, which token is drawn) is
+// integer arithmetic on fixed-point masses, or a fixed sequence of individually rounded
+// fp32 operations, so that results do not depend on the order in which threads run and
+// can be restated bit-for-bit on a CPU.  The row arithmetic keeps the reference's
+// structure (born: internal/autodiff/ops/softmax.go:214-238 -- subtract the row maximum,
+// exponentiate, sum) but never materialises the softmax.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace born {
+
+constexpr int kThreads = 256;        // threads per CTA in the row kernels
+constexpr int kChunk = 4096;         // logits per pipeline stage
+constexpr int kStages = 4;           // bulk-copy stages in flight per CTA
+constexpr int kMaxK = 1024;          // BORN_MAX_TOP_K / BORN_MAX_CANDIDATES
+constexpr int kCandCap = 2048;       // candidate buffer entries (>= kMaxK + one half piece)
+constexpr int kHistCap = 1024;       // history ids held per CTA
+constexpr uint32_t kIdxMask = 0xFFFFFFu;
+constexpr int kRecordHdrBytes = 32;
+
+// ---- bit casts / keys -------------------------------------------------------------------
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t h) { return __uint_as_float(h << 16); }
+
+// Order-preserving map float -> uint32 (larger float => larger key); -0 is folded onto +0
+// so that equal values have equal keys.  No float maps to key 0.
+__device__ __forceinline__ uint32_t zkey(float z) {
+    uint32_t b = __float_as_uint(z);
+    if (b == 0x80000000u) b = 0u;
+    return b ^ ((uint32_t)((int32_t)b >> 31) | 0x80000000u);
+}
+__device__ __forceinline__ float zkey_to_float(uint32_t k) {
+    uint32_t b = (k & 0x80000000u) ? (k ^ 0x80000000u) : ~k;
+    return __uint_as_float(b);
+}
+// 56-bit composite rank key: larger = ranks earlier (value descending, index ascending).
+__device__ __forceinline__ uint64_t make_ck(float z, int idx) {
+    return ((uint64_t)zkey(z) << 24) | (uint64_t)(kIdxMask - (uint32_t)idx);
+}
+__device__ __forceinline__ int ck_idx(uint64_t ck) { return (int)(kIdxMask - (uint32_t)(ck & kIdxMask)); }
+__device__ __forceinline__ float ck_z(uint64_t ck) { return zkey_to_float((uint32_t)(ck >> 24)); }
+__device__ __forceinline__ bool ck_alive(uint64_t ck) { return (ck >> 24) != 0; }
+
+// ---- deterministic exp and fixed-point mass --------------------------------------------
+// Same operation sequence as the CPU oracle: Cody-Waite reduction, degree-6 polynomial,
+// exponent-field scaling.  x <= 0; returns 0 below -80 and for NaN.
+__device__ __forceinline__ float exp_det(float x) {
+    if (!(x >= -80.0f)) return 0.0f;
+    const float magic = 12582912.0f;
+    float t = __fmul_rn(x, 0x1.715476p+0f);
+    float r = __fadd_rn(t, magic);
+    float nf = __fsub_rn(r, magic);
+    float f = __fmaf_rn(nf, -0x1.62e4p-1f, x);
+    f = __fmaf_rn(nf, -0x1.7f7d1cp-20f, f);
+    float p = 0x1.687bf6p-10f;
+    p = __fmaf_rn(p, f, 0x1.123b9ep-7f);
+    p = __fmaf_rn(p, f, 0x1.555b58p-5f);
+    p = __fmaf_rn(p, f, 0x1.55548ep-3f);
+    p = __fmaf_rn(p, f, 0x1.fffff8p-2f);
+    p = __fmaf_rn(p, f, 1.0f);
+    p = __fmaf_rn(p, f, 1.0f);
+    uint32_t n = __float_as_uint(r) - 0x4B400000u;
+    return __uint_as_float(__float_as_uint(p) + (n << 23));
+}
+// q = rne_u64(exp_det(x) * 2^40)
+__device__ __forceinline__ uint64_t mass_of(float x) {
+    return __float2ull_rn(__fmul_rn(exp_det(x), 1099511627776.0f));
+}
+// x = (z - m) * inv_T with two roundings
+__device__ __forceinline__ float scaled_shift(float z, float m, float inv_T) {
+    return __fmul_rn(__fsub_rn(z, m), inv_T);
+}
+
+__device__ __forceinline__ float max_nan(float a, float b) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+// ---- mbarrier + 1-D bulk copy (TMA) -----------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// Non-multicast bulk copy global -> this CTA's shared memory; both addresses 16-byte
+// aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+// Bounded wait: gives up after kMbarSpinLimit probes and reports false.
+constexpr uint32_t kMbarSpinLimit = 1u << 22;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t addr = smem_u32(bar);
+    for (uint32_t it = 0; it < kMbarSpinLimit; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+// ---- warp helpers ------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t shfl_u64(uint64_t v, int src) {
+    uint32_t lo = __shfl_sync(0xffffffffu, (uint32_t)v, src);
+    uint32_t hi = __shfl_sync(0xffffffffu, (uint32_t)(v >> 32), src);
+    return ((uint64_t)hi << 32) | lo;
+}
+__device__ __forceinline__ uint64_t shfl_up_u64(uint64_t v, int d) {
+    uint32_t lo = __shfl_up_sync(0xffffffffu, (uint32_t)v, d);
+    uint32_t hi = __shfl_up_sync(0xffffffffu, (uint32_t)(v >> 32), d);
+    return ((uint64_t)hi << 32) | lo;
+}
+__device__ __forceinline__ uint64_t shfl_xor_u64(uint64_t v, int m) {
+    uint32_t lo = __shfl_xor_sync(0xffffffffu, (uint32_t)v, m);
+    uint32_t hi = __shfl_xor_sync(0xffffffffu, (uint32_t)(v >> 32), m);
+    return ((uint64_t)hi << 32) | lo;
+}
+
+// Scratch for the radix searches: 256 weight bins + 256 count bins + results.
+struct SearchScratch {
+    unsigned long long w[256];
+    uint32_t c[256];
+    uint32_t digit;
+    uint32_t bin_count;
+    unsigned long long before;  // weight ahead of the chosen bin in walk order
+    unsigned long long found;
+};
+
+// Block-wide radix descent over n entries with unique integer keys of `kBits` bits.
+// Walking the entries in key order (descending when kDesc, else ascending) it returns the
+// key of the entry at which the running weight first exceeds `target`
+// (i.e. cum_before <= target < cum_before + weight).  The caller guarantees
+// target < total weight.  Weights are exact integers, so bin sums accumulated with shared
+// memory atomics do not depend on thread order.  All kThreads threads must call.
+// Histograms live in shared memory; the digit is located with warp ballot.
+template <bool kDesc, int kBits, typename KeyFn, typename WeightFn>
+__device__ uint64_t block_radix_search(int n, unsigned long long target, KeyFn key_of, WeightFn weight_of,
+                                       SearchScratch& sc) {
+    static_assert(kBits % 8 == 0, "whole digits");
+    const int tid = threadIdx.x;
+    uint64_t prefix = 0, pmask = 0;
+    sc.w[tid] = 0;
+    sc.c[tid] = 0;
+    __syncthreads();
+    for (int shift = kBits - 8; shift >= 0; shift -= 8) {
+        for (int i = tid; i < n; i += kThreads) {
+            uint64_t k = key_of(i);
+            if ((k & pmask) == prefix) {
+                uint32_t d = (uint32_t)(k >> shift) & 255u;
+                unsigned long long wt = weight_of(i);
+                if (wt) atomicAdd(&sc.w[d], wt);
+                atomicAdd(&sc.c[d], 1u);
+            }
+        }
+        __syncthreads();
+        if (tid < 32) {
+            // lane l walks 8 bins; walk position o = 8*l + j maps to bin (kDesc ? 255 - o : o)
+            unsigned long long loc[8];
+            unsigned long long lane_sum = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                int o = 8 * tid + j;
+                int b = kDesc ? 255 - o : o;
+                loc[j] = sc.w[b];
+                lane_sum += loc[j];
+            }
+            unsigned long long incl = lane_sum;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                unsigned long long up = shfl_up_u64(incl, d);
+                if (tid >= d) incl += up;
+            }
+            unsigned long long excl = incl - lane_sum;
+            uint32_t hit = __ballot_sync(0xffffffffu, incl > target);
+            int lane = hit ? (__ffs(hit) - 1) : 31;
+            if (tid == lane) {
+                unsigned long long acc = excl;
+                int jj = 7;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (acc + loc[j] > target) { jj = j; break; }
+                    acc += loc[j];
+                }
+                int o = 8 * tid + jj;
+                int b = kDesc ? 255 - o : o;
+                sc.digit = (uint32_t)b;
+                sc.before = acc;
+                sc.bin_count = sc.c[b];
+            }
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {  // leave the bins clean for the next pass
+                int o = 8 * tid + j;
+                int b = kDesc ? 255 - o : o;
+                sc.w[b] = 0;
+                sc.c[b] = 0;
+            }
+        }
+        __syncthreads();
+        uint32_t d = sc.digit;
+        target -= sc.before;
+        prefix |= (uint64_t)d << shift;
+        pmask |= (uint64_t)255u << shift;
+        if (sc.bin_count == 1u || shift == 0) {
+            if (shift == 0) return prefix;
+            for (int i = tid; i < n; i += kThreads) {
+                uint64_t k = key_of(i);
+                if ((k & pmask) == prefix) sc.found = k;
+            }
+            __syncthreads();
+            uint64_t r = sc.found;
+            __syncthreads();
+            return r;
+        }
+    }
+    return prefix;
+}
+
+// Block-wide sum of per-thread u64 values; `buf` holds 8 words.  All threads get the sum.
+__device__ __forceinline__ uint64_t block_sum_u64(uint64_t v, unsigned long long* buf) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v += shfl_xor_u64(v, d);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) buf[threadIdx.x >> 5] = v;
+    __syncthreads();
+    uint64_t s = 0;
+#pragma unroll
+    for (int w = 0; w < kThreads / 32; ++w) s += buf[w];
+    return s;
+}
+
+}  // namespace born

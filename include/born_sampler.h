@@ -1,0 +1,208 @@
+/*
+ * born_sampler.h -- C ABI of libborn_sampler.so: token sampling and constrained decoding
+ * over row-major [batch, vocab] logits on NVIDIA B200 (sm_100a).
+ *
+ * The library is what a Go host (born) binds through cgo or a purego-style dlopen: every
+ * entry point takes at most a handle, one pointer to a flat fixed-width struct and a
+ * stream, and returns an int32 status (0 = BORN_OK).  No struct is passed by value, no
+ * varargs, no C++ types.
+ *
+ * Where each entry point sits relative to the reference (born v0.1.1, paths inside that
+ * project):
+ *   - logits layout: contiguous row-major [batch, vocab], row b at b*vocab, int32 token
+ *     indices -- internal/tensor/shape.go:52-63, internal/nn/cross_entropy.go:73,85.
+ *   - the call replaces the per-row consumers of logits that the reference has:
+ *     nn.Accuracy / argmax (internal/nn/cross_entropy.go:241-284, greedy decode) and the
+ *     max-shifted softmax / log-sum-exp (internal/autodiff/ops/softmax.go:214-238,
+ *     internal/nn/cross_entropy.go:126-153).
+ *   - the reference's backend idiom is "extra capabilities are extra methods found by type
+ *     assertion" (internal/nn/activation.go:7-20,41-52) on top of tensor.Backend
+ *     (internal/tensor/backend.go:12-33); the host-side wrapper exposes these entry points
+ *     as such a capability (SamplerBackend).  Programmer errors panic on the Go side
+ *     (internal/backend/cpu/backend.go:35-37), runtime failures are returned as errors
+ *     (internal/tensor/raw.go:89-92): BORN_ERR_INVALID_ARGUMENT maps to the former, the
+ *     CUDA/NCCL codes to the latter.
+ *
+ * Ownership: the caller owns every input and output buffer.  The library owns only the
+ * workspace it allocated in born_sampler_create and never allocates per call.
+ * Threading: one handle = one stream of calls; distinct handles are independent.
+ */
+#ifndef BORN_SAMPLER_H
+#define BORN_SAMPLER_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes (return values) ---- */
+#define BORN_OK 0
+#define BORN_ERR_INVALID_ARGUMENT 1 /* null pointer, bad size, parameter out of range */
+#define BORN_ERR_CUDA 2             /* a CUDA runtime call failed; see born_last_error */
+#define BORN_ERR_NO_DEVICE 3        /* no usable CUDA device (the library has no CPU path) */
+#define BORN_ERR_UNSUPPORTED 4      /* valid request outside the limits below */
+#define BORN_ERR_NCCL 5             /* NCCL missing or a collective failed */
+#define BORN_ERR_DEVICE_TIMEOUT 6   /* a bounded on-device wait gave up; outputs are invalid */
+
+/* ---- per-row status (out_status[b]) ---- */
+#define BORN_ROW_OK 0
+#define BORN_ROW_ALL_MASKED 1 /* no allowed token with a logit above -inf: token = -1 */
+#define BORN_ROW_NAN 2        /* NaN logit among the allowed tokens: token = -1 */
+#define BORN_ROW_POS_INF 3    /* +inf logit among the allowed tokens: token = -1 */
+#define BORN_ROW_OVERFLOW 4   /* more surviving candidates than BORN_MAX_CANDIDATES: token = -1 */
+#define BORN_ROW_BAD_TOKEN 5  /* speculative verify: draft token outside [0, vocab) */
+
+/* ---- limits ---- */
+#define BORN_MAX_TOP_K 1024        /* also the survivor limit when top_k is off */
+#define BORN_MAX_CANDIDATES 1024
+#define BORN_MAX_HISTORY 1024      /* history ids per row */
+#define BORN_MAX_VOCAB (1 << 24)
+#define BORN_MAX_DRAFT 16          /* speculative draft length */
+#define BORN_MAX_SHARDS 16
+
+#define BORN_DTYPE_F32 0
+#define BORN_DTYPE_BF16 1
+
+#define BORN_MEM_DEVICE 0 /* every pointer in the args struct is device memory */
+#define BORN_MEM_HOST 1   /* every pointer is host memory; the call copies in, runs, copies
+                             out and returns after the stream has drained */
+
+#define BORN_FLAG_GREEDY 1u
+
+/* Sampling parameters of one row (32 bytes).  Zero means "off" for every filter, as in
+ * the reference's config structs (internal/optim/adam.go:78-91). */
+typedef struct born_row_params {
+    float temperature;        /* 0 => greedy (first maximum wins) */
+    float top_p;              /* (0,1): nucleus over the survivors; 0 or >= 1 => off */
+    float min_p;              /* (0,1]: keep tokens with p >= min_p * p_max; 0 => off */
+    int32_t top_k;            /* 1..BORN_MAX_TOP_K; 0 => off */
+    float repetition_penalty; /* > 0; 1 or 0 => off; z>0 ? z/r : z*r once per distinct token */
+    float frequency_penalty;  /* z -= f * count */
+    float presence_penalty;   /* z -= p once per distinct token */
+    uint32_t flags;           /* BORN_FLAG_GREEDY */
+} born_row_params;
+
+/* Arguments of born_sample.  Pipeline per row: upcast -> penalties over the token
+ * history -> grammar bitmask (-inf where the bit is 0) -> [greedy: first maximum] ->
+ * top-k by (value desc, index asc) -> temperature -> min-p -> top-p -> inverse-CDF draw
+ * in ascending token index with the caller's uniform. */
+typedef struct born_sample_args {
+    uint32_t struct_size; /* sizeof(born_sample_args) */
+    uint32_t memory;      /* BORN_MEM_DEVICE or BORN_MEM_HOST */
+    int32_t batch;
+    int32_t vocab;
+    int32_t logits_dtype; /* BORN_DTYPE_* */
+    int32_t history_stride;    /* ids per row in `history` (<= BORN_MAX_HISTORY) */
+    int64_t logits_row_stride; /* elements between rows (>= vocab) */
+    const void* logits;        /* [batch, logits_row_stride] */
+    const uint32_t* mask;      /* [batch, mask_row_stride] bitset, bit t&31 of word t>>5; NULL = none */
+    int64_t mask_row_stride;   /* words between rows (>= ceil(vocab/32)) */
+    const int32_t* history;     /* [batch, history_stride] prior token ids; ids outside [0,vocab) ignored; NULL = none */
+    const int32_t* history_len; /* [batch] valid ids per row; NULL = history_stride */
+    const born_row_params* row_params; /* [batch]; NULL = `params` for every row */
+    born_row_params params;
+    const float* uniforms; /* [batch] in [0,1); may be NULL when every row is greedy */
+    int32_t* out_token;    /* [batch] */
+    float* out_prob;       /* [batch] probability of the token within the kept set; NULL = skip */
+    float* out_lse;        /* [batch] log-sum-exp of the scaled logits over the whole row; NULL = skip */
+    int32_t* out_status;   /* [batch] BORN_ROW_* */
+    int32_t* out_kept_ids;   /* [batch, kept_stride] kept set in rank order; NULL = skip */
+    int32_t* out_kept_count; /* [batch]; NULL = skip */
+    int32_t kept_stride;
+    int32_t vocab_segments; /* 0/1 = off; G > 1: top-k is taken inside each of G equal contiguous
+                               vocab segments (what a vocab-sharded lm_head produces) */
+} born_sample_args;
+
+/* Arguments of born_spec_verify (fp32 logits).  For position j = 0..draft_len-1: accept
+ * draft token x_j iff u_accept * q_j(x_j) < p_j(x_j); at the first rejection draw from
+ * max(0, p_j - q_j) and stop; if every position is accepted and target_rows ==
+ * draft_len + 1, draw the bonus token from the last target row. */
+typedef struct born_spec_args {
+    uint32_t struct_size;
+    uint32_t memory;
+    int32_t batch;
+    int32_t draft_len;   /* K <= BORN_MAX_DRAFT */
+    int32_t vocab;
+    int32_t target_rows; /* K or K+1 */
+    const float* target_logits; /* [batch, target_rows, vocab] */
+    const float* draft_logits;  /* [batch, K, vocab] */
+    const int32_t* draft_tokens; /* [batch, K] */
+    const float* u_accept;   /* [batch, K] */
+    const float* u_resample; /* [batch, K+1]: entry j for a rejection at j, entry K for the bonus */
+    float temperature;       /* 0 => 1 */
+    int32_t reserved;
+    int32_t* out_accept_len; /* [batch] */
+    int32_t* out_tokens;     /* [batch, K+1] accepted tokens then the resampled/bonus token, -1 padded */
+    int32_t* out_status;     /* [batch] */
+} born_spec_args;
+
+/* Arguments of the vocab-sharded path.  Every rank holds columns
+ * [rank*vocab_local, (rank+1)*vocab_local) of every row.  born_shard_local writes one
+ * packed record per row into `packed`; after an all-gather of those records
+ * born_shard_merge draws the tokens; born_sample_sharded does all three. */
+typedef struct born_shard_args {
+    uint32_t struct_size;
+    uint32_t memory; /* BORN_MEM_DEVICE only */
+    int32_t batch;
+    int32_t vocab_local;
+    int32_t logits_dtype;
+    int32_t rank;
+    int32_t nranks;
+    int32_t top_k;     /* per shard, 1..BORN_MAX_TOP_K/nranks */
+    int64_t logits_row_stride;
+    const void* logits; /* [batch, logits_row_stride] local shard */
+    float temperature;
+    float top_p;
+    const float* uniforms; /* [batch]; identical on every rank */
+    void* packed;      /* local pass out: [batch, born_shard_record_bytes(top_k)] */
+    const void* gathered; /* merge in: [nranks, batch, record_bytes] */
+    int32_t* out_token;
+    float* out_prob;
+    float* out_lse;
+    int32_t* out_status;
+} born_shard_args;
+
+/* Replaces: nothing in the reference allocates device state; mirrors backend construction
+ * cpu.New() (internal/backend/cpu/backend.go:16-20).  Allocates the workspace for up to
+ * max_batch rows of max_vocab tokens on `device`.  Fails with BORN_ERR_NO_DEVICE when no
+ * CUDA device is usable. */
+int32_t born_sampler_create(int32_t device, int32_t max_batch, int32_t max_vocab, int32_t max_k, void** out_handle);
+int32_t born_sampler_destroy(void* handle);
+
+/* Replaces nn.Accuracy's per-row argmax (internal/nn/cross_entropy.go:241-284) and the
+ * softmax / log-sum-exp row passes (internal/autodiff/ops/softmax.go:214-238,
+ * internal/nn/cross_entropy.go:126-153) with the full sampling pipeline.  One kernel launch. */
+int32_t born_sample(void* handle, const born_sample_args* args, void* stream);
+
+/* No counterpart in the reference (it has no speculative decoding); the row arithmetic is
+ * the same max-shifted softmax as internal/autodiff/ops/softmax.go:214-238. */
+int32_t born_spec_verify(void* handle, const born_spec_args* args, void* stream);
+
+/* Vocab-sharded (tensor-parallel lm_head) sampling.  No counterpart in the reference
+ * (distributed execution is a roadmap item there, ROADMAP.md:217-227). */
+int32_t born_shard_record_bytes(int32_t top_k);
+int32_t born_shard_unique_id(void* out_id128);  /* 128-byte NCCL unique id (rank 0) */
+int32_t born_shard_init(void* handle, const void* nccl_unique_id, int32_t rank, int32_t nranks);
+int32_t born_shard_local(void* handle, const born_shard_args* args, void* stream);
+int32_t born_shard_merge(void* handle, const born_shard_args* args, void* stream);
+int32_t born_sample_sharded(void* handle, const born_shard_args* args, void* stream);
+
+/* Bytes of device workspace a handle holds (for capacity planning). */
+int64_t born_workspace_bytes(void* handle);
+/* Number of kernels the handle has launched since creation. */
+int64_t born_launch_count(void* handle);
+/* Device time of the last BORN_MEM_HOST call split as h2d / kernel / d2h, in ms. */
+int32_t born_last_timing(void* handle, float* out3);
+
+const char* born_last_error(void* handle);
+const char* born_version(void);
+
+/* Test hooks: run the library's deterministic exp / fixed-point mass on device arrays. */
+int32_t born_debug_exp(const float* x_dev, float* y_dev, int64_t n, void* stream);
+int32_t born_debug_mass(const float* x_dev, uint64_t* q_dev, int64_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BORN_SAMPLER_H */

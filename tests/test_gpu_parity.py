@@ -1,0 +1,458 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle on identical seeded
+inputs: token ids, kept sets and statuses bit-exact, kept-set probabilities bit-exact,
+log-sum-exp within 1e-5 relative of a float64 evaluation."""
+import os
+
+import numpy as np
+import pytest
+
+from born_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def torch_mod():
+    import torch
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    return torch
+
+
+def to_dev(a, bf16=False):
+    torch = torch_mod()
+    if a is None:
+        return None
+    if a.dtype == np.uint16:
+        return torch.from_numpy(a.view(np.int16).copy()).cuda().view(torch.bfloat16)
+    if a.dtype == np.uint32:
+        return torch.from_numpy(a.view(np.int32).copy()).cuda()
+    if a.dtype.names:  # structured row params
+        return torch.from_numpy(a.view(np.uint8).copy()).cuda()
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def lse_f64(oracle_like_logits, params_row, mask_row=None, hist_row=None):
+    from tests import np_sampler as NP
+    z = NP.prepare(oracle_like_logits, params_row, mask_row, hist_row).astype(np.float64)
+    greedy = params_row.get("greedy") or params_row.get("temperature", 0.0) == 0.0
+    inv_T = 1.0 if greedy else 1.0 / float(np.float32(params_row["temperature"]))
+    m = z.max()
+    return m * inv_T + np.log(np.exp((z - m) * inv_T).sum())
+
+
+def run_both(sampler, oracle, logits, params, u, mask=None, hist=None, hist_len=None, segments=1, want_kept=64,
+             per_row=None, host=False):
+    """Runs the oracle and the GPU on the same inputs; returns (gpu dict of numpy, oracle dict)."""
+    from born_b200 import SamplingConfig
+    from born_b200.sampler import row_params_array
+    if per_row is not None:
+        op = oracle.params_from_rows(per_row)
+    else:
+        op = oracle.make_params(**params)
+    ref = oracle.sample(logits, op, uniforms=u, mask=mask, history=hist, history_len=hist_len, segments=segments,
+                        want_kept=want_kept, nthreads=8)
+    kw = {}
+    if per_row is not None:
+        rp = row_params_array([SamplingConfig(**r) for r in per_row])
+        kw["row_params"] = rp if host else to_dev(rp)
+        cfg = None
+    else:
+        cfg = SamplingConfig(**params)
+    if host:
+        out = sampler.sample(logits, uniforms=u, config=cfg, mask=mask, history=hist, history_len=hist_len,
+                             want_lse=True, want_kept=want_kept, vocab_segments=segments, **kw)
+        got = out
+    else:
+        torch = torch_mod()
+        out = sampler.sample(to_dev(logits), uniforms=to_dev(u), config=cfg, mask=to_dev(mask), history=to_dev(hist),
+                             history_len=to_dev(hist_len), want_lse=True, want_kept=want_kept,
+                             vocab_segments=segments, **kw)
+        torch.cuda.synchronize()
+        got = {k: v.cpu().numpy() for k, v in out.items()}
+    return got, ref
+
+
+def assert_parity(got, ref, check_kept=True):
+    assert np.array_equal(got["status"], ref["status"]), (got["status"], ref["status"])
+    bad = np.nonzero(got["token"] != ref["token"])[0]
+    assert bad.size == 0, f"token mismatch rows {bad[:8]}: gpu {got['token'][bad[:8]]} oracle {ref['token'][bad[:8]]}"
+    assert np.array_equal(got["prob"].view(np.uint32), ref["prob"].view(np.uint32))
+    if check_kept and "kept_count" in got:
+        assert np.array_equal(got["kept_count"], ref["kept_count"])
+        assert np.array_equal(got["kept_ids"], ref["kept_ids"])
+
+
+# ------------------------------------------------------------------------------ arithmetic
+def test_exp_and_mass_bit_exact(sampler, oracle, lib):
+    torch = torch_mod()
+    n = 1 << 22
+    x = np.concatenate([
+        -np.abs(W.normal(1, 1, n) * 12.0),
+        np.linspace(-90.0, 0.0, n // 4),
+        -np.logspace(-9, 1.95, n // 4),
+        np.array([0.0, -0.0, -80.0, -80.00001, -1e30, -np.inf, np.nan]),
+    ]).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    yd = torch.empty_like(xd)
+    qd = torch.empty(x.size, dtype=torch.int64, device="cuda")
+    assert lib.born_debug_exp(xd.data_ptr(), yd.data_ptr(), x.size, None) == 0
+    assert lib.born_debug_mass(xd.data_ptr(), qd.data_ptr(), x.size, None) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(yd.cpu().numpy().view(np.uint32), oracle.exp_det(x).view(np.uint32))
+    assert np.array_equal(qd.cpu().numpy().view(np.uint64), oracle.mass(x))
+
+
+def test_committed_fixtures(sampler, oracle):
+    g = np.load(os.path.join(GOLD, "sampler_small.npz"))
+    for i in range(int(g["n_cases"])):
+        rec = g[f"c{i}_params"][0]
+        params = {k: rec[k].item() for k in rec.dtype.names if k != "flags"}
+        params["greedy"] = bool(rec["flags"] & 1)
+        got, _ = run_both(sampler, oracle, g[f"c{i}_logits"], params, g[f"c{i}_uniforms"],
+                          mask=g[f"c{i}_mask"] if f"c{i}_mask" in g else None,
+                          hist=g[f"c{i}_history"] if f"c{i}_history" in g else None,
+                          segments=int(g[f"c{i}_segments"]))
+        ref = {k: g[f"c{i}_out_{k}"] for k in ("token", "prob", "status", "kept_ids", "kept_count")}
+        assert_parity(got, ref)
+
+
+# ------------------------------------------------------------------------------ sampling
+PARAM_SETS = [
+    dict(temperature=1.0, top_k=50),
+    dict(temperature=0.8, top_k=40, top_p=0.95, repetition_penalty=1.1),
+    dict(temperature=0.7, min_p=0.05, top_p=0.9, frequency_penalty=0.5, presence_penalty=0.3),
+    dict(greedy=True),
+    dict(temperature=1.0, top_k=1),
+    dict(temperature=1.5, top_k=1024, top_p=0.99),
+    dict(temperature=0.3, top_k=7, min_p=0.3),
+]
+
+
+@pytest.mark.parametrize("V", [1, 2, 31, 32, 33, 127, 4095, 4096, 4097, 8193, 32000, 50001])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_shapes_and_ragged_edges(sampler, oracle, V, dtype):
+    B = 5
+    for pi, p in enumerate(PARAM_SETS):
+        seed = 31 * V + pi
+        z = (W.normal(seed, 1, B * V) * 3.0).astype(np.float32).reshape(B, V)
+        logits = z if dtype == "f32" else W.f32_to_bf16_bits(z)
+        u = W.uniform_f32(seed, 2, B)
+        hist = W.randint(seed, 3, B * 48, V).astype(np.int32).reshape(B, 48)
+        hist[:, -3:] = [-1, V, V + 7]  # ignored ids
+        got, ref = run_both(sampler, oracle, logits, p, u, hist=hist, want_kept=min(64, max(1, V)))
+        assert_parity(got, ref)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_mask_and_per_row_params(sampler, oracle, dtype):
+    B, V = 12, 20000
+    z = (W.normal(9, 1, B * V) * 2.5).astype(np.float32).reshape(B, V)
+    logits = z if dtype == "f32" else W.f32_to_bf16_bits(z)
+    words = (V + 31) // 32
+    bits = W.uniform(9, 2, B * words * 32).reshape(B, words * 32) < 0.05
+    bits[:, V:] = False
+    bits[:, 17] = True
+    mask = np.packbits(bits.reshape(B, words, 32), axis=-1, bitorder="little").view(np.uint32).reshape(B, words)
+    rows = [dict(greedy=True) if b % 2 == 0 else dict(temperature=1.0, top_k=50) for b in range(B)]
+    rows[3] = dict(temperature=0.7, min_p=0.1, top_p=0.9)
+    rows[5] = dict(temperature=0.0)
+    u = W.uniform_f32(9, 3, B)
+    got, ref = run_both(sampler, oracle, logits, None, u, mask=mask, per_row=rows)
+    assert_parity(got, ref)
+    allowed = np.unpackbits(mask.view(np.uint8), bitorder="little").reshape(B, -1)[:, :V].astype(bool)
+    for b in range(B):
+        assert allowed[b, got["token"][b]]
+        n = got["kept_count"][b]
+        assert allowed[b, got["kept_ids"][b][:n]].all()
+
+
+def test_ties_are_broken_by_index(sampler, oracle):
+    # bf16-like heavy ties at the top-k boundary, constant rows, two-valued rows
+    B, V = 6, 9000
+    rng = np.random.default_rng(3)
+    z = rng.integers(-4, 5, size=(B, V)).astype(np.float32)
+    z[1] = 1.25
+    z[2] = np.where(np.arange(V) % 2 == 0, 2.0, -2.0)
+    z[3, :] = -0.0
+    z[3, 100:200] = 0.0
+    u = W.uniform_f32(3, 1, B)
+    for p in (dict(temperature=1.0, top_k=10), dict(temperature=1.0, top_k=600, top_p=0.9), dict(greedy=True),
+              dict(temperature=2.0, top_k=1000)):
+        got, ref = run_both(sampler, oracle, z, p, u, want_kept=1024)
+        assert_parity(got, ref)
+
+
+def test_sorted_rows_exercise_buffer_overflow_path(sampler, oracle):
+    # ascending rows make every element a new candidate: the fast pass must fall back to the
+    # piecewise pass without losing or duplicating anything
+    B, V = 3, 40000
+    z = np.tile(np.arange(V, dtype=np.float32) * 1e-3, (B, 1))
+    z[1] = z[1][::-1]
+    z[2] = np.sort((W.normal(4, 1, V) * 3).astype(np.float32))
+    u = W.uniform_f32(4, 2, B)
+    for p in (dict(temperature=1.0, top_k=64), dict(temperature=0.01, top_k=1024, top_p=0.9), dict(greedy=True)):
+        got, ref = run_both(sampler, oracle, z, p, u, want_kept=1024)
+        assert_parity(got, ref)
+
+
+def test_invalid_rows_report_status(sampler, oracle):
+    B, V = 6, 5000
+    z = (W.normal(5, 1, B * V)).astype(np.float32).reshape(B, V)
+    z[1, 4321] = np.nan
+    z[2, 77] = np.inf
+    z[4, :] = -np.inf
+    words = (V + 31) // 32
+    mask = np.full((B, words), 0xFFFFFFFF, dtype=np.uint32)
+    mask[0] = 0
+    mask[3] = 0
+    mask[3, 5] = 1 << 9  # only token 169
+    mask[5, 4321 >> 5] &= ~np.uint32(1 << (4321 & 31))
+    z[5, 4321] = np.nan  # masked NaN: row stays valid
+    u = W.uniform_f32(5, 2, B)
+    got, ref = run_both(sampler, oracle, z, dict(temperature=1.0, top_k=20), u, mask=mask)
+    assert list(ref["status"]) == [1, 2, 3, 0, 1, 0]
+    assert_parity(got, ref)
+    assert got["token"][3] == 169 and list(got["token"][[0, 1, 2, 4]]) == [-1] * 4
+
+
+def test_survivor_limit_without_top_k(sampler, oracle):
+    # top-k off: exact while min-p cuts inside the 1024 best, BORN_ROW_OVERFLOW otherwise
+    B, V = 4, 30000
+    z = (W.normal(6, 1, B * V) * 3.0).astype(np.float32).reshape(B, V)
+    u = W.uniform_f32(6, 2, B)
+    got, ref = run_both(sampler, oracle, z, dict(temperature=0.7, min_p=0.05, top_p=0.9), u, want_kept=1024)
+    assert_parity(got, ref)
+    flat = np.zeros((2, V), dtype=np.float32)
+    torch = torch_mod()
+    from born_b200 import SamplingConfig
+    out = sampler.sample(to_dev(flat), uniforms=to_dev(u[:2]), config=SamplingConfig(temperature=1.0, top_p=0.9))
+    torch.cuda.synchronize()
+    assert out["status"].cpu().tolist() == [4, 4] and out["token"].cpu().tolist() == [-1, -1]
+    small = (W.normal(6, 3, 2 * 900) * 2).astype(np.float32).reshape(2, 900)  # fits: exact without filters
+    for p in (dict(temperature=1.0), dict(temperature=1.0, top_p=0.7)):
+        got, ref = run_both(sampler, oracle, small, p, u[:2], want_kept=1024)
+        assert_parity(got, ref)
+
+
+def test_lse_within_tolerance_of_float64(sampler, oracle):
+    B, V = 8, 128256
+    z = (W.normal(7, 1, B * V) * 3.0).astype(np.float32).reshape(B, V)
+    u = W.uniform_f32(7, 2, B)
+    p = dict(temperature=0.7, top_k=50)
+    got, ref = run_both(sampler, oracle, z, p, u)
+    assert_parity(got, ref)
+    for b in range(B):
+        truth = lse_f64(z[b], p)
+        # 1e-5 relative on sum(exp) is 1e-5 absolute on its logarithm
+        assert abs(got["lse"][b] - truth) <= 1e-5 + 1e-6 * abs(truth), (b, got["lse"][b], truth)
+
+
+def test_host_memory_call_equals_device_call(sampler, oracle):
+    B, V = 7, 33333
+    z = (W.normal(8, 1, B * V) * 2.0).astype(np.float32).reshape(B, V)
+    u = W.uniform_f32(8, 2, B)
+    hist = W.randint(8, 3, B * 100, V).astype(np.int32).reshape(B, 100)
+    hl = np.array([100, 0, 5, 99, 100, 1, 50], dtype=np.int32)
+    p = dict(temperature=0.9, top_k=30, top_p=0.9, repetition_penalty=1.2, presence_penalty=0.1)
+    got_h, ref = run_both(sampler, oracle, z, p, u, hist=hist, hist_len=hl, host=True)
+    got_d, _ = run_both(sampler, oracle, z, p, u, hist=hist, hist_len=hl, host=False)
+    assert_parity(got_h, ref)
+    assert_parity(got_d, ref)
+    t = sampler.last_timing_ms()
+    assert t["kernel"] > 0 and t["h2d"] > 0
+
+
+def test_misaligned_rows_take_the_plain_load_path(sampler, oracle):
+    torch = torch_mod()
+    B, V = 4, 10001  # odd vocab: rows are not 16-byte aligned
+    z = (W.normal(11, 1, B * V) * 2.0).astype(np.float32).reshape(B, V)
+    u = W.uniform_f32(11, 2, B)
+    got, ref = run_both(sampler, oracle, z, dict(temperature=1.0, top_k=25, top_p=0.9), u)
+    assert_parity(got, ref)
+    zb = W.f32_to_bf16_bits(z)
+    got, ref = run_both(sampler, oracle, zb, dict(temperature=1.0, top_k=25), u)
+    assert_parity(got, ref)
+    # strided rows (row stride > vocab)
+    from born_b200 import SamplingConfig
+    big = torch.zeros((B, V + 7), dtype=torch.float32, device="cuda")
+    big[:, :V] = torch.from_numpy(z).cuda()
+    out = sampler.sample(big[:, :V], uniforms=to_dev(u), config=SamplingConfig(temperature=1.0, top_k=25, top_p=0.9))
+    torch.cuda.synchronize()
+    ref2 = oracle.sample(z, oracle.make_params(temperature=1.0, top_k=25, top_p=0.9), uniforms=u)
+    assert np.array_equal(out["token"].cpu().numpy(), ref2["token"])
+
+
+# ------------------------------------------------------------------------------ configurations
+def test_config1_single_row(sampler, oracle):
+    c = W.config1(seed=0, steps=64)
+    logits = np.repeat(c["logits"], 64, axis=0)
+    hist = np.repeat(c["history"], 64, axis=0)
+    got, ref = run_both(sampler, oracle, logits, c["params"], c["uniforms"], hist=hist)
+    assert_parity(got, ref)
+    # one row at a time, as the reference-runnable configuration does
+    from born_b200 import SamplingConfig
+    torch = torch_mod()
+    ld, hd = to_dev(c["logits"]), to_dev(c["history"])
+    for s in range(8):
+        out = sampler.sample(ld, uniforms=to_dev(c["uniforms"][s:s + 1]), config=SamplingConfig(**c["params"]), history=hd)
+        torch.cuda.synchronize()
+        assert int(out["token"][0]) == int(ref["token"][s])
+
+
+def test_config2_batched_decode_full_size(sampler, oracle):
+    c = W.config2(seed=0, batch=64)
+    got, ref = run_both(sampler, oracle, c["logits"], c["params"], c["uniforms"], hist=c["history"], want_kept=256)
+    assert_parity(got, ref)
+    assert (ref["status"] == 0).all()
+    print("config2 near-cutoff rows:", int((ref["near_cutoff"] != 0).sum()))
+
+
+def test_config3_constrained_full_size(sampler, oracle):
+    c = W.config3(seed=0, batch=256)
+    got, ref = run_both(sampler, oracle, c["logits_bf16"], None, c["uniforms"], mask=c["mask"], per_row=c["row_params"])
+    assert_parity(got, ref)
+    # the greedy rows are the reference's argmax over the masked row
+    z = W.bf16_bits_to_f32(c["logits_bf16"][:4])
+    allowed = np.unpackbits(c["mask"][:4].view(np.uint8), bitorder="little").reshape(4, -1)[:, :z.shape[1]].astype(bool)
+    zm = np.where(allowed, z, -np.inf).astype(np.float32)
+    for b in (0, 2):
+        assert got["token"][b] == oracle.ref_argmax(zm[b])
+
+
+def test_config5_single_gpu_segmented(sampler, oracle):
+    c = W.config5(seed=0, batch=64)
+    got, ref = run_both(sampler, oracle, c["logits_bf16"], c["params"], c["uniforms"], segments=c["shards"],
+                        want_kept=512)
+    assert_parity(got, ref)
+
+
+def test_shard_local_and_merge_equal_segmented_sampling(sampler, oracle):
+    """The vocab-sharded pipeline on one GPU: G local passes, records concatenated the way an
+    all-gather lays them out, one merge.  Must equal the oracle's segmented sampling."""
+    torch = torch_mod()
+    c = W.config5(seed=1, batch=48, vocab=64000, shards=8)
+    G, B = 8, 48
+    Vl = 64000 // G
+    ld = to_dev(c["logits_bf16"])
+    k = c["params"]["top_k"]
+    gathered = torch.empty((G, B, sampler.record_bytes(k)), dtype=torch.uint8, device="cuda")
+    for g in range(G):
+        shard = ld[:, g * Vl:(g + 1) * Vl].contiguous()
+        sampler.shard_local(shard, g, G, k, temperature=1.0, top_p=0.95, packed=gathered[g])
+    out = sampler.shard_merge(gathered, to_dev(c["uniforms"]), Vl, 0, G, k, temperature=1.0, top_p=0.95)
+    torch.cuda.synchronize()
+    ref = oracle.sample(c["logits_bf16"], oracle.make_params(**c["params"]), uniforms=c["uniforms"], segments=G)
+    assert np.array_equal(out["token"].cpu().numpy(), ref["token"])
+    assert np.array_equal(out["prob"].cpu().numpy().view(np.uint32), ref["prob"].view(np.uint32))
+    z = W.bf16_bits_to_f32(c["logits_bf16"]).astype(np.float64)
+    truth = np.log(np.exp(z - z.max(1, keepdims=True)).sum(1)) + z.max(1)
+    assert np.max(np.abs(out["lse"].cpu().numpy() - truth)) <= 2e-5
+
+
+# ------------------------------------------------------------------------------ size-independent properties
+def test_full_size_properties_headline_shape(sampler, oracle):
+    """B=256 x V=128256 fp32: properties that need no oracle pass over the whole batch."""
+    torch = torch_mod()
+    from born_b200 import SamplingConfig
+    B, V = 256, 128256
+    g = torch.Generator(device="cuda").manual_seed(0)
+    z = torch.randn((B, V), generator=g, device="cuda") * 3.0
+    u = torch.rand(B, generator=g, device="cuda").clamp_(max=1 - 2 ** -24)
+    cfg = SamplingConfig(temperature=0.7, top_k=50, top_p=0.9)
+    a = sampler.sample(z, uniforms=u, config=cfg, want_lse=True, want_kept=64)
+    b = sampler.sample(z, uniforms=u, config=cfg, want_lse=True, want_kept=64)
+    torch.cuda.synchronize()
+    assert torch.equal(a["token"], b["token"]) and torch.equal(a["prob"], b["prob"])  # run-to-run determinism
+    assert (a["status"] == 0).all()
+    # kept ids are the top of a full sort (value desc, index asc), in order
+    n = a["kept_count"].cpu().numpy()
+    srt = torch.sort(z, dim=1, descending=True, stable=True).indices[:, :64].cpu().numpy()
+    kept = a["kept_ids"].cpu().numpy()
+    for r in range(B):
+        assert np.array_equal(kept[r, :n[r]], srt[r, :n[r]])
+        assert a["token"][r].item() in kept[r, :n[r]]
+    # shift invariance of the decision (softmax(x + c) = softmax(x)): exact for power-of-two-free shifts
+    # is not guaranteed in fp32, so use the lse identity instead: lse(x + c) = lse(x) + c / T
+    c = sampler.sample(z + 8.0, uniforms=u, config=cfg, want_lse=True)
+    torch.cuda.synchronize()
+    assert torch.allclose(c["lse"], a["lse"] + 8.0 / 0.7, rtol=0, atol=2e-4)
+    # lse against torch float64
+    ref = torch.logsumexp((z.double() / 0.7), dim=1)
+    assert (a["lse"].double() - ref).abs().max().item() <= 2e-5
+    # spot-check 8 rows against the oracle
+    rows = [0, 1, 37, 100, 128, 200, 254, 255]
+    zc = z[rows].cpu().numpy()
+    r = oracle.sample(zc, oracle.make_params(temperature=0.7, top_k=50, top_p=0.9), uniforms=u[rows].cpu().numpy())
+    assert np.array_equal(a["token"][rows].cpu().numpy(), r["token"])
+
+
+# ------------------------------------------------------------------------------ speculative decoding
+def test_spec_verify_fixture_and_config4(sampler, oracle):
+    torch = torch_mod()
+    g = np.load(os.path.join(GOLD, "sampler_small.npz"))
+    out = sampler.spec_verify(to_dev(g["spec_target"]), to_dev(g["spec_draft"]), to_dev(g["spec_draft_tok"]),
+                              to_dev(g["spec_u_accept"]), to_dev(g["spec_u_resample"]))
+    torch.cuda.synchronize()
+    assert np.array_equal(out["accept_len"].cpu().numpy(), g["spec_out_accept_len"])
+    assert np.array_equal(out["tokens"].cpu().numpy(), g["spec_out_tokens"])
+    assert np.array_equal(out["status"].cpu().numpy(), g["spec_out_status"])
+
+    c = W.config4(seed=0, batch=32)
+    dt = oracle.draft_tokens(c["draft"], c["u_draft"])
+    ref = oracle.spec_verify(c["target"], c["draft"], dt, c["u_accept"], c["u_resample"], nthreads=8)
+    out = sampler.spec_verify(to_dev(c["target"]), to_dev(c["draft"]), to_dev(dt), to_dev(c["u_accept"]),
+                              to_dev(c["u_resample"]))
+    torch.cuda.synchronize()
+    assert np.array_equal(out["accept_len"].cpu().numpy(), ref["accept_len"])
+    assert np.array_equal(out["tokens"].cpu().numpy(), ref["tokens"])
+    assert np.array_equal(out["status"].cpu().numpy(), ref["status"])
+    assert 0 < ref["accept_len"].mean() < 5  # both branches exercised
+    # host-memory call
+    outh = sampler.spec_verify(c["target"], c["draft"], dt, c["u_accept"], c["u_resample"])
+    assert np.array_equal(outh["tokens"], ref["tokens"])
+
+
+@pytest.mark.parametrize("V,K,rows", [(1000, 1, 2), (4097, 3, 3), (8192, 2, 3), (20001, 4, 5)])
+def test_spec_verify_shapes_and_edges(sampler, oracle, V, K, rows):
+    torch = torch_mod()
+    B = 6
+    tgt = (W.normal(V, 1, B * rows * V) * 2.0).astype(np.float32).reshape(B, rows, V)
+    drf = (tgt[:, :K] + (W.normal(V, 2, B * K * V) * 0.7).astype(np.float32).reshape(B, K, V)).astype(np.float32)
+    drf[1] = tgt[1, :K]          # identical distributions: always accepted
+    tgt[2, 0, 5] = np.nan        # invalid target row
+    dt = oracle.draft_tokens(drf, W.uniform_f32(V, 3, B * K).reshape(B, K))
+    dt[3, 0] = V + 3             # bad draft token
+    tgt[4, 0, dt[4, 0]] = -40.0  # certain rejection at position 0
+    ua = W.uniform_f32(V, 4, B * K).reshape(B, K)
+    ur = W.uniform_f32(V, 5, B * (K + 1)).reshape(B, K + 1)
+    ref = oracle.spec_verify(tgt, drf, dt, ua, ur, temperature=0.9)
+    out = sampler.spec_verify(to_dev(tgt), to_dev(drf), to_dev(dt), to_dev(ua), to_dev(ur), temperature=0.9)
+    torch.cuda.synchronize()
+    assert np.array_equal(out["status"].cpu().numpy(), ref["status"]), (out["status"], ref["status"])
+    assert np.array_equal(out["accept_len"].cpu().numpy(), ref["accept_len"])
+    assert np.array_equal(out["tokens"].cpu().numpy(), ref["tokens"])
+    assert ref["accept_len"][1] == K and ref["status"][2] == 2 and ref["status"][3] == 5 and ref["accept_len"][4] == 0
+
+
+# ------------------------------------------------------------------------------ errors
+def test_argument_errors_are_raised_not_ignored(sampler):
+    torch = torch_mod()
+    from born_b200 import InvalidArgument, SamplerError, SamplingConfig
+    z = torch.zeros((2, 100), device="cuda")
+    u = torch.zeros(2, device="cuda")
+    with pytest.raises(InvalidArgument):
+        sampler.sample(z, uniforms=None, config=SamplingConfig(temperature=1.0))
+    with pytest.raises(InvalidArgument):
+        sampler.sample(z, uniforms=u, config=SamplingConfig(temperature=-1.0))
+    with pytest.raises(InvalidArgument):
+        sampler.sample(z, uniforms=u, config=SamplingConfig(temperature=1.0, top_k=5000))
+    with pytest.raises(InvalidArgument):
+        sampler.sample(z.double(), uniforms=u, config=SamplingConfig(temperature=1.0))
+    with pytest.raises(InvalidArgument):
+        sampler.sample(torch.zeros((4096, 100), device="cuda"), uniforms=u, config=SamplingConfig(greedy=True))
+    with pytest.raises(SamplerError):
+        sampler.sample(z, uniforms=u, config=SamplingConfig(temperature=1.0),
+                       history=torch.zeros((2, 5000), dtype=torch.int32, device="cuda"))
+    out = sampler.sample(z, config=SamplingConfig(greedy=True))  # greedy needs no uniforms
+    torch.cuda.synchronize()
+    assert out["token"].cpu().tolist() == [0, 0]

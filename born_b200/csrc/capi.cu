@@ -345,7 +345,8 @@ int32_t born_sample(void* handle, const born_sample_args* a, void* stream) {
         if (a->row_params) return fail(h, BORN_ERR_UNSUPPORTED, "vocab_segments needs uniform parameters");
         if (a->params.top_k <= 0 || a->params.top_k * G > BORN_MAX_CANDIDATES)
             return fail(h, BORN_ERR_UNSUPPORTED, "vocab_segments needs 1 <= top_k*segments <= %d", BORN_MAX_CANDIDATES);
-        if ((a->vocab / G) % 32) return fail(h, BORN_ERR_UNSUPPORTED, "segment length must be a multiple of 32");
+        if (a->mask && (a->vocab / G) % 32)
+            return fail(h, BORN_ERR_UNSUPPORTED, "with a mask the segment length must be a multiple of 32");
         if ((int64_t)G * a->batch > h->max_records) return fail(h, BORN_ERR_UNSUPPORTED, "batch*segments exceeds the workspace");
     }
     CUDA_TRY(h, cudaSetDevice(h->device));

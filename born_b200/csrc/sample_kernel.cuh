@@ -138,7 +138,7 @@ __device__ void compact_to_k(Ctx& cx, int k) {
     int n = bs.count;
     if (n <= k) return;
     uint64_t* cand = cx.cand;
-    uint64_t T = block_radix_search<true, 56>(
+    uint64_t T = block_radix_search<true, 56, true>(
         n, (unsigned long long)(k - 1), [&](int i) { return cand[i]; }, [&](int) { return 1ull; }, *cx.sc);
     if (tid == 0) { bs.nl = 0; bs.nw = 0; }
     __syncthreads();
@@ -193,7 +193,7 @@ __device__ __forceinline__ void stats_one(ThreadStats& st, float z, float c2) {
 }
 
 // One vector group (16 bytes) of the tile: mask, statistics, candidate test.
-template <typename T, bool kHasMask, bool kLse, bool kStats>
+template <typename T, bool kHasMask, bool kLse, bool kStats, bool kCand = true>
 __device__ __forceinline__ void process_group(Ctx& cx, ThreadStats& st, const T* tile, const uint32_t* smask, int g,
                                               int c0, float tau, uint64_t tau_ck, int& lflag) {
     constexpr int VEC = VecOf<T>::n;
@@ -231,13 +231,15 @@ __device__ __forceinline__ void process_group(Ctx& cx, ThreadStats& st, const T*
             st.s += acc;
         }
     }
-    bool any = false;
+    if constexpr (kCand) {
+        bool any = false;
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) any |= (v[i] >= tau);
-    if (any) {
+        for (int i = 0; i < VEC; ++i) any |= (v[i] >= tau);
+        if (any) {
 #pragma unroll
-        for (int i = 0; i < VEC; ++i)
-            if (v[i] >= tau) try_append(cx, v[i], c0 + e + i, tau_ck, lflag);
+            for (int i = 0; i < VEC; ++i)
+                if (v[i] >= tau) try_append(cx, v[i], c0 + e + i, tau_ck, lflag);
+        }
     }
 }
 
@@ -310,10 +312,19 @@ __device__ __forceinline__ void process_chunk_fast(Ctx& cx, ThreadStats& st, con
                                                lflag);
 }
 
+__device__ __forceinline__ void publish_max(Ctx& cx, const ThreadStats& st) {
+    float wm = st.mx;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, d));
+    if ((threadIdx.x & 31) == 0 && wm > -INFINITY) atomicMax(&cx.bs->maxbits, zkey(wm));
+}
+
 // The same chunk in pieces small enough that the candidate buffer cannot overflow, with a
 // compaction check before every piece.  Used for the first chunk of a slice (tau is still
-// open) and to redo a chunk whose fast pass ran out of buffer.  Shared counters are read
-// between two barriers so that every thread takes the same branch.
+// open) and to redo a chunk whose fast pass ran out of buffer.  With kStats the statistics
+// of the whole chunk are taken first, so that the min-p prune already knows the chunk's
+// maximum when candidates are collected.  Shared counters are read between two barriers
+// so that every thread takes the same branch.
 template <typename T, bool kHasMask, bool kLse, bool kStats>
 __device__ void process_chunk_safe(Ctx& cx, ThreadStats& st, const T* tile, const uint32_t* smask, int c0, int nvalid,
                                    int nh) {
@@ -322,12 +333,27 @@ __device__ void process_chunk_safe(Ctx& cx, ThreadStats& st, const T* tile, cons
     constexpr int kPiece = (kThreads / 2) * VEC;  // <= 1024 appends per piece
     BlockShared& bs = *cx.bs;
     int lflag = 0;
+    if constexpr (kStats) {
+        if (nh > 0) {
+            for (int i = threadIdx.x; i < nh; i += kThreads) {
+                int id = cx.hlist[i];
+                if (id < c0 || id >= c0 + nvalid) continue;
+                if (i > 0 && cx.hlist[i - 1] == id) continue;
+                stats_one<kLse>(st, cx.hval[i], cx.c2);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < ITER; ++j)
+            process_group<T, kHasMask, kLse, true, false>(cx, st, tile, smask, threadIdx.x + kThreads * j, c0, 0.0f, 0,
+                                                          lflag);
+        if (cx.minp_on) publish_max(cx, st);
+    }
     if (nh > 0) {
         __syncthreads();
         const int cnt = bs.count;
         __syncthreads();
         if (cnt > cx.trigger || cnt + kHistCap > kCandCap) compact_to_k(cx, cx.k_eff);
-        patch_consume<kLse, kStats>(cx, st, c0, nvalid, nh, current_tau(cx), bs.tau_ck, lflag);
+        patch_consume<kLse, false>(cx, st, c0, nvalid, nh, current_tau(cx), bs.tau_ck, lflag);
     }
     for (int j = 0; j < ITER; ++j) {
         for (int h = 0; h < 2; ++h) {
@@ -336,8 +362,8 @@ __device__ void process_chunk_safe(Ctx& cx, ThreadStats& st, const T* tile, cons
             __syncthreads();
             if (cnt > cx.trigger || cnt + kPiece > kCandCap) compact_to_k(cx, cx.k_eff);
             if ((threadIdx.x >> 7) == h)
-                process_group<T, kHasMask, kLse, kStats>(cx, st, tile, smask, threadIdx.x + kThreads * j, c0,
-                                                         current_tau(cx), bs.tau_ck, lflag);
+                process_group<T, kHasMask, kLse, false>(cx, st, tile, smask, threadIdx.x + kThreads * j, c0,
+                                                        current_tau(cx), bs.tau_ck, lflag);
         }
     }
     __syncthreads();
@@ -512,12 +538,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_kernel(const SampleKernelA
             } else {
                 process_chunk_fast<T, kHasMask, kLse>(cx, st, tile, smask, c0, nvalid, nh, lflag);
             }
-            if (cx.minp_on) {  // publish the running maximum for the min-p prune
-                float wm = st.mx;
-#pragma unroll
-                for (int d = 16; d > 0; d >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, d));
-                if ((tid & 31) == 0 && wm > -INFINITY) atomicMax(&bs.maxbits, zkey(wm));
-            }
+            if (cx.minp_on) publish_max(cx, st);  // running maximum for the min-p prune
             // One barrier per chunk: it releases the tile and votes on the rare events.
             if (__syncthreads_or(lflag)) {
                 const int ov = bs.overflow, fl = bs.fail;
@@ -731,7 +752,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_kernel(const SampleKernelA
         uint64_t S = block_sum_u64(part, bs.red64);
         uint64_t Tp = __double2ull_rz(__dmul_rn((double)rp.top_p, __ull2double_rn(S)));
         if (Tp < 1) Tp = 1;
-        uint64_t C = block_radix_search<true, 56>(
+        uint64_t C = block_radix_search<true, 56, false>(
             n, Tp - 1, [&](int i) { return cand[i]; }, [&](int i) { return qbuf[i]; }, *cx.sc);
         for (int i = tid; i < n; i += kThreads)
             if (cand[i] < C && ck_alive(cand[i])) { qbuf[i] = 0; cand[i] &= (uint64_t)kIdxMask; }
@@ -743,7 +764,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_kernel(const SampleKernelA
     const float u = A.uniforms ? A.uniforms[row] : 0.0f;
     uint64_t t = __double2ull_rz(__dmul_rn((double)u, __ull2double_rn(S)));
     if (t > S - 1) t = S - 1;
-    const uint64_t tok64 = block_radix_search<false, 24>(
+    const uint64_t tok64 = block_radix_search<false, 24, false>(
         n, t, [&](int i) { return (uint64_t)ck_idx(cand[i]); }, [&](int i) { return qbuf[i]; }, *cx.sc);
     const int tok = (int)tok64;
     for (int i = tid; i < n; i += kThreads) {

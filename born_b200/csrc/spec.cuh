@@ -107,10 +107,19 @@ __device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, 
                  "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
-// Bounded wait: gives up after kMbarSpinLimit probes and reports false.
-constexpr uint32_t kMbarSpinLimit = 1u << 22;
+// Bounded wait: gives up after about two seconds of wall-clock time (or kMbarSpinLimit
+// probes, whichever comes first) and reports false; the caller records the failure and
+// leaves the kernel in an orderly way.
+constexpr uint32_t kMbarSpinLimit = 1u << 26;
+constexpr unsigned long long kMbarTimeoutNs = 2000000000ull;
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t addr = smem_u32(bar);
+    const uint32_t addr = smem_u32(bar);
+    unsigned long long t0 = 0;
     for (uint32_t it = 0; it < kMbarSpinLimit; ++it) {
         uint32_t ok;
         asm volatile(
@@ -121,6 +130,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
             : "r"(addr), "r"(parity)
             : "memory");
         if (ok) return true;
+        if ((it & 63u) == 63u) {
+            const unsigned long long now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kMbarTimeoutNs) return false;
+        }
     }
     return false;
 }
@@ -142,40 +156,75 @@ __device__ __forceinline__ uint64_t shfl_xor_u64(uint64_t v, int m) {
     return ((uint64_t)hi << 32) | lo;
 }
 
-// Scratch for the radix searches: 256 weight bins + 256 count bins + results.
+// Scratch for the radix searches: 256 count bins and 256 weight bins (weights are split
+// into two 20-bit halves so that plain 32-bit shared-memory atomics accumulate them exactly).
 struct SearchScratch {
-    unsigned long long w[256];
     uint32_t c[256];
+    uint32_t wlo[256];
+    uint32_t whi[256];
+    uint32_t red_and[2 * (kThreads / 32)];
+    uint32_t red_or[2 * (kThreads / 32)];
     uint32_t digit;
     uint32_t bin_count;
     unsigned long long before;  // weight ahead of the chosen bin in walk order
     unsigned long long found;
 };
 
-// Block-wide radix descent over n entries with unique integer keys of `kBits` bits.
-// Walking the entries in key order (descending when kDesc, else ascending) it returns the
-// key of the entry at which the running weight first exceeds `target`
-// (i.e. cum_before <= target < cum_before + weight).  The caller guarantees
-// target < total weight.  Weights are exact integers, so bin sums accumulated with shared
-// memory atomics do not depend on thread order.  All kThreads threads must call.
-// Histograms live in shared memory; the digit is located with warp ballot.
-template <bool kDesc, int kBits, typename KeyFn, typename WeightFn>
+// Block-wide radix descent over n <= 4095 entries with unique integer keys of at most
+// `kBits` bits.  Walking the entries in key order (descending when kDesc, else ascending)
+// it returns the key of the entry at which the running weight first exceeds `target`
+// (cum_before <= target < cum_before + weight); the caller guarantees target < total
+// weight.  With kUnit every entry weighs 1 (rank selection: target = k - 1 finds the k-th
+// entry); otherwise weights are fixed-point masses <= 2^40.  Weights are integers, so the
+// bin sums accumulated with shared-memory atomics do not depend on thread order.
+// The descent starts at the highest bit in which the keys differ, takes 8 bits per pass
+// (256 shared-memory bins, the crossing bin located by a warp scan and ballot) and stops
+// as soon as the crossing bin holds a single entry.  All kThreads threads must call.
+template <bool kDesc, int kBits, bool kUnit, typename KeyFn, typename WeightFn>
 __device__ uint64_t block_radix_search(int n, unsigned long long target, KeyFn key_of, WeightFn weight_of,
                                        SearchScratch& sc) {
-    static_assert(kBits % 8 == 0, "whole digits");
-    const int tid = threadIdx.x;
-    uint64_t prefix = 0, pmask = 0;
-    sc.w[tid] = 0;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // bits in which the keys differ
+    uint64_t k_and = ~0ull, k_or = 0ull;
+    for (int i = tid; i < n; i += kThreads) {
+        uint64_t k = key_of(i);
+        k_and &= k;
+        k_or |= k;
+    }
+    uint32_t a_lo = __reduce_and_sync(0xffffffffu, (uint32_t)k_and), a_hi = __reduce_and_sync(0xffffffffu, (uint32_t)(k_and >> 32));
+    uint32_t o_lo = __reduce_or_sync(0xffffffffu, (uint32_t)k_or), o_hi = __reduce_or_sync(0xffffffffu, (uint32_t)(k_or >> 32));
     sc.c[tid] = 0;
+    if (!kUnit) { sc.wlo[tid] = 0; sc.whi[tid] = 0; }
+    if (lane == 0) {
+        sc.red_and[2 * warp] = a_lo; sc.red_and[2 * warp + 1] = a_hi;
+        sc.red_or[2 * warp] = o_lo; sc.red_or[2 * warp + 1] = o_hi;
+    }
     __syncthreads();
-    for (int shift = kBits - 8; shift >= 0; shift -= 8) {
+#pragma unroll
+    for (int w = 0; w < kThreads / 32; ++w) {
+        a_lo &= sc.red_and[2 * w]; a_hi &= sc.red_and[2 * w + 1];
+        o_lo |= sc.red_or[2 * w]; o_hi |= sc.red_or[2 * w + 1];
+    }
+    const uint64_t all_and = ((uint64_t)a_hi << 32) | a_lo, all_or = ((uint64_t)o_hi << 32) | o_lo;
+    const uint64_t varying = all_and ^ all_or;
+    if (varying == 0) return all_or;  // a single entry
+    int shift = 63 - __clzll((long long)varying) - 7;
+    if (shift < 0) shift = 0;
+    uint64_t pmask = (shift + 8 >= 64) ? 0ull : (~0ull << (shift + 8));
+    uint64_t prefix = all_or & pmask;
+    for (;;) {
         for (int i = tid; i < n; i += kThreads) {
             uint64_t k = key_of(i);
             if ((k & pmask) == prefix) {
                 uint32_t d = (uint32_t)(k >> shift) & 255u;
-                unsigned long long wt = weight_of(i);
-                if (wt) atomicAdd(&sc.w[d], wt);
                 atomicAdd(&sc.c[d], 1u);
+                if (!kUnit) {
+                    unsigned long long wt = weight_of(i);
+                    if (wt) {
+                        atomicAdd(&sc.wlo[d], (uint32_t)(wt & 0xFFFFFu));
+                        atomicAdd(&sc.whi[d], (uint32_t)(wt >> 20));
+                    }
+                }
             }
         }
         __syncthreads();
@@ -187,7 +236,7 @@ __device__ uint64_t block_radix_search(int n, unsigned long long target, KeyFn k
             for (int j = 0; j < 8; ++j) {
                 int o = 8 * tid + j;
                 int b = kDesc ? 255 - o : o;
-                loc[j] = sc.w[b];
+                loc[j] = kUnit ? (unsigned long long)sc.c[b] : (((unsigned long long)sc.whi[b] << 20) + sc.wlo[b]);
                 lane_sum += loc[j];
             }
             unsigned long long incl = lane_sum;
@@ -198,8 +247,8 @@ __device__ uint64_t block_radix_search(int n, unsigned long long target, KeyFn k
             }
             unsigned long long excl = incl - lane_sum;
             uint32_t hit = __ballot_sync(0xffffffffu, incl > target);
-            int lane = hit ? (__ffs(hit) - 1) : 31;
-            if (tid == lane) {
+            int hl = hit ? (__ffs(hit) - 1) : 31;
+            if (tid == hl) {
                 unsigned long long acc = excl;
                 int jj = 7;
 #pragma unroll
@@ -216,19 +265,17 @@ __device__ uint64_t block_radix_search(int n, unsigned long long target, KeyFn k
             __syncwarp();
 #pragma unroll
             for (int j = 0; j < 8; ++j) {  // leave the bins clean for the next pass
-                int o = 8 * tid + j;
-                int b = kDesc ? 255 - o : o;
-                sc.w[b] = 0;
+                int b = 8 * tid + j;
                 sc.c[b] = 0;
+                if (!kUnit) { sc.wlo[b] = 0; sc.whi[b] = 0; }
             }
         }
         __syncthreads();
-        uint32_t d = sc.digit;
         target -= sc.before;
-        prefix |= (uint64_t)d << shift;
+        prefix |= (uint64_t)sc.digit << shift;
         pmask |= (uint64_t)255u << shift;
-        if (sc.bin_count == 1u || shift == 0) {
-            if (shift == 0) return prefix;
+        if (shift == 0) return prefix;
+        if (sc.bin_count == 1u) {
             for (int i = tid; i < n; i += kThreads) {
                 uint64_t k = key_of(i);
                 if ((k & pmask) == prefix) sc.found = k;
@@ -238,8 +285,8 @@ __device__ uint64_t block_radix_search(int n, unsigned long long target, KeyFn k
             __syncthreads();
             return r;
         }
+        shift = shift >= 8 ? shift - 8 : 0;
     }
-    return prefix;
 }
 
 // Block-wide sum of per-thread u64 values; `buf` holds 8 words.  All threads get the sum.

@@ -3,7 +3,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libborn_sampler.so")
+LIB_PATH = os.environ.get("BORN_SAMPLER_LIB") or os.path.join(HERE, "libborn_sampler.so")
 
 BORN_OK = 0
 ERR_INVALID_ARGUMENT = 1

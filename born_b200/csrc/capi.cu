@@ -114,7 +114,7 @@ template <typename T, bool M, bool Lse>
 int launch_variant(Handle* h, const SampleKernelArgs& A, dim3 grid, size_t smem, cudaStream_t st) {
     auto kern = sample_kernel<T, M, Lse>;
     CUDA_TRY(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, kThreads, smem, st>>>(A);
+    kern<<<grid, kBlockThreads, smem, st>>>(A);
     CUDA_TRY(h, cudaGetLastError());
     h->launches++;
     return BORN_OK;
@@ -228,7 +228,7 @@ int32_t born_sampler_create(int32_t device, int32_t max_batch, int32_t max_vocab
     for (int i = 0; i < 4 && rc == BORN_OK; ++i)
         if (cudaEventCreate(&h->ev[i]) != cudaSuccess) rc = BORN_ERR_CUDA;
     if (rc != BORN_OK) {
-        snprintf(g_err, sizeof g_err, "create failed: %s", h->err[0] ? h->err : "CUDA error");
+        snprintf(g_err, sizeof g_err, "create failed: %.480s", h->err[0] ? h->err : "CUDA error");
         born_sampler_destroy(h);
         return rc;
     }
@@ -288,6 +288,9 @@ static int sample_device(Handle* h, const born_sample_args* a, cudaStream_t st) 
     A.rec_slice_stride = h->record_stride;
     A.tickets = h->tickets;
     A.dev_error = h->dev_error;
+#ifdef BORN_PROFILE
+    if (const char* pp = getenv("BORN_PROF_PTR")) A.prof = (unsigned long long*)strtoull(pp, nullptr, 0);
+#endif
     const int esz = a->logits_dtype == BORN_DTYPE_F32 ? 4 : 2;
     if (a->vocab_segments > 1) {
         A.S = a->vocab_segments;

@@ -2,16 +2,19 @@
 // log-sum-exp -> top-k -> temperature -> min-p -> top-p -> inverse-CDF draw.
 //
 // Work decomposition.  A row of the [batch, vocab] logits is cut into S contiguous slices;
-// CTA (slice, row) streams its slice from HBM exactly once through a ring of kStages
-// shared-memory tiles filled by 1-D bulk copies (TMA, non-multicast) that complete on
-// mbarriers, and reads the tiles with 128-bit shared loads.  While streaming it keeps
+// CTA (slice, row) streams its slice from HBM exactly once.  One producer warp keeps a ring
+// of kStages shared-memory tiles full with 1-D bulk copies (TMA, non-multicast) that
+// complete on mbarriers; 256 compute threads read the tiles with 128-bit shared loads and
+// hand each tile back through a second mbarrier.  While streaming the compute threads keep
 //   * the running maximum (NaN-propagating) and an online log-sum-exp per thread,
-//   * a candidate buffer of (rank key) entries that still can be among the k best.
-// Elements enter the buffer when they reach the current threshold tau; when the buffer
-// fills up, a radix select (shared-memory histograms, digit located with warp ballot)
-// finds the exact k-th best entry, the buffer is compacted to k and tau rises.  Since the
-// kept set of every filter is a prefix of the rank order, the k best entries of a slice are
-// all that the rest of the pipeline needs.
+//   * a candidate buffer of rank keys that still can be among the k best.
+// A vector group enters the slow path only when its maximum reaches the current threshold
+// tau (one compare per 16 bytes); the hits of a warp are collected with ballots into slots
+// the warp reserves 32 at a time.  When the buffer fills up, a radix select (shared-memory
+// histograms, digit located with a warp scan and ballot) finds the exact k-th best entry,
+// the buffer is compacted to k and tau rises.  Since the kept set of every filter is a
+// prefix of the rank order, the k best entries of a slice are all that the rest of the
+// pipeline needs.
 // Each slice leaves a record (max, lse partial, <= k entries) in scratch memory; the last
 // CTA of a row to finish (atomic ticket, no spinning) merges the records and runs the
 // selection and the draw on exact integer masses.
@@ -26,6 +29,9 @@
 namespace born {
 
 enum : int { kModeFull = 0, kModeLocal = 1, kModeMerge = 2 };
+
+constexpr int kBlockThreads = kThreads + 32;  // compute threads + the producer warp
+constexpr int kHistBuckets = 128;             // history ids are bucketed by tile
 
 struct RecordHdr {  // 32 bytes, precedes the entries of a slice / shard record
     float m;        // maximum of the slice (NaN if a NaN was seen)
@@ -65,7 +71,22 @@ struct SampleKernelArgs {
     int64_t rec_row_stride, rec_slice_stride;
     uint32_t* tickets;
     int* dev_error;
+    unsigned long long* prof;  // phase time stamps per CTA (profiling builds only)
 };
+
+#ifdef BORN_PROFILE
+#define BORN_PROF(i)                                                                                   \
+    do {                                                                                               \
+        if (A.prof && threadIdx.x == 0)                                                                \
+            A.prof[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 16 + (i)] = (unsigned long long)clock64(); \
+    } while (0)
+#define BORN_PROF_T0() long long pt0_ = clock64()
+#define BORN_PROF_ACC(var) do { long long pt1_ = clock64(); (var) += pt1_ - pt0_; pt0_ = pt1_; } while (0)
+#else
+#define BORN_PROF(i) do { } while (0)
+#define BORN_PROF_T0() do { } while (0)
+#define BORN_PROF_ACC(var) do { } while (0)
+#endif
 
 template <typename T>
 struct VecOf;
@@ -92,7 +113,8 @@ __host__ __device__ inline SmemLayout smem_layout(int elem_bytes, bool has_mask,
 }
 
 struct BlockShared {  // static shared state of a CTA
-    unsigned long long bars[kStages];
+    unsigned long long full_bar[kStages];
+    unsigned long long empty_bar[kStages];
     unsigned long long tau_ck;
     unsigned long long red64[kThreads / 32];
     float redf[kThreads / 32];
@@ -105,6 +127,8 @@ struct BlockShared {  // static shared state of a CTA
     int nh;
     int nl, nw;
     int last;
+    int hoff[kHistBuckets + 1];
+    int hcur[kHistBuckets];
 };
 
 struct ThreadStats {
@@ -112,6 +136,11 @@ struct ThreadStats {
     float R;    // reference of the online log-sum-exp (z domain)
     float nRc;  // -R * c2
     float s;    // sum of 2^((z - R) * c2)
+};
+
+struct WarpSlots {  // the block of 32 buffer slots a warp is filling (warp-uniform)
+    int base;
+    int used;
 };
 
 struct Ctx {  // per-CTA pointers and row constants, all block-uniform
@@ -124,51 +153,58 @@ struct Ctx {  // per-CTA pointers and row constants, all block-uniform
     BlockShared* bs;
     int k_eff;
     int trigger;
+    int hshift;  // history bucket of tile c is c >> hshift
     float c2;
     float delta_minp;
     bool minp_on;
     born_row_params rp;
 };
 
-// Keep the k best entries of cand[0..count) (exact, by rank key) and raise tau.
-__device__ void compact_to_k(Ctx& cx, int k) {
+// Local flag bits a thread raises for the end-of-tile vote.
+enum : int { kFlagTrigger = 1, kFlagOverflow = 2, kFlagTimeout = 4 };
+
+// Keep the k best entries of cand[0..count) (exact, by rank key) and raise tau.  Returns
+// true when the buffer was rearranged (every warp must then give up its slot block).
+__device__ bool compact_to_k(Ctx& cx, int k) {
     BlockShared& bs = *cx.bs;
     const int tid = threadIdx.x;
-    __syncthreads();
+    cta_sync();
     int n = bs.count;
-    if (n <= k) return;
+    if (n > kCandCap) n = kCandCap;
+    if (n <= k) return false;
     uint64_t* cand = cx.cand;
     uint64_t T = block_radix_search<true, 56, true>(
         n, (unsigned long long)(k - 1), [&](int i) { return cand[i]; }, [&](int) { return 1ull; }, *cx.sc);
     if (tid == 0) { bs.nl = 0; bs.nw = 0; }
-    __syncthreads();
+    cta_sync();
     for (int i = tid; i < n; i += kThreads) {
         uint64_t c = cand[i];
         if (i < k) {
-            if (c < T) cx.lslot[atomicAdd(&bs.nl, 1)] = (uint16_t)i;
+            if (c < T) cx.lslot[smem_atom_add(&bs.nl, 1u)] = (uint16_t)i;
         } else if (c >= T) {
-            cx.wpos[atomicAdd(&bs.nw, 1)] = (uint16_t)i;
+            cx.wpos[smem_atom_add(&bs.nw, 1u)] = (uint16_t)i;
         }
     }
-    __syncthreads();
+    cta_sync();
     int nl = bs.nl;
     for (int j = tid; j < nl; j += kThreads) cand[cx.lslot[j]] = cand[cx.wpos[j]];
     if (tid == 0) {
         bs.count = k;
-        bs.tau_ck = T;
-        bs.tau = ck_z(T);
+        if (ck_alive(T)) {
+            bs.tau_ck = T;
+            bs.tau = ck_z(T);
+        }
         bs.dropped = 1;
     }
-    __syncthreads();
+    cta_sync();
+    return true;
 }
 
-// Local flag bits a thread raises for the end-of-chunk vote.
-enum : int { kFlagTrigger = 1, kFlagOverflow = 2, kFlagTimeout = 4 };
-
+// Single-slot append used on the rare paths (history entries, piecewise pass).
 __device__ __forceinline__ void try_append(Ctx& cx, float z, int idx, uint64_t tau_ck, int& lflag) {
     uint64_t ck = make_ck(z, idx);
     if (ck > tau_ck) {
-        int pos = atomicAdd(&cx.bs->count, 1);
+        int pos = (int)smem_atom_add(&cx.bs->count, 1u);
         if (pos < kCandCap) {
             cx.cand[pos] = ck;
             if (pos >= cx.trigger) lflag |= kFlagTrigger;
@@ -192,12 +228,10 @@ __device__ __forceinline__ void stats_one(ThreadStats& st, float z, float c2) {
     }
 }
 
-// One vector group (16 bytes) of the tile: mask, statistics, candidate test.
-template <typename T, bool kHasMask, bool kLse, bool kStats, bool kCand = true>
-__device__ __forceinline__ void process_group(Ctx& cx, ThreadStats& st, const T* tile, const uint32_t* smask, int g,
-                                              int c0, float tau, uint64_t tau_ck, int& lflag) {
+// 16 bytes of the tile as floats, grammar mask applied.
+template <typename T, bool kHasMask>
+__device__ __forceinline__ void load_group(const T* tile, const uint32_t* smask, int g, float (&v)[VecOf<T>::n]) {
     constexpr int VEC = VecOf<T>::n;
-    float v[VEC];
     if constexpr (VEC == 4) {
         float4 q = reinterpret_cast<const float4*>(tile)[g];
         v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
@@ -208,86 +242,161 @@ __device__ __forceinline__ void process_group(Ctx& cx, ThreadStats& st, const T*
         v[4] = __uint_as_float(q.z << 16); v[5] = __uint_as_float(q.z & 0xFFFF0000u);
         v[6] = __uint_as_float(q.w << 16); v[7] = __uint_as_float(q.w & 0xFFFF0000u);
     }
-    const int e = g * VEC;
     if constexpr (kHasMask) {
+        const int e = g * VEC;
         uint32_t bits = smask[e >> 5] >> (e & 31);
 #pragma unroll
         for (int i = 0; i < VEC; ++i) v[i] = ((bits >> i) & 1u) ? v[i] : -INFINITY;
     }
-    if constexpr (kStats) {
-        float m4 = v[0];
+}
+
+// Statistics of one vector group; returns the group maximum.
+template <bool kLse, int VEC>
+__device__ __forceinline__ float group_stats(ThreadStats& st, const float (&v)[VEC], float c2, bool stats) {
+    float m4 = v[0];
 #pragma unroll
-        for (int i = 1; i < VEC; ++i) m4 = max_nan(m4, v[i]);
+    for (int i = 1; i < VEC; ++i) m4 = max_nan(m4, v[i]);
+    if (stats) {
         st.mx = max_nan(st.mx, m4);
         if constexpr (kLse) {
             if (m4 > st.R) {
-                st.s *= ex2_approx(__fmul_rn(st.R - m4, cx.c2));
+                st.s *= ex2_approx(__fmul_rn(st.R - m4, c2));
                 st.R = m4;
-                st.nRc = -m4 * cx.c2;
+                st.nRc = -m4 * c2;
             }
             float acc = 0.0f;
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) acc += ex2_approx(fmaf(v[i], cx.c2, st.nRc));
+            for (int i = 0; i < VEC; ++i) acc += ex2_approx(fmaf(v[i], c2, st.nRc));
             st.s += acc;
         }
     }
-    if constexpr (kCand) {
-        bool any = false;
+    return m4;
+}
+
+// Warp-convergent collection of the candidates of one tile.  `hm` has bit j set when the
+// maximum of this thread's j-th vector group reached tau.  The flagged groups are read
+// again from the tile to find the elements; then, round by round, every lane offers at most
+// one element, a ballot counts the offers and every offering lane stores its entry at its
+// rank among the offers inside the warp's current block of 32 slots.  A new block is
+// reserved with a single shared-memory atomic when the current one cannot take the round;
+// its slots start out as dead entries (value part 0, unique low bits).  All 32 lanes call.
+template <typename T, bool kHasMask>
+__device__ __forceinline__ void warp_collect(Ctx& cx, WarpSlots& ws, const T* tile, const uint32_t* smask, uint32_t hm,
+                                             int c0, float tau, uint64_t tau_ck, int& lflag) {
+    constexpr int VEC = VecOf<T>::n;
+    constexpr int ITER = kChunk / VEC / kThreads;
+    const int lane = threadIdx.x & 31;
+    uint32_t em = 0;  // element-level hits: bit j*VEC+i
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) any |= (v[i] >= tau);
-        if (any) {
+    for (int j = 0; j < ITER; ++j) {
+        if (hm & (1u << j)) {
+            float v[VEC];
+            load_group<T, kHasMask>(tile, smask, threadIdx.x + kThreads * j, v);
 #pragma unroll
             for (int i = 0; i < VEC; ++i)
-                if (v[i] >= tau) try_append(cx, v[i], c0 + e + i, tau_ck, lflag);
+                if (v[i] >= tau) em |= 1u << (j * VEC + i);
         }
+    }
+    for (;;) {
+        const bool has = em != 0;
+        if (!__any_sync(0xffffffffu, has)) break;
+        uint64_t ck = 0;
+        bool pred = false;
+        if (has) {
+            const int b = __ffs(em) - 1;
+            em &= em - 1;
+            const int e = (threadIdx.x + kThreads * (b / VEC)) * VEC + (b % VEC);
+            float z;
+            if constexpr (sizeof(T) == 4) z = reinterpret_cast<const float*>(tile)[e];
+            else z = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(tile)[e]);
+            ck = make_ck(z, c0 + e);
+            pred = ck > tau_ck;
+        }
+        const uint32_t bal = __ballot_sync(0xffffffffu, pred);
+        if (!bal) continue;
+        const int n = __popc(bal);
+        if (ws.used + n > 32) {  // reserve a fresh block (warp-uniform branch)
+            int b = 0;
+            if (lane == 0) b = (int)smem_atom_add(&cx.bs->count, 32u);
+            b = __shfl_sync(0xffffffffu, b, 0);
+            if (b + 32 > kCandCap) {
+                if (lane == 0) cx.bs->overflow = 1;
+                lflag |= kFlagOverflow;
+                ws.used = 32;
+                return;
+            }
+            cx.cand[b + lane] = (uint64_t)(b + lane);
+            __syncwarp();
+            ws.base = b;
+            ws.used = 0;
+            if (b + 32 > cx.trigger) lflag |= kFlagTrigger;
+        }
+        if (pred) cx.cand[ws.base + ws.used + __popc(bal & ((1u << lane) - 1u))] = ck;
+        ws.used += n;
     }
 }
 
-// History entries of this chunk: compute the penalised logit once per distinct token,
-// park it in hval and take the token out of the tile (-inf).
+// Penalised logit of a history token (once per distinct token, `cnt` = its multiplicity).
+__device__ __forceinline__ float penalise(const born_row_params& rp, float z, int cnt) {
+    if (rp.repetition_penalty != 1.0f && rp.repetition_penalty != 0.0f)
+        z = (z > 0.0f) ? __fdiv_rn(z, rp.repetition_penalty) : __fmul_rn(z, rp.repetition_penalty);
+    if (rp.frequency_penalty != 0.0f || rp.presence_penalty != 0.0f) {
+        float pen = __fmul_rn(rp.frequency_penalty, (float)cnt);
+        pen = __fadd_rn(pen, rp.presence_penalty);
+        z = __fsub_rn(z, pen);
+    }
+    return z;
+}
+
+// History entries of this tile: compute the penalised logit once per distinct token, park
+// it in hval and take the token out of the tile (-inf).  Entries are bucketed by tile, so
+// only the bucket of tile c is visited; duplicates inside a bucket are found by comparing.
 template <typename T, bool kHasMask>
-__device__ __forceinline__ void patch_compute(Ctx& cx, T* tile, const uint32_t* smask, int c0, int nvalid, int nh) {
-    const born_row_params& rp = cx.rp;
-    const bool rep_on = (rp.repetition_penalty != 1.0f && rp.repetition_penalty != 0.0f);
-    const bool add_on = (rp.frequency_penalty != 0.0f || rp.presence_penalty != 0.0f);
+__device__ __forceinline__ void patch_compute(Ctx& cx, T* tile, const uint32_t* smask, int c, int c0, int nvalid) {
+    const int b = c >> cx.hshift;
+    const int lo = cx.bs->hoff[b], hi = cx.bs->hoff[b + 1];
     bool wrote = false;
-    for (int i = threadIdx.x; i < nh; i += kThreads) {
-        int id = cx.hlist[i];
+    for (int i = lo + (int)threadIdx.x; i < hi; i += kThreads) {
+        const int id = cx.hlist[i];
         if (id < c0 || id >= c0 + nvalid) continue;
-        if (i > 0 && cx.hlist[i - 1] == id) continue;
-        int cnt = 1;
-        while (i + cnt < nh && cx.hlist[i + cnt] == id) ++cnt;
-        int off = id - c0;
-        float z;
-        if constexpr (sizeof(T) == 4) z = reinterpret_cast<float*>(tile)[off];
-        else z = bf16_bits_to_f32(reinterpret_cast<uint16_t*>(tile)[off]);
-        if (rep_on) z = (z > 0.0f) ? __fdiv_rn(z, rp.repetition_penalty) : __fmul_rn(z, rp.repetition_penalty);
-        if (add_on) {
-            float pen = __fmul_rn(rp.frequency_penalty, (float)cnt);
-            pen = __fadd_rn(pen, rp.presence_penalty);
-            z = __fsub_rn(z, pen);
+        float out = -INFINITY;  // repeats of a token carry nothing
+        int cnt = 0;
+        bool first = true;
+        for (int j = lo; j < hi; ++j) {
+            const bool eq = (cx.hlist[j] == id);
+            cnt += eq ? 1 : 0;
+            if (eq && j < i) first = false;
         }
-        if constexpr (kHasMask) {
-            if (!((smask[off >> 5] >> (off & 31)) & 1u)) z = -INFINITY;
+        if (first) {
+            const int off = id - c0;
+            float z;
+            if constexpr (sizeof(T) == 4) z = reinterpret_cast<float*>(tile)[off];
+            else z = bf16_bits_to_f32(reinterpret_cast<uint16_t*>(tile)[off]);
+            z = penalise(cx.rp, z, cnt);
+            if constexpr (kHasMask) {
+                if (!((smask[off >> 5] >> (off & 31)) & 1u)) z = -INFINITY;
+            }
+            out = z;
+            if constexpr (sizeof(T) == 4) reinterpret_cast<float*>(tile)[off] = -INFINITY;
+            else reinterpret_cast<uint16_t*>(tile)[off] = 0xFF80u;
+            wrote = true;
         }
-        cx.hval[i] = z;
-        if constexpr (sizeof(T) == 4) reinterpret_cast<float*>(tile)[off] = -INFINITY;
-        else reinterpret_cast<uint16_t*>(tile)[off] = 0xFF80u;
-        wrote = true;
+        cx.hval[i] = out;
     }
     if (wrote) fence_proxy_async();
 }
 
-template <bool kLse, bool kStats>
-__device__ __forceinline__ void patch_consume(Ctx& cx, ThreadStats& st, int c0, int nvalid, int nh, float tau,
-                                              uint64_t tau_ck, int& lflag) {
-    for (int i = threadIdx.x; i < nh; i += kThreads) {
-        int id = cx.hlist[i];
+template <bool kLse>
+__device__ __forceinline__ void patch_consume(Ctx& cx, ThreadStats& st, int c, int c0, int nvalid, float tau,
+                                              uint64_t tau_ck, bool stats, bool collect, int& lflag) {
+    const int b = c >> cx.hshift;
+    const int lo = cx.bs->hoff[b], hi = cx.bs->hoff[b + 1];
+    for (int i = lo + (int)threadIdx.x; i < hi; i += kThreads) {
+        const int id = cx.hlist[i];
         if (id < c0 || id >= c0 + nvalid) continue;
-        if (i > 0 && cx.hlist[i - 1] == id) continue;
-        float z = cx.hval[i];
-        if (kStats) stats_one<kLse>(st, z, cx.c2);
-        if (z >= tau) try_append(cx, z, id, tau_ck, lflag);
+        const float z = cx.hval[i];  // -inf for repeats of a token
+        if (stats) stats_one<kLse>(st, z, cx.c2);
+        if (collect && z >= tau) try_append(cx, z, id, tau_ck, lflag);
     }
 }
 
@@ -297,105 +406,213 @@ __device__ __forceinline__ float current_tau(const Ctx& cx) {
     return tau;
 }
 
-// A whole chunk with no synchronisation inside (the common case).
-template <typename T, bool kHasMask, bool kLse>
-__device__ __forceinline__ void process_chunk_fast(Ctx& cx, ThreadStats& st, const T* tile, const uint32_t* smask,
-                                                   int c0, int nvalid, int nh, int& lflag) {
-    constexpr int VEC = VecOf<T>::n;
-    constexpr int ITER = kChunk / VEC / kThreads;
-    const float tau = current_tau(cx);
-    const uint64_t tau_ck = cx.bs->tau_ck;
-    if (nh > 0) patch_consume<kLse, true>(cx, st, c0, nvalid, nh, tau, tau_ck, lflag);
-#pragma unroll
-    for (int j = 0; j < ITER; ++j)
-        process_group<T, kHasMask, kLse, true>(cx, st, tile, smask, threadIdx.x + kThreads * j, c0, tau, tau_ck,
-                                               lflag);
-}
-
 __device__ __forceinline__ void publish_max(Ctx& cx, const ThreadStats& st) {
     float wm = st.mx;
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, d));
-    if ((threadIdx.x & 31) == 0 && wm > -INFINITY) atomicMax(&cx.bs->maxbits, zkey(wm));
+    if ((threadIdx.x & 31) == 0 && wm > -INFINITY) smem_red_max(&cx.bs->maxbits, zkey(wm));
 }
 
-// The same chunk in pieces small enough that the candidate buffer cannot overflow, with a
-// compaction check before every piece.  Used for the first chunk of a slice (tau is still
-// open) and to redo a chunk whose fast pass ran out of buffer.  With kStats the statistics
-// of the whole chunk are taken first, so that the min-p prune already knows the chunk's
-// maximum when candidates are collected.  Shared counters are read between two barriers
-// so that every thread takes the same branch.
-template <typename T, bool kHasMask, bool kLse, bool kStats>
-__device__ void process_chunk_safe(Ctx& cx, ThreadStats& st, const T* tile, const uint32_t* smask, int c0, int nvalid,
-                                   int nh) {
+// A whole tile with no block synchronisation inside (the common case): one pass over the
+// thread's vector groups for the statistics and a one-compare-per-group candidate test,
+// then at most one convergent collection step per warp.
+template <typename T, bool kHasMask, bool kLse>
+__device__ __forceinline__ void process_tile(Ctx& cx, ThreadStats& st, WarpSlots& ws, const T* tile,
+                                             const uint32_t* smask, int c, int c0, int nvalid, bool has_hist,
+                                             bool stats, bool collect, int& lflag) {
+    constexpr int VEC = VecOf<T>::n;
+    constexpr int ITER = kChunk / VEC / kThreads;
+    const float tau = current_tau(cx);
+    const uint64_t tau_ck = cx.bs->tau_ck;
+    if (has_hist) patch_consume<kLse>(cx, st, c, c0, nvalid, tau, tau_ck, stats, collect, lflag);
+    uint32_t hm = 0;
+#pragma unroll
+    for (int j = 0; j < ITER; ++j) {
+        float v[VEC];
+        load_group<T, kHasMask>(tile, smask, threadIdx.x + kThreads * j, v);
+        const float m4 = group_stats<kLse, VEC>(st, v, cx.c2, stats);
+        if (m4 >= tau) hm |= 1u << j;
+    }
+    if (collect && __any_sync(0xffffffffu, hm != 0))
+        warp_collect<T, kHasMask>(cx, ws, tile, smask, hm, c0, tau, tau_ck, lflag);
+}
+
+// The candidates of a tile in pieces small enough that the buffer cannot overflow, with a
+// compaction check before every piece.  Redoes a tile whose fast pass ran out of buffer
+// (statistics were already taken).  Shared counters are read between two barriers so that
+// every thread takes the same branch.
+template <typename T, bool kHasMask, bool kLse>
+__device__ void process_tile_piecewise(Ctx& cx, ThreadStats& st, const T* tile, const uint32_t* smask, int c, int c0,
+                                       int nvalid, bool has_hist) {
     constexpr int VEC = VecOf<T>::n;
     constexpr int ITER = kChunk / VEC / kThreads;
     constexpr int kPiece = (kThreads / 2) * VEC;  // <= 1024 appends per piece
     BlockShared& bs = *cx.bs;
     int lflag = 0;
-    if constexpr (kStats) {
-        if (nh > 0) {
-            for (int i = threadIdx.x; i < nh; i += kThreads) {
-                int id = cx.hlist[i];
-                if (id < c0 || id >= c0 + nvalid) continue;
-                if (i > 0 && cx.hlist[i - 1] == id) continue;
-                stats_one<kLse>(st, cx.hval[i], cx.c2);
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < ITER; ++j)
-            process_group<T, kHasMask, kLse, true, false>(cx, st, tile, smask, threadIdx.x + kThreads * j, c0, 0.0f, 0,
-                                                          lflag);
-        if (cx.minp_on) publish_max(cx, st);
-    }
-    if (nh > 0) {
-        __syncthreads();
+    if (has_hist) {
+        cta_sync();
         const int cnt = bs.count;
-        __syncthreads();
+        cta_sync();
         if (cnt > cx.trigger || cnt + kHistCap > kCandCap) compact_to_k(cx, cx.k_eff);
-        patch_consume<kLse, false>(cx, st, c0, nvalid, nh, current_tau(cx), bs.tau_ck, lflag);
+        patch_consume<kLse>(cx, st, c, c0, nvalid, current_tau(cx), bs.tau_ck, false, true, lflag);
     }
     for (int j = 0; j < ITER; ++j) {
         for (int h = 0; h < 2; ++h) {
-            __syncthreads();
+            cta_sync();
             const int cnt = bs.count;
-            __syncthreads();
+            cta_sync();
             if (cnt > cx.trigger || cnt + kPiece > kCandCap) compact_to_k(cx, cx.k_eff);
-            if ((threadIdx.x >> 7) == h)
-                process_group<T, kHasMask, kLse, false>(cx, st, tile, smask, threadIdx.x + kThreads * j, c0,
-                                                        current_tau(cx), bs.tau_ck, lflag);
-        }
-    }
-    __syncthreads();
-}
-
-// In-place bitonic sort of hlist[0..n2) (n2 a power of two).
-__device__ void sort_history(int32_t* h, int n2) {
-    for (int k = 2; k <= n2; k <<= 1) {
-        for (int j = k >> 1; j > 0; j >>= 1) {
-            __syncthreads();
-            for (int i = threadIdx.x; i < n2; i += kThreads) {
-                int ixj = i ^ j;
-                if (ixj > i) {
-                    int32_t a = h[i], b = h[ixj];
-                    bool up = ((i & k) == 0);
-                    if ((a > b) == up) { h[i] = b; h[ixj] = a; }
-                }
+            if ((threadIdx.x >> 7) == h) {
+                const float tau = current_tau(cx);
+                const uint64_t tau_ck = bs.tau_ck;
+                float v[VEC];
+                const int g = threadIdx.x + kThreads * j;
+                load_group<T, kHasMask>(tile, smask, g, v);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i)
+                    if (v[i] >= tau) try_append(cx, v[i], c0 + g * VEC + i, tau_ck, lflag);
             }
         }
     }
-    __syncthreads();
+    cta_sync();
+}
+
+// First tile of a slice.  The statistics of the whole tile are taken first; the k-th
+// largest of the 256 per-thread maxima is a valid lower bound of the slice's k-th largest
+// element (k <= 256), so it opens the threshold; the tile's maximum opens the min-p prune.
+// Then candidates are collected in one fast pass.
+template <typename T, bool kHasMask, bool kLse>
+__device__ void bootstrap_tile(Ctx& cx, ThreadStats& st, WarpSlots& ws, const T* tile, const uint32_t* smask, int c0,
+                               int nvalid, bool has_hist, int& lflag) {
+    BlockShared& bs = *cx.bs;
+    int dummy = 0;
+    process_tile<T, kHasMask, kLse>(cx, st, ws, tile, smask, 0, c0, nvalid, has_hist, true, false, dummy);
+    if (cx.minp_on) publish_max(cx, st);
+    if (cx.k_eff <= kThreads) {
+        // each thread's maximum stands for one distinct element
+        const bool have = st.mx > -INFINITY;  // false for NaN as well
+        cx.cand[threadIdx.x] = have ? (((uint64_t)zkey(st.mx) << 24) | (uint64_t)threadIdx.x) : (uint64_t)threadIdx.x;
+        const int nfin = cta_sync_count(have);
+        if (nfin >= cx.k_eff) {
+            uint64_t* cand = cx.cand;
+            uint64_t Tk = block_radix_search<true, 56, true>(
+                kThreads, (unsigned long long)(cx.k_eff - 1), [&](int i) { return cand[i]; }, [&](int) { return 1ull; },
+                *cx.sc);
+            if (threadIdx.x == 0) {
+                bs.tau = zkey_to_float((uint32_t)(Tk >> 24));
+                bs.tau_ck = ((Tk >> 24) << 24) - 1;  // every element of that value or above is a candidate
+                bs.dropped = 1;
+            }
+        }
+    }
+    cta_sync();
+    process_tile<T, kHasMask, kLse>(cx, st, ws, tile, smask, 0, c0, nvalid, has_hist, false, true, lflag);
+}
+
+// Token history of this slice, bucketed by tile (counting sort: histogram, scan, scatter).
+__device__ int bucket_history(Ctx& cx, const int32_t* gh, int len, int e_begin, int e_end) {
+    BlockShared& bs = *cx.bs;
+    const int tid = threadIdx.x;
+    int32_t* tmp = reinterpret_cast<int32_t*>(cx.hval);
+    if (tid < kHistBuckets) { bs.hoff[tid] = 0; bs.hcur[tid] = 0; }
+    if (tid == 0) bs.hoff[kHistBuckets] = 0;
+    cta_sync();
+    for (int i = tid; i < len; i += kThreads) {
+        const int id = gh[i];
+        const bool in = (id >= e_begin && id < e_end);
+        tmp[i] = in ? id : -1;
+        if (in) smem_red_add(&bs.hcur[((id - e_begin) / kChunk) >> cx.hshift], 1u);
+    }
+    cta_sync();
+    if (tid < 32) {  // exclusive scan over the 128 bucket counts, 4 per lane
+        int v[4], s = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { v[j] = bs.hcur[4 * tid + j]; s += v[j]; }
+        int incl = s;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            int up = __shfl_up_sync(0xffffffffu, incl, d);
+            if (tid >= d) incl += up;
+        }
+        int run = incl - s;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { bs.hoff[4 * tid + j] = run; bs.hcur[4 * tid + j] = run; run += v[j]; }
+        if (tid == 31) bs.hoff[kHistBuckets] = run;
+    }
+    cta_sync();
+    for (int i = tid; i < len; i += kThreads) {
+        const int id = tmp[i];
+        if (id >= 0) cx.hlist[smem_atom_add(&bs.hcur[((id - e_begin) / kChunk) >> cx.hshift], 1u)] = id;
+    }
+    cta_sync();
+    return bs.hoff[kHistBuckets];
 }
 
 template <typename T, bool kHasMask, bool kLse>
-__global__ void __launch_bounds__(kThreads, 2) sample_kernel(const SampleKernelArgs A) {
+__global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKernelArgs A) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ BlockShared bs;
     const int tid = threadIdx.x;
     const int row = blockIdx.y, slice = blockIdx.x;
-    const bool has_hist = A.history != nullptr;
-    const SmemLayout L = smem_layout((int)sizeof(T), kHasMask, has_hist);
+    const bool hist_arg = A.history != nullptr;
+    const SmemLayout L = smem_layout((int)sizeof(T), kHasMask, hist_arg);
 
+    // geometry of this CTA's slice (needed by the producer warp as well)
+    const int e_begin = slice * A.slice_len;
+    const int e_end = min(A.V, e_begin + A.slice_len);
+    const int nelem = max(0, e_end - e_begin);
+    const int nchunks = (A.mode == kModeMerge) ? 0 : (nelem + kChunk - 1) / kChunk;
+    const T* grow = reinterpret_cast<const T*>(A.logits) + (int64_t)row * A.row_stride + e_begin;
+    const uint32_t* gmask = kHasMask ? A.mask + (int64_t)row * A.mask_stride + (e_begin >> 5) : nullptr;
+    T* tiles = reinterpret_cast<T*>(smem + L.tiles);
+    uint32_t* masks = reinterpret_cast<uint32_t*>(smem + L.masks);
+    const bool tma_l = A.tma_logits != 0, tma_m = kHasMask && A.tma_mask != 0;
+    const bool use_bar = (A.mode != kModeMerge) && (tma_l || tma_m);
+
+    if (tid == 0) {
+        bs.tau = -FLT_MAX;
+        bs.tau_ck = 0;
+        bs.maxbits = zkey(-INFINITY);
+        bs.count = 0;
+        bs.overflow = 0;
+        bs.fail = 0;
+        bs.dropped = 0;
+        bs.nh = 0;
+        bs.last = 0;
+        if (use_bar) {
+            for (int s = 0; s < kStages; ++s) {
+                mbar_init(reinterpret_cast<uint64_t*>(&bs.full_bar[s]), 1);
+                mbar_init(reinterpret_cast<uint64_t*>(&bs.empty_bar[s]), 1);
+            }
+            mbar_fence_init();
+        }
+    }
+    __syncthreads();  // the only barrier all 288 threads share
+
+    if (tid >= kThreads) {
+        // ------------------------------------------------------------------ producer warp
+        if (tid == kThreads && use_bar) {
+            for (int c = 0; c < nchunks; ++c) {
+                const int st = c % kStages;
+                if (c >= kStages) {
+                    // the compute threads hand the tile back when they are done with it
+                    if (!mbar_wait_or_abort(reinterpret_cast<uint64_t*>(&bs.empty_bar[st]),
+                                            (uint32_t)(c / kStages - 1) & 1u, &bs.fail))
+                        break;
+                }
+                const int n = min(kChunk, nelem - c * kChunk);
+                const uint32_t bytes_l = tma_l ? (((uint32_t)n * (uint32_t)sizeof(T) + 15u) & ~15u) : 0u;
+                const uint32_t bytes_m = tma_m ? ((((uint32_t)(n + 31) >> 5) * 4u + 15u) & ~15u) : 0u;
+                uint64_t* bar = reinterpret_cast<uint64_t*>(&bs.full_bar[st]);
+                mbar_expect_tx(bar, bytes_l + bytes_m);
+                if (tma_l) bulk_load(tiles + (size_t)st * kChunk, grow + (size_t)c * kChunk, bytes_l, bar);
+                if (tma_m) bulk_load(masks + st * (kChunk / 32), gmask + c * (kChunk / 32), bytes_m, bar);
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------------- compute threads
     Ctx cx;
     cx.cand = reinterpret_cast<uint64_t*>(smem + L.cand);
     cx.sc = reinterpret_cast<SearchScratch*>(smem + L.search);
@@ -412,88 +629,43 @@ __global__ void __launch_bounds__(kThreads, 2) sample_kernel(const SampleKernelA
     cx.minp_on = !greedy && rp.min_p > 0.0f;
     cx.delta_minp = cx.minp_on ? (__logf(rp.min_p) - 0.05f) * rp.temperature : 0.0f;
     cx.k_eff = greedy ? 1 : (rp.top_k > 0 ? min(rp.top_k, kMaxK) : kMaxK);
-    cx.trigger = min(max(2 * cx.k_eff, 64), kCandCap - 512);
+    cx.trigger = min(max(2 * cx.k_eff, 512), kCandCap - 512);
+    cx.hshift = 0;
+    while ((nchunks >> cx.hshift) > kHistBuckets) ++cx.hshift;
 
-    if (tid == 0) {
-        bs.tau = -FLT_MAX;
-        bs.tau_ck = 0;
-        bs.maxbits = zkey(-INFINITY);
-        bs.count = 0;
-        bs.overflow = 0;
-        bs.fail = 0;
-        bs.dropped = 0;
-        bs.nh = 0;
-        bs.last = 0;
-    }
-
+    BORN_PROF(0);
     float m_row = -INFINITY;  // maximum over the whole row (known after the merge)
     float lse_sum = 0.0f;     // sum of 2^((z - m_row) * c2) over the whole row
     int dropped = 0;
 
     if (A.mode != kModeMerge) {
         // ------------------------------------------------------------------ streaming pass
-        const int e_begin = slice * A.slice_len;
-        const int e_end = min(A.V, e_begin + A.slice_len);
-        const int nelem = max(0, e_end - e_begin);
-        const int nchunks = (nelem + kChunk - 1) / kChunk;
-        const T* grow = reinterpret_cast<const T*>(A.logits) + (int64_t)row * A.row_stride + e_begin;
-        const uint32_t* gmask = kHasMask ? A.mask + (int64_t)row * A.mask_stride + (e_begin >> 5) : nullptr;
-        T* tiles = reinterpret_cast<T*>(smem + L.tiles);
-        uint32_t* masks = reinterpret_cast<uint32_t*>(smem + L.masks);
-        const bool tma_l = A.tma_logits != 0, tma_m = kHasMask && A.tma_mask != 0;
-        const bool use_bar = tma_l || tma_m;
-
-        if (tid == 0) {
-            for (int s = 0; s < kStages; ++s) mbar_init(reinterpret_cast<uint64_t*>(&bs.bars[s]), 1);
-            mbar_fence_init();
-        }
-        __syncthreads();
-
-        auto issue = [&](int c) {  // thread 0 only
-            const int st = c % kStages;
-            const int n = min(kChunk, nelem - c * kChunk);
-            uint32_t bytes_l = tma_l ? (((uint32_t)n * (uint32_t)sizeof(T) + 15u) & ~15u) : 0u;
-            uint32_t bytes_m = tma_m ? ((((uint32_t)(n + 31) >> 5) * 4u + 15u) & ~15u) : 0u;
-            uint64_t* bar = reinterpret_cast<uint64_t*>(&bs.bars[st]);
-            mbar_expect_tx(bar, bytes_l + bytes_m);
-            if (tma_l) bulk_load(tiles + (size_t)st * kChunk, grow + (size_t)c * kChunk, bytes_l, bar);
-            if (tma_m) bulk_load(masks + st * (kChunk / 32), gmask + c * (kChunk / 32), bytes_m, bar);
-        };
-        if (tid == 0 && use_bar)
-            for (int c = 0; c < min(kStages, nchunks); ++c) issue(c);
-
-        // token history of this slice, sorted so that duplicates are adjacent
-        int nh = 0;
-        if (has_hist) {
+        bool has_hist = false;
+        if (hist_arg) {
             const bool pen_on = (rp.repetition_penalty != 1.0f && rp.repetition_penalty != 0.0f) ||
                                 rp.frequency_penalty != 0.0f || rp.presence_penalty != 0.0f;
             if (pen_on) {
                 int len = A.history_len ? A.history_len[row] : A.history_stride;
                 len = max(0, min(min(len, A.history_stride), kHistCap));
-                const int32_t* gh = A.history + (int64_t)row * A.history_stride;
-                for (int i = tid; i < len; i += kThreads) {
-                    int id = gh[i];
-                    if (id >= e_begin && id < e_end) cx.hlist[atomicAdd(&bs.nh, 1)] = id;
-                }
-                __syncthreads();
-                nh = bs.nh;
-                if (nh > 1) {
-                    int n2 = 2;
-                    while (n2 < nh) n2 <<= 1;
-                    for (int i = nh + tid; i < n2; i += kThreads) cx.hlist[i] = 0x7FFFFFFF;
-                    sort_history(cx.hlist, n2);
-                }
+                has_hist = bucket_history(cx, A.history + (int64_t)row * A.history_stride, len, e_begin, e_end) > 0;
             }
         }
 
+        BORN_PROF(1);
         ThreadStats st;
         st.mx = -INFINITY;
         st.R = -1e30f;
         st.nRc = 1e30f * cx.c2;
         st.s = 0.0f;
+        WarpSlots ws;
+        ws.base = 0;
+        ws.used = 32;
 
         int c_fail = -1;
+        long long pa_wait = 0, pa_prep = 0, pa_proc = 0, pa_vote = 0, pa_rare = 0;
+        (void)pa_wait; (void)pa_prep; (void)pa_proc; (void)pa_vote; (void)pa_rare;
         for (int c = 0; c < nchunks; ++c) {
+            BORN_PROF_T0();
             const int stg = c % kStages;
             const uint32_t parity = (uint32_t)(c / kStages) & 1u;
             const int c0 = e_begin + c * kChunk;
@@ -502,11 +674,12 @@ __global__ void __launch_bounds__(kThreads, 2) sample_kernel(const SampleKernelA
             uint32_t* smask = masks + stg * (kChunk / 32);
             int lflag = 0;
             if (use_bar) {
-                if (!mbar_wait(reinterpret_cast<uint64_t*>(&bs.bars[stg]), parity)) {
+                if (!mbar_wait(reinterpret_cast<uint64_t*>(&bs.full_bar[stg]), parity)) {
                     bs.fail = 1;
                     lflag |= kFlagTimeout;
                 }
             }
+            BORN_PROF_ACC(pa_wait);
             bool need_sync = false;
             if (!tma_l) {  // rows that are not 16-byte aligned: plain loads
                 const T* src = grow + (size_t)c * kChunk;
@@ -526,72 +699,85 @@ __global__ void __launch_bounds__(kThreads, 2) sample_kernel(const SampleKernelA
                 fence_proxy_async();
                 need_sync = true;
             }
-            if (need_sync && nh > 0) __syncthreads();
-            if (nh > 0) {
-                patch_compute<T, kHasMask>(cx, tile, smask, c0, nvalid, nh);
+            const bool tile_hist = has_hist && (bs.hoff[(c >> cx.hshift) + 1] > bs.hoff[c >> cx.hshift]);
+            if (tile_hist) {
+                if (need_sync) cta_sync();
+                patch_compute<T, kHasMask>(cx, tile, smask, c, c0, nvalid);
                 need_sync = true;
             }
-            if (need_sync) __syncthreads();
+            if (need_sync) cta_sync();
+            BORN_PROF_ACC(pa_prep);
 
             if (c == 0) {
-                process_chunk_safe<T, kHasMask, kLse, true>(cx, st, tile, smask, c0, nvalid, nh);
+                bootstrap_tile<T, kHasMask, kLse>(cx, st, ws, tile, smask, c0, nvalid, tile_hist, lflag);
             } else {
-                process_chunk_fast<T, kHasMask, kLse>(cx, st, tile, smask, c0, nvalid, nh, lflag);
+                process_tile<T, kHasMask, kLse>(cx, st, ws, tile, smask, c, c0, nvalid, tile_hist, true, true, lflag);
             }
             if (cx.minp_on) publish_max(cx, st);  // running maximum for the min-p prune
-            // One barrier per chunk: it releases the tile and votes on the rare events.
-            if (__syncthreads_or(lflag)) {
+            BORN_PROF_ACC(pa_proc);
+            // One barrier per tile: it closes the tile and votes on the rare events.
+            const int vote = cta_sync_or(lflag);
+            BORN_PROF_ACC(pa_vote);
+            if (vote) {
                 const int ov = bs.overflow, fl = bs.fail;
-                __syncthreads();
+                cta_sync();
                 if (fl) { c_fail = c; break; }
                 if (ov) {
-                    // the fast pass ran out of buffer: its appends sit at the tail of the
-                    // buffer; cut them off and redo the chunk piecewise
+                    // the fast pass ran out of buffer: retire what it appended from this tile
+                    // and redo the tile piecewise
                     const int ncur = min(bs.count, kCandCap);
-                    if (tid == 0) bs.nl = ncur;
-                    __syncthreads();
                     for (int i = tid; i < ncur; i += kThreads) {
-                        int idx = ck_idx(cx.cand[i]);
-                        if (idx >= c0 && idx < c0 + kChunk) atomicMin(&bs.nl, i);
+                        const uint64_t e = cx.cand[i];
+                        const int idx = ck_idx(e);
+                        if (ck_alive(e) && idx >= c0 && idx < c0 + kChunk) cx.cand[i] = (uint64_t)i;
                     }
-                    __syncthreads();
-                    if (tid == 0) { bs.count = bs.nl; bs.overflow = 0; }
-                    __syncthreads();
-                    process_chunk_safe<T, kHasMask, kLse, false>(cx, st, tile, smask, c0, nvalid, nh);
+                    cta_sync();
+                    if (tid == 0) { bs.count = ncur; bs.overflow = 0; }
+                    cta_sync();
+                    process_tile_piecewise<T, kHasMask, kLse>(cx, st, tile, smask, c, c0, nvalid, tile_hist);
                 }
                 compact_to_k(cx, cx.k_eff);
+                ws.used = 32;  // slot blocks do not survive a rearranged buffer
             }
-            if (tid == 0 && use_bar && c + kStages < nchunks) {
-                fence_proxy_async();
-                issue(c + kStages);
-            }
+            // hand the tile back to the producer
+            if (tid == 0 && use_bar) mbar_arrive(reinterpret_cast<uint64_t*>(&bs.empty_bar[stg]));
+            BORN_PROF_ACC(pa_rare);
+            if (c == 0) BORN_PROF(2);
         }
+        BORN_PROF(3);
+#ifdef BORN_PROFILE
+        if (A.prof && tid == 0) {
+            unsigned long long* pr = A.prof + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 16;
+            pr[8] = pa_wait; pr[9] = pa_prep; pr[10] = pa_proc; pr[11] = pa_vote; pr[12] = pa_rare;
+        }
+#endif
         if (c_fail >= 0) {
-            // A bulk copy never arrived.  Wait (bounded) for the copies still in flight so
-            // that this CTA's shared memory is quiet before it exits, then report.
+            // A bulk copy never arrived.  The producer sees bs.fail and stops issuing; wait
+            // (bounded) for the copies already in flight so that this CTA's shared memory is
+            // quiet before it exits, then report.
             if (tid == 0) {
                 for (int cc = c_fail + 1; cc < min(nchunks, c_fail + kStages); ++cc)
-                    mbar_wait(reinterpret_cast<uint64_t*>(&bs.bars[cc % kStages]), (uint32_t)(cc / kStages) & 1u);
+                    mbar_wait(reinterpret_cast<uint64_t*>(&bs.full_bar[cc % kStages]), (uint32_t)(cc / kStages) & 1u);
                 atomicExch(A.dev_error, 1);
                 if (A.out_status) A.out_status[row] = 100 + BORN_ERR_DEVICE_TIMEOUT;
                 if (A.out_token) A.out_token[row] = -1;
             }
-            __syncthreads();
+            cta_sync();
             return;
         }
         compact_to_k(cx, cx.k_eff);
-        __syncthreads();
+        cta_sync();
 
         // slice statistics
         float wm = st.mx;
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) wm = max_nan(wm, __shfl_xor_sync(0xffffffffu, wm, d));
         if ((tid & 31) == 0) bs.redf[tid >> 5] = wm;
-        __syncthreads();
+        cta_sync();
         float m_slice = bs.redf[0];
 #pragma unroll
         for (int w = 1; w < kThreads / 32; ++w) m_slice = max_nan(m_slice, bs.redf[w]);
-        __syncthreads();
+        cta_sync();
         float s_slice = 0.0f;
         if (kLse) {
             float v = st.s * ex2_approx(__fmul_rn(st.R - m_slice, cx.c2));
@@ -599,11 +785,12 @@ __global__ void __launch_bounds__(kThreads, 2) sample_kernel(const SampleKernelA
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
             if ((tid & 31) == 0) bs.redf[tid >> 5] = v;
-            __syncthreads();
+            cta_sync();
 #pragma unroll
             for (int w = 0; w < kThreads / 32; ++w) s_slice += bs.redf[w];
-            __syncthreads();
+            cta_sync();
         }
+        BORN_PROF(4);
 
         if (A.mode == kModeFull && A.S == 1) {
             m_row = m_slice;
@@ -612,9 +799,12 @@ __global__ void __launch_bounds__(kThreads, 2) sample_kernel(const SampleKernelA
         } else {
             // leave the record, then take a ticket; only the last CTA of the row goes on
             uint8_t* rec = A.records + (int64_t)row * A.rec_row_stride + (int64_t)slice * A.rec_slice_stride;
-            const int n = bs.count;
+            const int n = min(bs.count, cx.k_eff);
             uint64_t* ent = reinterpret_cast<uint64_t*>(rec + kRecordHdrBytes);
-            for (int i = tid; i < n; i += kThreads) ent[i] = cx.cand[i] - (uint64_t)A.idx_offset;
+            for (int i = tid; i < n; i += kThreads) {
+                const uint64_t e = cx.cand[i];
+                ent[i] = ck_alive(e) ? e - (uint64_t)A.idx_offset : 0ull;
+            }
             if (tid == 0) {
                 RecordHdr h;
                 h.m = m_slice; h.lse_s = s_slice; h.count = (uint32_t)n; h.flags = (uint32_t)bs.dropped;
@@ -623,13 +813,13 @@ __global__ void __launch_bounds__(kThreads, 2) sample_kernel(const SampleKernelA
             }
             if (A.mode == kModeLocal) return;
             __threadfence();
-            __syncthreads();
+            cta_sync();
             if (tid == 0) {
                 uint32_t t = atomicAdd(&A.tickets[row], 1u);
                 bs.last = (t == (uint32_t)(A.S - 1));
                 if (bs.last) A.tickets[row] = 0;  // ready for the next launch
             }
-            __syncthreads();
+            cta_sync();
             if (!bs.last) return;
             __threadfence();
         }
@@ -637,9 +827,9 @@ __global__ void __launch_bounds__(kThreads, 2) sample_kernel(const SampleKernelA
 
     // ---------------------------------------------------------------------- merge records
     if (A.mode == kModeMerge || A.S > 1) {
-        __syncthreads();
+        cta_sync();
         if (tid == 0) bs.count = 0;
-        __syncthreads();
+        cta_sync();
         m_row = -INFINITY;
         for (int s = 0; s < A.S; ++s) {
             const uint8_t* rec = A.records + (int64_t)row * A.rec_row_stride + (int64_t)s * A.rec_slice_stride;
@@ -655,16 +845,20 @@ __global__ void __launch_bounds__(kThreads, 2) sample_kernel(const SampleKernelA
             if (!A.segment_mode && bs.count + cnt > kCandCap) compact_to_k(cx, cx.k_eff);
             const int base = bs.count;
             const unsigned long long* ent = reinterpret_cast<const unsigned long long*>(rec + kRecordHdrBytes);
-            for (int i = tid; i < cnt && base + i < kCandCap; i += kThreads) cx.cand[base + i] = __ldcg(ent + i);
-            __syncthreads();
+            for (int i = tid; i < cnt && base + i < kCandCap; i += kThreads) {
+                const uint64_t e = __ldcg(ent + i);
+                cx.cand[base + i] = ck_alive(e) ? e : (uint64_t)(base + i);  // dead slots stay unique
+            }
+            cta_sync();
             if (tid == 0) bs.count = min(base + cnt, kCandCap);
-            __syncthreads();
+            cta_sync();
         }
     }
 
     // ------------------------------------------------------------- selection and draw
-    __syncthreads();
-    int n = bs.count;
+    cta_sync();
+    BORN_PROF(5);
+    int n = min(bs.count, kCandCap);
     int status = BORN_ROW_OK;
     if (m_row != m_row) status = BORN_ROW_NAN;
     else if (m_row == INFINITY) status = BORN_ROW_POS_INF;
@@ -684,7 +878,6 @@ __global__ void __launch_bounds__(kThreads, 2) sample_kernel(const SampleKernelA
     if (!A.segment_mode && n > cx.k_eff) {
         compact_to_k(cx, cx.k_eff);
         n = cx.k_eff;
-        dropped = 1;
     }
     dropped |= bs.dropped;
     uint64_t* cand = cx.cand;
@@ -696,7 +889,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_kernel(const SampleKernelA
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) best = max(best, shfl_xor_u64(best, d));
         if ((tid & 31) == 0) bs.red64[tid >> 5] = best;
-        __syncthreads();
+        cta_sync();
         if (tid == 0) {
             for (int w = 1; w < kThreads / 32; ++w) best = max(best, (uint64_t)bs.red64[w]);
             int tok = ck_idx(best);
@@ -715,17 +908,21 @@ __global__ void __launch_bounds__(kThreads, 2) sample_kernel(const SampleKernelA
     uint64_t low_ck = ~0ull;
     for (int i = tid; i < n; i += kThreads) {
         uint64_t c = cand[i];
-        float x = scaled_shift(ck_z(c), m_row, inv_T);
-        qbuf[i] = (x < -30.0f) ? 0ull : mass_of(x);
-        low_ck = min(low_ck, c);
+        if (ck_alive(c)) {
+            float x = scaled_shift(ck_z(c), m_row, inv_T);
+            qbuf[i] = (x < -30.0f) ? 0ull : mass_of(x);
+            low_ck = min(low_ck, c);
+        } else {
+            qbuf[i] = 0ull;
+        }
     }
     if (rp.top_k <= 0 && dropped) {
         // survivor limit reached with top-k off: exact only if min-p cuts inside the buffer
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) low_ck = min(low_ck, shfl_xor_u64(low_ck, d));
-        __syncthreads();
+        cta_sync();
         if ((tid & 31) == 0) bs.red64[tid >> 5] = low_ck;
-        __syncthreads();
+        cta_sync();
         for (int w = 0; w < kThreads / 32; ++w) low_ck = min(low_ck, (uint64_t)bs.red64[w]);
         float xl = scaled_shift(ck_z(low_ck), m_row, inv_T);
         uint64_t ql = (xl < -30.0f) ? 0ull : mass_of(xl);
@@ -740,11 +937,11 @@ __global__ void __launch_bounds__(kThreads, 2) sample_kernel(const SampleKernelA
             return;
         }
     }
-    __syncthreads();
+    cta_sync();
     if (Qa) {
         for (int i = tid; i < n; i += kThreads)
-            if (qbuf[i] < Qa) { qbuf[i] = 0; cand[i] &= (uint64_t)kIdxMask; }
-        __syncthreads();
+            if (qbuf[i] < Qa && ck_alive(cand[i])) { qbuf[i] = 0; cand[i] &= (uint64_t)kIdxMask; }
+        cta_sync();
     }
     if (rp.top_p > 0.0f && rp.top_p < 1.0f) {
         uint64_t part = 0;
@@ -756,7 +953,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_kernel(const SampleKernelA
             n, Tp - 1, [&](int i) { return cand[i]; }, [&](int i) { return qbuf[i]; }, *cx.sc);
         for (int i = tid; i < n; i += kThreads)
             if (cand[i] < C && ck_alive(cand[i])) { qbuf[i] = 0; cand[i] &= (uint64_t)kIdxMask; }
-        __syncthreads();
+        cta_sync();
     }
     uint64_t part = 0;
     for (int i = tid; i < n; i += kThreads) part += qbuf[i];
@@ -775,6 +972,7 @@ __global__ void __launch_bounds__(kThreads, 2) sample_kernel(const SampleKernelA
                 A.out_prob[row] = __double2float_rn(__ddiv_rn(__ull2double_rn(qbuf[i]), __ull2double_rn(S)));
         }
     }
+    BORN_PROF(6);
     if (A.out_kept_count || A.out_kept_ids) {
         int alive = 0;
         for (int i = tid; i < n; i += kThreads) {

@@ -14,7 +14,7 @@ namespace born {
 
 constexpr int kThreads = 256;        // threads per CTA in the row kernels
 constexpr int kChunk = 4096;         // logits per pipeline stage
-constexpr int kStages = 4;           // bulk-copy stages in flight per CTA
+constexpr int kStages = 5;           // bulk-copy stages in flight per CTA
 constexpr int kMaxK = 1024;          // BORN_MAX_TOP_K / BORN_MAX_CANDIDATES
 constexpr int kCandCap = 2048;       // candidate buffer entries (>= kMaxK + one half piece)
 constexpr int kHistCap = 1024;       // history ids held per CTA
@@ -87,6 +87,24 @@ __device__ __forceinline__ float ex2_approx(float x) {
 // ---- mbarrier + 1-D bulk copy (TMA) -----------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// Shared-memory atomics with the address space spelled out.  The pointers in this library
+// travel through structs, where the compiler can no longer prove that they point to shared
+// memory and would fall back to generic-address atomics.
+__device__ __forceinline__ uint32_t smem_atom_add(void* p, uint32_t v) {
+    uint32_t old;
+    asm volatile("atom.shared.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(smem_u32(p)), "r"(v) : "memory");
+    return old;
+}
+__device__ __forceinline__ void smem_red_add(void* p, uint32_t v) {
+    asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void smem_red_max(void* p, uint32_t v) {
+    asm volatile("red.shared.max.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void smem_red_min(void* p, uint32_t v) {
+    asm volatile("red.shared.min.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
@@ -130,6 +148,62 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
             : "r"(addr), "r"(parity)
             : "memory");
         if (ok) return true;
+        if ((it & 63u) == 63u) {
+            const unsigned long long now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kMbarTimeoutNs) return false;
+        }
+    }
+    return false;
+}
+
+// ---- barriers of the 256 compute threads ----------------------------------------------------
+// The row kernels run 256 compute threads plus, in the streaming kernel, one producer warp
+// that only issues bulk copies.  Everything the compute threads synchronise on uses named
+// barrier 1 with a count of 256, so the producer warp never takes part.
+__device__ __forceinline__ void cta_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ int cta_sync_or(int pred) {
+    int r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.s32 p, %1, 0;\n\t"
+        "bar.red.or.pred q, 1, 256, p;\n\t"
+        "selp.s32 %0, 1, 0, q;\n\t}"
+        : "=r"(r)
+        : "r"(pred)
+        : "memory");
+    return r;
+}
+__device__ __forceinline__ int cta_sync_count(int pred) {
+    int r;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.s32 p, %1, 0;\n\t"
+        "bar.red.popc.u32 %0, 1, 256, p;\n\t}"
+        : "=r"(r)
+        : "r"(pred)
+        : "memory");
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait that also gives up when *abort becomes non-zero (set by the compute threads
+// when they leave early).
+__device__ __forceinline__ bool mbar_wait_or_abort(uint64_t* bar, uint32_t parity, const volatile int* abort) {
+    const uint32_t addr = smem_u32(bar);
+    unsigned long long t0 = 0;
+    for (uint32_t it = 0; it < kMbarSpinLimit; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if (*abort) return false;
         if ((it & 63u) == 63u) {
             const unsigned long long now = global_timer_ns();
             if (t0 == 0) t0 = now;
@@ -199,7 +273,7 @@ __device__ uint64_t block_radix_search(int n, unsigned long long target, KeyFn k
         sc.red_and[2 * warp] = a_lo; sc.red_and[2 * warp + 1] = a_hi;
         sc.red_or[2 * warp] = o_lo; sc.red_or[2 * warp + 1] = o_hi;
     }
-    __syncthreads();
+    cta_sync();
 #pragma unroll
     for (int w = 0; w < kThreads / 32; ++w) {
         a_lo &= sc.red_and[2 * w]; a_hi &= sc.red_and[2 * w + 1];
@@ -217,17 +291,17 @@ __device__ uint64_t block_radix_search(int n, unsigned long long target, KeyFn k
             uint64_t k = key_of(i);
             if ((k & pmask) == prefix) {
                 uint32_t d = (uint32_t)(k >> shift) & 255u;
-                atomicAdd(&sc.c[d], 1u);
+                smem_red_add(&sc.c[d], 1u);
                 if (!kUnit) {
                     unsigned long long wt = weight_of(i);
                     if (wt) {
-                        atomicAdd(&sc.wlo[d], (uint32_t)(wt & 0xFFFFFu));
-                        atomicAdd(&sc.whi[d], (uint32_t)(wt >> 20));
+                        smem_red_add(&sc.wlo[d], (uint32_t)(wt & 0xFFFFFu));
+                        smem_red_add(&sc.whi[d], (uint32_t)(wt >> 20));
                     }
                 }
             }
         }
-        __syncthreads();
+        cta_sync();
         if (tid < 32) {
             // lane l walks 8 bins; walk position o = 8*l + j maps to bin (kDesc ? 255 - o : o)
             unsigned long long loc[8];
@@ -270,7 +344,7 @@ __device__ uint64_t block_radix_search(int n, unsigned long long target, KeyFn k
                 if (!kUnit) { sc.wlo[b] = 0; sc.whi[b] = 0; }
             }
         }
-        __syncthreads();
+        cta_sync();
         target -= sc.before;
         prefix |= (uint64_t)sc.digit << shift;
         pmask |= (uint64_t)255u << shift;
@@ -280,9 +354,9 @@ __device__ uint64_t block_radix_search(int n, unsigned long long target, KeyFn k
                 uint64_t k = key_of(i);
                 if ((k & pmask) == prefix) sc.found = k;
             }
-            __syncthreads();
+            cta_sync();
             uint64_t r = sc.found;
-            __syncthreads();
+            cta_sync();
             return r;
         }
         shift = shift >= 8 ? shift - 8 : 0;
@@ -293,9 +367,9 @@ __device__ uint64_t block_radix_search(int n, unsigned long long target, KeyFn k
 __device__ __forceinline__ uint64_t block_sum_u64(uint64_t v, unsigned long long* buf) {
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) v += shfl_xor_u64(v, d);
-    __syncthreads();
+    cta_sync();
     if ((threadIdx.x & 31) == 0) buf[threadIdx.x >> 5] = v;
-    __syncthreads();
+    cta_sync();
     uint64_t s = 0;
 #pragma unroll
     for (int w = 0; w < kThreads / 32; ++w) s += buf[w];

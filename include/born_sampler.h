@@ -57,7 +57,7 @@ extern "C" {
 #define BORN_MAX_TOP_K 1024        /* also the survivor limit when top_k is off */
 #define BORN_MAX_CANDIDATES 1024
 #define BORN_MAX_HISTORY 1024      /* history ids per row */
-#define BORN_MAX_VOCAB (1 << 24)
+#define BORN_MAX_VOCAB ((1 << 24) - 4096)
 #define BORN_MAX_DRAFT 16          /* speculative draft length */
 #define BORN_MAX_SHARDS 16
 

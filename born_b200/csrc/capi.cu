@@ -678,3 +678,75 @@ int32_t born_sample_sharded(void* handle, const born_shard_args* a, void* stream
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------ allocation-free entry
+// Scratch for born_sample_static: slice records, row tickets and the device error word in
+// one file-scope array that every GPU loading this library holds until exit.
+namespace {
+constexpr int kStaticMaxBatch = BORN_STATIC_MAX_BATCH;
+constexpr int kStaticMaxRecords = 2 * BORN_STATIC_MAX_BATCH;
+constexpr size_t kStaticRecordStride = kRecordHdrBytes + (size_t)kMaxK * 8;
+constexpr size_t kStaticRecordsBytes = kStaticMaxRecords * kStaticRecordStride;
+constexpr size_t kStaticTicketsBytes = sizeof(uint32_t) * 2 * kStaticMaxBatch;
+constexpr size_t kStaticBytes = kStaticRecordsBytes + kStaticTicketsBytes + 256;
+constexpr int kStaticMaxDevices = 64;
+}  // namespace
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
+
+namespace {
+Handle g_static_handle[kStaticMaxDevices];
+bool g_static_ready[kStaticMaxDevices];
+}  // namespace
+
+extern "C" int32_t born_sample_static(const born_sample_args* a, void* stream) {
+    if (!a) return fail(nullptr, BORN_ERR_INVALID_ARGUMENT, "born_sample_static: args is NULL");
+    if (a->struct_size != sizeof(born_sample_args))
+        return fail(nullptr, BORN_ERR_INVALID_ARGUMENT, "born_sample_static: struct_size %u != %zu", a->struct_size,
+                    sizeof(born_sample_args));
+    if (a->memory != BORN_MEM_DEVICE)
+        return fail(nullptr, BORN_ERR_UNSUPPORTED,
+                    "born_sample_static takes device memory only (a host-memory call would need staging buffers)");
+    if (a->batch > kStaticMaxBatch)
+        return fail(nullptr, BORN_ERR_UNSUPPORTED, "born_sample_static: batch %d exceeds the static scratch limit of %d rows",
+                    a->batch, kStaticMaxBatch);
+    if (a->vocab_segments > 1 && (int64_t)a->vocab_segments * a->batch > kStaticMaxRecords)
+        return fail(nullptr, BORN_ERR_UNSUPPORTED, "born_sample_static: batch*vocab_segments exceeds %d scratch records",
+                    kStaticMaxRecords);
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(nullptr, BORN_ERR_NO_DEVICE, "no CUDA device: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kStaticMaxDevices) return fail(nullptr, BORN_ERR_UNSUPPORTED, "device index %d not supported", dev);
+    Handle* h = &g_static_handle[dev];
+    if (!g_static_ready[dev]) {
+        // First call on this device (it is the current one): turn the symbol into a device
+        // address.  In host code the array's name is only a stand-in, not a device pointer.
+        unsigned char* base = nullptr;
+        e = cudaGetSymbolAddress((void**)&base, g_static_scratch);
+        if (e != cudaSuccess || !base)
+            return fail(nullptr, BORN_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed: %s", cudaGetErrorString(e));
+        int sms = 0, major = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
+            return fail(nullptr, BORN_ERR_CUDA, "cudaDeviceGetAttribute failed");
+        if (major != 10) return fail(nullptr, BORN_ERR_NO_DEVICE, "device %d is not sm_100; this library is built for sm_100a only", dev);
+        h->device = dev;
+        h->max_batch = kStaticMaxBatch;
+        h->max_vocab = BORN_MAX_VOCAB;
+        h->max_k = BORN_MAX_TOP_K;
+        h->num_sms = sms;
+        h->max_records = kStaticMaxRecords;
+        h->record_stride = (int64_t)kStaticRecordStride;
+        h->records = base;
+        h->tickets = reinterpret_cast<uint32_t*>(base + kStaticRecordsBytes);
+        h->dev_error = reinterpret_cast<int*>(base + kStaticRecordsBytes + kStaticTicketsBytes);
+        g_static_ready[dev] = true;
+    }
+    // The array keeps whatever the previous call left; the tickets and the error word
+    // must start at zero.
+    e = cudaMemsetAsync(h->tickets, 0, kStaticTicketsBytes + 256, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(nullptr, BORN_ERR_CUDA, "cudaMemsetAsync(static scratch) failed: %s", cudaGetErrorString(e));
+    int32_t rc = born_sample(h, a, stream);
+    if (rc != BORN_OK) snprintf(g_err, sizeof g_err, "%.500s", h->err);
+    return rc;
+}

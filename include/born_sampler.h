@@ -188,6 +188,22 @@ int32_t born_shard_local(void* handle, const born_shard_args* args, void* stream
 int32_t born_shard_merge(void* handle, const born_shard_args* args, void* stream);
 int32_t born_sample_sharded(void* handle, const born_shard_args* args, void* stream);
 
+/* No counterpart in the reference.  born_sample for callers that must not allocate device
+ * memory -- code running where cudaMalloc is off limits (a pre-sized serving process whose
+ * memory pool owns the whole GPU, a latency-critical decode loop, a host binding without a
+ * place to keep a handle).  It needs no handle: the slice records and row tickets the kernel
+ * uses as scratch live in a fixed array inside the library image, BORN_STATIC_SCRATCH_BYTES
+ * per GPU that loads the library.  Limits: device pointers only (BORN_MEM_DEVICE),
+ * batch <= BORN_STATIC_MAX_BATCH, batch * vocab_segments <= 2 * BORN_STATIC_MAX_BATCH;
+ * anything larger is refused with BORN_ERR_UNSUPPORTED.  Runs on the current device.  The
+ * first call on a device looks up the array's address; make that call before any stream
+ * capture.  All calls on a device share the one array: calls that overlap on the GPU
+ * (different streams, different threads) race and give wrong results -- serialise them.
+ * Errors are reported through born_last_error(NULL). */
+#define BORN_STATIC_MAX_BATCH 256
+#define BORN_STATIC_SCRATCH_BYTES (2 * BORN_STATIC_MAX_BATCH * (32 + 8 * BORN_MAX_CANDIDATES) + 8 * BORN_STATIC_MAX_BATCH + 256)
+int32_t born_sample_static(const born_sample_args* args, void* stream);
+
 /* Bytes of device workspace a handle holds (for capacity planning). */
 int64_t born_workspace_bytes(void* handle);
 /* Number of kernels the handle has launched since creation. */

@@ -121,7 +121,8 @@ struct BlockShared {  // static shared state of a CTA
     float tau;
     uint32_t maxbits;
     int count;
-    int overflow;
+    int event;       // a compaction is wanted: warps meet at the rendezvous
+    int done_warps;  // warps that have finished their tiles
     int fail;
     int dropped;
     int nh;
@@ -160,9 +161,6 @@ struct Ctx {  // per-CTA pointers and row constants, all block-uniform
     born_row_params rp;
 };
 
-// Local flag bits a thread raises for the end-of-tile vote.
-enum : int { kFlagTrigger = 1, kFlagOverflow = 2, kFlagTimeout = 4 };
-
 // Keep the k best entries of cand[0..count) (exact, by rank key) and raise tau.  Returns
 // true when the buffer was rearranged (every warp must then give up its slot block).
 __device__ bool compact_to_k(Ctx& cx, int k) {
@@ -200,21 +198,6 @@ __device__ bool compact_to_k(Ctx& cx, int k) {
     return true;
 }
 
-// Single-slot append used on the rare paths (history entries, piecewise pass).
-__device__ __forceinline__ void try_append(Ctx& cx, float z, int idx, uint64_t tau_ck, int& lflag) {
-    uint64_t ck = make_ck(z, idx);
-    if (ck > tau_ck) {
-        int pos = (int)smem_atom_add(&cx.bs->count, 1u);
-        if (pos < kCandCap) {
-            cx.cand[pos] = ck;
-            if (pos >= cx.trigger) lflag |= kFlagTrigger;
-        } else {
-            cx.bs->overflow = 1;
-            lflag |= kFlagOverflow;
-        }
-    }
-}
-
 template <bool kLse>
 __device__ __forceinline__ void stats_one(ThreadStats& st, float z, float c2) {
     st.mx = max_nan(st.mx, z);
@@ -230,7 +213,8 @@ __device__ __forceinline__ void stats_one(ThreadStats& st, float z, float c2) {
 
 // 16 bytes of the tile as floats, grammar mask applied.
 template <typename T, bool kHasMask>
-__device__ __forceinline__ void load_group(const T* tile, const uint32_t* smask, int g, float (&v)[VecOf<T>::n]) {
+__device__ __forceinline__ void load_group(const T* tile, const uint32_t* smask, int g, int nvalid,
+                                           float (&v)[VecOf<T>::n]) {
     constexpr int VEC = VecOf<T>::n;
     if constexpr (VEC == 4) {
         float4 q = reinterpret_cast<const float4*>(tile)[g];
@@ -247,6 +231,11 @@ __device__ __forceinline__ void load_group(const T* tile, const uint32_t* smask,
         uint32_t bits = smask[e >> 5] >> (e & 31);
 #pragma unroll
         for (int i = 0; i < VEC; ++i) v[i] = ((bits >> i) & 1u) ? v[i] : -INFINITY;
+    }
+    if (nvalid < kChunk) {  // last tile of the row: nothing beyond the row counts
+#pragma unroll
+        for (int i = 0; i < VEC; ++i)
+            if (g * VEC + i >= nvalid) v[i] = -INFINITY;
     }
 }
 
@@ -273,25 +262,77 @@ __device__ __forceinline__ float group_stats(ThreadStats& st, const float (&v)[V
     return m4;
 }
 
-// Warp-convergent collection of the candidates of one tile.  `hm` has bit j set when the
-// maximum of this thread's j-th vector group reached tau.  The flagged groups are read
-// again from the tile to find the elements; then, round by round, every lane offers at most
-// one element, a ballot counts the offers and every offering lane stores its entry at its
-// rank among the offers inside the warp's current block of 32 slots.  A new block is
-// reserved with a single shared-memory atomic when the current one cannot take the round;
-// its slots start out as dead entries (value part 0, unique low bits).  All 32 lanes call.
+// Rendezvous of the 256 compute threads.  Warps stream their tiles without any block-wide
+// barrier; only a rare event (the candidate buffer reached its trigger or is full) brings
+// them together.  A warp comes here when it sees bs.event at a tile boundary, when it cannot
+// get buffer space, or when it has finished all its tiles; the buffer is compacted if an
+// event is pending.  Returns true when every warp has finished and no event was pending.
+__device__ bool rendezvous(Ctx& cx, WarpSlots& ws) {
+    BlockShared& bs = *cx.bs;
+    cta_sync();
+    const int ev = bs.event, dn = bs.done_warps;
+    cta_sync();
+    if (ev) {
+        compact_to_k(cx, cx.k_eff);
+        if (threadIdx.x == 0) bs.event = 0;
+        cta_sync();
+        ws.used = 32;  // slot blocks do not survive a rearranged buffer
+    }
+    return !ev && dn == kThreads / 32;
+}
+
+// Convergent append: every lane of the warp calls with its own (pred, ck).  A ballot counts
+// the offers; each offering lane stores its entry at its rank among the offers inside the
+// warp's current block of 32 slots.  A new block is reserved with one shared-memory atomic
+// when the current one cannot take the round; its slots start out as dead entries (value
+// part 0, unique low bits).  When the buffer is full the warp raises the event and waits at
+// the rendezvous for the compaction, then tries again.
+__device__ __forceinline__ void warp_append(Ctx& cx, WarpSlots& ws, bool pred, uint64_t ck) {
+    const int lane = threadIdx.x & 31;
+    uint32_t bal;
+    int n;
+    for (;;) {
+        bal = __ballot_sync(0xffffffffu, pred);
+        if (!bal) return;
+        n = __popc(bal);
+        if (ws.used + n <= 32) break;
+        int b = 0;  // reserve a fresh block (warp-uniform path)
+        if (lane == 0) b = (int)smem_atom_add(&cx.bs->count, 32u);
+        b = __shfl_sync(0xffffffffu, b, 0);
+        if (b + 32 <= kCandCap) {
+            cx.cand[b + lane] = (uint64_t)(b + lane);
+            __syncwarp();
+            ws.base = b;
+            ws.used = 0;
+            if (b + 32 > cx.trigger && lane == 0) cx.bs->event = 1;  // compaction at the next tile boundary
+        } else {
+            // no room: the part of the refused block that lies inside the buffer must not
+            // keep stale entries, the compaction reads the whole buffer
+            if (b + lane < kCandCap) cx.cand[b + lane] = (uint64_t)(b + lane);
+            if (lane == 0) cx.bs->event = 1;
+            __syncwarp();
+            rendezvous(cx, ws);
+            pred = pred && ck > cx.bs->tau_ck;  // the threshold has risen: some offers can be withdrawn
+        }
+    }
+    if (pred) cx.cand[ws.base + ws.used + __popc(bal & ((1u << lane) - 1u))] = ck;
+    ws.used += n;
+}
+
+// Candidates of one tile for this warp.  `hm` has bit j set when the maximum of this
+// thread's j-th vector group reached tau.  The flagged groups are read again from the tile
+// to find the elements; then, round by round, every lane offers at most one element.
 template <typename T, bool kHasMask>
 __device__ __forceinline__ void warp_collect(Ctx& cx, WarpSlots& ws, const T* tile, const uint32_t* smask, uint32_t hm,
-                                             int c0, float tau, uint64_t tau_ck, int& lflag) {
+                                             int c0, int nvalid, float tau) {
     constexpr int VEC = VecOf<T>::n;
     constexpr int ITER = kChunk / VEC / kThreads;
-    const int lane = threadIdx.x & 31;
     uint32_t em = 0;  // element-level hits: bit j*VEC+i
 #pragma unroll
     for (int j = 0; j < ITER; ++j) {
         if (hm & (1u << j)) {
             float v[VEC];
-            load_group<T, kHasMask>(tile, smask, threadIdx.x + kThreads * j, v);
+            load_group<T, kHasMask>(tile, smask, threadIdx.x + kThreads * j, nvalid, v);
 #pragma unroll
             for (int i = 0; i < VEC; ++i)
                 if (v[i] >= tau) em |= 1u << (j * VEC + i);
@@ -310,29 +351,9 @@ __device__ __forceinline__ void warp_collect(Ctx& cx, WarpSlots& ws, const T* ti
             if constexpr (sizeof(T) == 4) z = reinterpret_cast<const float*>(tile)[e];
             else z = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(tile)[e]);
             ck = make_ck(z, c0 + e);
-            pred = ck > tau_ck;
+            pred = ck > cx.bs->tau_ck;
         }
-        const uint32_t bal = __ballot_sync(0xffffffffu, pred);
-        if (!bal) continue;
-        const int n = __popc(bal);
-        if (ws.used + n > 32) {  // reserve a fresh block (warp-uniform branch)
-            int b = 0;
-            if (lane == 0) b = (int)smem_atom_add(&cx.bs->count, 32u);
-            b = __shfl_sync(0xffffffffu, b, 0);
-            if (b + 32 > kCandCap) {
-                if (lane == 0) cx.bs->overflow = 1;
-                lflag |= kFlagOverflow;
-                ws.used = 32;
-                return;
-            }
-            cx.cand[b + lane] = (uint64_t)(b + lane);
-            __syncwarp();
-            ws.base = b;
-            ws.used = 0;
-            if (b + 32 > cx.trigger) lflag |= kFlagTrigger;
-        }
-        if (pred) cx.cand[ws.base + ws.used + __popc(bal & ((1u << lane) - 1u))] = ck;
-        ws.used += n;
+        warp_append(cx, ws, pred, ck);
     }
 }
 
@@ -348,61 +369,70 @@ __device__ __forceinline__ float penalise(const born_row_params& rp, float z, in
     return z;
 }
 
-// History entries of this tile: compute the penalised logit once per distinct token, park
-// it in hval and take the token out of the tile (-inf).  Entries are bucketed by tile, so
-// only the bucket of tile c is visited; duplicates inside a bucket are found by comparing.
-template <typename T, bool kHasMask>
-__device__ __forceinline__ void patch_compute(Ctx& cx, T* tile, const uint32_t* smask, int c, int c0, int nvalid) {
+// History tokens of this tile that fall on elements this warp owns (the warp that reads a
+// vector group is the only one that ever touches it, so no other warp is involved): the
+// token's logit is penalised once per distinct token, the token is taken out of the tile
+// (-inf) and its new value goes through the statistics and the candidate test on its own.
+// Entries are bucketed by tile; duplicates inside a bucket are found by comparing.
+template <typename T, bool kHasMask, bool kLse>
+__device__ __forceinline__ void warp_patch(Ctx& cx, ThreadStats& st, WarpSlots& ws, T* tile, const uint32_t* smask,
+                                           int c, int c0, int nvalid, float tau, bool stats, bool collect,
+                                           int replay) {
+    // replay: 0 = patch, take statistics and collect in one go; 1 = patch and take statistics,
+    // remember the new values; 2 = collect from the remembered values (first tile of a slice,
+    // whose candidates are collected only after the threshold bootstrap)
+    constexpr int VEC = VecOf<T>::n;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int b = c >> cx.hshift;
     const int lo = cx.bs->hoff[b], hi = cx.bs->hoff[b + 1];
     bool wrote = false;
-    for (int i = lo + (int)threadIdx.x; i < hi; i += kThreads) {
-        const int id = cx.hlist[i];
-        if (id < c0 || id >= c0 + nvalid) continue;
-        float out = -INFINITY;  // repeats of a token carry nothing
-        int cnt = 0;
-        bool first = true;
-        for (int j = lo; j < hi; ++j) {
-            const bool eq = (cx.hlist[j] == id);
-            cnt += eq ? 1 : 0;
-            if (eq && j < i) first = false;
-        }
-        if (first) {
+    for (int base = lo; base < hi; base += 32) {
+        const int i = base + lane;
+        float z = -INFINITY;
+        int id = -1;
+        bool first = false;
+        if (i < hi) {
+            id = cx.hlist[i];
             const int off = id - c0;
-            float z;
-            if constexpr (sizeof(T) == 4) z = reinterpret_cast<float*>(tile)[off];
-            else z = bf16_bits_to_f32(reinterpret_cast<uint16_t*>(tile)[off]);
-            z = penalise(cx.rp, z, cnt);
-            if constexpr (kHasMask) {
-                if (!((smask[off >> 5] >> (off & 31)) & 1u)) z = -INFINITY;
+            if (off >= 0 && off < nvalid && (((off / VEC) % kThreads) >> 5) == warp) {
+                int cnt = 0;
+                first = true;
+                for (int j = lo; j < hi; ++j) {
+                    const bool eq = (cx.hlist[j] == id);
+                    cnt += eq ? 1 : 0;
+                    if (eq && j < i) first = false;
+                }
+                if (first && replay == 2) {
+                    z = cx.hval[i];
+                } else if (first) {
+                    if constexpr (sizeof(T) == 4) z = reinterpret_cast<float*>(tile)[off];
+                    else z = bf16_bits_to_f32(reinterpret_cast<uint16_t*>(tile)[off]);
+                    z = penalise(cx.rp, z, cnt);
+                    if constexpr (kHasMask) {
+                        if (!((smask[off >> 5] >> (off & 31)) & 1u)) z = -INFINITY;
+                    }
+                    if constexpr (sizeof(T) == 4) reinterpret_cast<float*>(tile)[off] = -INFINITY;
+                    else reinterpret_cast<uint16_t*>(tile)[off] = 0xFF80u;
+                    wrote = true;
+                    if (replay == 1) cx.hval[i] = z;
+                }
             }
-            out = z;
-            if constexpr (sizeof(T) == 4) reinterpret_cast<float*>(tile)[off] = -INFINITY;
-            else reinterpret_cast<uint16_t*>(tile)[off] = 0xFF80u;
-            wrote = true;
         }
-        cx.hval[i] = out;
+        if (first && stats) stats_one<kLse>(st, z, cx.c2);
+        if (collect) {
+            uint64_t ck = 0;
+            bool pred = first && z >= tau;
+            if (pred) { ck = make_ck(z, id); pred = ck > cx.bs->tau_ck; }
+            warp_append(cx, ws, pred, ck);
+        }
     }
     if (wrote) fence_proxy_async();
-}
-
-template <bool kLse>
-__device__ __forceinline__ void patch_consume(Ctx& cx, ThreadStats& st, int c, int c0, int nvalid, float tau,
-                                              uint64_t tau_ck, bool stats, bool collect, int& lflag) {
-    const int b = c >> cx.hshift;
-    const int lo = cx.bs->hoff[b], hi = cx.bs->hoff[b + 1];
-    for (int i = lo + (int)threadIdx.x; i < hi; i += kThreads) {
-        const int id = cx.hlist[i];
-        if (id < c0 || id >= c0 + nvalid) continue;
-        const float z = cx.hval[i];  // -inf for repeats of a token
-        if (stats) stats_one<kLse>(st, z, cx.c2);
-        if (collect && z >= tau) try_append(cx, z, id, tau_ck, lflag);
-    }
+    __syncwarp();
 }
 
 __device__ __forceinline__ float current_tau(const Ctx& cx) {
-    float tau = cx.bs->tau;
-    if (cx.minp_on) tau = fmaxf(tau, zkey_to_float(cx.bs->maxbits) + cx.delta_minp);
+    float tau = *reinterpret_cast<const volatile float*>(&cx.bs->tau);
+    if (cx.minp_on) tau = fmaxf(tau, zkey_to_float(*reinterpret_cast<const volatile uint32_t*>(&cx.bs->maxbits)) + cx.delta_minp);
     return tau;
 }
 
@@ -413,80 +443,34 @@ __device__ __forceinline__ void publish_max(Ctx& cx, const ThreadStats& st) {
     if ((threadIdx.x & 31) == 0 && wm > -INFINITY) smem_red_max(&cx.bs->maxbits, zkey(wm));
 }
 
-// A whole tile with no block synchronisation inside (the common case): one pass over the
-// thread's vector groups for the statistics and a one-compare-per-group candidate test,
-// then at most one convergent collection step per warp.
+// One tile for one warp, no block synchronisation: history patches on the warp's own
+// elements, one pass over the thread's vector groups for the statistics and a
+// one-compare-per-group candidate test, then at most one collection step.
 template <typename T, bool kHasMask, bool kLse>
-__device__ __forceinline__ void process_tile(Ctx& cx, ThreadStats& st, WarpSlots& ws, const T* tile,
-                                             const uint32_t* smask, int c, int c0, int nvalid, bool has_hist,
-                                             bool stats, bool collect, int& lflag) {
+__device__ __forceinline__ void process_tile(Ctx& cx, ThreadStats& st, WarpSlots& ws, T* tile, const uint32_t* smask,
+                                             int c, int c0, int nvalid, bool tile_hist, bool stats, bool collect,
+                                             int replay = 0) {
     constexpr int VEC = VecOf<T>::n;
     constexpr int ITER = kChunk / VEC / kThreads;
     const float tau = current_tau(cx);
-    const uint64_t tau_ck = cx.bs->tau_ck;
-    if (has_hist) patch_consume<kLse>(cx, st, c, c0, nvalid, tau, tau_ck, stats, collect, lflag);
+    if (tile_hist) warp_patch<T, kHasMask, kLse>(cx, st, ws, tile, smask, c, c0, nvalid, tau, stats, collect, replay);
     uint32_t hm = 0;
 #pragma unroll
     for (int j = 0; j < ITER; ++j) {
         float v[VEC];
-        load_group<T, kHasMask>(tile, smask, threadIdx.x + kThreads * j, v);
+        load_group<T, kHasMask>(tile, smask, threadIdx.x + kThreads * j, nvalid, v);
         const float m4 = group_stats<kLse, VEC>(st, v, cx.c2, stats);
         if (m4 >= tau) hm |= 1u << j;
     }
     if (collect && __any_sync(0xffffffffu, hm != 0))
-        warp_collect<T, kHasMask>(cx, ws, tile, smask, hm, c0, tau, tau_ck, lflag);
+        warp_collect<T, kHasMask>(cx, ws, tile, smask, hm, c0, nvalid, tau);
 }
 
-// The candidates of a tile in pieces small enough that the buffer cannot overflow, with a
-// compaction check before every piece.  Redoes a tile whose fast pass ran out of buffer
-// (statistics were already taken).  Shared counters are read between two barriers so that
-// every thread takes the same branch.
-template <typename T, bool kHasMask, bool kLse>
-__device__ void process_tile_piecewise(Ctx& cx, ThreadStats& st, const T* tile, const uint32_t* smask, int c, int c0,
-                                       int nvalid, bool has_hist) {
-    constexpr int VEC = VecOf<T>::n;
-    constexpr int ITER = kChunk / VEC / kThreads;
-    constexpr int kPiece = (kThreads / 2) * VEC;  // <= 1024 appends per piece
+// After the statistics of the first tile: the k-th largest of the 256 per-thread maxima is
+// a valid lower bound of the slice's k-th largest element (k <= 256), so it opens the
+// threshold; the tile's maximum opens the min-p prune.
+__device__ void bootstrap_threshold(Ctx& cx, const ThreadStats& st) {
     BlockShared& bs = *cx.bs;
-    int lflag = 0;
-    if (has_hist) {
-        cta_sync();
-        const int cnt = bs.count;
-        cta_sync();
-        if (cnt > cx.trigger || cnt + kHistCap > kCandCap) compact_to_k(cx, cx.k_eff);
-        patch_consume<kLse>(cx, st, c, c0, nvalid, current_tau(cx), bs.tau_ck, false, true, lflag);
-    }
-    for (int j = 0; j < ITER; ++j) {
-        for (int h = 0; h < 2; ++h) {
-            cta_sync();
-            const int cnt = bs.count;
-            cta_sync();
-            if (cnt > cx.trigger || cnt + kPiece > kCandCap) compact_to_k(cx, cx.k_eff);
-            if ((threadIdx.x >> 7) == h) {
-                const float tau = current_tau(cx);
-                const uint64_t tau_ck = bs.tau_ck;
-                float v[VEC];
-                const int g = threadIdx.x + kThreads * j;
-                load_group<T, kHasMask>(tile, smask, g, v);
-#pragma unroll
-                for (int i = 0; i < VEC; ++i)
-                    if (v[i] >= tau) try_append(cx, v[i], c0 + g * VEC + i, tau_ck, lflag);
-            }
-        }
-    }
-    cta_sync();
-}
-
-// First tile of a slice.  The statistics of the whole tile are taken first; the k-th
-// largest of the 256 per-thread maxima is a valid lower bound of the slice's k-th largest
-// element (k <= 256), so it opens the threshold; the tile's maximum opens the min-p prune.
-// Then candidates are collected in one fast pass.
-template <typename T, bool kHasMask, bool kLse>
-__device__ void bootstrap_tile(Ctx& cx, ThreadStats& st, WarpSlots& ws, const T* tile, const uint32_t* smask, int c0,
-                               int nvalid, bool has_hist, int& lflag) {
-    BlockShared& bs = *cx.bs;
-    int dummy = 0;
-    process_tile<T, kHasMask, kLse>(cx, st, ws, tile, smask, 0, c0, nvalid, has_hist, true, false, dummy);
     if (cx.minp_on) publish_max(cx, st);
     if (cx.k_eff <= kThreads) {
         // each thread's maximum stands for one distinct element
@@ -506,7 +490,6 @@ __device__ void bootstrap_tile(Ctx& cx, ThreadStats& st, WarpSlots& ws, const T*
         }
     }
     cta_sync();
-    process_tile<T, kHasMask, kLse>(cx, st, ws, tile, smask, 0, c0, nvalid, has_hist, false, true, lflag);
 }
 
 // Token history of this slice, bucketed by tile (counting sort: histogram, scan, scatter).
@@ -574,7 +557,8 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         bs.tau_ck = 0;
         bs.maxbits = zkey(-INFINITY);
         bs.count = 0;
-        bs.overflow = 0;
+        bs.event = 0;
+        bs.done_warps = 0;
         bs.fail = 0;
         bs.dropped = 0;
         bs.nh = 0;
@@ -582,7 +566,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         if (use_bar) {
             for (int s = 0; s < kStages; ++s) {
                 mbar_init(reinterpret_cast<uint64_t*>(&bs.full_bar[s]), 1);
-                mbar_init(reinterpret_cast<uint64_t*>(&bs.empty_bar[s]), 1);
+                mbar_init(reinterpret_cast<uint64_t*>(&bs.empty_bar[s]), kThreads / 32);
             }
             mbar_fence_init();
         }
@@ -661,103 +645,89 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         ws.base = 0;
         ws.used = 32;
 
-        int c_fail = -1;
-        long long pa_wait = 0, pa_prep = 0, pa_proc = 0, pa_vote = 0, pa_rare = 0;
-        (void)pa_wait; (void)pa_prep; (void)pa_proc; (void)pa_vote; (void)pa_rare;
+        // Warps stream their share of every tile on their own: they wait for the tile's bulk
+        // copy, work on the vector groups they own, and hand the tile back with one mbarrier
+        // arrival per warp.  The only block-wide meetings are the threshold bootstrap after
+        // the first tile and the rendezvous for rare events.
+        const int lane = tid & 31;
+        bool failed = false;
+        long long pa_wait = 0, pa_proc = 0, pa_rdv = 0;
+        (void)pa_wait; (void)pa_proc; (void)pa_rdv;
         for (int c = 0; c < nchunks; ++c) {
             BORN_PROF_T0();
             const int stg = c % kStages;
-            const uint32_t parity = (uint32_t)(c / kStages) & 1u;
             const int c0 = e_begin + c * kChunk;
             const int nvalid = min(kChunk, e_end - c0);
             T* tile = tiles + (size_t)stg * kChunk;
-            uint32_t* smask = masks + stg * (kChunk / 32);
-            int lflag = 0;
-            if (use_bar) {
-                if (!mbar_wait(reinterpret_cast<uint64_t*>(&bs.full_bar[stg]), parity)) {
+            const uint32_t* smask = tma_m ? masks + stg * (kChunk / 32) : gmask + c * (kChunk / 32);
+            if (c > 0 && *reinterpret_cast<const volatile int*>(&bs.event)) rendezvous(cx, ws);
+            BORN_PROF_ACC(pa_rdv);
+            if (use_bar && !failed) {
+                // wait for the tile; a warp parked here must still answer a rendezvous, or the
+                // warp that called it (and holds an older tile) would never hand that tile back
+                for (;;) {
+                    const int w = mbar_wait_or_event(reinterpret_cast<uint64_t*>(&bs.full_bar[stg]),
+                                                     (uint32_t)(c / kStages) & 1u, &bs.event);
+                    if (w == 1) break;
+                    if (w == 2 && c > 0) { rendezvous(cx, ws); continue; }
+                    if (w == 2) continue;  // before the bootstrap nobody can have raised an event
                     bs.fail = 1;
-                    lflag |= kFlagTimeout;
+                    failed = true;
+                    break;
                 }
             }
             BORN_PROF_ACC(pa_wait);
-            bool need_sync = false;
-            if (!tma_l) {  // rows that are not 16-byte aligned: plain loads
-                const T* src = grow + (size_t)c * kChunk;
-                for (int i = tid; i < nvalid; i += kThreads) tile[i] = src[i];
-                need_sync = true;
-            }
-            if (kHasMask && !tma_m) {
-                const uint32_t* src = gmask + c * (kChunk / 32);
-                for (int i = tid; i < ((nvalid + 31) >> 5); i += kThreads) smask[i] = src[i];
-                need_sync = true;
-            }
-            if (nvalid < kChunk) {  // tail of the row: neutralise what lies beyond it
-                for (int i = nvalid + tid; i < kChunk; i += kThreads) {
-                    if constexpr (sizeof(T) == 4) reinterpret_cast<float*>(tile)[i] = -INFINITY;
-                    else reinterpret_cast<uint16_t*>(tile)[i] = 0xFF80u;
+            if (!failed) {
+                if (!tma_l) {  // rows that are not 16-byte aligned: each thread fetches its own groups
+                    constexpr int VEC = VecOf<T>::n;
+                    const T* src = grow + (size_t)c * kChunk;
+                    for (int j = 0; j < kChunk / VEC / kThreads; ++j)
+                        for (int i = 0; i < VEC; ++i) {
+                            const int e = (tid + kThreads * j) * VEC + i;
+                            if (e < nvalid) tile[e] = src[e];
+                        }
+                    __syncwarp();
                 }
-                fence_proxy_async();
-                need_sync = true;
+                const bool tile_hist = has_hist && (bs.hoff[(c >> cx.hshift) + 1] > bs.hoff[c >> cx.hshift]);
+                if (c == 0) {
+                    // statistics of the first tile, then the threshold bootstrap (block-wide),
+                    // then its candidates under the new threshold
+                    process_tile<T, kHasMask, kLse>(cx, st, ws, tile, smask, 0, c0, nvalid, tile_hist, true, false, 1);
+                    bootstrap_threshold(cx, st);
+                    process_tile<T, kHasMask, kLse>(cx, st, ws, tile, smask, 0, c0, nvalid, tile_hist, false, true, 2);
+                } else {
+                    process_tile<T, kHasMask, kLse>(cx, st, ws, tile, smask, c, c0, nvalid, tile_hist, true, true);
+                }
+                if (cx.minp_on) publish_max(cx, st);  // running maximum for the min-p prune
+            } else if (c == 0) {
+                bootstrap_threshold(cx, st);  // keep the block-wide step in lockstep
             }
-            const bool tile_hist = has_hist && (bs.hoff[(c >> cx.hshift) + 1] > bs.hoff[c >> cx.hshift]);
-            if (tile_hist) {
-                if (need_sync) cta_sync();
-                patch_compute<T, kHasMask>(cx, tile, smask, c, c0, nvalid);
-                need_sync = true;
-            }
-            if (need_sync) cta_sync();
-            BORN_PROF_ACC(pa_prep);
-
-            if (c == 0) {
-                bootstrap_tile<T, kHasMask, kLse>(cx, st, ws, tile, smask, c0, nvalid, tile_hist, lflag);
-            } else {
-                process_tile<T, kHasMask, kLse>(cx, st, ws, tile, smask, c, c0, nvalid, tile_hist, true, true, lflag);
-            }
-            if (cx.minp_on) publish_max(cx, st);  // running maximum for the min-p prune
+            // hand this warp's share of the tile back to the producer
+            __syncwarp();
+            if (lane == 0 && use_bar) mbar_arrive(reinterpret_cast<uint64_t*>(&bs.empty_bar[stg]));
             BORN_PROF_ACC(pa_proc);
-            // One barrier per tile: it closes the tile and votes on the rare events.
-            const int vote = cta_sync_or(lflag);
-            BORN_PROF_ACC(pa_vote);
-            if (vote) {
-                const int ov = bs.overflow, fl = bs.fail;
-                cta_sync();
-                if (fl) { c_fail = c; break; }
-                if (ov) {
-                    // the fast pass ran out of buffer: retire what it appended from this tile
-                    // and redo the tile piecewise
-                    const int ncur = min(bs.count, kCandCap);
-                    for (int i = tid; i < ncur; i += kThreads) {
-                        const uint64_t e = cx.cand[i];
-                        const int idx = ck_idx(e);
-                        if (ck_alive(e) && idx >= c0 && idx < c0 + kChunk) cx.cand[i] = (uint64_t)i;
-                    }
-                    cta_sync();
-                    if (tid == 0) { bs.count = ncur; bs.overflow = 0; }
-                    cta_sync();
-                    process_tile_piecewise<T, kHasMask, kLse>(cx, st, tile, smask, c, c0, nvalid, tile_hist);
-                }
-                compact_to_k(cx, cx.k_eff);
-                ws.used = 32;  // slot blocks do not survive a rearranged buffer
-            }
-            // hand the tile back to the producer
-            if (tid == 0 && use_bar) mbar_arrive(reinterpret_cast<uint64_t*>(&bs.empty_bar[stg]));
-            BORN_PROF_ACC(pa_rare);
             if (c == 0) BORN_PROF(2);
         }
+        // finished: stay available for rendezvous until every warp is through
+        __syncwarp();
+        if (lane == 0) smem_red_add(&bs.done_warps, 1u);
+        while (!rendezvous(cx, ws)) { }
         BORN_PROF(3);
 #ifdef BORN_PROFILE
         if (A.prof && tid == 0) {
             unsigned long long* pr = A.prof + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 16;
-            pr[8] = pa_wait; pr[9] = pa_prep; pr[10] = pa_proc; pr[11] = pa_vote; pr[12] = pa_rare;
+            pr[8] = pa_wait; pr[9] = pa_rdv; pr[10] = pa_proc;
         }
 #endif
-        if (c_fail >= 0) {
-            // A bulk copy never arrived.  The producer sees bs.fail and stops issuing; wait
-            // (bounded) for the copies already in flight so that this CTA's shared memory is
-            // quiet before it exits, then report.
+        if (bs.fail) {
+            // A bulk copy never arrived.  The producer sees bs.fail and stops issuing; thread 0
+            // waits (bounded) for copies that may still be in flight so that this CTA's shared
+            // memory is quiet before it exits, then reports.
             if (tid == 0) {
-                for (int cc = c_fail + 1; cc < min(nchunks, c_fail + kStages); ++cc)
-                    mbar_wait(reinterpret_cast<uint64_t*>(&bs.full_bar[cc % kStages]), (uint32_t)(cc / kStages) & 1u);
+                for (int s = 0; s < kStages; ++s) {
+                    uint64_t* fb = reinterpret_cast<uint64_t*>(&bs.full_bar[s]);
+                    mbar_wait(fb, 0);
+                }
                 atomicExch(A.dev_error, 1);
                 if (A.out_status) A.out_status[row] = 100 + BORN_ERR_DEVICE_TIMEOUT;
                 if (A.out_token) A.out_token[row] = -1;

@@ -213,6 +213,31 @@ __device__ __forceinline__ bool mbar_wait_or_abort(uint64_t* bar, uint32_t parit
     return false;
 }
 
+// Bounded wait that returns 1 when the phase completed, 2 as soon as *event is non-zero
+// (checked between probes by the whole warp, so the answer is warp-uniform), 0 on a timeout.
+__device__ __forceinline__ int mbar_wait_or_event(uint64_t* bar, uint32_t parity, const volatile int* event) {
+    const uint32_t addr = smem_u32(bar);
+    unsigned long long t0 = 0;
+    for (uint32_t it = 0; it < kMbarSpinLimit; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (__all_sync(0xffffffffu, ok != 0)) return 1;
+        if (__any_sync(0xffffffffu, *event != 0)) return 2;
+        if ((it & 63u) == 63u) {
+            const unsigned long long now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (__any_sync(0xffffffffu, now - t0 > kMbarTimeoutNs)) return 0;
+        }
+    }
+    return 0;
+}
+
 // ---- warp helpers ------------------------------------------------------------------------
 __device__ __forceinline__ uint64_t shfl_u64(uint64_t v, int src) {
     uint32_t lo = __shfl_sync(0xffffffffu, (uint32_t)v, src);

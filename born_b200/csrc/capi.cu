@@ -136,15 +136,15 @@ int launch_sample(Handle* h, const SampleKernelArgs& A, int dtype, cudaStream_t 
 #undef V_
 }
 
-// Slices per row: enough CTAs to keep every SM busy for several rounds, but at least four
-// chunks per slice so that the bootstrap chunk stays a small part of the slice.
+// Slices per row.  With at least one row per SM every row is one CTA (a slice costs a
+// threshold bootstrap and a record merge); smaller batches are cut so that about two CTAs
+// per SM exist, but never below four tiles per slice.
 void choose_slices(const Handle* h, int B, int V, int* S, int* slice_len) {
     const int nchunks = (V + kChunk - 1) / kChunk;
     int s = 1;
     if (h->force_slices > 0) s = h->force_slices;
-    else {
-        const int target = 4 * h->num_sms;
-        s = (target + B - 1) / B;
+    else if (B < h->num_sms) {
+        s = (2 * h->num_sms + B - 1) / B;
         int cap = nchunks / 4;
         if (cap < 1) cap = 1;
         if (s > cap) s = cap;

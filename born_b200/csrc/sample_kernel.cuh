@@ -105,9 +105,14 @@ __host__ __device__ inline SmemLayout smem_layout(int elem_bytes, bool has_mask,
     L.tiles = off; off += kStages * kChunk * elem_bytes;
     L.masks = off; off += has_mask ? kStages * (kChunk / 32) * 4 : 0;
     L.cand = off; off += kCandCap * 8;
-    L.search = off; off += (int)((sizeof(SearchScratch) + 127) / 128 * 128);
-    L.pairs = off; off += kMaxK * 2 * 2;
-    L.hist = off; off += has_hist ? kHistCap * 8 : 0;
+    // the radix-search scratch and the pairing lists of the compaction are never live together
+    L.search = off;
+    L.pairs = off;
+    {
+        const int a = (int)((sizeof(SearchScratch) + 127) / 128 * 128), b = kMaxK * 2 * 2;
+        off += a > b ? a : b;
+    }
+    L.hist = off; off += has_hist ? kHistCap * 10 : 0;  // ids, replay values, multiplicities
     L.total = off;
     return L;
 }
@@ -118,7 +123,8 @@ struct BlockShared {  // static shared state of a CTA
     unsigned long long tau_ck;
     unsigned long long red64[kThreads / 32];
     float redf[kThreads / 32];
-    float tau;
+    float wbound[kThreads / 32];  // per warp: a lower bound of the k-th largest value (lane maxima)
+    uint32_t taubits;  // key of tau; only ever raised (red.max)
     uint32_t maxbits;
     int count;
     int event;       // a compaction is wanted: warps meet at the rendezvous
@@ -130,18 +136,17 @@ struct BlockShared {  // static shared state of a CTA
     int last;
     int hoff[kHistBuckets + 1];
     int hcur[kHistBuckets];
+#ifdef BORN_PROFILE
+    long long pf_search, pf_pair, pf_calls;
+#endif
 };
 
 struct ThreadStats {
     float mx;   // running maximum (NaN-propagating)
     float R;    // reference of the online log-sum-exp (z domain)
     float nRc;  // -R * c2
-    float s;    // sum of 2^((z - R) * c2)
-};
-
-struct WarpSlots {  // the block of 32 buffer slots a warp is filling (warp-uniform)
-    int base;
-    int used;
+    float2 s;   // two partial sums of 2^((z - R) * c2) (packed fp32x2 arithmetic)
+    float pub;  // largest maximum this thread has published for the min-p prune
 };
 
 struct Ctx {  // per-CTA pointers and row constants, all block-uniform
@@ -151,6 +156,7 @@ struct Ctx {  // per-CTA pointers and row constants, all block-uniform
     uint16_t* wpos;
     int32_t* hlist;
     float* hval;
+    uint16_t* hcnt;  // multiplicity of a history id, 0 for repeats of an id already listed
     BlockShared* bs;
     int k_eff;
     int trigger;
@@ -171,8 +177,14 @@ __device__ bool compact_to_k(Ctx& cx, int k) {
     if (n > kCandCap) n = kCandCap;
     if (n <= k) return false;
     uint64_t* cand = cx.cand;
+#ifdef BORN_PROFILE
+    long long pf0 = clock64();
+#endif
     uint64_t T = block_radix_search<true, 56, true>(
         n, (unsigned long long)(k - 1), [&](int i) { return cand[i]; }, [&](int) { return 1ull; }, *cx.sc);
+#ifdef BORN_PROFILE
+    long long pf1 = clock64();
+#endif
     if (tid == 0) { bs.nl = 0; bs.nw = 0; }
     cta_sync();
     for (int i = tid; i < n; i += kThreads) {
@@ -190,9 +202,12 @@ __device__ bool compact_to_k(Ctx& cx, int k) {
         bs.count = k;
         if (ck_alive(T)) {
             bs.tau_ck = T;
-            bs.tau = ck_z(T);
+            smem_red_max(&bs.taubits, (uint32_t)(T >> 24));
         }
         bs.dropped = 1;
+#ifdef BORN_PROFILE
+        bs.pf_search += pf1 - pf0; bs.pf_pair += clock64() - pf1; bs.pf_calls += 1000000 + n;
+#endif
     }
     cta_sync();
     return true;
@@ -203,11 +218,11 @@ __device__ __forceinline__ void stats_one(ThreadStats& st, float z, float c2) {
     st.mx = max_nan(st.mx, z);
     if (kLse) {
         if (z > st.R) {
-            st.s *= ex2_approx(__fmul_rn(st.R - z, c2));
+            { const float f = ex2_approx(__fmul_rn(st.R - z, c2)); st.s.x *= f; st.s.y *= f; }
             st.R = z;
             st.nRc = -z * c2;
         }
-        st.s += ex2_approx(fmaf(z, c2, st.nRc));
+        st.s.x += ex2_approx(fmaf(z, c2, st.nRc));
     }
 }
 
@@ -239,24 +254,37 @@ __device__ __forceinline__ void load_group(const T* tile, const uint32_t* smask,
     }
 }
 
-// Statistics of one vector group; returns the group maximum.
+__device__ __forceinline__ float max3_nan(float a, float b, float c) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
+// Statistics of one vector group; returns the group maximum.  The log-sum-exp terms are
+// formed two at a time with packed fp32x2 multiply-adds and adds (it feeds no decision).
 template <bool kLse, int VEC>
 __device__ __forceinline__ float group_stats(ThreadStats& st, const float (&v)[VEC], float c2, bool stats) {
-    float m4 = v[0];
-#pragma unroll
-    for (int i = 1; i < VEC; ++i) m4 = max_nan(m4, v[i]);
+    float m4;
+    if constexpr (VEC == 4) {
+        m4 = max_nan(max3_nan(v[0], v[1], v[2]), v[3]);
+    } else {
+        m4 = max3_nan(max3_nan(v[0], v[1], v[2]), max3_nan(v[3], v[4], v[5]), max_nan(v[6], v[7]));
+    }
     if (stats) {
         st.mx = max_nan(st.mx, m4);
         if constexpr (kLse) {
             if (m4 > st.R) {
-                st.s *= ex2_approx(__fmul_rn(st.R - m4, c2));
+                const float f = ex2_approx(__fmul_rn(st.R - m4, c2));
+                st.s = __fmul2_rn(st.s, make_float2(f, f));
                 st.R = m4;
                 st.nRc = -m4 * c2;
             }
-            float acc = 0.0f;
+            const float2 cc = make_float2(c2, c2), rr = make_float2(st.nRc, st.nRc);
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) acc += ex2_approx(fmaf(v[i], c2, st.nRc));
-            st.s += acc;
+            for (int i = 0; i < VEC; i += 2) {
+                const float2 t = __ffma2_rn(make_float2(v[i], v[i + 1]), cc, rr);
+                st.s = __fadd2_rn(st.s, make_float2(ex2_approx(t.x), ex2_approx(t.y)));
+            }
         }
     }
     return m4;
@@ -264,10 +292,11 @@ __device__ __forceinline__ float group_stats(ThreadStats& st, const float (&v)[V
 
 // Rendezvous of the 256 compute threads.  Warps stream their tiles without any block-wide
 // barrier; only a rare event (the candidate buffer reached its trigger or is full) brings
-// them together.  A warp comes here when it sees bs.event at a tile boundary, when it cannot
-// get buffer space, or when it has finished all its tiles; the buffer is compacted if an
-// event is pending.  Returns true when every warp has finished and no event was pending.
-__device__ bool rendezvous(Ctx& cx, WarpSlots& ws) {
+// them together.  A warp comes here when it sees bs.event at a tile boundary, when one of
+// its lanes cannot get buffer space, or when it has finished all its tiles; the buffer is
+// compacted if an event is pending.  Returns true when every warp has finished and no event
+// was pending.
+__device__ bool rendezvous(Ctx& cx) {
     BlockShared& bs = *cx.bs;
     cta_sync();
     const int ev = bs.event, dn = bs.done_warps;
@@ -276,84 +305,85 @@ __device__ bool rendezvous(Ctx& cx, WarpSlots& ws) {
         compact_to_k(cx, cx.k_eff);
         if (threadIdx.x == 0) bs.event = 0;
         cta_sync();
-        ws.used = 32;  // slot blocks do not survive a rearranged buffer
     }
     return !ev && dn == kThreads / 32;
 }
 
-// Convergent append: every lane of the warp calls with its own (pred, ck).  A ballot counts
-// the offers; each offering lane stores its entry at its rank among the offers inside the
-// warp's current block of 32 slots.  A new block is reserved with one shared-memory atomic
-// when the current one cannot take the round; its slots start out as dead entries (value
-// part 0, unique low bits).  When the buffer is full the warp raises the event and waits at
-// the rendezvous for the compaction, then tries again.
-__device__ __forceinline__ void warp_append(Ctx& cx, WarpSlots& ws, bool pred, uint64_t ck) {
-    const int lane = threadIdx.x & 31;
-    uint32_t bal;
-    int n;
+// Append one entry per offering lane.  Every lane of the warp calls; lanes with an offer
+// take a slot with a shared-memory atomic.  When the buffer is full the whole warp goes to
+// the rendezvous for the compaction and the lanes still holding an offer try again.
+__device__ __forceinline__ void settle_one(Ctx& cx, bool pending, uint64_t ck) {
     for (;;) {
-        bal = __ballot_sync(0xffffffffu, pred);
-        if (!bal) return;
-        n = __popc(bal);
-        if (ws.used + n <= 32) break;
-        int b = 0;  // reserve a fresh block (warp-uniform path)
-        if (lane == 0) b = (int)smem_atom_add(&cx.bs->count, 32u);
-        b = __shfl_sync(0xffffffffu, b, 0);
-        if (b + 32 <= kCandCap) {
-            cx.cand[b + lane] = (uint64_t)(b + lane);
-            __syncwarp();
-            ws.base = b;
-            ws.used = 0;
-            if (b + 32 > cx.trigger && lane == 0) cx.bs->event = 1;  // compaction at the next tile boundary
-        } else {
-            // no room: the part of the refused block that lies inside the buffer must not
-            // keep stale entries, the compaction reads the whole buffer
-            if (b + lane < kCandCap) cx.cand[b + lane] = (uint64_t)(b + lane);
-            if (lane == 0) cx.bs->event = 1;
-            __syncwarp();
-            rendezvous(cx, ws);
-            pred = pred && ck > cx.bs->tau_ck;  // the threshold has risen: some offers can be withdrawn
+        if (pending) {
+            const int pos = (int)smem_atom_add(&cx.bs->count, 1u);
+            if (pos < kCandCap) {
+                cx.cand[pos] = ck;
+                if (pos + 1 > cx.trigger) cx.bs->event = 1;  // compaction at the next tile boundary
+                pending = false;
+            } else {
+                cx.bs->event = 1;
+            }
         }
+        if (!__any_sync(0xffffffffu, pending)) break;
+        rendezvous(cx);
+        pending = pending && ck > cx.bs->tau_ck;  // the threshold has risen
     }
-    if (pred) cx.cand[ws.base + ws.used + __popc(bal & ((1u << lane) - 1u))] = ck;
-    ws.used += n;
 }
 
 // Candidates of one tile for this warp.  `hm` has bit j set when the maximum of this
-// thread's j-th vector group reached tau.  The flagged groups are read again from the tile
-// to find the elements; then, round by round, every lane offers at most one element.
+// thread's j-th vector group reached tau.  Only the lanes with a flagged group do any work:
+// they read the group again, test its elements exactly (value and rank key), take as many
+// buffer slots as they have hits with ONE shared-memory atomic and store the entries.  The
+// warp meets again with a single vote; if some lane found the buffer full, the warp goes to
+// the rendezvous for the compaction and that lane tries again.
 template <typename T, bool kHasMask>
-__device__ __forceinline__ void warp_collect(Ctx& cx, WarpSlots& ws, const T* tile, const uint32_t* smask, uint32_t hm,
-                                             int c0, int nvalid, float tau) {
+__device__ __forceinline__ void warp_collect(Ctx& cx, const T* tile, const uint32_t* smask, uint32_t hm, int c0,
+                                             int nvalid, float tau) {
     constexpr int VEC = VecOf<T>::n;
     constexpr int ITER = kChunk / VEC / kThreads;
     uint32_t em = 0;  // element-level hits: bit j*VEC+i
+    if (hm) {
+        const uint64_t tau_ck = cx.bs->tau_ck;
 #pragma unroll
-    for (int j = 0; j < ITER; ++j) {
-        if (hm & (1u << j)) {
-            float v[VEC];
-            load_group<T, kHasMask>(tile, smask, threadIdx.x + kThreads * j, nvalid, v);
+        for (int j = 0; j < ITER; ++j) {
+            if (hm & (1u << j)) {
+                float v[VEC];
+                const int g = threadIdx.x + kThreads * j;
+                load_group<T, kHasMask>(tile, smask, g, nvalid, v);
 #pragma unroll
-            for (int i = 0; i < VEC; ++i)
-                if (v[i] >= tau) em |= 1u << (j * VEC + i);
+                for (int i = 0; i < VEC; ++i)
+                    if (v[i] >= tau && make_ck(v[i], c0 + g * VEC + i) > tau_ck) em |= 1u << (j * VEC + i);
+            }
         }
     }
+    bool pending = em != 0;
     for (;;) {
-        const bool has = em != 0;
-        if (!__any_sync(0xffffffffu, has)) break;
-        uint64_t ck = 0;
-        bool pred = false;
-        if (has) {
-            const int b = __ffs(em) - 1;
-            em &= em - 1;
-            const int e = (threadIdx.x + kThreads * (b / VEC)) * VEC + (b % VEC);
-            float z;
-            if constexpr (sizeof(T) == 4) z = reinterpret_cast<const float*>(tile)[e];
-            else z = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(tile)[e]);
-            ck = make_ck(z, c0 + e);
-            pred = ck > cx.bs->tau_ck;
+        if (pending) {
+            const int cnt = __popc(em);
+            const int pos = (int)smem_atom_add(&cx.bs->count, (uint32_t)cnt);
+            if (pos + cnt <= kCandCap) {
+                int p = pos;
+                uint32_t m = em;
+                while (m) {
+                    const int b = __ffs(m) - 1;
+                    m &= m - 1;
+                    const int e = (threadIdx.x + kThreads * (b / VEC)) * VEC + (b % VEC);
+                    float z;
+                    if constexpr (sizeof(T) == 4) z = reinterpret_cast<const float*>(tile)[e];
+                    else z = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(tile)[e]);
+                    cx.cand[p++] = make_ck(z, c0 + e);
+                }
+                if (pos + cnt > cx.trigger) cx.bs->event = 1;  // compaction at the next tile boundary
+                pending = false;
+            } else {
+                // no room: the compaction reads the whole buffer, so the slots up to its end
+                // must not keep stale entries (dead entries: value part 0, unique low bits)
+                for (int p = pos; p < kCandCap; ++p) cx.cand[p] = (uint64_t)p;
+                cx.bs->event = 1;
+            }
         }
-        warp_append(cx, ws, pred, ck);
+        if (!__any_sync(0xffffffffu, pending)) break;
+        rendezvous(cx);
     }
 }
 
@@ -373,9 +403,9 @@ __device__ __forceinline__ float penalise(const born_row_params& rp, float z, in
 // vector group is the only one that ever touches it, so no other warp is involved): the
 // token's logit is penalised once per distinct token, the token is taken out of the tile
 // (-inf) and its new value goes through the statistics and the candidate test on its own.
-// Entries are bucketed by tile; duplicates inside a bucket are found by comparing.
+// Entries are bucketed by tile and carry their multiplicity (repeats carry 0).
 template <typename T, bool kHasMask, bool kLse>
-__device__ __forceinline__ void warp_patch(Ctx& cx, ThreadStats& st, WarpSlots& ws, T* tile, const uint32_t* smask,
+__device__ __forceinline__ void warp_patch(Ctx& cx, ThreadStats& st, T* tile, const uint32_t* smask,
                                            int c, int c0, int nvalid, float tau, bool stats, bool collect,
                                            int replay) {
     // replay: 0 = patch, take statistics and collect in one go; 1 = patch and take statistics,
@@ -394,14 +424,9 @@ __device__ __forceinline__ void warp_patch(Ctx& cx, ThreadStats& st, WarpSlots& 
         if (i < hi) {
             id = cx.hlist[i];
             const int off = id - c0;
-            if (off >= 0 && off < nvalid && (((off / VEC) % kThreads) >> 5) == warp) {
-                int cnt = 0;
+            const int cnt = cx.hcnt[i];  // 0: a repeat of an id listed earlier
+            if (cnt > 0 && off >= 0 && off < nvalid && (((off / VEC) % kThreads) >> 5) == warp) {
                 first = true;
-                for (int j = lo; j < hi; ++j) {
-                    const bool eq = (cx.hlist[j] == id);
-                    cnt += eq ? 1 : 0;
-                    if (eq && j < i) first = false;
-                }
                 if (first && replay == 2) {
                     z = cx.hval[i];
                 } else if (first) {
@@ -423,7 +448,7 @@ __device__ __forceinline__ void warp_patch(Ctx& cx, ThreadStats& st, WarpSlots& 
             uint64_t ck = 0;
             bool pred = first && z >= tau;
             if (pred) { ck = make_ck(z, id); pred = ck > cx.bs->tau_ck; }
-            warp_append(cx, ws, pred, ck);
+            settle_one(cx, pred, ck);
         }
     }
     if (wrote) fence_proxy_async();
@@ -431,29 +456,31 @@ __device__ __forceinline__ void warp_patch(Ctx& cx, ThreadStats& st, WarpSlots& 
 }
 
 __device__ __forceinline__ float current_tau(const Ctx& cx) {
-    float tau = *reinterpret_cast<const volatile float*>(&cx.bs->tau);
+    float tau = zkey_to_float(*reinterpret_cast<const volatile uint32_t*>(&cx.bs->taubits));
     if (cx.minp_on) tau = fmaxf(tau, zkey_to_float(*reinterpret_cast<const volatile uint32_t*>(&cx.bs->maxbits)) + cx.delta_minp);
     return tau;
 }
 
-__device__ __forceinline__ void publish_max(Ctx& cx, const ThreadStats& st) {
-    float wm = st.mx;
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, d));
-    if ((threadIdx.x & 31) == 0 && wm > -INFINITY) smem_red_max(&cx.bs->maxbits, zkey(wm));
+// Running maximum for the min-p prune: a thread publishes only when its own maximum has
+// grown past what it published before (rare after the first tiles).
+__device__ __forceinline__ void publish_max(Ctx& cx, ThreadStats& st) {
+    if (st.mx > st.pub) {
+        st.pub = st.mx;
+        smem_red_max(&cx.bs->maxbits, zkey(st.mx));
+    }
 }
 
 // One tile for one warp, no block synchronisation: history patches on the warp's own
 // elements, one pass over the thread's vector groups for the statistics and a
 // one-compare-per-group candidate test, then at most one collection step.
 template <typename T, bool kHasMask, bool kLse>
-__device__ __forceinline__ void process_tile(Ctx& cx, ThreadStats& st, WarpSlots& ws, T* tile, const uint32_t* smask,
+__device__ __forceinline__ void process_tile(Ctx& cx, ThreadStats& st, T* tile, const uint32_t* smask,
                                              int c, int c0, int nvalid, bool tile_hist, bool stats, bool collect,
                                              int replay = 0) {
     constexpr int VEC = VecOf<T>::n;
     constexpr int ITER = kChunk / VEC / kThreads;
     const float tau = current_tau(cx);
-    if (tile_hist) warp_patch<T, kHasMask, kLse>(cx, st, ws, tile, smask, c, c0, nvalid, tau, stats, collect, replay);
+    if (tile_hist) warp_patch<T, kHasMask, kLse>(cx, st, tile, smask, c, c0, nvalid, tau, stats, collect, replay);
     uint32_t hm = 0;
 #pragma unroll
     for (int j = 0; j < ITER; ++j) {
@@ -463,31 +490,56 @@ __device__ __forceinline__ void process_tile(Ctx& cx, ThreadStats& st, WarpSlots
         if (m4 >= tau) hm |= 1u << j;
     }
     if (collect && __any_sync(0xffffffffu, hm != 0))
-        warp_collect<T, kHasMask>(cx, ws, tile, smask, hm, c0, nvalid, tau);
+        warp_collect<T, kHasMask>(cx, tile, smask, hm, c0, nvalid, tau);
 }
 
-// After the statistics of the first tile: the k-th largest of the 256 per-thread maxima is
-// a valid lower bound of the slice's k-th largest element (k <= 256), so it opens the
-// threshold; the tile's maximum opens the min-p prune.
-__device__ void bootstrap_threshold(Ctx& cx, const ThreadStats& st) {
-    BlockShared& bs = *cx.bs;
-    if (cx.minp_on) publish_max(cx, st);
-    if (cx.k_eff <= kThreads) {
-        // each thread's maximum stands for one distinct element
-        const bool have = st.mx > -INFINITY;  // false for NaN as well
-        cx.cand[threadIdx.x] = have ? (((uint64_t)zkey(st.mx) << 24) | (uint64_t)threadIdx.x) : (uint64_t)threadIdx.x;
-        const int nfin = cta_sync_count(have);
-        if (nfin >= cx.k_eff) {
-            uint64_t* cand = cx.cand;
-            uint64_t Tk = block_radix_search<true, 56, true>(
-                kThreads, (unsigned long long)(cx.k_eff - 1), [&](int i) { return cand[i]; }, [&](int) { return 1ull; },
-                *cx.sc);
-            if (threadIdx.x == 0) {
-                bs.tau = zkey_to_float((uint32_t)(Tk >> 24));
-                bs.tau_ck = ((Tk >> 24) << 24) - 1;  // every element of that value or above is a candidate
-                bs.dropped = 1;
+// Lane-maxima bound.  Every lane's running maximum belongs to a different token, so the
+// j-th largest of a warp's 32 lane maxima has at least j tokens at or above it; with
+// j = ceil(k / 8) the smallest of the eight warps' values has at least k tokens at or above
+// it and is a valid lower bound of the row's k-th largest value -- no sorting, no barrier.
+// It tracks the true k-th value closely because the best k tokens rarely share a lane.
+// Each warp publishes its value; tau is raised to the minimum over the warps (values of
+// warps that have not caught up are older, hence lower, hence still valid).
+__device__ __forceinline__ void publish_lane_bound(Ctx& cx, const ThreadStats& st) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float v = (st.mx == st.mx) ? st.mx : -INFINITY;
+    uint32_t key = zkey(v);
+    const int j = (cx.k_eff + kThreads / 32 - 1) / (kThreads / 32);
+    uint32_t kj;
+    if (j == 1) {
+        kj = __reduce_max_sync(0xffffffffu, key);
+    } else {
+        // warp bitonic sort, descending by lane: 15 compare-exchange steps, one shuffle each
+#pragma unroll
+        for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+            for (int d = k >> 1; d > 0; d >>= 1) {
+                const uint32_t other = __shfl_xor_sync(0xffffffffu, key, d);
+                const bool up = ((lane & k) == 0);          // this run is sorted descending
+                const bool lower = ((lane & d) == 0);        // lower lane of the pair
+                key = (up == lower) ? max(key, other) : min(key, other);
             }
         }
+        kj = __shfl_sync(0xffffffffu, key, j - 1);
+    }
+    const float w = zkey_to_float(kj);
+    if (lane == 0) *reinterpret_cast<volatile float*>(&cx.bs->wbound[warp]) = w;
+    __syncwarp();
+    float m = *reinterpret_cast<const volatile float*>(&cx.bs->wbound[0]);
+#pragma unroll
+    for (int i = 1; i < kThreads / 32; ++i) m = fminf(m, *reinterpret_cast<const volatile float*>(&cx.bs->wbound[i]));
+    if (lane == 0 && m > -FLT_MAX) smem_red_max(&cx.bs->taubits, zkey(m));
+}
+
+// After the statistics of the first tile (block-wide, once per slice): open the threshold
+// from the lane maxima and the min-p prune from the tile's maximum.
+__device__ void bootstrap_threshold(Ctx& cx, ThreadStats& st) {
+    if (cx.minp_on) publish_max(cx, st);
+    if (cx.k_eff <= kThreads) {
+        publish_lane_bound(cx, st);
+        cta_sync();
+        publish_lane_bound(cx, st);  // now every warp's value is there
+        if (threadIdx.x == 0) cx.bs->dropped = 1;
     }
     cta_sync();
 }
@@ -528,7 +580,23 @@ __device__ int bucket_history(Ctx& cx, const int32_t* gh, int len, int e_begin, 
         if (id >= 0) cx.hlist[smem_atom_add(&bs.hcur[((id - e_begin) / kChunk) >> cx.hshift], 1u)] = id;
     }
     cta_sync();
-    return bs.hoff[kHistBuckets];
+    // multiplicity of every id within its bucket; repeats of an id are marked with 0
+    const int total = bs.hoff[kHistBuckets];
+    for (int i = tid; i < total; i += kThreads) {
+        const int id = cx.hlist[i];
+        const int b = ((id - e_begin) / kChunk) >> cx.hshift;
+        const int lo = bs.hoff[b], hi = bs.hoff[b + 1];
+        int cnt = 0;
+        bool first = true;
+        for (int j = lo; j < hi; ++j) {
+            const bool eq = (cx.hlist[j] == id);
+            cnt += eq ? 1 : 0;
+            if (eq && j < i) first = false;
+        }
+        cx.hcnt[i] = first ? (uint16_t)cnt : (uint16_t)0;
+    }
+    cta_sync();
+    return total;
 }
 
 template <typename T, bool kHasMask, bool kLse>
@@ -553,11 +621,15 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     const bool use_bar = (A.mode != kModeMerge) && (tma_l || tma_m);
 
     if (tid == 0) {
-        bs.tau = -FLT_MAX;
+        bs.taubits = zkey(-FLT_MAX);
+        for (int w = 0; w < kThreads / 32; ++w) bs.wbound[w] = -FLT_MAX;
         bs.tau_ck = 0;
         bs.maxbits = zkey(-INFINITY);
         bs.count = 0;
         bs.event = 0;
+#ifdef BORN_PROFILE
+        bs.pf_search = bs.pf_pair = bs.pf_calls = 0;
+#endif
         bs.done_warps = 0;
         bs.fail = 0;
         bs.dropped = 0;
@@ -604,6 +676,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     cx.wpos = cx.lslot + kMaxK;
     cx.hlist = reinterpret_cast<int32_t*>(smem + L.hist);
     cx.hval = reinterpret_cast<float*>(smem + L.hist + kHistCap * 4);
+    cx.hcnt = reinterpret_cast<uint16_t*>(smem + L.hist + kHistCap * 8);
     cx.bs = &bs;
     cx.rp = A.row_params ? A.row_params[row] : A.params;
     const born_row_params& rp = cx.rp;
@@ -640,10 +713,8 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         st.mx = -INFINITY;
         st.R = -1e30f;
         st.nRc = 1e30f * cx.c2;
-        st.s = 0.0f;
-        WarpSlots ws;
-        ws.base = 0;
-        ws.used = 32;
+        st.s = make_float2(0.0f, 0.0f);
+        st.pub = -INFINITY;
 
         // Warps stream their share of every tile on their own: they wait for the tile's bulk
         // copy, work on the vector groups they own, and hand the tile back with one mbarrier
@@ -660,7 +731,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             const int nvalid = min(kChunk, e_end - c0);
             T* tile = tiles + (size_t)stg * kChunk;
             const uint32_t* smask = tma_m ? masks + stg * (kChunk / 32) : gmask + c * (kChunk / 32);
-            if (c > 0 && *reinterpret_cast<const volatile int*>(&bs.event)) rendezvous(cx, ws);
+            if (c > 0 && *reinterpret_cast<const volatile int*>(&bs.event)) rendezvous(cx);
             BORN_PROF_ACC(pa_rdv);
             if (use_bar && !failed) {
                 // wait for the tile; a warp parked here must still answer a rendezvous, or the
@@ -669,7 +740,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
                     const int w = mbar_wait_or_event(reinterpret_cast<uint64_t*>(&bs.full_bar[stg]),
                                                      (uint32_t)(c / kStages) & 1u, &bs.event);
                     if (w == 1) break;
-                    if (w == 2 && c > 0) { rendezvous(cx, ws); continue; }
+                    if (w == 2 && c > 0) { rendezvous(cx); continue; }
                     if (w == 2) continue;  // before the bootstrap nobody can have raised an event
                     bs.fail = 1;
                     failed = true;
@@ -692,13 +763,18 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
                 if (c == 0) {
                     // statistics of the first tile, then the threshold bootstrap (block-wide),
                     // then its candidates under the new threshold
-                    process_tile<T, kHasMask, kLse>(cx, st, ws, tile, smask, 0, c0, nvalid, tile_hist, true, false, 1);
+                    process_tile<T, kHasMask, kLse>(cx, st, tile, smask, 0, c0, nvalid, tile_hist, true, false, 1);
                     bootstrap_threshold(cx, st);
-                    process_tile<T, kHasMask, kLse>(cx, st, ws, tile, smask, 0, c0, nvalid, tile_hist, false, true, 2);
+                    process_tile<T, kHasMask, kLse>(cx, st, tile, smask, 0, c0, nvalid, tile_hist, false, true, 2);
                 } else {
-                    process_tile<T, kHasMask, kLse>(cx, st, ws, tile, smask, c, c0, nvalid, tile_hist, true, true);
+                    process_tile<T, kHasMask, kLse>(cx, st, tile, smask, c, c0, nvalid, tile_hist, true, true);
                 }
                 if (cx.minp_on) publish_max(cx, st);  // running maximum for the min-p prune
+                if (cx.k_eff <= kThreads) {
+                    // tighten tau from the lane maxima once per doubling of the tiles seen
+                    const int x = c + 1, p2 = 1 << (31 - __clz(x));
+                    if (c > 0 && x == p2) publish_lane_bound(cx, st);
+                }
             } else if (c == 0) {
                 bootstrap_threshold(cx, st);  // keep the block-wide step in lockstep
             }
@@ -708,10 +784,12 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             BORN_PROF_ACC(pa_proc);
             if (c == 0) BORN_PROF(2);
         }
-        // finished: stay available for rendezvous until every warp is through
+        // finished: one last bound from the lane maxima, then stay available for rendezvous
+        // until every warp is through
+        if (cx.k_eff <= kThreads && !failed && nchunks > 0) publish_lane_bound(cx, st);
         __syncwarp();
         if (lane == 0) smem_red_add(&bs.done_warps, 1u);
-        while (!rendezvous(cx, ws)) { }
+        while (!rendezvous(cx)) { }
         BORN_PROF(3);
 #ifdef BORN_PROFILE
         if (A.prof && tid == 0) {
@@ -735,7 +813,8 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             cta_sync();
             return;
         }
-        compact_to_k(cx, cx.k_eff);
+        const bool own_row = (A.mode == kModeFull && A.S == 1);
+        if (!own_row) compact_to_k(cx, cx.k_eff);  // records hold at most k entries
         cta_sync();
 
         // slice statistics
@@ -750,8 +829,9 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         cta_sync();
         float s_slice = 0.0f;
         if (kLse) {
-            float v = st.s * ex2_approx(__fmul_rn(st.R - m_slice, cx.c2));
-            if (!(st.s > 0.0f)) v = 0.0f;
+            const float ssum = st.s.x + st.s.y;
+            float v = ssum * ex2_approx(__fmul_rn(st.R - m_slice, cx.c2));
+            if (!(ssum > 0.0f)) v = 0.0f;
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
             if ((tid & 31) == 0) bs.redf[tid >> 5] = v;
@@ -845,10 +925,6 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         }
         return;
     }
-    if (!A.segment_mode && n > cx.k_eff) {
-        compact_to_k(cx, cx.k_eff);
-        n = cx.k_eff;
-    }
     dropped |= bs.dropped;
     uint64_t* cand = cx.cand;
     unsigned long long* qbuf = reinterpret_cast<unsigned long long*>(smem + L.tiles);  // tiles are idle now
@@ -872,9 +948,112 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         return;
     }
 
+    // Gather the entries that can still matter: alive and, when this CTA streamed the whole
+    // row itself, not below the final lane-maxima bound.
+    const uint64_t Qa = cx.minp_on ? __double2ull_ru((double)rp.min_p * 1099511627776.0) : 0ull;
+    const float u = A.uniforms ? A.uniforms[row] : 0.0f;
+    uint64_t* sel = reinterpret_cast<uint64_t*>(smem + L.search);  // 256 keys, then 256 masses
+    unsigned long long* selq = reinterpret_cast<unsigned long long*>(sel + kThreads);
+    const bool own_row = (A.mode == kModeFull && A.S == 1);
+    const float tau_f = (own_row && cx.k_eff <= kThreads) ? zkey_to_float(bs.taubits) : -INFINITY;
+    if (tid == 0) bs.nl = 0;
+    cta_sync();
+    for (int i = tid; i < n; i += kThreads) {
+        const uint64_t c = cand[i];
+        if (ck_alive(c) && ck_z(c) >= tau_f) {
+            const int pos = (int)smem_atom_add(&bs.nl, 1u);
+            if (pos < kThreads) sel[pos] = c;
+        }
+    }
+    cta_sync();
+    const int na = bs.nl;
+    if (na <= kThreads) {
+        // ---- small set: one entry per thread, everything by all-pairs comparison (no sort,
+        // no histogram): rank for top-k, mass ahead in rank order for top-p, mass ahead in
+        // index order for the draw.  Sums are exact integers.
+        const bool mine = tid < na;
+        const uint64_t ck = mine ? sel[tid] : 0ull;
+        int rank = 0;
+        for (int j = 0; j < na; ++j) rank += (sel[j] > ck) ? 1 : 0;
+        bool kept = mine && (A.segment_mode || rank < cx.k_eff);
+        uint64_t q = 0;
+        if (kept) {
+            const float x = scaled_shift(ck_z(ck), m_row, inv_T);
+            q = (x < -30.0f) ? 0ull : mass_of(x);
+        }
+        if (rp.top_k <= 0 && dropped) {
+            // survivor limit reached with top-k off: exact only if min-p cuts inside the set
+            uint64_t low = mine ? ck : ~0ull;
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) low = min(low, shfl_xor_u64(low, d));
+            if ((tid & 31) == 0) bs.red64[tid >> 5] = low;
+            cta_sync();
+            for (int w = 0; w < kThreads / 32; ++w) low = min(low, (uint64_t)bs.red64[w]);
+            cta_sync();
+            const float xl = scaled_shift(ck_z(low), m_row, inv_T);
+            const uint64_t ql = (xl < -30.0f) ? 0ull : mass_of(xl);
+            if (!(cx.minp_on && (ql + (ql >> 18) + 4ull < Qa))) {
+                if (tid == 0) {
+                    A.out_token[row] = -1;
+                    A.out_status[row] = BORN_ROW_OVERFLOW;
+                    if (A.out_prob) A.out_prob[row] = 0.0f;
+                    if (A.out_kept_count) A.out_kept_count[row] = 0;
+                }
+                return;
+            }
+        }
+        if (Qa && q < Qa) { kept = false; q = 0; }
+        cta_sync();  // every thread has read sel[] for its rank
+        sel[tid] = kept ? ck : (ck & (uint64_t)kIdxMask);
+        selq[tid] = q;
+        cta_sync();
+        if (rp.top_p > 0.0f && rp.top_p < 1.0f) {
+            uint64_t before = 0;
+            for (int j = 0; j < na; ++j) before += (sel[j] > ck) ? selq[j] : 0ull;
+            const uint64_t S = block_sum_u64(q, bs.red64);
+            uint64_t Tp = __double2ull_rz(__dmul_rn((double)rp.top_p, __ull2double_rn(S)));
+            if (Tp < 1) Tp = 1;
+            if (kept && !(before < Tp)) { kept = false; q = 0; }
+            cta_sync();
+            sel[tid] = kept ? ck : (ck & (uint64_t)kIdxMask);
+            selq[tid] = q;
+            cta_sync();
+        }
+        const uint32_t my_low = (uint32_t)(ck & kIdxMask);  // larger low bits = smaller token index
+        uint64_t pre = 0;
+        for (int j = 0; j < na; ++j) pre += ((uint32_t)(sel[j] & kIdxMask) > my_low) ? selq[j] : 0ull;
+        const uint64_t S = block_sum_u64(q, bs.red64);
+        if (S == 0) {  // cannot happen while the row maximum is finite; never divide by it
+            if (tid == 0) { A.out_token[row] = -1; A.out_status[row] = BORN_ROW_ALL_MASKED; }
+            return;
+        }
+        uint64_t t = __double2ull_rz(__dmul_rn((double)u, __ull2double_rn(S)));
+        if (t > S - 1) t = S - 1;
+        if (kept && pre <= t && t < pre + q) {
+            A.out_token[row] = ck_idx(ck);
+            A.out_status[row] = BORN_ROW_OK;
+            if (A.out_prob) A.out_prob[row] = __double2float_rn(__ddiv_rn(__ull2double_rn(q), __ull2double_rn(S)));
+        }
+        BORN_PROF(6);
+        if (A.out_kept_count || A.out_kept_ids) {
+            if (kept && A.out_kept_ids) {
+                int kr = 0;
+                for (int j = 0; j < na; ++j) kr += (ck_alive(sel[j]) && sel[j] > ck) ? 1 : 0;
+                if (kr < A.kept_stride) A.out_kept_ids[(int64_t)row * A.kept_stride + kr] = ck_idx(ck);
+            }
+            const uint64_t tot = block_sum_u64(kept ? 1ull : 0ull, bs.red64);
+            if (tid == 0 && A.out_kept_count) A.out_kept_count[row] = (int)tot;
+        }
+        return;
+    }
+
+    // ---- large set: radix select / radix threshold searches over the whole buffer
+    if (!A.segment_mode && n > cx.k_eff) {
+        compact_to_k(cx, cx.k_eff);
+        n = cx.k_eff;
+    }
+    dropped |= bs.dropped;
     // fixed-point masses relative to the row maximum
-    uint64_t Qa = 0;
-    if (cx.minp_on) Qa = __double2ull_ru((double)rp.min_p * 1099511627776.0);
     uint64_t low_ck = ~0ull;
     for (int i = tid; i < n; i += kThreads) {
         uint64_t c = cand[i];
@@ -928,7 +1107,6 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     uint64_t part = 0;
     for (int i = tid; i < n; i += kThreads) part += qbuf[i];
     const uint64_t S = block_sum_u64(part, bs.red64);
-    const float u = A.uniforms ? A.uniforms[row] : 0.0f;
     uint64_t t = __double2ull_rz(__dmul_rn((double)u, __ull2double_rn(S)));
     if (t > S - 1) t = S - 1;
     const uint64_t tok64 = block_radix_search<false, 24, false>(
@@ -943,6 +1121,12 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         }
     }
     BORN_PROF(6);
+#ifdef BORN_PROFILE
+    if (A.prof && tid == 0) {
+        unsigned long long* pr = A.prof + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 16;
+        pr[11] = bs.pf_search; pr[12] = bs.pf_pair; pr[13] = bs.pf_calls;
+    }
+#endif
     if (A.out_kept_count || A.out_kept_ids) {
         int alive = 0;
         for (int i = tid; i < n; i += kThreads) {

@@ -217,6 +217,17 @@ __device__ __forceinline__ bool mbar_wait_or_abort(uint64_t* bar, uint32_t parit
 // (checked between probes by the whole warp, so the answer is warp-uniform), 0 on a timeout.
 __device__ __forceinline__ int mbar_wait_or_event(uint64_t* bar, uint32_t parity, const volatile int* event) {
     const uint32_t addr = smem_u32(bar);
+    {   // the tile is usually there already: one probe, no votes
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return 1;
+    }
     unsigned long long t0 = 0;
     for (uint32_t it = 0; it < kMbarSpinLimit; ++it) {
         uint32_t ok;

@@ -32,6 +32,8 @@ enum : int { kModeFull = 0, kModeLocal = 1, kModeMerge = 2 };
 
 constexpr int kBlockThreads = kThreads + 32;  // compute threads + the producer warp
 constexpr int kHistBuckets = 128;             // history ids are bucketed by tile
+constexpr int kPrivPerLane = 4;               // candidate slots every compute thread owns
+constexpr int kPrivCap = kPrivPerLane * kThreads;
 
 struct RecordHdr {  // 32 bytes, precedes the entries of a slice / shard record
     float m;        // maximum of the slice (NaN if a NaN was seen)
@@ -78,7 +80,7 @@ struct SampleKernelArgs {
 #define BORN_PROF(i)                                                                                   \
     do {                                                                                               \
         if (A.prof && threadIdx.x == 0)                                                                \
-            A.prof[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 16 + (i)] = (unsigned long long)clock64(); \
+            A.prof[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 32 + (i)] = (unsigned long long)clock64(); \
     } while (0)
 #define BORN_PROF_T0() long long pt0_ = clock64()
 #define BORN_PROF_ACC(var) do { long long pt1_ = clock64(); (var) += pt1_ - pt0_; pt0_ = pt1_; } while (0)
@@ -120,6 +122,7 @@ __host__ __device__ inline SmemLayout smem_layout(int elem_bytes, bool has_mask,
 struct BlockShared {  // static shared state of a CTA
     unsigned long long full_bar[kStages];
     unsigned long long empty_bar[kStages];
+    unsigned long long ready_bar[kStages];  // tile patched by the producer warp (fp32 rows with penalties)
     unsigned long long tau_ck;
     unsigned long long red64[kThreads / 32];
     float redf[kThreads / 32];
@@ -132,7 +135,9 @@ struct BlockShared {  // static shared state of a CTA
     int fail;
     int dropped;
     int nh;
-    int nl, nw;
+    int nl, nw, nsw;
+    int trig;        // fill of the shared area that asks for a compaction
+    int hist_ready;  // the history buckets are built (read by the producer warp)
     int last;
     int hoff[kHistBuckets + 1];
     int hcur[kHistBuckets];
@@ -147,6 +152,9 @@ struct ThreadStats {
     float nRc;  // -R * c2
     float2 s;   // two partial sums of 2^((z - R) * c2) (packed fp32x2 arithmetic)
     float pub;  // largest maximum this thread has published for the min-p prune
+#ifdef BORN_PROFILE
+    long long pf_hit;
+#endif
 };
 
 struct Ctx {  // per-CTA pointers and row constants, all block-uniform
@@ -160,53 +168,103 @@ struct Ctx {  // per-CTA pointers and row constants, all block-uniform
     BlockShared* bs;
     int k_eff;
     int trigger;
+    int psize;  // entries of the buffer that are thread-private slots (kPrivCap while streaming, 0 after)
     int hshift;  // history bucket of tile c is c >> hshift
     float c2;
     float delta_minp;
     bool minp_on;
     born_row_params rp;
+#ifdef BORN_PROFILE
+    unsigned long long* pr;  // this CTA's profiling record
+#endif
 };
 
-// Keep the k best entries of cand[0..count) (exact, by rank key) and raise tau.  Returns
-// true when the buffer was rearranged (every warp must then give up its slot block).
-__device__ bool compact_to_k(Ctx& cx, int k) {
+// The candidate buffer.  The first cx.psize entries are private slots: thread t owns entries
+// t, t+256, t+512, t+768 and fills them in that order, counting in a register (no atomic, no
+// waiting for a slot number); the rest is a shared area filled through the atomic counter
+// bs.count, used by lanes whose private slots are full.  A thread that walks the buffer as
+// i = tid, tid+256, ... meets exactly its own private slots, so it can tell the filled ones
+// from its register.  Unfilled slots read as dead entries (value part 0, unique low bits).
+// Private slots are not filtered by the exact rank-key threshold when they are written (the
+// hot path only compares values); what does not belong is dropped when the buffer is read.
+struct LanePriv {
+    int pcnt;  // filled private slots of this thread
+};
+
+// Private slots hold the raw pair (float bits << 32 | token index) exactly as the hot loop
+// stored it; the rank key is formed when a slot is read (cold paths only).
+__device__ __forceinline__ uint64_t raw_to_ck(uint64_t raw) {
+    return make_ck(__uint_as_float((uint32_t)(raw >> 32)), (int)(uint32_t)raw);
+}
+__device__ __forceinline__ uint64_t slot_key(const Ctx& cx, const LanePriv& lp, int i, int scount) {
+    if (i < cx.psize) return ((i >> 8) < lp.pcnt) ? raw_to_ck(cx.cand[i]) : (uint64_t)i;
+    return (i - cx.psize < scount) ? cx.cand[i] : (uint64_t)i;
+}
+
+// Keep the k best entries of the buffer (exact, by rank key) and raise tau.  Private entries
+// stay with their owners, the shared area is compacted in place.  Returns true when entries
+// were dropped.
+__device__ bool compact_to_k(Ctx& cx, LanePriv& lp, int k) {
     BlockShared& bs = *cx.bs;
     const int tid = threadIdx.x;
     cta_sync();
-    int n = bs.count;
-    if (n > kCandCap) n = kCandCap;
-    if (n <= k) return false;
+    const int sc = min(bs.count, kCandCap - cx.psize);
+    if (tid == 0) { bs.nl = 0; bs.nw = 0; bs.nsw = 0; }
+    cta_sync();
+    if (lp.pcnt) smem_red_add(&bs.nl, (uint32_t)lp.pcnt);
+    cta_sync();
+    const int total = bs.nl + sc;
+    cta_sync();
+    if (total <= k) {
+        if (tid == 0 && bs.count > sc) bs.count = sc;  // refused appends only inflated the counter
+        cta_sync();
+        return false;
+    }
     uint64_t* cand = cx.cand;
 #ifdef BORN_PROFILE
     long long pf0 = clock64();
 #endif
-    uint64_t T = block_radix_search<true, 56, true>(
-        n, (unsigned long long)(k - 1), [&](int i) { return cand[i]; }, [&](int) { return 1ull; }, *cx.sc);
+    const uint64_t T = block_radix_search<true, 56, true>(
+        kCandCap, (unsigned long long)(k - 1), [&](int i) { return slot_key(cx, lp, i, sc); },
+        [&](int) { return 1ull; }, *cx.sc);
 #ifdef BORN_PROFILE
     long long pf1 = clock64();
 #endif
+    // private entries: every thread filters its own
+    int np = 0;
+    for (int s = 0; s < lp.pcnt; ++s) {
+        const uint64_t raw = cand[s * kThreads + tid];
+        if (raw_to_ck(raw) >= T) cand[(np++) * kThreads + tid] = raw;
+    }
+    lp.pcnt = np;
+    // shared area: survivors to the front
+    uint64_t* sh = cand + cx.psize;
     if (tid == 0) { bs.nl = 0; bs.nw = 0; }
+    for (int i = tid; i < sc; i += kThreads)
+        if (sh[i] >= T) smem_red_add(&bs.nsw, 1u);
     cta_sync();
-    for (int i = tid; i < n; i += kThreads) {
-        uint64_t c = cand[i];
-        if (i < k) {
+    const int w = bs.nsw;
+    for (int i = tid; i < sc; i += kThreads) {
+        const uint64_t c = sh[i];
+        if (i < w) {
             if (c < T) cx.lslot[smem_atom_add(&bs.nl, 1u)] = (uint16_t)i;
         } else if (c >= T) {
             cx.wpos[smem_atom_add(&bs.nw, 1u)] = (uint16_t)i;
         }
     }
     cta_sync();
-    int nl = bs.nl;
-    for (int j = tid; j < nl; j += kThreads) cand[cx.lslot[j]] = cand[cx.wpos[j]];
+    const int nl = bs.nl;
+    for (int j = tid; j < nl; j += kThreads) sh[cx.lslot[j]] = sh[cx.wpos[j]];
     if (tid == 0) {
-        bs.count = k;
+        bs.count = w;
+        bs.trig = min(max(w + 256, cx.trigger), kCandCap - cx.psize - 64);
         if (ck_alive(T)) {
             bs.tau_ck = T;
             smem_red_max(&bs.taubits, (uint32_t)(T >> 24));
         }
         bs.dropped = 1;
 #ifdef BORN_PROFILE
-        bs.pf_search += pf1 - pf0; bs.pf_pair += clock64() - pf1; bs.pf_calls += 1000000 + n;
+        bs.pf_search += pf1 - pf0; bs.pf_pair += clock64() - pf1; bs.pf_calls += 1000000 + total;
 #endif
     }
     cta_sync();
@@ -296,94 +354,80 @@ __device__ __forceinline__ float group_stats(ThreadStats& st, const float (&v)[V
 // its lanes cannot get buffer space, or when it has finished all its tiles; the buffer is
 // compacted if an event is pending.  Returns true when every warp has finished and no event
 // was pending.
-__device__ bool rendezvous(Ctx& cx) {
+__device__ bool rendezvous(Ctx& cx, LanePriv& lp) {
     BlockShared& bs = *cx.bs;
     cta_sync();
     const int ev = bs.event, dn = bs.done_warps;
     cta_sync();
     if (ev) {
-        compact_to_k(cx, cx.k_eff);
+        compact_to_k(cx, lp, cx.k_eff);
         if (threadIdx.x == 0) bs.event = 0;
         cta_sync();
     }
     return !ev && dn == kThreads / 32;
 }
 
-// Append one entry per offering lane.  Every lane of the warp calls; lanes with an offer
-// take a slot with a shared-memory atomic.  When the buffer is full the whole warp goes to
-// the rendezvous for the compaction and the lanes still holding an offer try again.
-__device__ __forceinline__ void settle_one(Ctx& cx, bool pending, uint64_t ck) {
+// One candidate from the lane that found it: exact rank-key test, then a store into the
+// lane's next private slot -- no atomic, nothing to wait for.  A lane whose private slots are
+// full takes a slot of the shared area with a shared-memory atomic.  Returns false when that
+// area is full too (the caller keeps the element for the retry after the compaction).
+__device__ bool lane_put_shared(Ctx& cx, uint64_t ck) {
+    if (!(ck > cx.bs->tau_ck)) return true;  // cannot be among the k best any more
+    const int scap = kCandCap - cx.psize;
+    const int pos = (int)smem_atom_add(&cx.bs->count, 1u);
+    if (pos < scap) {
+        cx.cand[cx.psize + pos] = ck;
+        if (pos + 1 > cx.bs->trig) cx.bs->event = 1;  // compaction at the next tile boundary
+        return true;
+    }
+    cx.bs->event = 1;
+    return false;
+}
+// The hot-path store: value bits and token index as one 8-byte shared store into the lane's
+// next private slot; only a lane whose slots are full goes through the shared area.
+__device__ __forceinline__ bool lane_put(Ctx& cx, LanePriv& lp, float z, int idx) {
+    if (lp.pcnt < kPrivPerLane && cx.psize) {
+        reinterpret_cast<uint2*>(cx.cand)[lp.pcnt * kThreads + threadIdx.x] = make_uint2((uint32_t)idx, __float_as_uint(z));
+        ++lp.pcnt;
+        return true;
+    }
+    return lane_put_shared(cx, make_ck(z, idx));
+}
+__device__ __forceinline__ bool lane_put_ck(Ctx& cx, LanePriv& lp, uint64_t ck) {
+    // history tokens (cold): straight to the shared area, which holds rank keys
+    (void)lp;
+    return lane_put_shared(cx, ck);
+}
+
+// One offer per lane, called by the whole warp (history tokens): lanes that find the buffer
+// full take the warp to the rendezvous and try again after the compaction.
+__device__ __forceinline__ void settle_one(Ctx& cx, LanePriv& lp, bool pending, uint64_t ck) {
     for (;;) {
-        if (pending) {
-            const int pos = (int)smem_atom_add(&cx.bs->count, 1u);
-            if (pos < kCandCap) {
-                cx.cand[pos] = ck;
-                if (pos + 1 > cx.trigger) cx.bs->event = 1;  // compaction at the next tile boundary
-                pending = false;
-            } else {
-                cx.bs->event = 1;
-            }
-        }
+        if (pending && lane_put_ck(cx, lp, ck)) pending = false;
         if (!__any_sync(0xffffffffu, pending)) break;
-        rendezvous(cx);
-        pending = pending && ck > cx.bs->tau_ck;  // the threshold has risen
+        rendezvous(cx, lp);
     }
 }
 
-// Candidates of one tile for this warp.  `hm` has bit j set when the maximum of this
-// thread's j-th vector group reached tau.  Only the lanes with a flagged group do any work:
-// they read the group again, test its elements exactly (value and rank key), take as many
-// buffer slots as they have hits with ONE shared-memory atomic and store the entries.  The
-// warp meets again with a single vote; if some lane found the buffer full, the warp goes to
-// the rendezvous for the compaction and that lane tries again.
-template <typename T, bool kHasMask>
-__device__ __forceinline__ void warp_collect(Ctx& cx, const T* tile, const uint32_t* smask, uint32_t hm, int c0,
-                                             int nvalid, float tau) {
+// Rare path: some lane found the buffer full.  The warp goes to the rendezvous for the
+// compaction; the lanes then offer the elements they kept back (bit j*VEC+i of `ovf`), read
+// again from the tile the warp still holds.
+template <typename T>
+__device__ void warp_retry(Ctx& cx, LanePriv& lp, const T* tile, uint32_t ovf, int c0) {
     constexpr int VEC = VecOf<T>::n;
-    constexpr int ITER = kChunk / VEC / kThreads;
-    uint32_t em = 0;  // element-level hits: bit j*VEC+i
-    if (hm) {
-        const uint64_t tau_ck = cx.bs->tau_ck;
-#pragma unroll
-        for (int j = 0; j < ITER; ++j) {
-            if (hm & (1u << j)) {
-                float v[VEC];
-                const int g = threadIdx.x + kThreads * j;
-                load_group<T, kHasMask>(tile, smask, g, nvalid, v);
-#pragma unroll
-                for (int i = 0; i < VEC; ++i)
-                    if (v[i] >= tau && make_ck(v[i], c0 + g * VEC + i) > tau_ck) em |= 1u << (j * VEC + i);
-            }
+    while (__any_sync(0xffffffffu, ovf != 0)) {
+        rendezvous(cx, lp);
+        uint32_t m = ovf;
+        ovf = 0;
+        while (m) {
+            const int b = __ffs(m) - 1;
+            m &= m - 1;
+            const int e = (threadIdx.x + kThreads * (b / VEC)) * VEC + (b % VEC);
+            float z;
+            if constexpr (sizeof(T) == 4) z = reinterpret_cast<const float*>(tile)[e];
+            else z = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(tile)[e]);
+            if (!lane_put(cx, lp, z, c0 + e)) ovf |= 1u << b;
         }
-    }
-    bool pending = em != 0;
-    for (;;) {
-        if (pending) {
-            const int cnt = __popc(em);
-            const int pos = (int)smem_atom_add(&cx.bs->count, (uint32_t)cnt);
-            if (pos + cnt <= kCandCap) {
-                int p = pos;
-                uint32_t m = em;
-                while (m) {
-                    const int b = __ffs(m) - 1;
-                    m &= m - 1;
-                    const int e = (threadIdx.x + kThreads * (b / VEC)) * VEC + (b % VEC);
-                    float z;
-                    if constexpr (sizeof(T) == 4) z = reinterpret_cast<const float*>(tile)[e];
-                    else z = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(tile)[e]);
-                    cx.cand[p++] = make_ck(z, c0 + e);
-                }
-                if (pos + cnt > cx.trigger) cx.bs->event = 1;  // compaction at the next tile boundary
-                pending = false;
-            } else {
-                // no room: the compaction reads the whole buffer, so the slots up to its end
-                // must not keep stale entries (dead entries: value part 0, unique low bits)
-                for (int p = pos; p < kCandCap; ++p) cx.cand[p] = (uint64_t)p;
-                cx.bs->event = 1;
-            }
-        }
-        if (!__any_sync(0xffffffffu, pending)) break;
-        rendezvous(cx);
     }
 }
 
@@ -405,7 +449,7 @@ __device__ __forceinline__ float penalise(const born_row_params& rp, float z, in
 // (-inf) and its new value goes through the statistics and the candidate test on its own.
 // Entries are bucketed by tile and carry their multiplicity (repeats carry 0).
 template <typename T, bool kHasMask, bool kLse>
-__device__ __forceinline__ void warp_patch(Ctx& cx, ThreadStats& st, T* tile, const uint32_t* smask,
+__device__ __forceinline__ void warp_patch(Ctx& cx, ThreadStats& st, LanePriv& lp, T* tile, const uint32_t* smask,
                                            int c, int c0, int nvalid, float tau, bool stats, bool collect,
                                            int replay) {
     // replay: 0 = patch, take statistics and collect in one go; 1 = patch and take statistics,
@@ -448,7 +492,7 @@ __device__ __forceinline__ void warp_patch(Ctx& cx, ThreadStats& st, T* tile, co
             uint64_t ck = 0;
             bool pred = first && z >= tau;
             if (pred) { ck = make_ck(z, id); pred = ck > cx.bs->tau_ck; }
-            settle_one(cx, pred, ck);
+            settle_one(cx, lp, pred, ck);
         }
     }
     if (wrote) fence_proxy_async();
@@ -474,23 +518,34 @@ __device__ __forceinline__ void publish_max(Ctx& cx, ThreadStats& st) {
 // elements, one pass over the thread's vector groups for the statistics and a
 // one-compare-per-group candidate test, then at most one collection step.
 template <typename T, bool kHasMask, bool kLse>
-__device__ __forceinline__ void process_tile(Ctx& cx, ThreadStats& st, T* tile, const uint32_t* smask,
+__device__ __forceinline__ void process_tile(Ctx& cx, ThreadStats& st, LanePriv& lp, T* tile, const uint32_t* smask,
                                              int c, int c0, int nvalid, bool tile_hist, bool stats, bool collect,
                                              int replay = 0) {
     constexpr int VEC = VecOf<T>::n;
     constexpr int ITER = kChunk / VEC / kThreads;
     const float tau = current_tau(cx);
-    if (tile_hist) warp_patch<T, kHasMask, kLse>(cx, st, tile, smask, c, c0, nvalid, tau, stats, collect, replay);
-    uint32_t hm = 0;
+    if (tile_hist) warp_patch<T, kHasMask, kLse>(cx, st, lp, tile, smask, c, c0, nvalid, tau, stats, collect, replay);
+    uint32_t ovf = 0;  // elements that found the buffer full (bit j*VEC+i)
 #pragma unroll
     for (int j = 0; j < ITER; ++j) {
         float v[VEC];
-        load_group<T, kHasMask>(tile, smask, threadIdx.x + kThreads * j, nvalid, v);
+        const int g = threadIdx.x + kThreads * j;
+        load_group<T, kHasMask>(tile, smask, g, nvalid, v);
         const float m4 = group_stats<kLse, VEC>(st, v, cx.c2, stats);
-        if (m4 >= tau) hm |= 1u << j;
+#ifdef BORN_PROFILE
+        const long long ph0 = clock64();
+#endif
+        if (collect && m4 >= tau) {  // rare per lane: the hits are handled where they are found
+#pragma unroll
+            for (int i = 0; i < VEC; ++i)
+                if (v[i] >= tau && !lane_put(cx, lp, v[i], c0 + g * VEC + i)) ovf |= 1u << (j * VEC + i);
+        }
+        __syncwarp();  // bring the lanes back together here, not at the end of the tile
+#ifdef BORN_PROFILE
+        st.pf_hit += clock64() - ph0;
+#endif
     }
-    if (collect && __any_sync(0xffffffffu, hm != 0))
-        warp_collect<T, kHasMask>(cx, tile, smask, hm, c0, nvalid, tau);
+    if (collect && __any_sync(0xffffffffu, ovf != 0)) warp_retry<T>(cx, lp, tile, ovf, c0);
 }
 
 // Lane-maxima bound.  Every lane's running maximum belongs to a different token, so the
@@ -500,7 +555,7 @@ __device__ __forceinline__ void process_tile(Ctx& cx, ThreadStats& st, T* tile, 
 // It tracks the true k-th value closely because the best k tokens rarely share a lane.
 // Each warp publishes its value; tau is raised to the minimum over the warps (values of
 // warps that have not caught up are older, hence lower, hence still valid).
-__device__ __forceinline__ void publish_lane_bound(Ctx& cx, const ThreadStats& st) {
+__device__ void publish_lane_bound(Ctx& cx, const ThreadStats& st) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float v = (st.mx == st.mx) ? st.mx : -INFINITY;
     uint32_t key = zkey(v);
@@ -523,6 +578,10 @@ __device__ __forceinline__ void publish_lane_bound(Ctx& cx, const ThreadStats& s
         kj = __shfl_sync(0xffffffffu, key, j - 1);
     }
     const float w = zkey_to_float(kj);
+    if (cx.k_eff == 1) {  // any single token is a bound for k = 1: take the best one
+        if (lane == 0 && w > -FLT_MAX) smem_red_max(&cx.bs->taubits, kj);
+        return;
+    }
     if (lane == 0) *reinterpret_cast<volatile float*>(&cx.bs->wbound[warp]) = w;
     __syncwarp();
     float m = *reinterpret_cast<const volatile float*>(&cx.bs->wbound[0]);
@@ -627,6 +686,8 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         bs.maxbits = zkey(-INFINITY);
         bs.count = 0;
         bs.event = 0;
+        bs.hist_ready = 0;
+        bs.trig = kCandCap;
 #ifdef BORN_PROFILE
         bs.pf_search = bs.pf_pair = bs.pf_calls = 0;
 #endif
@@ -639,30 +700,93 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             for (int s = 0; s < kStages; ++s) {
                 mbar_init(reinterpret_cast<uint64_t*>(&bs.full_bar[s]), 1);
                 mbar_init(reinterpret_cast<uint64_t*>(&bs.empty_bar[s]), kThreads / 32);
+                mbar_init(reinterpret_cast<uint64_t*>(&bs.ready_bar[s]), 1);
             }
             mbar_fence_init();
         }
     }
     __syncthreads();  // the only barrier all 288 threads share
 
+    // Row parameters (both sides of the CTA need them).
+    const born_row_params rp0 = A.row_params ? A.row_params[row] : A.params;
+    const bool greedy0 = (rp0.flags & BORN_FLAG_GREEDY) || rp0.temperature == 0.0f;
+    (void)greedy0;
+    const bool pen_on = (rp0.repetition_penalty != 1.0f && rp0.repetition_penalty != 0.0f) ||
+                        rp0.frequency_penalty != 0.0f || rp0.presence_penalty != 0.0f;
+    // fp32 tiles can hold a penalised logit, so for them the otherwise idle producer warp
+    // applies the history penalties in place before it releases the tile to the compute warps
+    const bool producer_patches = hist_arg && pen_on && sizeof(T) == 4 && tma_l && A.mode != kModeMerge;
+    int hshift0 = 0;
+    while ((nchunks >> hshift0) > kHistBuckets) ++hshift0;
+
     if (tid >= kThreads) {
         // ------------------------------------------------------------------ producer warp
-        if (tid == kThreads && use_bar) {
-            for (int c = 0; c < nchunks; ++c) {
-                const int st = c % kStages;
+        if (!use_bar) return;
+        const int lane = tid - kThreads;
+        const int lag = 2;  // a tile is patched this many iterations after it was issued
+        if (producer_patches) {       // wait (bounded) for the compute threads to bucket the history
+            unsigned long long t0 = global_timer_ns();
+            while (!*reinterpret_cast<const volatile int*>(&bs.hist_ready)) {
+                if (*reinterpret_cast<const volatile int*>(&bs.fail)) return;
+                if (global_timer_ns() - t0 > kMbarTimeoutNs) { bs.fail = 1; return; }
+            }
+        }
+        const int32_t* hlist = reinterpret_cast<const int32_t*>(smem + L.hist);
+        const uint16_t* hcnt = reinterpret_cast<const uint16_t*>(smem + L.hist + kHistCap * 8);
+        const int iters = nchunks + (producer_patches ? lag : 0);
+        for (int it = 0; it < iters; ++it) {
+            int stop = 0;
+            if (it < nchunks && lane == 0) {
+                const int c = it, st = c % kStages;
                 if (c >= kStages) {
-                    // the compute threads hand the tile back when they are done with it
+                    // the compute warps hand the tile back when they are done with it
                     if (!mbar_wait_or_abort(reinterpret_cast<uint64_t*>(&bs.empty_bar[st]),
                                             (uint32_t)(c / kStages - 1) & 1u, &bs.fail))
-                        break;
+                        stop = 1;
                 }
-                const int n = min(kChunk, nelem - c * kChunk);
-                const uint32_t bytes_l = tma_l ? (((uint32_t)n * (uint32_t)sizeof(T) + 15u) & ~15u) : 0u;
-                const uint32_t bytes_m = tma_m ? ((((uint32_t)(n + 31) >> 5) * 4u + 15u) & ~15u) : 0u;
-                uint64_t* bar = reinterpret_cast<uint64_t*>(&bs.full_bar[st]);
-                mbar_expect_tx(bar, bytes_l + bytes_m);
-                if (tma_l) bulk_load(tiles + (size_t)st * kChunk, grow + (size_t)c * kChunk, bytes_l, bar);
-                if (tma_m) bulk_load(masks + st * (kChunk / 32), gmask + c * (kChunk / 32), bytes_m, bar);
+                if (!stop) {
+                    const int n = min(kChunk, nelem - c * kChunk);
+                    const uint32_t bytes_l = tma_l ? (((uint32_t)n * (uint32_t)sizeof(T) + 15u) & ~15u) : 0u;
+                    const uint32_t bytes_m = tma_m ? ((((uint32_t)(n + 31) >> 5) * 4u + 15u) & ~15u) : 0u;
+                    uint64_t* bar = reinterpret_cast<uint64_t*>(&bs.full_bar[st]);
+                    mbar_expect_tx(bar, bytes_l + bytes_m);
+                    if (tma_l) bulk_load(tiles + (size_t)st * kChunk, grow + (size_t)c * kChunk, bytes_l, bar);
+                    if (tma_m) bulk_load(masks + st * (kChunk / 32), gmask + c * (kChunk / 32), bytes_m, bar);
+                }
+            }
+            if (__any_sync(0xffffffffu, stop)) break;
+            if (producer_patches && it >= lag) {
+                const int c = it - lag, st = c % kStages;
+                const bool ok = mbar_wait_or_abort(reinterpret_cast<uint64_t*>(&bs.full_bar[st]),
+                                                   (uint32_t)(c / kStages) & 1u, &bs.fail);
+                if (!__all_sync(0xffffffffu, ok)) {
+                    bs.fail = 1;
+                    break;
+                }
+                float* tile = reinterpret_cast<float*>(tiles) + (size_t)st * kChunk;
+                const int c0 = e_begin + c * kChunk, nvalid = min(kChunk, e_end - c0);
+                const int b = c >> hshift0;
+                const int lo = bs.hoff[b], hi = bs.hoff[b + 1];
+                bool wrote = false;
+                for (int i = lo + lane; i < hi; i += 32) {
+                    const int cnt = hcnt[i];
+                    const int off = hlist[i] - c0;
+                    if (cnt > 0 && off >= 0 && off < nvalid) {
+                        float z = tile[off];
+                        if (rp0.repetition_penalty != 1.0f && rp0.repetition_penalty != 0.0f)
+                            z = (z > 0.0f) ? __fdiv_rn(z, rp0.repetition_penalty) : __fmul_rn(z, rp0.repetition_penalty);
+                        if (rp0.frequency_penalty != 0.0f || rp0.presence_penalty != 0.0f) {
+                            float pen = __fmul_rn(rp0.frequency_penalty, (float)cnt);
+                            pen = __fadd_rn(pen, rp0.presence_penalty);
+                            z = __fsub_rn(z, pen);
+                        }
+                        tile[off] = z;
+                        wrote = true;
+                    }
+                }
+                if (wrote) fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(&bs.ready_bar[st]));
             }
         }
         return;
@@ -678,7 +802,10 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     cx.hval = reinterpret_cast<float*>(smem + L.hist + kHistCap * 4);
     cx.hcnt = reinterpret_cast<uint16_t*>(smem + L.hist + kHistCap * 8);
     cx.bs = &bs;
-    cx.rp = A.row_params ? A.row_params[row] : A.params;
+#ifdef BORN_PROFILE
+    cx.pr = A.prof ? A.prof + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 32 : nullptr;
+#endif
+    cx.rp = rp0;
     const born_row_params& rp = cx.rp;
     const bool greedy = (rp.flags & BORN_FLAG_GREEDY) || rp.temperature == 0.0f;
     const float inv_T = greedy ? 1.0f : __fdiv_rn(1.0f, rp.temperature);
@@ -686,10 +813,14 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     cx.minp_on = !greedy && rp.min_p > 0.0f;
     cx.delta_minp = cx.minp_on ? (__logf(rp.min_p) - 0.05f) * rp.temperature : 0.0f;
     cx.k_eff = greedy ? 1 : (rp.top_k > 0 ? min(rp.top_k, kMaxK) : kMaxK);
-    cx.trigger = min(max(2 * cx.k_eff, 512), kCandCap - 512);
+    cx.psize = (A.mode == kModeMerge) ? 0 : kPrivCap;
+    cx.trigger = min(max(2 * cx.k_eff, 512), kCandCap - kPrivCap - 128);  // fill of the shared area that asks for a compaction
+    if (tid == 0) bs.trig = cx.trigger;
     cx.hshift = 0;
     while ((nchunks >> cx.hshift) > kHistBuckets) ++cx.hshift;
 
+    LanePriv lp;
+    lp.pcnt = 0;
     BORN_PROF(0);
     float m_row = -INFINITY;  // maximum over the whole row (known after the merge)
     float lse_sum = 0.0f;     // sum of 2^((z - m_row) * c2) over the whole row
@@ -698,13 +829,14 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     if (A.mode != kModeMerge) {
         // ------------------------------------------------------------------ streaming pass
         bool has_hist = false;
-        if (hist_arg) {
-            const bool pen_on = (rp.repetition_penalty != 1.0f && rp.repetition_penalty != 0.0f) ||
-                                rp.frequency_penalty != 0.0f || rp.presence_penalty != 0.0f;
-            if (pen_on) {
-                int len = A.history_len ? A.history_len[row] : A.history_stride;
-                len = max(0, min(min(len, A.history_stride), kHistCap));
-                has_hist = bucket_history(cx, A.history + (int64_t)row * A.history_stride, len, e_begin, e_end) > 0;
+        if (hist_arg && pen_on) {
+            int len = A.history_len ? A.history_len[row] : A.history_stride;
+            len = max(0, min(min(len, A.history_stride), kHistCap));
+            const int nh = bucket_history(cx, A.history + (int64_t)row * A.history_stride, len, e_begin, e_end);
+            has_hist = nh > 0 && !producer_patches;  // otherwise the tiles arrive patched
+            if (producer_patches && tid == 0) {
+                __threadfence_block();
+                *reinterpret_cast<volatile int*>(&bs.hist_ready) = 1;
             }
         }
 
@@ -715,6 +847,9 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         st.nRc = 1e30f * cx.c2;
         st.s = make_float2(0.0f, 0.0f);
         st.pub = -INFINITY;
+#ifdef BORN_PROFILE
+        st.pf_hit = 0;
+#endif
 
         // Warps stream their share of every tile on their own: they wait for the tile's bulk
         // copy, work on the vector groups they own, and hand the tile back with one mbarrier
@@ -731,16 +866,16 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             const int nvalid = min(kChunk, e_end - c0);
             T* tile = tiles + (size_t)stg * kChunk;
             const uint32_t* smask = tma_m ? masks + stg * (kChunk / 32) : gmask + c * (kChunk / 32);
-            if (c > 0 && *reinterpret_cast<const volatile int*>(&bs.event)) rendezvous(cx);
+            if (c > 0 && *reinterpret_cast<const volatile int*>(&bs.event)) rendezvous(cx, lp);
             BORN_PROF_ACC(pa_rdv);
             if (use_bar && !failed) {
                 // wait for the tile; a warp parked here must still answer a rendezvous, or the
                 // warp that called it (and holds an older tile) would never hand that tile back
                 for (;;) {
-                    const int w = mbar_wait_or_event(reinterpret_cast<uint64_t*>(&bs.full_bar[stg]),
+                    const int w = mbar_wait_or_event(reinterpret_cast<uint64_t*>(producer_patches ? &bs.ready_bar[stg] : &bs.full_bar[stg]),
                                                      (uint32_t)(c / kStages) & 1u, &bs.event);
                     if (w == 1) break;
-                    if (w == 2 && c > 0) { rendezvous(cx); continue; }
+                    if (w == 2 && c > 0) { rendezvous(cx, lp); continue; }
                     if (w == 2) continue;  // before the bootstrap nobody can have raised an event
                     bs.fail = 1;
                     failed = true;
@@ -763,11 +898,11 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
                 if (c == 0) {
                     // statistics of the first tile, then the threshold bootstrap (block-wide),
                     // then its candidates under the new threshold
-                    process_tile<T, kHasMask, kLse>(cx, st, tile, smask, 0, c0, nvalid, tile_hist, true, false, 1);
+                    process_tile<T, kHasMask, kLse>(cx, st, lp, tile, smask, 0, c0, nvalid, tile_hist, true, false, 1);
                     bootstrap_threshold(cx, st);
-                    process_tile<T, kHasMask, kLse>(cx, st, tile, smask, 0, c0, nvalid, tile_hist, false, true, 2);
+                    process_tile<T, kHasMask, kLse>(cx, st, lp, tile, smask, 0, c0, nvalid, tile_hist, false, true, 2);
                 } else {
-                    process_tile<T, kHasMask, kLse>(cx, st, tile, smask, c, c0, nvalid, tile_hist, true, true);
+                    process_tile<T, kHasMask, kLse>(cx, st, lp, tile, smask, c, c0, nvalid, tile_hist, true, true);
                 }
                 if (cx.minp_on) publish_max(cx, st);  // running maximum for the min-p prune
                 if (cx.k_eff <= kThreads) {
@@ -789,12 +924,16 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         if (cx.k_eff <= kThreads && !failed && nchunks > 0) publish_lane_bound(cx, st);
         __syncwarp();
         if (lane == 0) smem_red_add(&bs.done_warps, 1u);
-        while (!rendezvous(cx)) { }
+        while (!rendezvous(cx, lp)) { }
         BORN_PROF(3);
 #ifdef BORN_PROFILE
         if (A.prof && tid == 0) {
-            unsigned long long* pr = A.prof + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 16;
+            unsigned long long* pr = A.prof + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 32;
             pr[8] = pa_wait; pr[9] = pa_rdv; pr[10] = pa_proc;
+        }
+        if (A.prof && lane == 0) {
+            unsigned long long* pr = A.prof + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 32;
+            pr[16 + (tid >> 5)] = pa_proc; pr[24 + (tid >> 5)] = st.pf_hit;
         }
 #endif
         if (bs.fail) {
@@ -814,7 +953,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             return;
         }
         const bool own_row = (A.mode == kModeFull && A.S == 1);
-        if (!own_row) compact_to_k(cx, cx.k_eff);  // records hold at most k entries
+        if (!own_row) compact_to_k(cx, lp, cx.k_eff);  // records hold at most k entries
         cta_sync();
 
         // slice statistics
@@ -849,12 +988,19 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         } else {
             // leave the record, then take a ticket; only the last CTA of the row goes on
             uint8_t* rec = A.records + (int64_t)row * A.rec_row_stride + (int64_t)slice * A.rec_slice_stride;
-            const int n = min(bs.count, cx.k_eff);
             uint64_t* ent = reinterpret_cast<uint64_t*>(rec + kRecordHdrBytes);
-            for (int i = tid; i < n; i += kThreads) {
-                const uint64_t e = cx.cand[i];
-                ent[i] = ck_alive(e) ? e - (uint64_t)A.idx_offset : 0ull;
+            const int sc = min(bs.count, kCandCap - cx.psize);
+            if (tid == 0) bs.nl = 0;
+            cta_sync();
+            for (int i = tid; i < kCandCap; i += kThreads) {
+                const uint64_t e = slot_key(cx, lp, i, sc);
+                if (ck_alive(e)) {
+                    const int pos = (int)smem_atom_add(&bs.nl, 1u);
+                    if (pos < cx.k_eff) ent[pos] = e - (uint64_t)A.idx_offset;
+                }
             }
+            cta_sync();
+            const int n = min(bs.nl, cx.k_eff);
             if (tid == 0) {
                 RecordHdr h;
                 h.m = m_slice; h.lse_s = s_slice; h.count = (uint32_t)n; h.flags = (uint32_t)bs.dropped;
@@ -879,6 +1025,8 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     if (A.mode == kModeMerge || A.S > 1) {
         cta_sync();
         if (tid == 0) bs.count = 0;
+        lp.pcnt = 0;
+        cx.psize = 0;  // the whole buffer is one shared area from here on
         cta_sync();
         m_row = -INFINITY;
         for (int s = 0; s < A.S; ++s) {
@@ -892,7 +1040,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             const int cnt = (int)__ldcg(reinterpret_cast<const uint32_t*>(rec) + 2);
             dropped |= (int)(__ldcg(reinterpret_cast<const uint32_t*>(rec) + 3) & 1u);
             if (kLse && ss_ > 0.0f) lse_sum += ss_ * ex2_approx(__fmul_rn(ms_ - m_row, cx.c2));
-            if (!A.segment_mode && bs.count + cnt > kCandCap) compact_to_k(cx, cx.k_eff);
+            if (!A.segment_mode && bs.count + cnt > kCandCap) compact_to_k(cx, lp, cx.k_eff);
             const int base = bs.count;
             const unsigned long long* ent = reinterpret_cast<const unsigned long long*>(rec + kRecordHdrBytes);
             for (int i = tid; i < cnt && base + i < kCandCap; i += kThreads) {
@@ -908,11 +1056,13 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     // ------------------------------------------------------------- selection and draw
     cta_sync();
     BORN_PROF(5);
-    int n = min(bs.count, kCandCap);
+    const int sc_fin = min(bs.count, kCandCap - cx.psize);  // filled part of the shared area
+    int n = kCandCap;                                      // walk the whole buffer; unfilled slots read as dead
+    auto ent_at = [&](int i) { return slot_key(cx, lp, i, sc_fin); };
     int status = BORN_ROW_OK;
     if (m_row != m_row) status = BORN_ROW_NAN;
     else if (m_row == INFINITY) status = BORN_ROW_POS_INF;
-    else if (m_row == -INFINITY || n == 0) status = BORN_ROW_ALL_MASKED;
+    else if (m_row == -INFINITY) status = BORN_ROW_ALL_MASKED;
     else if (!greedy && rp.top_k > kMaxK) status = BORN_ROW_OVERFLOW;
     if (kLse && A.out_lse && tid == 0)
         A.out_lse[row] = (status == BORN_ROW_OK) ? m_row * inv_T + __log2f(lse_sum) * 0.69314718f : NAN;
@@ -931,7 +1081,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
 
     if (greedy) {
         uint64_t best = 0;
-        for (int i = tid; i < n; i += kThreads) best = max(best, cand[i]);
+        for (int i = tid; i < n; i += kThreads) best = max(best, ent_at(i));
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) best = max(best, shfl_xor_u64(best, d));
         if ((tid & 31) == 0) bs.red64[tid >> 5] = best;
@@ -959,7 +1109,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     if (tid == 0) bs.nl = 0;
     cta_sync();
     for (int i = tid; i < n; i += kThreads) {
-        const uint64_t c = cand[i];
+        const uint64_t c = ent_at(i);
         if (ck_alive(c) && ck_z(c) >= tau_f) {
             const int pos = (int)smem_atom_add(&bs.nl, 1u);
             if (pos < kThreads) sel[pos] = c;
@@ -1047,12 +1197,24 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         return;
     }
 
-    // ---- large set: radix select / radix threshold searches over the whole buffer
-    if (!A.segment_mode && n > cx.k_eff) {
-        compact_to_k(cx, cx.k_eff);
-        n = cx.k_eff;
-    }
+    // ---- large set: radix select, then radix threshold searches over a flat copy
+    if (!A.segment_mode) compact_to_k(cx, lp, cx.k_eff);
     dropped |= bs.dropped;
+    {
+        // flatten the surviving entries (private slots and shared area) into the idle tiles
+        const int sc2 = min(bs.count, kCandCap - cx.psize);
+        uint64_t* flat = reinterpret_cast<uint64_t*>(smem + L.tiles);
+        if (tid == 0) bs.nl = 0;
+        cta_sync();
+        for (int i = tid; i < kCandCap; i += kThreads) {
+            const uint64_t e = slot_key(cx, lp, i, sc2);
+            if (ck_alive(e)) flat[smem_atom_add(&bs.nl, 1u)] = e;
+        }
+        cta_sync();
+        n = bs.nl;
+        cand = flat;
+        qbuf = reinterpret_cast<unsigned long long*>(flat + kCandCap);
+    }
     // fixed-point masses relative to the row maximum
     uint64_t low_ck = ~0ull;
     for (int i = tid; i < n; i += kThreads) {
@@ -1123,8 +1285,8 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     BORN_PROF(6);
 #ifdef BORN_PROFILE
     if (A.prof && tid == 0) {
-        unsigned long long* pr = A.prof + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 16;
-        pr[11] = bs.pf_search; pr[12] = bs.pf_pair; pr[13] = bs.pf_calls;
+        unsigned long long* pr = A.prof + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 32;
+        pr[11] = bs.pf_search; pr[12] = bs.pf_pair; pr[13] = bs.pf_calls; pr[15] = (unsigned long long)n;
     }
 #endif
     if (A.out_kept_count || A.out_kept_ids) {

@@ -4,7 +4,7 @@
 // Work decomposition.  A row of the [batch, vocab] logits is cut into S contiguous slices;
 // CTA (slice, row) streams its slice from HBM exactly once.  One producer warp keeps a ring
 // of kStages shared-memory tiles full with 1-D bulk copies (TMA, non-multicast) that
-// complete on mbarriers; 256 compute threads read the tiles with 128-bit shared loads and
+// complete on mbarriers; kThreads compute threads read the tiles with 128-bit shared loads and
 // hand each tile back through a second mbarrier.  While streaming the compute threads keep
 //   * the running maximum (NaN-propagating) and an online log-sum-exp per thread,
 //   * a candidate buffer of rank keys that still can be among the k best.
@@ -33,6 +33,7 @@ enum : int { kModeFull = 0, kModeLocal = 1, kModeMerge = 2 };
 constexpr int kBlockThreads = kThreads + 32;  // compute threads + the producer warp
 constexpr int kHistBuckets = 128;             // history ids are bucketed by tile
 constexpr int kPrivPerLane = 4;               // candidate slots every compute thread owns
+constexpr int kSmallSet = 256;                // candidate sets up to this size are finished by all-pairs ranking
 constexpr int kPrivCap = kPrivPerLane * kThreads;
 
 struct RecordHdr {  // 32 bytes, precedes the entries of a slice / shard record
@@ -111,7 +112,7 @@ __host__ __device__ inline SmemLayout smem_layout(int elem_bytes, bool has_mask,
     L.search = off;
     L.pairs = off;
     {
-        const int a = (int)((sizeof(SearchScratch) + 127) / 128 * 128), b = kMaxK * 2 * 2;
+        const int a = (int)((sizeof(SearchScratch) + 127) / 128 * 128), b = kMaxK * 2 * 2;  // also 2 * kSmallSet * 8
         off += a > b ? a : b;
     }
     L.hist = off; off += has_hist ? kHistCap * 10 : 0;  // ids, replay values, multiplicities
@@ -180,10 +181,10 @@ struct Ctx {  // per-CTA pointers and row constants, all block-uniform
 };
 
 // The candidate buffer.  The first cx.psize entries are private slots: thread t owns entries
-// t, t+256, t+512, t+768 and fills them in that order, counting in a register (no atomic, no
+// t, t+kThreads, ... and fills them in that order, counting in a register (no atomic, no
 // waiting for a slot number); the rest is a shared area filled through the atomic counter
 // bs.count, used by lanes whose private slots are full.  A thread that walks the buffer as
-// i = tid, tid+256, ... meets exactly its own private slots, so it can tell the filled ones
+// i = tid, tid+kThreads, ... meets exactly its own private slots, so it can tell the filled ones
 // from its register.  Unfilled slots read as dead entries (value part 0, unique low bits).
 // Private slots are not filtered by the exact rank-key threshold when they are written (the
 // hot path only compares values); what does not belong is dropped when the buffer is read.
@@ -197,7 +198,7 @@ __device__ __forceinline__ uint64_t raw_to_ck(uint64_t raw) {
     return make_ck(__uint_as_float((uint32_t)(raw >> 32)), (int)(uint32_t)raw);
 }
 __device__ __forceinline__ uint64_t slot_key(const Ctx& cx, const LanePriv& lp, int i, int scount) {
-    if (i < cx.psize) return ((i >> 8) < lp.pcnt) ? raw_to_ck(cx.cand[i]) : (uint64_t)i;
+    if (i < cx.psize) return ((i / kThreads) < lp.pcnt) ? raw_to_ck(cx.cand[i]) : (uint64_t)i;
     return (i - cx.psize < scount) ? cx.cand[i] : (uint64_t)i;
 }
 
@@ -348,7 +349,7 @@ __device__ __forceinline__ float group_stats(ThreadStats& st, const float (&v)[V
     return m4;
 }
 
-// Rendezvous of the 256 compute threads.  Warps stream their tiles without any block-wide
+// Rendezvous of the compute threads.  Warps stream their tiles without any block-wide
 // barrier; only a rare event (the candidate buffer reached its trigger or is full) brings
 // them together.  A warp comes here when it sees bs.event at a tile boundary, when one of
 // its lanes cannot get buffer space, or when it has finished all its tiles; the buffer is
@@ -550,7 +551,7 @@ __device__ __forceinline__ void process_tile(Ctx& cx, ThreadStats& st, LanePriv&
 
 // Lane-maxima bound.  Every lane's running maximum belongs to a different token, so the
 // j-th largest of a warp's 32 lane maxima has at least j tokens at or above it; with
-// j = ceil(k / 8) the smallest of the eight warps' values has at least k tokens at or above
+// j = ceil(k / #warps) the smallest of the warps' values has at least k tokens at or above
 // it and is a valid lower bound of the row's k-th largest value -- no sorting, no barrier.
 // It tracks the true k-th value closely because the best k tokens rarely share a lane.
 // Each warp publishes its value; tau is raised to the minimum over the warps (values of
@@ -1102,8 +1103,8 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     // row itself, not below the final lane-maxima bound.
     const uint64_t Qa = cx.minp_on ? __double2ull_ru((double)rp.min_p * 1099511627776.0) : 0ull;
     const float u = A.uniforms ? A.uniforms[row] : 0.0f;
-    uint64_t* sel = reinterpret_cast<uint64_t*>(smem + L.search);  // 256 keys, then 256 masses
-    unsigned long long* selq = reinterpret_cast<unsigned long long*>(sel + kThreads);
+    uint64_t* sel = reinterpret_cast<uint64_t*>(smem + L.search);  // kSmallSet keys, then kSmallSet masses
+    unsigned long long* selq = reinterpret_cast<unsigned long long*>(sel + kSmallSet);
     const bool own_row = (A.mode == kModeFull && A.S == 1);
     const float tau_f = (own_row && cx.k_eff <= kThreads) ? zkey_to_float(bs.taubits) : -INFINITY;
     if (tid == 0) bs.nl = 0;
@@ -1112,12 +1113,12 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         const uint64_t c = ent_at(i);
         if (ck_alive(c) && ck_z(c) >= tau_f) {
             const int pos = (int)smem_atom_add(&bs.nl, 1u);
-            if (pos < kThreads) sel[pos] = c;
+            if (pos < kSmallSet) sel[pos] = c;
         }
     }
     cta_sync();
     const int na = bs.nl;
-    if (na <= kThreads) {
+    if (na <= kSmallSet) {
         // ---- small set: one entry per thread, everything by all-pairs comparison (no sort,
         // no histogram): rank for top-k, mass ahead in rank order for top-p, mass ahead in
         // index order for the draw.  Sums are exact integers.
@@ -1154,8 +1155,10 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         }
         if (Qa && q < Qa) { kept = false; q = 0; }
         cta_sync();  // every thread has read sel[] for its rank
-        sel[tid] = kept ? ck : (ck & (uint64_t)kIdxMask);
-        selq[tid] = q;
+        if (tid < kSmallSet) {
+            sel[tid] = kept ? ck : (ck & (uint64_t)kIdxMask);
+            selq[tid] = q;
+        }
         cta_sync();
         if (rp.top_p > 0.0f && rp.top_p < 1.0f) {
             uint64_t before = 0;
@@ -1165,8 +1168,10 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             if (Tp < 1) Tp = 1;
             if (kept && !(before < Tp)) { kept = false; q = 0; }
             cta_sync();
-            sel[tid] = kept ? ck : (ck & (uint64_t)kIdxMask);
-            selq[tid] = q;
+            if (tid < kSmallSet) {
+                sel[tid] = kept ? ck : (ck & (uint64_t)kIdxMask);
+                selq[tid] = q;
+            }
             cta_sync();
         }
         const uint32_t my_low = (uint32_t)(ck & kIdxMask);  // larger low bits = smaller token index

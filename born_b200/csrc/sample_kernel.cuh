@@ -142,6 +142,7 @@ struct BlockShared {  // static shared state of a CTA
     int last;
     int hoff[kHistBuckets + 1];
     int hcur[kHistBuckets];
+    uint8_t pcnt_ret[kThreads];  // filled private slots of a thread, handed back by out-of-line code
 #ifdef BORN_PROFILE
     long long pf_search, pf_pair, pf_calls;
 #endif
@@ -205,7 +206,7 @@ __device__ __forceinline__ uint64_t slot_key(const Ctx& cx, const LanePriv& lp, 
 // Keep the k best entries of the buffer (exact, by rank key) and raise tau.  Private entries
 // stay with their owners, the shared area is compacted in place.  Returns true when entries
 // were dropped.
-__device__ bool compact_to_k(Ctx& cx, LanePriv& lp, int k) {
+__device__ __forceinline__ bool compact_to_k_body(Ctx& cx, LanePriv& lp, int k) {
     BlockShared& bs = *cx.bs;
     const int tid = threadIdx.x;
     cta_sync();
@@ -272,6 +273,19 @@ __device__ bool compact_to_k(Ctx& cx, LanePriv& lp, int k) {
     return true;
 }
 
+__device__ __forceinline__ uint32_t compact_to_k_cold(const Ctx* sh, int pcnt, int k) {
+    Ctx cx = *sh;
+    LanePriv lp;
+    lp.pcnt = pcnt;
+    const bool dropped = compact_to_k_body(cx, lp, k);
+    return (uint32_t)lp.pcnt | (dropped ? 0x100u : 0u);
+}
+__device__ __forceinline__ bool compact_to_k(const Ctx& cx, LanePriv& lp, int k) {
+    const uint32_t r = compact_to_k_cold(&cx, lp.pcnt, k);
+    lp.pcnt = (int)(r & 0xffu);
+    return (r >> 8) != 0;
+}
+
 template <bool kLse>
 __device__ __forceinline__ void stats_one(ThreadStats& st, float z, float c2) {
     st.mx = max_nan(st.mx, z);
@@ -319,34 +333,40 @@ __device__ __forceinline__ float max3_nan(float a, float b, float c) {
     return r;
 }
 
-// Statistics of one vector group; returns the group maximum.  The log-sum-exp terms are
-// formed two at a time with packed fp32x2 multiply-adds and adds (it feeds no decision).
-template <bool kLse, int VEC>
-__device__ __forceinline__ float group_stats(ThreadStats& st, const float (&v)[VEC], float c2, bool stats) {
-    float m4;
+// Maximum of one vector group (NaN-propagating).
+template <int VEC>
+__device__ __forceinline__ float group_max(const float (&v)[VEC]) {
     if constexpr (VEC == 4) {
-        m4 = max_nan(max3_nan(v[0], v[1], v[2]), v[3]);
+        return max_nan(max3_nan(v[0], v[1], v[2]), v[3]);
     } else {
-        m4 = max3_nan(max3_nan(v[0], v[1], v[2]), max3_nan(v[3], v[4], v[5]), max_nan(v[6], v[7]));
+        return max3_nan(max3_nan(v[0], v[1], v[2]), max3_nan(v[3], v[4], v[5]), max_nan(v[6], v[7]));
     }
-    if (stats) {
-        st.mx = max_nan(st.mx, m4);
-        if constexpr (kLse) {
-            if (m4 > st.R) {
-                const float f = ex2_approx(__fmul_rn(st.R - m4, c2));
-                st.s = __fmul2_rn(st.s, make_float2(f, f));
-                st.R = m4;
-                st.nRc = -m4 * c2;
-            }
-            const float2 cc = make_float2(c2, c2), rr = make_float2(st.nRc, st.nRc);
+}
+
+// Online log-sum-exp of a thread's share of one tile.  The running reference st.R moves at
+// most once per tile (to the share's maximum mt), then every term is formed two at a time
+// with packed fp32x2 multiply-adds and adds, in two independent chains.  It feeds no decision.
+template <int ITER, int VEC>
+__device__ __forceinline__ void tile_lse(ThreadStats& st, const float (&v)[ITER][VEC], float mt, float c2) {
+    if (mt > st.R) {
+        const float f = ex2_approx(__fmul_rn(st.R - mt, c2));
+        st.s = __fmul2_rn(st.s, make_float2(f, f));
+        st.R = mt;
+        st.nRc = -mt * c2;
+    }
+    const float2 cc = make_float2(c2, c2), rr = make_float2(st.nRc, st.nRc);
+    float2 s1 = make_float2(0.0f, 0.0f);
 #pragma unroll
-            for (int i = 0; i < VEC; i += 2) {
-                const float2 t = __ffma2_rn(make_float2(v[i], v[i + 1]), cc, rr);
-                st.s = __fadd2_rn(st.s, make_float2(ex2_approx(t.x), ex2_approx(t.y)));
-            }
+    for (int j = 0; j < ITER; ++j) {
+#pragma unroll
+        for (int i = 0; i < VEC; i += 4) {
+            const float2 t0 = __ffma2_rn(make_float2(v[j][i], v[j][i + 1]), cc, rr);
+            const float2 t1 = __ffma2_rn(make_float2(v[j][i + 2], v[j][i + 3]), cc, rr);
+            st.s = __fadd2_rn(st.s, make_float2(ex2_approx(t0.x), ex2_approx(t0.y)));
+            s1 = __fadd2_rn(s1, make_float2(ex2_approx(t1.x), ex2_approx(t1.y)));
         }
     }
-    return m4;
+    st.s = __fadd2_rn(st.s, s1);
 }
 
 // Rendezvous of the compute threads.  Warps stream their tiles without any block-wide
@@ -355,7 +375,7 @@ __device__ __forceinline__ float group_stats(ThreadStats& st, const float (&v)[V
 // its lanes cannot get buffer space, or when it has finished all its tiles; the buffer is
 // compacted if an event is pending.  Returns true when every warp has finished and no event
 // was pending.
-__device__ bool rendezvous(Ctx& cx, LanePriv& lp) {
+__device__ __forceinline__ bool rendezvous_body(Ctx& cx, LanePriv& lp) {
     BlockShared& bs = *cx.bs;
     cta_sync();
     const int ev = bs.event, dn = bs.done_warps;
@@ -367,21 +387,38 @@ __device__ bool rendezvous(Ctx& cx, LanePriv& lp) {
     }
     return !ev && dn == kThreads / 32;
 }
+// Wrappers that pass the per-thread state by value (the count of filled private slots goes in
+// and comes back in the return value), so that nothing of the caller's registers has its
+// address taken should the compiler decide not to inline the body.
+__device__ __forceinline__ uint32_t rendezvous_cold(const Ctx* sh, int pcnt) {
+    Ctx cx = *sh;
+    LanePriv lp;
+    lp.pcnt = pcnt;
+    const bool done = rendezvous_body(cx, lp);
+    return (uint32_t)lp.pcnt | (done ? 0x100u : 0u);
+}
+__device__ __forceinline__ bool rendezvous(const Ctx& cx, LanePriv& lp) {
+    const uint32_t r = rendezvous_cold(&cx, lp.pcnt);
+    lp.pcnt = (int)(r & 0xffu);
+    return (r >> 8) != 0;
+}
 
 // One candidate from the lane that found it: exact rank-key test, then a store into the
 // lane's next private slot -- no atomic, nothing to wait for.  A lane whose private slots are
 // full takes a slot of the shared area with a shared-memory atomic.  Returns false when that
 // area is full too (the caller keeps the element for the retry after the compaction).
-__device__ bool lane_put_shared(Ctx& cx, uint64_t ck) {
-    if (!(ck > cx.bs->tau_ck)) return true;  // cannot be among the k best any more
-    const int scap = kCandCap - cx.psize;
-    const int pos = (int)smem_atom_add(&cx.bs->count, 1u);
+__device__ __forceinline__ bool lane_put_shared(const Ctx* sh, uint64_t ck) {
+    BlockShared* bs = sh->bs;
+    if (!(ck > bs->tau_ck)) return true;  // cannot be among the k best any more
+    const int psize = sh->psize;
+    const int scap = kCandCap - psize;
+    const int pos = (int)smem_atom_add(&bs->count, 1u);
     if (pos < scap) {
-        cx.cand[cx.psize + pos] = ck;
-        if (pos + 1 > cx.bs->trig) cx.bs->event = 1;  // compaction at the next tile boundary
+        sh->cand[psize + pos] = ck;
+        if (pos + 1 > bs->trig) bs->event = 1;  // compaction at the next tile boundary
         return true;
     }
-    cx.bs->event = 1;
+    bs->event = 1;
     return false;
 }
 // The hot-path store: value bits and token index as one 8-byte shared store into the lane's
@@ -392,12 +429,12 @@ __device__ __forceinline__ bool lane_put(Ctx& cx, LanePriv& lp, float z, int idx
         ++lp.pcnt;
         return true;
     }
-    return lane_put_shared(cx, make_ck(z, idx));
+    return lane_put_shared(&cx, make_ck(z, idx));
 }
 __device__ __forceinline__ bool lane_put_ck(Ctx& cx, LanePriv& lp, uint64_t ck) {
     // history tokens (cold): straight to the shared area, which holds rank keys
     (void)lp;
-    return lane_put_shared(cx, ck);
+    return lane_put_shared(&cx, ck);
 }
 
 // One offer per lane, called by the whole warp (history tokens): lanes that find the buffer
@@ -414,10 +451,9 @@ __device__ __forceinline__ void settle_one(Ctx& cx, LanePriv& lp, bool pending, 
 // compaction; the lanes then offer the elements they kept back (bit j*VEC+i of `ovf`), read
 // again from the tile the warp still holds.
 template <typename T>
-__device__ void warp_retry(Ctx& cx, LanePriv& lp, const T* tile, uint32_t ovf, int c0) {
+__device__ __forceinline__ void warp_retry_body(Ctx& cx, LanePriv& lp, const T* tile, uint32_t ovf, int c0) {
     constexpr int VEC = VecOf<T>::n;
-    while (__any_sync(0xffffffffu, ovf != 0)) {
-        rendezvous(cx, lp);
+    for (;;) {
         uint32_t m = ovf;
         ovf = 0;
         while (m) {
@@ -429,7 +465,22 @@ __device__ void warp_retry(Ctx& cx, LanePriv& lp, const T* tile, uint32_t ovf, i
             else z = bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(tile)[e]);
             if (!lane_put(cx, lp, z, c0 + e)) ovf |= 1u << b;
         }
+        if (!__any_sync(0xffffffffu, ovf != 0)) break;
+        rendezvous(cx, lp);  // the buffer is full: compaction, then offer again
     }
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t warp_retry_cold(const Ctx* sh, int pcnt, const T* tile, uint32_t ovf, int c0) {
+    Ctx cx = *sh;
+    LanePriv lp;
+    lp.pcnt = pcnt;
+    warp_retry_body<T>(cx, lp, tile, ovf, c0);
+    return (uint32_t)lp.pcnt;
+}
+template <typename T>
+__device__ __forceinline__ void warp_retry(const Ctx& cx, LanePriv& lp, const T* tile, uint32_t ovf, int c0) {
+    lp.pcnt = (int)warp_retry_cold<T>(&cx, lp.pcnt, tile, ovf, c0);
 }
 
 // Penalised logit of a history token (once per distinct token, `cnt` = its multiplicity).
@@ -450,9 +501,9 @@ __device__ __forceinline__ float penalise(const born_row_params& rp, float z, in
 // (-inf) and its new value goes through the statistics and the candidate test on its own.
 // Entries are bucketed by tile and carry their multiplicity (repeats carry 0).
 template <typename T, bool kHasMask, bool kLse>
-__device__ __forceinline__ void warp_patch(Ctx& cx, ThreadStats& st, LanePriv& lp, T* tile, const uint32_t* smask,
-                                           int c, int c0, int nvalid, float tau, bool stats, bool collect,
-                                           int replay) {
+__device__ __forceinline__ void warp_patch_body(Ctx& cx, ThreadStats& st, LanePriv& lp, T* tile, const uint32_t* smask,
+                                                int c, int c0, int nvalid, float tau, bool stats, bool collect,
+                                                int replay) {
     // replay: 0 = patch, take statistics and collect in one go; 1 = patch and take statistics,
     // remember the new values; 2 = collect from the remembered values (first tile of a slice,
     // whose candidates are collected only after the threshold bootstrap)
@@ -500,6 +551,46 @@ __device__ __forceinline__ void warp_patch(Ctx& cx, ThreadStats& st, LanePriv& l
     __syncwarp();
 }
 
+// Tiles that hold history tokens of a row whose tiles the producer cannot patch.  The
+// statistics of the patched values come back as (their maximum, the sum of
+// 2^((z - maximum) * c2)) and are merged by the caller; the slot count comes back through
+// shared memory.
+template <typename T, bool kHasMask, bool kLse>
+__device__ __forceinline__ unsigned long long warp_patch_cold(const Ctx* sh, int pcnt, T* tile, const uint32_t* smask,
+                                                           int c, int c0, int nvalid, float tau, int flags) {
+    Ctx cx = *sh;
+    LanePriv lp;
+    lp.pcnt = pcnt;
+    ThreadStats ps;
+    ps.mx = -INFINITY; ps.R = -1e30f; ps.nRc = 1e30f * cx.c2; ps.s = make_float2(0.0f, 0.0f); ps.pub = -INFINITY;
+    warp_patch_body<T, kHasMask, kLse>(cx, ps, lp, tile, smask, c, c0, nvalid, tau, (flags & 1) != 0, (flags & 2) != 0, flags >> 2);
+    cx.bs->pcnt_ret[threadIdx.x] = (uint8_t)lp.pcnt;
+    // the sum is relative to the largest patched value when that is above -1e30 (else it is 0)
+    return ((unsigned long long)__float_as_uint(ps.s.x + ps.s.y) << 32) | __float_as_uint(ps.mx);
+}
+template <typename T, bool kHasMask, bool kLse>
+__device__ __forceinline__ void warp_patch(const Ctx& cx, ThreadStats& st, LanePriv& lp, T* tile, const uint32_t* smask,
+                                           int c, int c0, int nvalid, float tau, bool stats, bool collect, int replay) {
+    const unsigned long long r = warp_patch_cold<T, kHasMask, kLse>(&cx, lp.pcnt, tile, smask, c, c0, nvalid, tau,
+                                                                    (stats ? 1 : 0) | (collect ? 2 : 0) | (replay << 2));
+    lp.pcnt = cx.bs->pcnt_ret[threadIdx.x];
+    if (stats) {
+        const float pm = __uint_as_float((uint32_t)r), psum = __uint_as_float((uint32_t)(r >> 32));
+        st.mx = max_nan(st.mx, pm);
+        if constexpr (kLse) {
+            if (pm > -1e30f) {  // some patched value is finite (NaN fails the test, the row fails anyway)
+                if (pm > st.R) {
+                    const float f = ex2_approx(__fmul_rn(st.R - pm, cx.c2));
+                    st.s = __fmul2_rn(st.s, make_float2(f, f));
+                    st.R = pm;
+                    st.nRc = -pm * cx.c2;
+                }
+                st.s.x += psum * ex2_approx(fmaf(pm, cx.c2, st.nRc));
+            }
+        }
+    }
+}
+
 __device__ __forceinline__ float current_tau(const Ctx& cx) {
     float tau = zkey_to_float(*reinterpret_cast<const volatile uint32_t*>(&cx.bs->taubits));
     if (cx.minp_on) tau = fmaxf(tau, zkey_to_float(*reinterpret_cast<const volatile uint32_t*>(&cx.bs->maxbits)) + cx.delta_minp);
@@ -527,26 +618,84 @@ __device__ __forceinline__ void process_tile(Ctx& cx, ThreadStats& st, LanePriv&
     const float tau = current_tau(cx);
     if (tile_hist) warp_patch<T, kHasMask, kLse>(cx, st, lp, tile, smask, c, c0, nvalid, tau, stats, collect, replay);
     uint32_t ovf = 0;  // elements that found the buffer full (bit j*VEC+i)
+    // all of the thread's groups are loaded before anything depends on them, and the tile
+    // costs one statistics update and one candidate test per thread
+    float v[ITER][VEC], m[ITER];
 #pragma unroll
-    for (int j = 0; j < ITER; ++j) {
-        float v[VEC];
-        const int g = threadIdx.x + kThreads * j;
-        load_group<T, kHasMask>(tile, smask, g, nvalid, v);
-        const float m4 = group_stats<kLse, VEC>(st, v, cx.c2, stats);
-#ifdef BORN_PROFILE
-        const long long ph0 = clock64();
-#endif
-        if (collect && m4 >= tau) {  // rare per lane: the hits are handled where they are found
+    for (int j = 0; j < ITER; ++j) load_group<T, kHasMask>(tile, smask, threadIdx.x + kThreads * j, nvalid, v[j]);
 #pragma unroll
-            for (int i = 0; i < VEC; ++i)
-                if (v[i] >= tau && !lane_put(cx, lp, v[i], c0 + g * VEC + i)) ovf |= 1u << (j * VEC + i);
-        }
-        __syncwarp();  // bring the lanes back together here, not at the end of the tile
-#ifdef BORN_PROFILE
-        st.pf_hit += clock64() - ph0;
-#endif
+    for (int j = 0; j < ITER; ++j) m[j] = group_max<VEC>(v[j]);
+    float mt = m[0];
+#pragma unroll
+    for (int j = 1; j < ITER; ++j) mt = max_nan(mt, m[j]);
+    if (stats) {
+        st.mx = max_nan(st.mx, mt);
+        if constexpr (kLse) tile_lse<ITER, VEC>(st, v, mt, cx.c2);
     }
+#ifdef BORN_PROFILE
+    const long long ph0 = clock64();
+#endif
+    if (collect && mt >= tau) {  // rare per lane
+#pragma unroll
+        for (int j = 0; j < ITER; ++j) {
+            if (m[j] >= tau) {
+                const int g = threadIdx.x + kThreads * j;
+#pragma unroll
+                for (int i = 0; i < VEC; ++i)
+                    if (v[j][i] >= tau && !lane_put(cx, lp, v[j][i], c0 + g * VEC + i)) ovf |= 1u << (j * VEC + i);
+            }
+        }
+    }
+    __syncwarp();
+#ifdef BORN_PROFILE
+    st.pf_hit += clock64() - ph0;
+#endif
     if (collect && __any_sync(0xffffffffu, ovf != 0)) warp_retry<T>(cx, lp, tile, ovf, c0);
+}
+
+// The streaming loop's tile: full tiles of rows whose history (if any) the producer has
+// already applied.  Straight-line code -- loads, maxima, log-sum-exp, and a candidate test
+// that fails for almost every thread; a hit goes into the lane's private slots and only
+// when those are full is the element reported back (bit j*VEC+i of the result) for the
+// caller to settle outside the loop.
+template <typename T, bool kHasMask, bool kLse>
+__device__ __forceinline__ uint32_t fast_tile(const Ctx& cx, ThreadStats& st, LanePriv& lp, const T* tile,
+                                              const uint32_t* smask, int c0, float tau) {
+    constexpr int VEC = VecOf<T>::n;
+    constexpr int ITER = kChunk / VEC / kThreads;
+    float v[ITER][VEC], m[ITER];
+#pragma unroll
+    for (int j = 0; j < ITER; ++j) load_group<T, kHasMask>(tile, smask, threadIdx.x + kThreads * j, kChunk, v[j]);
+#pragma unroll
+    for (int j = 0; j < ITER; ++j) m[j] = group_max<VEC>(v[j]);
+    float mt = m[0];
+#pragma unroll
+    for (int j = 1; j < ITER; ++j) mt = max_nan(mt, m[j]);
+    st.mx = max_nan(st.mx, mt);
+    if constexpr (kLse) tile_lse<ITER, VEC>(st, v, mt, cx.c2);
+    uint32_t ovf = 0;
+    if (mt >= tau) {  // rare per lane
+#pragma unroll
+        for (int j = 0; j < ITER; ++j) {
+            if (m[j] >= tau) {
+                const int g = threadIdx.x + kThreads * j;
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) {
+                    if (v[j][i] >= tau) {
+                        if (lp.pcnt < kPrivPerLane) {
+                            reinterpret_cast<uint2*>(cx.cand)[lp.pcnt * kThreads + threadIdx.x] =
+                                make_uint2((uint32_t)(c0 + g * VEC + i), __float_as_uint(v[j][i]));
+                            ++lp.pcnt;
+                        } else {
+                            ovf |= 1u << (j * VEC + i);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    __syncwarp();
+    return ovf;
 }
 
 // Lane-maxima bound.  Every lane's running maximum belongs to a different token, so the
@@ -556,11 +705,11 @@ __device__ __forceinline__ void process_tile(Ctx& cx, ThreadStats& st, LanePriv&
 // It tracks the true k-th value closely because the best k tokens rarely share a lane.
 // Each warp publishes its value; tau is raised to the minimum over the warps (values of
 // warps that have not caught up are older, hence lower, hence still valid).
-__device__ void publish_lane_bound(Ctx& cx, const ThreadStats& st) {
+__device__ __forceinline__ void publish_lane_bound_cold(BlockShared* bsp, int k_eff, float mx) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const float v = (st.mx == st.mx) ? st.mx : -INFINITY;
+    const float v = (mx == mx) ? mx : -INFINITY;
     uint32_t key = zkey(v);
-    const int j = (cx.k_eff + kThreads / 32 - 1) / (kThreads / 32);
+    const int j = (k_eff + kThreads / 32 - 1) / (kThreads / 32);
     uint32_t kj;
     if (j == 1) {
         kj = __reduce_max_sync(0xffffffffu, key);
@@ -579,21 +728,25 @@ __device__ void publish_lane_bound(Ctx& cx, const ThreadStats& st) {
         kj = __shfl_sync(0xffffffffu, key, j - 1);
     }
     const float w = zkey_to_float(kj);
-    if (cx.k_eff == 1) {  // any single token is a bound for k = 1: take the best one
-        if (lane == 0 && w > -FLT_MAX) smem_red_max(&cx.bs->taubits, kj);
+    if (k_eff == 1) {  // any single token is a bound for k = 1: take the best one
+        if (lane == 0 && w > -FLT_MAX) smem_red_max(&bsp->taubits, kj);
         return;
     }
-    if (lane == 0) *reinterpret_cast<volatile float*>(&cx.bs->wbound[warp]) = w;
+    if (lane == 0) *reinterpret_cast<volatile float*>(&bsp->wbound[warp]) = w;
     __syncwarp();
-    float m = *reinterpret_cast<const volatile float*>(&cx.bs->wbound[0]);
+    float m = *reinterpret_cast<const volatile float*>(&bsp->wbound[0]);
 #pragma unroll
-    for (int i = 1; i < kThreads / 32; ++i) m = fminf(m, *reinterpret_cast<const volatile float*>(&cx.bs->wbound[i]));
-    if (lane == 0 && m > -FLT_MAX) smem_red_max(&cx.bs->taubits, zkey(m));
+    for (int i = 1; i < kThreads / 32; ++i) m = fminf(m, *reinterpret_cast<const volatile float*>(&bsp->wbound[i]));
+    if (lane == 0 && m > -FLT_MAX) smem_red_max(&bsp->taubits, zkey(m));
+}
+
+__device__ __forceinline__ void publish_lane_bound(const Ctx& cx, const ThreadStats& st) {
+    publish_lane_bound_cold(cx.bs, cx.k_eff, st.mx);
 }
 
 // After the statistics of the first tile (block-wide, once per slice): open the threshold
 // from the lane maxima and the min-p prune from the tile's maximum.
-__device__ void bootstrap_threshold(Ctx& cx, ThreadStats& st) {
+__device__ __forceinline__ void bootstrap_threshold(Ctx& cx, ThreadStats& st) {
     if (cx.minp_on) publish_max(cx, st);
     if (cx.k_eff <= kThreads) {
         publish_lane_bound(cx, st);
@@ -605,7 +758,7 @@ __device__ void bootstrap_threshold(Ctx& cx, ThreadStats& st) {
 }
 
 // Token history of this slice, bucketed by tile (counting sort: histogram, scan, scatter).
-__device__ int bucket_history(Ctx& cx, const int32_t* gh, int len, int e_begin, int e_end) {
+__device__ __forceinline__ int bucket_history_body(Ctx& cx, const int32_t* gh, int len, int e_begin, int e_end) {
     BlockShared& bs = *cx.bs;
     const int tid = threadIdx.x;
     int32_t* tmp = reinterpret_cast<int32_t*>(cx.hval);
@@ -657,6 +810,11 @@ __device__ int bucket_history(Ctx& cx, const int32_t* gh, int len, int e_begin, 
     }
     cta_sync();
     return total;
+}
+
+__device__ __forceinline__ int bucket_history(const Ctx* sh, const int32_t* gh, int len, int e_begin, int e_end) {
+    Ctx cx = *sh;
+    return bucket_history_body(cx, gh, len, e_begin, e_end);
 }
 
 template <typename T, bool kHasMask, bool kLse>
@@ -725,13 +883,6 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         if (!use_bar) return;
         const int lane = tid - kThreads;
         const int lag = 2;  // a tile is patched this many iterations after it was issued
-        if (producer_patches) {       // wait (bounded) for the compute threads to bucket the history
-            unsigned long long t0 = global_timer_ns();
-            while (!*reinterpret_cast<const volatile int*>(&bs.hist_ready)) {
-                if (*reinterpret_cast<const volatile int*>(&bs.fail)) return;
-                if (global_timer_ns() - t0 > kMbarTimeoutNs) { bs.fail = 1; return; }
-            }
-        }
         const int32_t* hlist = reinterpret_cast<const int32_t*>(smem + L.hist);
         const uint16_t* hcnt = reinterpret_cast<const uint16_t*>(smem + L.hist + kHistCap * 8);
         const int iters = nchunks + (producer_patches ? lag : 0);
@@ -757,6 +908,17 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             }
             if (__any_sync(0xffffffffu, stop)) break;
             if (producer_patches && it >= lag) {
+                if (it == lag) {
+                    // the first copies are in flight; now wait (bounded) for the compute
+                    // threads to finish bucketing the history
+                    unsigned long long t0 = global_timer_ns();
+                    int bad = 0;
+                    while (!*reinterpret_cast<const volatile int*>(&bs.hist_ready)) {
+                        if (*reinterpret_cast<const volatile int*>(&bs.fail)) { bad = 1; break; }
+                        if (global_timer_ns() - t0 > kMbarTimeoutNs) { bs.fail = 1; bad = 1; break; }
+                    }
+                    if (__any_sync(0xffffffffu, bad)) break;
+                }
                 const int c = it - lag, st = c % kStages;
                 const bool ok = mbar_wait_or_abort(reinterpret_cast<uint64_t*>(&bs.full_bar[st]),
                                                    (uint32_t)(c / kStages) & 1u, &bs.fail);
@@ -833,7 +995,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         if (hist_arg && pen_on) {
             int len = A.history_len ? A.history_len[row] : A.history_stride;
             len = max(0, min(min(len, A.history_stride), kHistCap));
-            const int nh = bucket_history(cx, A.history + (int64_t)row * A.history_stride, len, e_begin, e_end);
+            const int nh = bucket_history(&cx, A.history + (int64_t)row * A.history_stride, len, e_begin, e_end);
             has_hist = nh > 0 && !producer_patches;  // otherwise the tiles arrive patched
             if (producer_patches && tid == 0) {
                 __threadfence_block();
@@ -860,65 +1022,122 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         bool failed = false;
         long long pa_wait = 0, pa_proc = 0, pa_rdv = 0;
         (void)pa_wait; (void)pa_proc; (void)pa_rdv;
-        for (int c = 0; c < nchunks; ++c) {
-            BORN_PROF_T0();
-            const int stg = c % kStages;
-            const int c0 = e_begin + c * kChunk;
-            const int nvalid = min(kChunk, e_end - c0);
-            T* tile = tiles + (size_t)stg * kChunk;
-            const uint32_t* smask = tma_m ? masks + stg * (kChunk / 32) : gmask + c * (kChunk / 32);
-            if (c > 0 && *reinterpret_cast<const volatile int*>(&bs.event)) rendezvous(cx, lp);
-            BORN_PROF_ACC(pa_rdv);
-            if (use_bar && !failed) {
-                // wait for the tile; a warp parked here must still answer a rendezvous, or the
-                // warp that called it (and holds an older tile) would never hand that tile back
-                for (;;) {
-                    const int w = mbar_wait_or_event(reinterpret_cast<uint64_t*>(producer_patches ? &bs.ready_bar[stg] : &bs.full_bar[stg]),
-                                                     (uint32_t)(c / kStages) & 1u, &bs.event);
-                    if (w == 1) break;
-                    if (w == 2 && c > 0) { rendezvous(cx, lp); continue; }
-                    if (w == 2) continue;  // before the bootstrap nobody can have raised an event
-                    bs.fail = 1;
-                    failed = true;
-                    break;
-                }
+        // wait for tile c; a warp parked here must still answer a rendezvous, or the warp
+        // that called it (and holds an older tile) would never hand that tile back
+        auto wait_tile = [&](int c, int stg) {
+            if (!use_bar || failed) return;
+            uint64_t* bar = reinterpret_cast<uint64_t*>(producer_patches ? &bs.ready_bar[stg] : &bs.full_bar[stg]);
+            for (;;) {
+                const int w = mbar_wait_or_event(bar, (uint32_t)(c / kStages) & 1u, &bs.event);
+                if (w == 1) return;
+                if (w == 2 && c > 0) { rendezvous(cx, lp); continue; }
+                if (w == 2) continue;  // before the bootstrap nobody can have raised an event
+                bs.fail = 1;
+                failed = true;
+                return;
             }
+        };
+        // rows that are not 16-byte aligned: each thread fetches its own groups
+        auto fetch_tile = [&](int c, T* tile, int nvalid) {
+            constexpr int VEC = VecOf<T>::n;
+            const T* src = grow + (size_t)c * kChunk;
+            for (int j = 0; j < kChunk / VEC / kThreads; ++j)
+                for (int i = 0; i < VEC; ++i) {
+                    const int e = (tid + kThreads * j) * VEC + i;
+                    if (e < nvalid) tile[e] = src[e];
+                }
+            __syncwarp();
+        };
+        if (nchunks > 0) {
+            // first tile: statistics, then the threshold bootstrap (block-wide), then the
+            // tile's candidates under the new threshold
+            BORN_PROF_T0();
+            const int nvalid = min(kChunk, e_end - e_begin);
+            const uint32_t* smask = tma_m ? masks : gmask;
+            wait_tile(0, 0);
             BORN_PROF_ACC(pa_wait);
             if (!failed) {
-                if (!tma_l) {  // rows that are not 16-byte aligned: each thread fetches its own groups
-                    constexpr int VEC = VecOf<T>::n;
-                    const T* src = grow + (size_t)c * kChunk;
-                    for (int j = 0; j < kChunk / VEC / kThreads; ++j)
-                        for (int i = 0; i < VEC; ++i) {
-                            const int e = (tid + kThreads * j) * VEC + i;
-                            if (e < nvalid) tile[e] = src[e];
-                        }
-                    __syncwarp();
-                }
-                const bool tile_hist = has_hist && (bs.hoff[(c >> cx.hshift) + 1] > bs.hoff[c >> cx.hshift]);
-                if (c == 0) {
-                    // statistics of the first tile, then the threshold bootstrap (block-wide),
-                    // then its candidates under the new threshold
-                    process_tile<T, kHasMask, kLse>(cx, st, lp, tile, smask, 0, c0, nvalid, tile_hist, true, false, 1);
-                    bootstrap_threshold(cx, st);
-                    process_tile<T, kHasMask, kLse>(cx, st, lp, tile, smask, 0, c0, nvalid, tile_hist, false, true, 2);
-                } else {
-                    process_tile<T, kHasMask, kLse>(cx, st, lp, tile, smask, c, c0, nvalid, tile_hist, true, true);
-                }
-                if (cx.minp_on) publish_max(cx, st);  // running maximum for the min-p prune
-                if (cx.k_eff <= kThreads) {
-                    // tighten tau from the lane maxima once per doubling of the tiles seen
-                    const int x = c + 1, p2 = 1 << (31 - __clz(x));
-                    if (c > 0 && x == p2) publish_lane_bound(cx, st);
-                }
-            } else if (c == 0) {
+                if (!tma_l) fetch_tile(0, tiles, nvalid);
+                const bool tile_hist = has_hist && (bs.hoff[1] > bs.hoff[0]);
+                process_tile<T, kHasMask, kLse>(cx, st, lp, tiles, smask, 0, e_begin, nvalid, tile_hist, true, false, 1);
+                bootstrap_threshold(cx, st);
+                process_tile<T, kHasMask, kLse>(cx, st, lp, tiles, smask, 0, e_begin, nvalid, tile_hist, false, true, 2);
+                if (cx.minp_on) publish_max(cx, st);
+            } else {
                 bootstrap_threshold(cx, st);  // keep the block-wide step in lockstep
             }
-            // hand this warp's share of the tile back to the producer
             __syncwarp();
-            if (lane == 0 && use_bar) mbar_arrive(reinterpret_cast<uint64_t*>(&bs.empty_bar[stg]));
+            if (lane == 0 && use_bar) mbar_arrive(reinterpret_cast<uint64_t*>(&bs.empty_bar[0]));
             BORN_PROF_ACC(pa_proc);
-            if (c == 0) BORN_PROF(2);
+            BORN_PROF(2);
+        }
+        // The streaming loop proper holds only the common case -- a full tile that needs no
+        // consumer-side history patch, every hit fitting the lane's private slots -- so that
+        // its code stays small enough for the instruction cache.  Everything else leaves the
+        // loop with a reason, is dealt with below it, and the loop is entered again.
+        enum : int { kGoOn = 0, kEvent, kSlowTile, kOverflow, kRefresh, kFail, kDone };
+        int c = 1, stg = 1 % kStages;
+        uint32_t ovf = 0;
+        // tiles that take the slow route: the last partial tile, rows fetched by the threads
+        // themselves, tiles whose history tokens the compute warps must patch
+        const bool slow_all = !tma_l || !use_bar;
+        const int c_full = (nelem % kChunk) ? nchunks - 1 : nchunks;  // tiles [0, c_full) are full
+        for (;;) {
+            int why = kDone;
+#pragma unroll 1
+            while (c < nchunks && !failed) {
+                BORN_PROF_T0();
+                if (*reinterpret_cast<const volatile int*>(&bs.event)) { why = kEvent; break; }
+                if (use_bar) {
+                    uint64_t* bar = reinterpret_cast<uint64_t*>(producer_patches ? &bs.ready_bar[stg] : &bs.full_bar[stg]);
+                    const int w = mbar_wait_or_event(bar, (uint32_t)(c / kStages) & 1u, &bs.event);
+                    if (w != 1) { why = (w == 2) ? kEvent : kFail; break; }
+                }
+                BORN_PROF_ACC(pa_wait);
+                if (slow_all || c >= c_full ||
+                    (has_hist && bs.hoff[(c >> cx.hshift) + 1] > bs.hoff[c >> cx.hshift])) { why = kSlowTile; break; }
+                const T* tile = tiles + (size_t)stg * kChunk;
+                const uint32_t* smask = tma_m ? masks + stg * (kChunk / 32) : gmask + c * (kChunk / 32);
+                ovf = fast_tile<T, kHasMask, kLse>(cx, st, lp, tile, smask, e_begin + c * kChunk, current_tau(cx));
+                if (cx.minp_on) publish_max(cx, st);  // running maximum for the min-p prune
+                if (__any_sync(0xffffffffu, ovf != 0)) { why = kOverflow; break; }
+                if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(&bs.empty_bar[stg]));  // tile back to the producer
+                stg = (stg + 1 == kStages) ? 0 : stg + 1;
+                ++c;
+                BORN_PROF_ACC(pa_proc);
+                if ((c & (c - 1)) == 0) { why = kRefresh; break; }
+            }
+            if (why == kDone || failed) break;
+            if (why == kFail) {
+                bs.fail = 1;
+                failed = true;
+                break;
+            }
+            if (why == kEvent) {
+                rendezvous(cx, lp);  // then the same tile again
+                continue;
+            }
+            if (why == kSlowTile || why == kOverflow) {
+                const int c0 = e_begin + c * kChunk;
+                const int nvalid = min(kChunk, e_end - c0);
+                T* tile = tiles + (size_t)stg * kChunk;
+                const uint32_t* smask = tma_m ? masks + stg * (kChunk / 32) : gmask + c * (kChunk / 32);
+                if (why == kSlowTile) {
+                    if (!tma_l) fetch_tile(c, tile, nvalid);
+                    const bool tile_hist = has_hist && (bs.hoff[(c >> cx.hshift) + 1] > bs.hoff[c >> cx.hshift]);
+                    process_tile<T, kHasMask, kLse>(cx, st, lp, tile, smask, c, c0, nvalid, tile_hist, true, true);
+                    if (cx.minp_on) publish_max(cx, st);
+                } else {
+                    warp_retry<T>(cx, lp, tile, ovf, c0);  // the hits that found the private slots full
+                }
+                __syncwarp();
+                if (lane == 0 && use_bar) mbar_arrive(reinterpret_cast<uint64_t*>(&bs.empty_bar[stg]));
+                stg = (stg + 1 == kStages) ? 0 : stg + 1;
+                ++c;
+                if ((c & (c - 1)) != 0) continue;
+            }
+            // tighten tau from the lane maxima once per doubling of the tiles seen
+            if (cx.k_eff <= kThreads) publish_lane_bound(cx, st);
         }
         // finished: one last bound from the lane maxima, then stay available for rendezvous
         // until every warp is through

@@ -126,6 +126,7 @@ struct BlockShared {  // static shared state of a CTA
     unsigned long long ready_bar[kStages];  // tile patched by the producer warp (fp32 rows with penalties)
     unsigned long long tau_ck;
     unsigned long long red64[kThreads / 32];
+    unsigned long long acc[4];  // block-wide integer sums of the final selection (shared-memory atomics)
     float redf[kThreads / 32];
     float wbound[kThreads / 32];  // per warp: a lower bound of the k-th largest value (lane maxima)
     uint32_t taubits;  // key of tau; only ever raised (red.max)
@@ -142,7 +143,6 @@ struct BlockShared {  // static shared state of a CTA
     int last;
     int hoff[kHistBuckets + 1];
     int hcur[kHistBuckets];
-    uint8_t pcnt_ret[kThreads];  // filled private slots of a thread, handed back by out-of-line code
 #ifdef BORN_PROFILE
     long long pf_search, pf_pair, pf_calls;
 #endif
@@ -553,27 +553,22 @@ __device__ __forceinline__ void warp_patch_body(Ctx& cx, ThreadStats& st, LanePr
 
 // Tiles that hold history tokens of a row whose tiles the producer cannot patch.  The
 // statistics of the patched values come back as (their maximum, the sum of
-// 2^((z - maximum) * c2)) and are merged by the caller; the slot count comes back through
-// shared memory.
+// 2^((z - maximum) * c2)) and are merged by the caller.
 template <typename T, bool kHasMask, bool kLse>
-__device__ __forceinline__ unsigned long long warp_patch_cold(const Ctx* sh, int pcnt, T* tile, const uint32_t* smask,
+__device__ __forceinline__ unsigned long long warp_patch_cold(const Ctx* sh, LanePriv& lp, T* tile, const uint32_t* smask,
                                                            int c, int c0, int nvalid, float tau, int flags) {
     Ctx cx = *sh;
-    LanePriv lp;
-    lp.pcnt = pcnt;
     ThreadStats ps;
     ps.mx = -INFINITY; ps.R = -1e30f; ps.nRc = 1e30f * cx.c2; ps.s = make_float2(0.0f, 0.0f); ps.pub = -INFINITY;
     warp_patch_body<T, kHasMask, kLse>(cx, ps, lp, tile, smask, c, c0, nvalid, tau, (flags & 1) != 0, (flags & 2) != 0, flags >> 2);
-    cx.bs->pcnt_ret[threadIdx.x] = (uint8_t)lp.pcnt;
     // the sum is relative to the largest patched value when that is above -1e30 (else it is 0)
     return ((unsigned long long)__float_as_uint(ps.s.x + ps.s.y) << 32) | __float_as_uint(ps.mx);
 }
 template <typename T, bool kHasMask, bool kLse>
 __device__ __forceinline__ void warp_patch(const Ctx& cx, ThreadStats& st, LanePriv& lp, T* tile, const uint32_t* smask,
                                            int c, int c0, int nvalid, float tau, bool stats, bool collect, int replay) {
-    const unsigned long long r = warp_patch_cold<T, kHasMask, kLse>(&cx, lp.pcnt, tile, smask, c, c0, nvalid, tau,
+    const unsigned long long r = warp_patch_cold<T, kHasMask, kLse>(&cx, lp, tile, smask, c, c0, nvalid, tau,
                                                                     (stats ? 1 : 0) | (collect ? 2 : 0) | (replay << 2));
-    lp.pcnt = cx.bs->pcnt_ret[threadIdx.x];
     if (stats) {
         const float pm = __uint_as_float((uint32_t)r), psum = __uint_as_float((uint32_t)(r >> 32));
         st.mx = max_nan(st.mx, pm);
@@ -1153,7 +1148,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         }
         if (A.prof && lane == 0) {
             unsigned long long* pr = A.prof + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 32;
-            pr[16 + (tid >> 5)] = pa_proc; pr[24 + (tid >> 5)] = st.pf_hit;
+            pr[16 + (tid >> 5)] = pa_proc;
         }
 #endif
         if (bs.fail) {
@@ -1318,40 +1313,73 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         return;
     }
 
-    // Gather the entries that can still matter: alive and, when this CTA streamed the whole
-    // row itself, not below the final lane-maxima bound.
+    // Gather the entries that can still matter: alive, not below the final lane-maxima bound
+    // when this CTA streamed the whole row itself, and not below the min-p cut taken from the
+    // row's final maximum (an entry below it has a mass below min_p times the largest one).
+    // Each thread looks at the private slots it filled and at its share of the shared area.
     const uint64_t Qa = cx.minp_on ? __double2ull_ru((double)rp.min_p * 1099511627776.0) : 0ull;
     const float u = A.uniforms ? A.uniforms[row] : 0.0f;
     uint64_t* sel = reinterpret_cast<uint64_t*>(smem + L.search);  // kSmallSet keys, then kSmallSet masses
     unsigned long long* selq = reinterpret_cast<unsigned long long*>(sel + kSmallSet);
     const bool own_row = (A.mode == kModeFull && A.S == 1);
-    const float tau_f = (own_row && cx.k_eff <= kThreads) ? zkey_to_float(bs.taubits) : -INFINITY;
-    if (tid == 0) bs.nl = 0;
+    const bool need_low = (rp.top_k <= 0 && dropped);  // the set's lowest entry must be seen unpruned
+    float tau_g = (own_row && cx.k_eff <= kThreads) ? zkey_to_float(bs.taubits) : -INFINITY;
+    if (cx.minp_on && !need_low && !A.segment_mode) tau_g = fmaxf(tau_g, m_row + cx.delta_minp);
+    if (tid == 0) { bs.nl = 0; bs.acc[0] = 0; bs.acc[1] = 0; bs.acc[2] = 0; }
     cta_sync();
-    for (int i = tid; i < n; i += kThreads) {
-        const uint64_t c = ent_at(i);
-        if (ck_alive(c) && ck_z(c) >= tau_f) {
+    if (cx.psize) {
+        for (int s = 0; s < lp.pcnt; ++s) {
+            const uint64_t raw = cand[s * kThreads + tid];
+            const float z = __uint_as_float((uint32_t)(raw >> 32));
+            if (z >= tau_g) {
+                const int pos = (int)smem_atom_add(&bs.nl, 1u);
+                if (pos < kSmallSet) sel[pos] = raw_to_ck(raw);
+            }
+        }
+    }
+    for (int i = tid; i < sc_fin; i += kThreads) {
+        const uint64_t c = cand[cx.psize + i];
+        if (ck_alive(c) && ck_z(c) >= tau_g) {
             const int pos = (int)smem_atom_add(&bs.nl, 1u);
             if (pos < kSmallSet) sel[pos] = c;
         }
     }
     cta_sync();
     const int na = bs.nl;
+    BORN_PROF(24);
+#ifdef BORN_PROFILE
+    if (A.prof && tid == 0) A.prof[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 32 + 14] = (unsigned long long)na;
+#endif
     if (na <= kSmallSet) {
-        // ---- small set: one entry per thread, everything by all-pairs comparison (no sort,
-        // no histogram): rank for top-k, mass ahead in rank order for top-p, mass ahead in
-        // index order for the draw.  Sums are exact integers.
-        const bool mine = tid < na;
-        const uint64_t ck = mine ? sel[tid] : 0ull;
+        // ---- small set: everything by all-pairs comparison (no sort, no histogram): rank for
+        // top-k, mass ahead in rank order for top-p, mass ahead in index order for the draw.
+        // An entry is shared by P = 2^lg adjacent threads (as many as fit into the block), each
+        // walking every P-th entry; the partial counts meet by shuffles.  Sums are exact integers.
+        int lg = 0;
+        while (lg < 5 && (na << (lg + 1)) <= kThreads) ++lg;
+        const int P = 1 << lg, part = tid & (P - 1), ent = tid >> lg;
+        const bool mine = ent < na;
+        const bool lead = mine && part == 0;
+        const uint64_t ck = mine ? sel[ent] : 0ull;
+        auto group_sum = [&](uint64_t v) {
+            for (int d = 1; d < P; d <<= 1) v += shfl_xor_u64(v, d);
+            return v;
+        };
+        auto block_add = [&](uint64_t v, int slot) {  // v counts once per entry (its leading thread)
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) v += shfl_xor_u64(v, d);
+            if ((tid & 31) == 0 && v) atomicAdd(&bs.acc[slot], (unsigned long long)v);
+        };
         int rank = 0;
-        for (int j = 0; j < na; ++j) rank += (sel[j] > ck) ? 1 : 0;
+        for (int j = part; j < na; j += P) rank += (sel[j] > ck) ? 1 : 0;
+        rank = (int)group_sum((uint64_t)rank);
         bool kept = mine && (A.segment_mode || rank < cx.k_eff);
         uint64_t q = 0;
         if (kept) {
             const float x = scaled_shift(ck_z(ck), m_row, inv_T);
             q = (x < -30.0f) ? 0ull : mass_of(x);
         }
-        if (rp.top_k <= 0 && dropped) {
+        if (need_low) {
             // survivor limit reached with top-k off: exact only if min-p cuts inside the set
             uint64_t low = mine ? ck : ~0ull;
 #pragma unroll
@@ -1373,50 +1401,60 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             }
         }
         if (Qa && q < Qa) { kept = false; q = 0; }
+        BORN_PROF(25);
         cta_sync();  // every thread has read sel[] for its rank
-        if (tid < kSmallSet) {
-            sel[tid] = kept ? ck : (ck & (uint64_t)kIdxMask);
-            selq[tid] = q;
+        if (lead) {
+            sel[ent] = kept ? ck : (ck & (uint64_t)kIdxMask);
+            selq[ent] = q;
         }
+        block_add(lead ? q : 0ull, 0);
         cta_sync();
+        uint64_t S = bs.acc[0];
         if (rp.top_p > 0.0f && rp.top_p < 1.0f) {
             uint64_t before = 0;
-            for (int j = 0; j < na; ++j) before += (sel[j] > ck) ? selq[j] : 0ull;
-            const uint64_t S = block_sum_u64(q, bs.red64);
+            for (int j = part; j < na; j += P) before += (sel[j] > ck) ? selq[j] : 0ull;
+            before = group_sum(before);
             uint64_t Tp = __double2ull_rz(__dmul_rn((double)rp.top_p, __ull2double_rn(S)));
             if (Tp < 1) Tp = 1;
             if (kept && !(before < Tp)) { kept = false; q = 0; }
             cta_sync();
-            if (tid < kSmallSet) {
-                sel[tid] = kept ? ck : (ck & (uint64_t)kIdxMask);
-                selq[tid] = q;
+            if (lead) {
+                sel[ent] = kept ? ck : (ck & (uint64_t)kIdxMask);
+                selq[ent] = q;
             }
+            block_add(lead ? q : 0ull, 1);
             cta_sync();
+            S = bs.acc[1];
         }
+        BORN_PROF(26);
         const uint32_t my_low = (uint32_t)(ck & kIdxMask);  // larger low bits = smaller token index
         uint64_t pre = 0;
-        for (int j = 0; j < na; ++j) pre += ((uint32_t)(sel[j] & kIdxMask) > my_low) ? selq[j] : 0ull;
-        const uint64_t S = block_sum_u64(q, bs.red64);
+        for (int j = part; j < na; j += P) pre += ((uint32_t)(sel[j] & kIdxMask) > my_low) ? selq[j] : 0ull;
+        pre = group_sum(pre);
         if (S == 0) {  // cannot happen while the row maximum is finite; never divide by it
             if (tid == 0) { A.out_token[row] = -1; A.out_status[row] = BORN_ROW_ALL_MASKED; }
             return;
         }
         uint64_t t = __double2ull_rz(__dmul_rn((double)u, __ull2double_rn(S)));
         if (t > S - 1) t = S - 1;
-        if (kept && pre <= t && t < pre + q) {
+        if (lead && kept && pre <= t && t < pre + q) {
             A.out_token[row] = ck_idx(ck);
             A.out_status[row] = BORN_ROW_OK;
             if (A.out_prob) A.out_prob[row] = __double2float_rn(__ddiv_rn(__ull2double_rn(q), __ull2double_rn(S)));
         }
         BORN_PROF(6);
         if (A.out_kept_count || A.out_kept_ids) {
-            if (kept && A.out_kept_ids) {
+            if (A.out_kept_ids) {
                 int kr = 0;
-                for (int j = 0; j < na; ++j) kr += (ck_alive(sel[j]) && sel[j] > ck) ? 1 : 0;
-                if (kr < A.kept_stride) A.out_kept_ids[(int64_t)row * A.kept_stride + kr] = ck_idx(ck);
+                for (int j = part; j < na; j += P) kr += (ck_alive(sel[j]) && sel[j] > ck) ? 1 : 0;
+                kr = (int)group_sum((uint64_t)kr);
+                if (lead && kept && kr < A.kept_stride) A.out_kept_ids[(int64_t)row * A.kept_stride + kr] = ck_idx(ck);
             }
-            const uint64_t tot = block_sum_u64(kept ? 1ull : 0ull, bs.red64);
-            if (tid == 0 && A.out_kept_count) A.out_kept_count[row] = (int)tot;
+            if (A.out_kept_count) {
+                block_add((lead && kept) ? 1ull : 0ull, 2);
+                cta_sync();
+                if (tid == 0) A.out_kept_count[row] = (int)bs.acc[2];
+            }
         }
         return;
     }

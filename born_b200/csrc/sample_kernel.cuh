@@ -131,6 +131,7 @@ struct BlockShared {  // static shared state of a CTA
     float wbound[kThreads / 32];  // per warp: a lower bound of the k-th largest value (lane maxima)
     uint32_t taubits;  // key of tau; only ever raised (red.max)
     uint32_t maxbits;
+    float u_row;     // the row's uniform variate, fetched at the start
     int count;
     int event;       // a compaction is wanted: warps meet at the rendezvous
     int done_warps;  // warps that have finished their tiles
@@ -753,18 +754,18 @@ __device__ __forceinline__ void bootstrap_threshold(Ctx& cx, ThreadStats& st) {
 }
 
 // Token history of this slice, bucketed by tile (counting sort: histogram, scan, scatter).
-__device__ __forceinline__ int bucket_history_body(Ctx& cx, const int32_t* gh, int len, int e_begin, int e_end) {
+__device__ __forceinline__ int bucket_history_body(Ctx& cx, const int (&hid)[kHistCap / kThreads], int len, int e_begin, int e_end) {
+    // the ids are in registers already (thread t holds ids t, t + kThreads, ...); the bucket
+    // counters were cleared before the CTA's first barrier
     BlockShared& bs = *cx.bs;
     const int tid = threadIdx.x;
-    int32_t* tmp = reinterpret_cast<int32_t*>(cx.hval);
-    if (tid < kHistBuckets) { bs.hoff[tid] = 0; bs.hcur[tid] = 0; }
-    if (tid == 0) bs.hoff[kHistBuckets] = 0;
-    cta_sync();
-    for (int i = tid; i < len; i += kThreads) {
-        const int id = gh[i];
-        const bool in = (id >= e_begin && id < e_end);
-        tmp[i] = in ? id : -1;
-        if (in) smem_red_add(&bs.hcur[((id - e_begin) / kChunk) >> cx.hshift], 1u);
+    int bkt[kHistCap / kThreads];
+#pragma unroll
+    for (int k = 0; k < kHistCap / kThreads; ++k) {
+        const int id = hid[k];
+        const bool in = (tid + k * kThreads < len) && (id >= e_begin && id < e_end);
+        bkt[k] = in ? (((id - e_begin) / kChunk) >> cx.hshift) : -1;
+        if (in) smem_red_add(&bs.hcur[bkt[k]], 1u);
     }
     cta_sync();
     if (tid < 32) {  // exclusive scan over the 128 bucket counts, 4 per lane
@@ -783,10 +784,9 @@ __device__ __forceinline__ int bucket_history_body(Ctx& cx, const int32_t* gh, i
         if (tid == 31) bs.hoff[kHistBuckets] = run;
     }
     cta_sync();
-    for (int i = tid; i < len; i += kThreads) {
-        const int id = tmp[i];
-        if (id >= 0) cx.hlist[smem_atom_add(&bs.hcur[((id - e_begin) / kChunk) >> cx.hshift], 1u)] = id;
-    }
+#pragma unroll
+    for (int k = 0; k < kHistCap / kThreads; ++k)
+        if (bkt[k] >= 0) cx.hlist[smem_atom_add(&bs.hcur[bkt[k]], 1u)] = hid[k];
     cta_sync();
     // multiplicity of every id within its bucket; repeats of an id are marked with 0
     const int total = bs.hoff[kHistBuckets];
@@ -807,9 +807,9 @@ __device__ __forceinline__ int bucket_history_body(Ctx& cx, const int32_t* gh, i
     return total;
 }
 
-__device__ __forceinline__ int bucket_history(const Ctx* sh, const int32_t* gh, int len, int e_begin, int e_end) {
+__device__ __forceinline__ int bucket_history(const Ctx* sh, const int (&hid)[kHistCap / kThreads], int len, int e_begin, int e_end) {
     Ctx cx = *sh;
-    return bucket_history_body(cx, gh, len, e_begin, e_end);
+    return bucket_history_body(cx, hid, len, e_begin, e_end);
 }
 
 template <typename T, bool kHasMask, bool kLse>
@@ -833,7 +833,27 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     const bool tma_l = A.tma_logits != 0, tma_m = kHasMask && A.tma_mask != 0;
     const bool use_bar = (A.mode != kModeMerge) && (tma_l || tma_m);
 
+    // Everything the CTA needs from global memory besides the logits is asked for now, so
+    // that the round trips overlap each other and the barrier set-up instead of queueing up
+    // in front of the first tile and behind the last one.
+    const born_row_params rp0 = A.row_params ? A.row_params[row] : A.params;
+    const float u_row0 = (A.uniforms && tid == 0) ? A.uniforms[row] : 0.0f;  // parked in shared memory below
+    int hist_len0 = 0;
+    int hid[kHistCap / kThreads];
+#pragma unroll
+    for (int k = 0; k < kHistCap / kThreads; ++k) hid[k] = -1;
+    if (hist_arg && tid < kThreads && A.mode != kModeMerge) {
+        hist_len0 = A.history_len ? A.history_len[row] : A.history_stride;
+        const int32_t* gh = A.history + (int64_t)row * A.history_stride;
+        const int cap = min(A.history_stride, kHistCap);
+#pragma unroll
+        for (int k = 0; k < kHistCap / kThreads; ++k)
+            if (tid + k * kThreads < cap) hid[k] = gh[tid + k * kThreads];
+    }
+    if (tid < kHistBuckets) { bs.hoff[tid] = 0; bs.hcur[tid] = 0; }
     if (tid == 0) {
+        bs.u_row = u_row0;
+        bs.hoff[kHistBuckets] = 0;
         bs.taubits = zkey(-FLT_MAX);
         for (int w = 0; w < kThreads / 32; ++w) bs.wbound[w] = -FLT_MAX;
         bs.tau_ck = 0;
@@ -861,8 +881,6 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     }
     __syncthreads();  // the only barrier all 288 threads share
 
-    // Row parameters (both sides of the CTA need them).
-    const born_row_params rp0 = A.row_params ? A.row_params[row] : A.params;
     const bool greedy0 = (rp0.flags & BORN_FLAG_GREEDY) || rp0.temperature == 0.0f;
     (void)greedy0;
     const bool pen_on = (rp0.repetition_penalty != 1.0f && rp0.repetition_penalty != 0.0f) ||
@@ -988,9 +1006,8 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         // ------------------------------------------------------------------ streaming pass
         bool has_hist = false;
         if (hist_arg && pen_on) {
-            int len = A.history_len ? A.history_len[row] : A.history_stride;
-            len = max(0, min(min(len, A.history_stride), kHistCap));
-            const int nh = bucket_history(&cx, A.history + (int64_t)row * A.history_stride, len, e_begin, e_end);
+            const int len = max(0, min(min(hist_len0, A.history_stride), kHistCap));
+            const int nh = bucket_history(&cx, hid, len, e_begin, e_end);
             has_hist = nh > 0 && !producer_patches;  // otherwise the tiles arrive patched
             if (producer_patches && tid == 0) {
                 __threadfence_block();
@@ -1318,7 +1335,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     // row's final maximum (an entry below it has a mass below min_p times the largest one).
     // Each thread looks at the private slots it filled and at its share of the shared area.
     const uint64_t Qa = cx.minp_on ? __double2ull_ru((double)rp.min_p * 1099511627776.0) : 0ull;
-    const float u = A.uniforms ? A.uniforms[row] : 0.0f;
+    const float u = bs.u_row;
     uint64_t* sel = reinterpret_cast<uint64_t*>(smem + L.search);  // kSmallSet keys, then kSmallSet masses
     unsigned long long* selq = reinterpret_cast<unsigned long long*>(sel + kSmallSet);
     const bool own_row = (A.mode == kModeFull && A.S == 1);

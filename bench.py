@@ -47,6 +47,8 @@ WORKLOADS = {
     "c3_constrained_b256": dict(B=256, V=151936, dtype="bf16", H=0, mask=True, params=None),
     "c5_sharded": dict(B=1024, V=256000, dtype="bf16", H=0, mask=False,
                        params=dict(temperature=1.0, top_k=64, top_p=0.95)),
+    # speculative verification: 32 sequences x 5 draft positions (+ bonus row); metric is its own
+    "c4_spec_verify": dict(B=32, V=128256, dtype="f32", H=0, mask=False, K=5, params=None),
 }
 
 
@@ -221,6 +223,133 @@ def run_reference(args, w, name):
     print(json.dumps(line), flush=True)
 
 
+def run_spec(args, w, name):
+    """Speculative verification (born_spec_verify): one step verifies B sequences of K draft
+    tokens against K+1 target rows.  Every rank verifies its own batch (no communication)."""
+    import torch
+    import torch.distributed as dist
+    from born_b200 import Sampler, build
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the sampling path has no CPU fallback")
+    build.build()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    B, V, K = w["B"], w["V"], w["K"]
+    nbuf = 1 if args.small else 3
+    g = torch.Generator(device=device).manual_seed(4321 + rank)
+    sets = []
+    for _ in range(nbuf):
+        tgt = torch.randn((B, K + 1, V), generator=g, device=device) * 2.0
+        drf = (tgt[:, :K, :] + 0.5 * torch.randn((B, K, V), generator=g, device=device)).contiguous()
+        tok = torch.multinomial(torch.softmax(drf.view(B * K, V), dim=-1), 1, generator=g).view(B, K).to(torch.int32)
+        sets.append(dict(target=tgt, draft=drf, tok=tok.contiguous(),
+                         ua=torch.rand((B, K), generator=g, device=device),
+                         ur=torch.rand((B, K + 1), generator=g, device=device).clamp_(max=1.0 - 2.0 ** -24)))
+    sampler = Sampler(device=local, max_batch=B, max_vocab=V)
+    stream = torch.cuda.current_stream()
+    sp = stream.cuda_stream
+
+    def step(i):
+        s_ = sets[i % nbuf]
+        return sampler.spec_verify(s_["target"], s_["draft"], s_["tok"], s_["ua"], s_["ur"], stream=sp)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    clocks = ClockSampler(local)
+    clocks.start()
+    l0 = sampler.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for i in range(args.steps):
+        step(i)
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = sampler.launch_count - l0
+    t_end = time.time() + 0.6
+    i = 0
+    while time.time() < t_end:
+        step(i)
+        i += 1
+        if i % 16 == 0:
+            torch.cuda.synchronize()
+    torch.cuda.synchronize()
+    clocks.stop_flag = True
+    clocks.join(timeout=3)
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    if rank == 0:
+        from oracle import born_oracle as O
+        O.build()
+        res = step(0)
+        torch.cuda.synchronize()
+        nchk = min(B, 8)
+        s0 = sets[0]
+        ref = O.spec_verify(s0["target"][:nchk].cpu().numpy(), s0["draft"][:nchk].cpu().numpy(),
+                            s0["tok"][:nchk].cpu().numpy(), s0["ua"][:nchk].cpu().numpy(),
+                            s0["ur"][:nchk].cpu().numpy(), nthreads=os.cpu_count() or 1)
+        alen = res["accept_len"][:nchk].cpu().numpy()
+        toks = res["tokens"][:nchk].cpu().numpy()
+        mism = 0
+        for b in range(nchk):
+            n = int(ref["accept_len"][b]) + 1
+            mism += int(alen[b] != ref["accept_len"][b]) + int((toks[b, :n] != ref["tokens"][b, :n]).any())
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            cores = os.cpu_count() or 1
+            hs = {k: v[:nchk].cpu().numpy() for k, v in s0.items()}
+            t0 = time.perf_counter()
+            reps = 0
+            while time.perf_counter() - t0 < 10.0:
+                O.spec_verify(hs["target"], hs["draft"], hs["tok"], hs["ua"], hs["ur"], nthreads=cores)
+                reps += 1
+            dt = time.perf_counter() - t0
+            cpu = {"value": nchk * reps / dt, "unit": "sequences/s", "cores": cores, "kind": "port",
+                   "sample": f"{nchk} sequences of the workload x {reps} passes, {cores} threads over sequences"}
+        peaks = {}
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                peaks = json.load(f)
+        except Exception:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        bytes_launch = B * (2 * K + 1) * V * 4
+        kernel_ms = ms / args.steps
+        achieved = bytes_launch / (kernel_ms * 1e-3) / 1e9
+        line = {
+            "metric": "spec_verified_sequences_per_s", "value": B * args.steps * world / (ms * 1e-3),
+            "unit": "sequences/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": kernel_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": name, "batch_per_gpu": B, "draft_len": K, "vocab": V,
+                       "parallelism": "batch-parallel x%d" % world,
+                       "l2": f"{nbuf} rotating input sets, {nbuf * bytes_launch / 1e6:.0f} MB > L2"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": "measured" if peaks else "fallback",
+                         "algorithmic_bytes_per_launch": bytes_launch, "frac_of_8TBs": achieved / 8000.0},
+            "cpu_baseline": cpu, "e2e": None, "gpu_launches": int(launches), "clocks": clocks.summary(),
+            "parity": {"sequences_checked": nchk, "mismatches": mism},
+        }
+        print(json.dumps(line), flush=True)
+    sampler.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -235,11 +364,15 @@ def main():
     w = WORKLOADS[args.workload]
     name = args.workload
     if args.impl == "reference":
+        if name == "c4_spec_verify":
+            raise SystemExit("--impl reference times the sampling workloads; c4_spec_verify reports its own cpu_baseline")
         args.steps = args.steps or 5
         args.warmup = 1 if args.warmup is None else args.warmup
         return run_reference(args, w, name)
     args.steps = args.steps or 200
     args.warmup = 20 if args.warmup is None else args.warmup
+    if name == "c4_spec_verify":
+        return run_spec(args, w, name)
 
     import torch
     import torch.distributed as dist
@@ -266,7 +399,9 @@ def main():
     bufs = make_inputs(torch, wl, seed=1234 + (0 if sharded else rank), device=device, nbuf=nbuf)
     if sharded:  # uniforms must be identical on every rank
         dist.broadcast(bufs[0]["uniforms"], src=0)
-    sampler = Sampler(device=local, max_batch=B, max_vocab=max(V_local, 1024))
+    # the one-GPU form of the sharded workload cuts every row into 8 vocab segments (8 records a row)
+    sampler = Sampler(device=local, max_batch=B * (2 if name == "c5_sharded" and not sharded else 1),
+                      max_vocab=max(V_local, 1024))
     cfg, rp = row_params_for(w)
     rp_dev = torch.from_numpy(rp.view(np.uint8)).to(device) if rp is not None else None
     stream = torch.cuda.current_stream()

@@ -1185,7 +1185,12 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             return;
         }
         const bool own_row = (A.mode == kModeFull && A.S == 1);
-        if (!own_row) compact_to_k(cx, lp, cx.k_eff);  // records hold at most k entries
+        // A record that stands for a vocabulary shard or segment holds exactly its k best (that
+        // is the algorithm's definition); a plain slice record of a row that is finished on this
+        // GPU may hold any superset of them that fits.
+        const bool exact_rec = (A.mode == kModeLocal) || A.segment_mode;
+        const int rec_cap = exact_rec ? cx.k_eff : kMaxK;
+        if (!own_row) compact_to_k(cx, lp, rec_cap);
         cta_sync();
 
         // slice statistics
@@ -1222,17 +1227,21 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             uint8_t* rec = A.records + (int64_t)row * A.rec_row_stride + (int64_t)slice * A.rec_slice_stride;
             uint64_t* ent = reinterpret_cast<uint64_t*>(rec + kRecordHdrBytes);
             const int sc = min(bs.count, kCandCap - cx.psize);
+            // nothing below the slice's final bounds can be among the row's k best or pass min-p
+            float tau_rec = (cx.k_eff <= kThreads) ? zkey_to_float(bs.taubits) : -INFINITY;
+            if (cx.minp_on && m_slice == m_slice) tau_rec = fmaxf(tau_rec, m_slice + cx.delta_minp);
+            if (exact_rec) tau_rec = -INFINITY;  // after the compaction: exactly the k best
             if (tid == 0) bs.nl = 0;
             cta_sync();
             for (int i = tid; i < kCandCap; i += kThreads) {
                 const uint64_t e = slot_key(cx, lp, i, sc);
-                if (ck_alive(e)) {
+                if (ck_alive(e) && ck_z(e) >= tau_rec) {
                     const int pos = (int)smem_atom_add(&bs.nl, 1u);
-                    if (pos < cx.k_eff) ent[pos] = e - (uint64_t)A.idx_offset;
+                    if (pos < rec_cap) ent[pos] = e - (uint64_t)A.idx_offset;
                 }
             }
             cta_sync();
-            const int n = min(bs.nl, cx.k_eff);
+            const int n = min(bs.nl, rec_cap);
             if (tid == 0) {
                 RecordHdr h;
                 h.m = m_slice; h.lse_s = s_slice; h.count = (uint32_t)n; h.flags = (uint32_t)bs.dropped;
@@ -1342,6 +1351,9 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     const bool need_low = (rp.top_k <= 0 && dropped);  // the set's lowest entry must be seen unpruned
     float tau_g = (own_row && cx.k_eff <= kThreads) ? zkey_to_float(bs.taubits) : -INFINITY;
     if (cx.minp_on && !need_low && !A.segment_mode) tau_g = fmaxf(tau_g, m_row + cx.delta_minp);
+    // a merged row whose records hold far more than k entries is cut to its k best first
+    if (!own_row && !A.segment_mode && cx.k_eff <= kSmallSet && bs.count > kSmallSet) compact_to_k(cx, lp, cx.k_eff);
+    const int sc_g = min(bs.count, kCandCap - cx.psize);
     if (tid == 0) { bs.nl = 0; bs.acc[0] = 0; bs.acc[1] = 0; bs.acc[2] = 0; }
     cta_sync();
     if (cx.psize) {
@@ -1354,7 +1366,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             }
         }
     }
-    for (int i = tid; i < sc_fin; i += kThreads) {
+    for (int i = tid; i < sc_g; i += kThreads) {
         const uint64_t c = cand[cx.psize + i];
         if (ck_alive(c) && ck_z(c) >= tau_g) {
             const int pos = (int)smem_atom_add(&bs.nl, 1u);
@@ -1366,6 +1378,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     BORN_PROF(24);
 #ifdef BORN_PROFILE
     if (A.prof && tid == 0) A.prof[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 32 + 14] = (unsigned long long)na;
+    if (A.prof) atomicAdd(&A.prof[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 32 + 13], (unsigned long long)lp.pcnt + (tid == 0 ? (unsigned long long)sc_g : 0ull));
 #endif
     if (na <= kSmallSet) {
         // ---- small set: everything by all-pairs comparison (no sort, no histogram): rank for
@@ -1420,55 +1433,71 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         if (Qa && q < Qa) { kept = false; q = 0; }
         BORN_PROF(25);
         cta_sync();  // every thread has read sel[] for its rank
-        if (lead) {
-            sel[ent] = kept ? ck : (ck & (uint64_t)kIdxMask);
-            selq[ent] = q;
+        // The nk best entries (all of them in segment mode) go to sel[0..nk) in rank order;
+        // an entry that min-p removed stays in place as a dead one with no mass.
+        const int nk = A.segment_mode ? na : min(na, cx.k_eff);
+        if (lead && rank < nk) {
+            sel[rank] = kept ? ck : (ck & (uint64_t)kIdxMask);
+            selq[rank] = q;
         }
         block_add(lead ? q : 0ull, 0);
         cta_sync();
         uint64_t S = bs.acc[0];
+        // the threads are dealt out again, over the nk entries that are left
+        int lg2 = 0;
+        while (lg2 < 5 && (nk << (lg2 + 1)) <= kThreads) ++lg2;
+        const int P2 = 1 << lg2, part2 = tid & (P2 - 1), ent2 = tid >> lg2;
+        const bool mine2 = ent2 < nk;
+        const bool lead2 = mine2 && part2 == 0;
+        const uint64_t ck2 = mine2 ? sel[ent2] : 0ull;
+        uint64_t q2 = mine2 ? (uint64_t)selq[ent2] : 0ull;
+        bool kept2 = mine2 && ck_alive(ck2);
+        auto group_sum2 = [&](uint64_t v) {
+            for (int d = 1; d < P2; d <<= 1) v += shfl_xor_u64(v, d);
+            return v;
+        };
         if (rp.top_p > 0.0f && rp.top_p < 1.0f) {
-            uint64_t before = 0;
-            for (int j = part; j < na; j += P) before += (sel[j] > ck) ? selq[j] : 0ull;
-            before = group_sum(before);
+            uint64_t before = 0;  // mass ahead in rank order = mass of the entries in front
+            for (int j = part2; j < ent2 && j < nk; j += P2) before += selq[j];
+            before = group_sum2(before);
             uint64_t Tp = __double2ull_rz(__dmul_rn((double)rp.top_p, __ull2double_rn(S)));
             if (Tp < 1) Tp = 1;
-            if (kept && !(before < Tp)) { kept = false; q = 0; }
+            if (kept2 && !(before < Tp)) { kept2 = false; q2 = 0; }
             cta_sync();
-            if (lead) {
-                sel[ent] = kept ? ck : (ck & (uint64_t)kIdxMask);
-                selq[ent] = q;
+            if (lead2) {
+                sel[ent2] = kept2 ? ck2 : (ck2 & (uint64_t)kIdxMask);
+                selq[ent2] = q2;
             }
-            block_add(lead ? q : 0ull, 1);
+            block_add(lead2 ? q2 : 0ull, 1);
             cta_sync();
             S = bs.acc[1];
         }
         BORN_PROF(26);
-        const uint32_t my_low = (uint32_t)(ck & kIdxMask);  // larger low bits = smaller token index
+        const uint32_t my_low = (uint32_t)(ck2 & kIdxMask);  // larger low bits = smaller token index
         uint64_t pre = 0;
-        for (int j = part; j < na; j += P) pre += ((uint32_t)(sel[j] & kIdxMask) > my_low) ? selq[j] : 0ull;
-        pre = group_sum(pre);
+        for (int j = part2; j < nk; j += P2) pre += ((uint32_t)(sel[j] & kIdxMask) > my_low) ? selq[j] : 0ull;
+        pre = group_sum2(pre);
         if (S == 0) {  // cannot happen while the row maximum is finite; never divide by it
             if (tid == 0) { A.out_token[row] = -1; A.out_status[row] = BORN_ROW_ALL_MASKED; }
             return;
         }
         uint64_t t = __double2ull_rz(__dmul_rn((double)u, __ull2double_rn(S)));
         if (t > S - 1) t = S - 1;
-        if (lead && kept && pre <= t && t < pre + q) {
-            A.out_token[row] = ck_idx(ck);
+        if (lead2 && kept2 && pre <= t && t < pre + q2) {
+            A.out_token[row] = ck_idx(ck2);
             A.out_status[row] = BORN_ROW_OK;
-            if (A.out_prob) A.out_prob[row] = __double2float_rn(__ddiv_rn(__ull2double_rn(q), __ull2double_rn(S)));
+            if (A.out_prob) A.out_prob[row] = __double2float_rn(__ddiv_rn(__ull2double_rn(q2), __ull2double_rn(S)));
         }
         BORN_PROF(6);
         if (A.out_kept_count || A.out_kept_ids) {
             if (A.out_kept_ids) {
-                int kr = 0;
-                for (int j = part; j < na; j += P) kr += (ck_alive(sel[j]) && sel[j] > ck) ? 1 : 0;
-                kr = (int)group_sum((uint64_t)kr);
-                if (lead && kept && kr < A.kept_stride) A.out_kept_ids[(int64_t)row * A.kept_stride + kr] = ck_idx(ck);
+                int kr = 0;  // kept entries ahead in rank order
+                for (int j = part2; j < ent2 && j < nk; j += P2) kr += ck_alive(sel[j]) ? 1 : 0;
+                kr = (int)group_sum2((uint64_t)kr);
+                if (lead2 && kept2 && kr < A.kept_stride) A.out_kept_ids[(int64_t)row * A.kept_stride + kr] = ck_idx(ck2);
             }
             if (A.out_kept_count) {
-                block_add((lead && kept) ? 1ull : 0ull, 2);
+                block_add((lead2 && kept2) ? 1ull : 0ull, 2);
                 cta_sync();
                 if (tid == 0) A.out_kept_count[row] = (int)bs.acc[2];
             }

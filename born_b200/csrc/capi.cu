@@ -139,7 +139,8 @@ int launch_sample(Handle* h, const SampleKernelArgs& A, int dtype, cudaStream_t 
 // Slices per row.  With at least one row per SM every row is one CTA (a slice costs a
 // threshold bootstrap and a record merge); smaller batches are cut so that about two CTAs
 // per SM exist, but never below four tiles per slice.
-void choose_slices(const Handle* h, int B, int V, int* S, int* slice_len) {
+void choose_slices(const Handle* h, int B, int V, int elem_bytes, int* S, int* slice_len) {
+    const int kChunk = kTileBytes / elem_bytes;  // logits per pipeline stage
     const int nchunks = (V + kChunk - 1) / kChunk;
     int s = 1;
     if (h->force_slices > 0) s = h->force_slices;
@@ -297,7 +298,7 @@ static int sample_device(Handle* h, const born_sample_args* a, cudaStream_t st) 
         A.slice_len = a->vocab / a->vocab_segments;
         A.segment_mode = 1;
     } else {
-        choose_slices(h, a->batch, a->vocab, &A.S, &A.slice_len);
+        choose_slices(h, a->batch, a->vocab, esz, &A.S, &A.slice_len);
     }
     A.rec_row_stride = h->record_stride * A.S;
     A.tma_logits = ((uintptr_t)a->logits % 16 == 0) && ((a->logits_row_stride * esz) % 16 == 0) &&
@@ -608,7 +609,7 @@ static int shard_local(Handle* h, const born_shard_args* a, void* packed, bool w
     A.V = a->vocab_local;
     A.mode = kModeLocal;
     A.S = 1;
-    A.slice_len = (a->vocab_local + kChunk - 1) / kChunk * kChunk;
+    A.slice_len = (a->vocab_local + kTileBytes / esz - 1) / (kTileBytes / esz) * (kTileBytes / esz);
     A.idx_offset = a->rank * a->vocab_local;
     A.records = (uint8_t*)packed;
     A.rec_row_stride = born_shard_record_bytes(a->top_k);

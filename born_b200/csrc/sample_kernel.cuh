@@ -41,7 +41,8 @@ struct RecordHdr {  // 32 bytes, precedes the entries of a slice / shard record
     float lse_s;    // sum of 2^((z - m) * c2) over the slice
     uint32_t count; // entries that follow
     uint32_t flags; // bit 0: entries were dropped (more than k candidates existed)
-    uint32_t pad[4];
+    float bound;    // at least k tokens of the slice are at or above this value (-inf: no bound)
+    uint32_t pad[3];
 };
 static_assert(sizeof(RecordHdr) == kRecordHdrBytes, "record header size");
 
@@ -91,6 +92,10 @@ struct SampleKernelArgs {
 #define BORN_PROF_ACC(var) do { } while (0)
 #endif
 
+// A pipeline stage holds kTileBytes of logits whatever their type: 4096 fp32 or 8192 bf16.
+template <typename T>
+struct TileOf { static constexpr int n = kTileBytes / (int)sizeof(T); };
+
 template <typename T>
 struct VecOf;
 template <>
@@ -105,8 +110,8 @@ struct SmemLayout {
 __host__ __device__ inline SmemLayout smem_layout(int elem_bytes, bool has_mask, bool has_hist) {
     SmemLayout L;
     int off = 0;
-    L.tiles = off; off += kStages * kChunk * elem_bytes;
-    L.masks = off; off += has_mask ? kStages * (kChunk / 32) * 4 : 0;
+    L.tiles = off; off += kStages * kTileBytes;
+    L.masks = off; off += has_mask ? kStages * (kTileBytes / elem_bytes / 32) * 4 : 0;
     L.cand = off; off += kCandCap * 8;
     // the radix-search scratch and the pairing lists of the compaction are never live together
     L.search = off;
@@ -274,15 +279,21 @@ __device__ __forceinline__ bool compact_to_k_body(Ctx& cx, LanePriv& lp, int k) 
     return true;
 }
 
-__device__ __forceinline__ uint32_t compact_to_k_cold(const Ctx* sh, int pcnt, int k) {
-    Ctx cx = *sh;
+// The compaction takes its state by value -- the few pointers it needs, and the thread's
+// count of filled private slots in and out.  (Measured: as a real out-of-line function it
+// shrinks the kernel by 140 KB of code but the call ABI costs the streaming loop 15 %.)
+__device__ __forceinline__ uint32_t compact_to_k_cold(BlockShared* bs, uint64_t* cand, SearchScratch* sc, uint16_t* lslot,
+                                                   int psize, int trigger, int pcnt, int k) {
+    Ctx cx;
+    cx.bs = bs; cx.cand = cand; cx.sc = sc; cx.lslot = lslot; cx.wpos = lslot + kMaxK;
+    cx.psize = psize; cx.trigger = trigger;
     LanePriv lp;
     lp.pcnt = pcnt;
     const bool dropped = compact_to_k_body(cx, lp, k);
     return (uint32_t)lp.pcnt | (dropped ? 0x100u : 0u);
 }
 __device__ __forceinline__ bool compact_to_k(const Ctx& cx, LanePriv& lp, int k) {
-    const uint32_t r = compact_to_k_cold(&cx, lp.pcnt, k);
+    const uint32_t r = compact_to_k_cold(cx.bs, cx.cand, cx.sc, cx.lslot, cx.psize, cx.trigger, lp.pcnt, k);
     lp.pcnt = (int)(r & 0xffu);
     return (r >> 8) != 0;
 }
@@ -321,7 +332,7 @@ __device__ __forceinline__ void load_group(const T* tile, const uint32_t* smask,
 #pragma unroll
         for (int i = 0; i < VEC; ++i) v[i] = ((bits >> i) & 1u) ? v[i] : -INFINITY;
     }
-    if (nvalid < kChunk) {  // last tile of the row: nothing beyond the row counts
+    if (nvalid < TileOf<T>::n) {  // last tile of the row: nothing beyond the row counts
 #pragma unroll
         for (int i = 0; i < VEC; ++i)
             if (g * VEC + i >= nvalid) v[i] = -INFINITY;
@@ -610,39 +621,44 @@ __device__ __forceinline__ void process_tile(Ctx& cx, ThreadStats& st, LanePriv&
                                              int c, int c0, int nvalid, bool tile_hist, bool stats, bool collect,
                                              int replay = 0) {
     constexpr int VEC = VecOf<T>::n;
-    constexpr int ITER = kChunk / VEC / kThreads;
+    constexpr int ITER = TileOf<T>::n / VEC / kThreads;
     const float tau = current_tau(cx);
     if (tile_hist) warp_patch<T, kHasMask, kLse>(cx, st, lp, tile, smask, c, c0, nvalid, tau, stats, collect, replay);
     uint32_t ovf = 0;  // elements that found the buffer full (bit j*VEC+i)
-    // all of the thread's groups are loaded before anything depends on them, and the tile
-    // costs one statistics update and one candidate test per thread
-    float v[ITER][VEC], m[ITER];
-#pragma unroll
-    for (int j = 0; j < ITER; ++j) load_group<T, kHasMask>(tile, smask, threadIdx.x + kThreads * j, nvalid, v[j]);
-#pragma unroll
-    for (int j = 0; j < ITER; ++j) m[j] = group_max<VEC>(v[j]);
-    float mt = m[0];
-#pragma unroll
-    for (int j = 1; j < ITER; ++j) mt = max_nan(mt, m[j]);
-    if (stats) {
-        st.mx = max_nan(st.mx, mt);
-        if constexpr (kLse) tile_lse<ITER, VEC>(st, v, mt, cx.c2);
-    }
+    // the thread's groups are taken GB at a time (16 values in registers): all of a batch is
+    // loaded before anything depends on it, and it costs one statistics update and one
+    // candidate test
+    constexpr int GB = 16 / VEC, NB = ITER / GB;
 #ifdef BORN_PROFILE
     const long long ph0 = clock64();
 #endif
-    if (collect && mt >= tau) {  // rare per lane
 #pragma unroll
-        for (int j = 0; j < ITER; ++j) {
-            if (m[j] >= tau) {
-                const int g = threadIdx.x + kThreads * j;
+    for (int h = 0; h < NB; ++h) {
+        float v[GB][VEC], m[GB];
 #pragma unroll
-                for (int i = 0; i < VEC; ++i)
-                    if (v[j][i] >= tau && !lane_put(cx, lp, v[j][i], c0 + g * VEC + i)) ovf |= 1u << (j * VEC + i);
+        for (int j = 0; j < GB; ++j) load_group<T, kHasMask>(tile, smask, threadIdx.x + kThreads * (h * GB + j), nvalid, v[j]);
+#pragma unroll
+        for (int j = 0; j < GB; ++j) m[j] = group_max<VEC>(v[j]);
+        float mt = m[0];
+#pragma unroll
+        for (int j = 1; j < GB; ++j) mt = max_nan(mt, m[j]);
+        if (stats) {
+            st.mx = max_nan(st.mx, mt);
+            if constexpr (kLse) tile_lse<GB, VEC>(st, v, mt, cx.c2);
+        }
+        if (collect && mt >= tau) {  // rare per lane
+#pragma unroll
+            for (int j = 0; j < GB; ++j) {
+                if (m[j] >= tau) {
+                    const int g = threadIdx.x + kThreads * (h * GB + j);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i)
+                        if (v[j][i] >= tau && !lane_put(cx, lp, v[j][i], c0 + g * VEC + i)) ovf |= 1u << ((h * GB + j) * VEC + i);
+                }
             }
         }
+        __syncwarp();
     }
-    __syncwarp();
 #ifdef BORN_PROFILE
     st.pf_hit += clock64() - ph0;
 #endif
@@ -658,32 +674,37 @@ template <typename T, bool kHasMask, bool kLse>
 __device__ __forceinline__ uint32_t fast_tile(const Ctx& cx, ThreadStats& st, LanePriv& lp, const T* tile,
                                               const uint32_t* smask, int c0, float tau) {
     constexpr int VEC = VecOf<T>::n;
-    constexpr int ITER = kChunk / VEC / kThreads;
-    float v[ITER][VEC], m[ITER];
-#pragma unroll
-    for (int j = 0; j < ITER; ++j) load_group<T, kHasMask>(tile, smask, threadIdx.x + kThreads * j, kChunk, v[j]);
-#pragma unroll
-    for (int j = 0; j < ITER; ++j) m[j] = group_max<VEC>(v[j]);
-    float mt = m[0];
-#pragma unroll
-    for (int j = 1; j < ITER; ++j) mt = max_nan(mt, m[j]);
-    st.mx = max_nan(st.mx, mt);
-    if constexpr (kLse) tile_lse<ITER, VEC>(st, v, mt, cx.c2);
+    constexpr int ITER = TileOf<T>::n / VEC / kThreads;
+    constexpr int GB = 16 / VEC, NB = ITER / GB;  // groups per batch of 16 values, batches per tile
     uint32_t ovf = 0;
-    if (mt >= tau) {  // rare per lane
 #pragma unroll
-        for (int j = 0; j < ITER; ++j) {
-            if (m[j] >= tau) {
-                const int g = threadIdx.x + kThreads * j;
+    for (int h = 0; h < NB; ++h) {
+        float v[GB][VEC], m[GB];
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) {
-                    if (v[j][i] >= tau) {
-                        if (lp.pcnt < kPrivPerLane) {
-                            reinterpret_cast<uint2*>(cx.cand)[lp.pcnt * kThreads + threadIdx.x] =
-                                make_uint2((uint32_t)(c0 + g * VEC + i), __float_as_uint(v[j][i]));
-                            ++lp.pcnt;
-                        } else {
-                            ovf |= 1u << (j * VEC + i);
+        for (int j = 0; j < GB; ++j)
+            load_group<T, kHasMask>(tile, smask, threadIdx.x + kThreads * (h * GB + j), TileOf<T>::n, v[j]);
+#pragma unroll
+        for (int j = 0; j < GB; ++j) m[j] = group_max<VEC>(v[j]);
+        float mt = m[0];
+#pragma unroll
+        for (int j = 1; j < GB; ++j) mt = max_nan(mt, m[j]);
+        st.mx = max_nan(st.mx, mt);
+        if constexpr (kLse) tile_lse<GB, VEC>(st, v, mt, cx.c2);
+        if (mt >= tau) {  // rare per lane
+#pragma unroll
+            for (int j = 0; j < GB; ++j) {
+                if (m[j] >= tau) {
+                    const int g = threadIdx.x + kThreads * (h * GB + j);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) {
+                        if (v[j][i] >= tau) {
+                            if (lp.pcnt < kPrivPerLane) {
+                                reinterpret_cast<uint2*>(cx.cand)[lp.pcnt * kThreads + threadIdx.x] =
+                                    make_uint2((uint32_t)(c0 + g * VEC + i), __float_as_uint(v[j][i]));
+                                ++lp.pcnt;
+                            } else {
+                                ovf |= 1u << ((h * GB + j) * VEC + i);
+                            }
                         }
                     }
                 }
@@ -754,7 +775,7 @@ __device__ __forceinline__ void bootstrap_threshold(Ctx& cx, ThreadStats& st) {
 }
 
 // Token history of this slice, bucketed by tile (counting sort: histogram, scan, scatter).
-__device__ __forceinline__ int bucket_history_body(Ctx& cx, const int (&hid)[kHistCap / kThreads], int len, int e_begin, int e_end) {
+__device__ __forceinline__ int bucket_history_body(Ctx& cx, const int (&hid)[kHistCap / kThreads], int len, int e_begin, int e_end, int tile_elems) {
     // the ids are in registers already (thread t holds ids t, t + kThreads, ...); the bucket
     // counters were cleared before the CTA's first barrier
     BlockShared& bs = *cx.bs;
@@ -764,7 +785,7 @@ __device__ __forceinline__ int bucket_history_body(Ctx& cx, const int (&hid)[kHi
     for (int k = 0; k < kHistCap / kThreads; ++k) {
         const int id = hid[k];
         const bool in = (tid + k * kThreads < len) && (id >= e_begin && id < e_end);
-        bkt[k] = in ? (((id - e_begin) / kChunk) >> cx.hshift) : -1;
+        bkt[k] = in ? (((id - e_begin) / tile_elems) >> cx.hshift) : -1;
         if (in) smem_red_add(&bs.hcur[bkt[k]], 1u);
     }
     cta_sync();
@@ -792,7 +813,7 @@ __device__ __forceinline__ int bucket_history_body(Ctx& cx, const int (&hid)[kHi
     const int total = bs.hoff[kHistBuckets];
     for (int i = tid; i < total; i += kThreads) {
         const int id = cx.hlist[i];
-        const int b = ((id - e_begin) / kChunk) >> cx.hshift;
+        const int b = ((id - e_begin) / tile_elems) >> cx.hshift;
         const int lo = bs.hoff[b], hi = bs.hoff[b + 1];
         int cnt = 0;
         bool first = true;
@@ -807,9 +828,9 @@ __device__ __forceinline__ int bucket_history_body(Ctx& cx, const int (&hid)[kHi
     return total;
 }
 
-__device__ __forceinline__ int bucket_history(const Ctx* sh, const int (&hid)[kHistCap / kThreads], int len, int e_begin, int e_end) {
+__device__ __forceinline__ int bucket_history(const Ctx* sh, const int (&hid)[kHistCap / kThreads], int len, int e_begin, int e_end, int tile_elems) {
     Ctx cx = *sh;
-    return bucket_history_body(cx, hid, len, e_begin, e_end);
+    return bucket_history_body(cx, hid, len, e_begin, e_end, tile_elems);
 }
 
 template <typename T, bool kHasMask, bool kLse>
@@ -825,6 +846,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     const int e_begin = slice * A.slice_len;
     const int e_end = min(A.V, e_begin + A.slice_len);
     const int nelem = max(0, e_end - e_begin);
+    constexpr int kChunk = TileOf<T>::n;  // logits per pipeline stage
     const int nchunks = (A.mode == kModeMerge) ? 0 : (nelem + kChunk - 1) / kChunk;
     const T* grow = reinterpret_cast<const T*>(A.logits) + (int64_t)row * A.row_stride + e_begin;
     const uint32_t* gmask = kHasMask ? A.mask + (int64_t)row * A.mask_stride + (e_begin >> 5) : nullptr;
@@ -1007,7 +1029,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         bool has_hist = false;
         if (hist_arg && pen_on) {
             const int len = max(0, min(min(hist_len0, A.history_stride), kHistCap));
-            const int nh = bucket_history(&cx, hid, len, e_begin, e_end);
+            const int nh = bucket_history(&cx, hid, len, e_begin, e_end, kChunk);
             has_hist = nh > 0 && !producer_patches;  // otherwise the tiles arrive patched
             if (producer_patches && tid == 0) {
                 __threadfence_block();
@@ -1229,7 +1251,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             const int sc = min(bs.count, kCandCap - cx.psize);
             // nothing below the slice's final bounds can be among the row's k best or pass min-p
             float tau_rec = (cx.k_eff <= kThreads) ? zkey_to_float(bs.taubits) : -INFINITY;
-            if (cx.minp_on && m_slice == m_slice) tau_rec = fmaxf(tau_rec, m_slice + cx.delta_minp);
+            if (cx.minp_on && m_slice == m_slice && !(rp.top_k <= 0 && bs.dropped)) tau_rec = fmaxf(tau_rec, m_slice + cx.delta_minp);
             if (exact_rec) tau_rec = -INFINITY;  // after the compaction: exactly the k best
             if (tid == 0) bs.nl = 0;
             cta_sync();
@@ -1245,7 +1267,8 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             if (tid == 0) {
                 RecordHdr h;
                 h.m = m_slice; h.lse_s = s_slice; h.count = (uint32_t)n; h.flags = (uint32_t)bs.dropped;
-                h.pad[0] = h.pad[1] = h.pad[2] = h.pad[3] = 0;
+                h.bound = (cx.k_eff <= kThreads && !greedy) ? zkey_to_float(bs.taubits) : -INFINITY;
+                h.pad[0] = h.pad[1] = h.pad[2] = 0;
                 *reinterpret_cast<RecordHdr*>(rec) = h;
             }
             if (A.mode == kModeLocal) return;
@@ -1269,29 +1292,66 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         lp.pcnt = 0;
         cx.psize = 0;  // the whole buffer is one shared area from here on
         cta_sync();
+        // Headers first (all of them at once: the loads are independent), then the entries of
+        // every record in one sweep without a barrier in between.  Entries below the best of
+        // the slices' own bounds, or below the min-p cut of the row maximum, are left out.
         m_row = -INFINITY;
+        float tau_row = -INFINITY;
+        int total = 0;
+#pragma unroll 4
         for (int s = 0; s < A.S; ++s) {
             const uint8_t* rec = A.records + (int64_t)row * A.rec_row_stride + (int64_t)s * A.rec_slice_stride;
-            m_row = max_nan(m_row, __ldcg(reinterpret_cast<const float*>(rec)));
+            const uint4 h0 = __ldcg(reinterpret_cast<const uint4*>(rec));
+            const float b0 = __ldcg(reinterpret_cast<const float*>(rec) + 4);
+            m_row = max_nan(m_row, __uint_as_float(h0.x));
+            tau_row = fmaxf(tau_row, b0);
+            total += (int)h0.z;
+            dropped |= (int)(h0.w & 1u);
         }
+        if (A.segment_mode) tau_row = -INFINITY;  // segments keep exactly their k best
+        else if (cx.minp_on && m_row == m_row && !(rp.top_k <= 0 && dropped))
+            tau_row = fmaxf(tau_row, m_row + cx.delta_minp);  // (a row that lost entries must show its lowest one)
+        if (tid == 0) bs.nw = 0;
+        cta_sync();
+#pragma unroll 2
         for (int s = 0; s < A.S; ++s) {
             const uint8_t* rec = A.records + (int64_t)row * A.rec_row_stride + (int64_t)s * A.rec_slice_stride;
-            const float ms_ = __ldcg(reinterpret_cast<const float*>(rec));
-            const float ss_ = __ldcg(reinterpret_cast<const float*>(rec) + 1);
-            const int cnt = (int)__ldcg(reinterpret_cast<const uint32_t*>(rec) + 2);
-            dropped |= (int)(__ldcg(reinterpret_cast<const uint32_t*>(rec) + 3) & 1u);
+            const uint4 h0 = __ldcg(reinterpret_cast<const uint4*>(rec));
+            const float ms_ = __uint_as_float(h0.x), ss_ = __uint_as_float(h0.y);
+            const int cnt = (int)h0.z;
             if (kLse && ss_ > 0.0f) lse_sum += ss_ * ex2_approx(__fmul_rn(ms_ - m_row, cx.c2));
-            if (!A.segment_mode && bs.count + cnt > kCandCap) compact_to_k(cx, lp, cx.k_eff);
-            const int base = bs.count;
             const unsigned long long* ent = reinterpret_cast<const unsigned long long*>(rec + kRecordHdrBytes);
-            for (int i = tid; i < cnt && base + i < kCandCap; i += kThreads) {
+            for (int i = tid; i < cnt; i += kThreads) {
                 const uint64_t e = __ldcg(ent + i);
-                cx.cand[base + i] = ck_alive(e) ? e : (uint64_t)(base + i);  // dead slots stay unique
+                if (ck_alive(e) && ck_z(e) >= tau_row) {
+                    const int pos = (int)smem_atom_add(&bs.count, 1u);
+                    if (pos < kCandCap) cx.cand[pos] = e;
+                    else bs.nw = 1;  // does not fit: redo record by record with compactions
+                }
             }
-            cta_sync();
-            if (tid == 0) bs.count = min(base + cnt, kCandCap);
-            cta_sync();
         }
+        cta_sync();
+        const bool refill = bs.nw != 0;
+        cta_sync();
+        if (refill) {
+            if (tid == 0) bs.count = 0;
+            cta_sync();
+            for (int s = 0; s < A.S; ++s) {
+                const uint8_t* rec = A.records + (int64_t)row * A.rec_row_stride + (int64_t)s * A.rec_slice_stride;
+                const int cnt = (int)__ldcg(reinterpret_cast<const uint32_t*>(rec) + 2);
+                if (!A.segment_mode && bs.count + cnt > kCandCap) compact_to_k(cx, lp, cx.k_eff);
+                const int base = bs.count;
+                const unsigned long long* ent = reinterpret_cast<const unsigned long long*>(rec + kRecordHdrBytes);
+                for (int i = tid; i < cnt && base + i < kCandCap; i += kThreads) {
+                    const uint64_t e = __ldcg(ent + i);
+                    cx.cand[base + i] = ck_alive(e) ? e : (uint64_t)(base + i);  // dead slots stay unique
+                }
+                cta_sync();
+                if (tid == 0) bs.count = min(base + cnt, kCandCap);
+                cta_sync();
+            }
+        }
+        (void)total;
     }
 
     // ------------------------------------------------------------- selection and draw
@@ -1378,7 +1438,6 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     BORN_PROF(24);
 #ifdef BORN_PROFILE
     if (A.prof && tid == 0) A.prof[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 32 + 14] = (unsigned long long)na;
-    if (A.prof) atomicAdd(&A.prof[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 32 + 13], (unsigned long long)lp.pcnt + (tid == 0 ? (unsigned long long)sc_g : 0ull));
 #endif
     if (na <= kSmallSet) {
         // ---- small set: everything by all-pairs comparison (no sort, no histogram): rank for

@@ -13,7 +13,7 @@
 namespace born {
 
 constexpr int kThreads = 256;        // threads per CTA in the row kernels
-constexpr int kChunk = 4096;         // logits per pipeline stage
+constexpr int kTileBytes = 16384;    // bytes of logits per pipeline stage (4096 fp32 / 8192 bf16)
 constexpr int kStages = 5;           // bulk-copy stages in flight per CTA
 constexpr int kMaxK = 1024;          // BORN_MAX_TOP_K / BORN_MAX_CANDIDATES
 constexpr int kCandCap = 2048;       // candidate buffer entries (>= kMaxK + one half piece)

@@ -52,7 +52,8 @@ def key_to_float(k):
 def encode_records(shard_logits, top_k, idx_offset, inv_T=1.0):
     """Records of one shard: [rows, record_bytes(top_k)] uint8.
 
-    Header: float32 max, float32 sum of 2^((z-max)*inv_T*log2e), uint32 count, uint32 flags.
+    Header: float32 max, float32 sum of 2^((z-max)*inv_T*log2e), uint32 count, uint32 flags,
+    float32 bound (a value that at least top_k tokens of the shard reach; -inf = none).
     Entries: uint64 rank keys (value key << 24 | (0xFFFFFF - global index)), best first is not
     required; unused entries are 0."""
     z = np.ascontiguousarray(shard_logits, dtype=np.float32)
@@ -71,6 +72,7 @@ def encode_records(shard_logits, top_k, idx_offset, inv_T=1.0):
         hdr[4:8] = np.array([s], dtype=np.float32).view(np.uint8)
         hdr[8:12] = np.array([len(order)], dtype=np.uint32).view(np.uint8)
         hdr[12:16] = np.array([1 if len(fin) > top_k else 0], dtype=np.uint32).view(np.uint8)
+        hdr[16:20] = np.array([-np.inf], dtype=np.float32).view(np.uint8)
         out[r, RECORD_HDR_BYTES:RECORD_HDR_BYTES + 8 * len(order)] = keys.view(np.uint8)
     return out
 

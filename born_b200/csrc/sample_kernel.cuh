@@ -1206,13 +1206,11 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             cta_sync();
             return;
         }
-        const bool own_row = (A.mode == kModeFull && A.S == 1);
         // A record that stands for a vocabulary shard or segment holds exactly its k best (that
         // is the algorithm's definition); a plain slice record of a row that is finished on this
         // GPU may hold any superset of them that fits.
         const bool exact_rec = (A.mode == kModeLocal) || A.segment_mode;
         const int rec_cap = exact_rec ? cx.k_eff : kMaxK;
-        if (!own_row) compact_to_k(cx, lp, rec_cap);
         cta_sync();
 
         // slice statistics
@@ -1248,25 +1246,73 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             // leave the record, then take a ticket; only the last CTA of the row goes on
             uint8_t* rec = A.records + (int64_t)row * A.rec_row_stride + (int64_t)slice * A.rec_slice_stride;
             uint64_t* ent = reinterpret_cast<uint64_t*>(rec + kRecordHdrBytes);
-            const int sc = min(bs.count, kCandCap - cx.psize);
-            // nothing below the slice's final bounds can be among the row's k best or pass min-p
-            float tau_rec = (cx.k_eff <= kThreads) ? zkey_to_float(bs.taubits) : -INFINITY;
-            if (cx.minp_on && m_slice == m_slice && !(rp.top_k <= 0 && bs.dropped)) tau_rec = fmaxf(tau_rec, m_slice + cx.delta_minp);
-            if (exact_rec) tau_rec = -INFINITY;  // after the compaction: exactly the k best
-            if (tid == 0) bs.nl = 0;
-            cta_sync();
-            for (int i = tid; i < kCandCap; i += kThreads) {
-                const uint64_t e = slot_key(cx, lp, i, sc);
-                if (ck_alive(e) && ck_z(e) >= tau_rec) {
-                    const int pos = (int)smem_atom_add(&bs.nl, 1u);
-                    if (pos < rec_cap) ent[pos] = e - (uint64_t)A.idx_offset;
+            int n = -1;
+            uint32_t rec_flags = 0;
+            if (exact_rec && cx.k_eff <= kThreads) {
+                // Exactly the k best, without a radix select: the entries at or above the final
+                // lane-maxima bound (a few more than k) are ranked against each other, several
+                // threads to an entry, and an entry of rank r < k goes to position r.
+                uint64_t* sel = reinterpret_cast<uint64_t*>(smem + L.search);
+                const float tb = zkey_to_float(bs.taubits);
+                const int scx = min(bs.count, kCandCap - cx.psize);
+                if (tid == 0) bs.nl = 0;
+                cta_sync();
+                if (cx.psize) {
+                    for (int s = 0; s < lp.pcnt; ++s) {
+                        const uint64_t raw = cx.cand[s * kThreads + tid];
+                        if (__uint_as_float((uint32_t)(raw >> 32)) >= tb) {
+                            const int pos = (int)smem_atom_add(&bs.nl, 1u);
+                            if (pos < kSmallSet) sel[pos] = raw_to_ck(raw);
+                        }
+                    }
                 }
+                for (int i = tid; i < scx; i += kThreads) {
+                    const uint64_t e = cx.cand[cx.psize + i];
+                    if (ck_alive(e) && ck_z(e) >= tb) {
+                        const int pos = (int)smem_atom_add(&bs.nl, 1u);
+                        if (pos < kSmallSet) sel[pos] = e;
+                    }
+                }
+                cta_sync();
+                const int na = bs.nl;
+                if (na <= kSmallSet) {
+                    int lg = 0;
+                    while (lg < 5 && (na << (lg + 1)) <= kThreads) ++lg;
+                    const int P = 1 << lg, part = tid & (P - 1), e_i = tid >> lg;
+                    const uint64_t ck = (e_i < na) ? sel[e_i] : 0ull;
+                    int rank = 0;
+                    for (int j2 = part; j2 < na; j2 += P) rank += (sel[j2] > ck) ? 1 : 0;
+                    for (int d = 1; d < P; d <<= 1) rank += __shfl_xor_sync(0xffffffffu, rank, d);
+                    if (e_i < na && part == 0 && rank < cx.k_eff) ent[rank] = ck - (uint64_t)A.idx_offset;
+                    n = min(na, cx.k_eff);
+                    rec_flags = (uint32_t)(bs.dropped | (na > cx.k_eff ? 1 : 0));
+                }
+                cta_sync();
             }
-            cta_sync();
-            const int n = min(bs.nl, rec_cap);
+            if (n < 0) {
+                compact_to_k(cx, lp, rec_cap);
+                cta_sync();
+                const int sc = min(bs.count, kCandCap - cx.psize);
+                // nothing below the slice's final bounds can be among the row's k best or pass min-p
+                float tau_rec = (cx.k_eff <= kThreads) ? zkey_to_float(bs.taubits) : -INFINITY;
+                if (cx.minp_on && m_slice == m_slice && !(rp.top_k <= 0 && bs.dropped)) tau_rec = fmaxf(tau_rec, m_slice + cx.delta_minp);
+                if (exact_rec) tau_rec = -INFINITY;  // after the compaction: exactly the k best
+                if (tid == 0) bs.nl = 0;
+                cta_sync();
+                for (int i = tid; i < kCandCap; i += kThreads) {
+                    const uint64_t e = slot_key(cx, lp, i, sc);
+                    if (ck_alive(e) && ck_z(e) >= tau_rec) {
+                        const int pos = (int)smem_atom_add(&bs.nl, 1u);
+                        if (pos < rec_cap) ent[pos] = e - (uint64_t)A.idx_offset;
+                    }
+                }
+                cta_sync();
+                n = min(bs.nl, rec_cap);
+                rec_flags = (uint32_t)bs.dropped;
+            }
             if (tid == 0) {
                 RecordHdr h;
-                h.m = m_slice; h.lse_s = s_slice; h.count = (uint32_t)n; h.flags = (uint32_t)bs.dropped;
+                h.m = m_slice; h.lse_s = s_slice; h.count = (uint32_t)n; h.flags = rec_flags;
                 h.bound = (cx.k_eff <= kThreads && !greedy) ? zkey_to_float(bs.taubits) : -INFINITY;
                 h.pad[0] = h.pad[1] = h.pad[2] = 0;
                 *reinterpret_cast<RecordHdr*>(rec) = h;

@@ -133,6 +133,7 @@ struct BlockShared {  // static shared state of a CTA
     unsigned long long red64[kThreads / 32];
     unsigned long long acc[4];  // block-wide integer sums of the final selection (shared-memory atomics)
     float redf[kThreads / 32];
+    float redf2[kThreads / 32];
     float wbound[kThreads / 32];  // per warp: a lower bound of the k-th largest value (lane maxima)
     uint32_t taubits;  // key of tau; only ever raised (red.max)
     uint32_t maxbits;
@@ -1213,29 +1214,36 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         const int rec_cap = exact_rec ? cx.k_eff : kMaxK;
         cta_sync();
 
-        // slice statistics
+        // slice statistics: every warp reduces its maximum and, relative to that, its share of
+        // the log-sum-exp by shuffles; the eight pairs meet in shared memory behind one barrier
         float wm = st.mx;
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) wm = max_nan(wm, __shfl_xor_sync(0xffffffffu, wm, d));
-        if ((tid & 31) == 0) bs.redf[tid >> 5] = wm;
+        float wsum = 0.0f;
+        if (kLse) {
+            const float ssum = st.s.x + st.s.y;
+            wsum = ssum * ex2_approx(__fmul_rn(st.R - wm, cx.c2));
+            if (!(ssum > 0.0f) || !(wm == wm)) wsum = 0.0f;
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, d);
+        }
+        if ((tid & 31) == 0) {
+            bs.redf[tid >> 5] = wm;
+            bs.redf2[tid >> 5] = wsum;
+        }
         cta_sync();
         float m_slice = bs.redf[0];
 #pragma unroll
         for (int w = 1; w < kThreads / 32; ++w) m_slice = max_nan(m_slice, bs.redf[w]);
-        cta_sync();
         float s_slice = 0.0f;
         if (kLse) {
-            const float ssum = st.s.x + st.s.y;
-            float v = ssum * ex2_approx(__fmul_rn(st.R - m_slice, cx.c2));
-            if (!(ssum > 0.0f)) v = 0.0f;
 #pragma unroll
-            for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
-            if ((tid & 31) == 0) bs.redf[tid >> 5] = v;
-            cta_sync();
-#pragma unroll
-            for (int w = 0; w < kThreads / 32; ++w) s_slice += bs.redf[w];
-            cta_sync();
+            for (int w = 0; w < kThreads / 32; ++w) {
+                const float ws = bs.redf2[w];
+                if (ws > 0.0f) s_slice += ws * ex2_approx(__fmul_rn(bs.redf[w] - m_slice, cx.c2));
+            }
         }
+        cta_sync();
         BORN_PROF(4);
 
         if (A.mode == kModeFull && A.S == 1) {

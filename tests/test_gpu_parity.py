@@ -195,6 +195,29 @@ def test_sorted_rows_exercise_buffer_overflow_path(sampler, oracle):
         assert_parity(got, ref)
 
 
+def test_small_batches_are_cut_into_slices_and_merged(sampler, oracle):
+    # fewer rows than SMs: every row is streamed by several CTAs whose records the last one
+    # merges -- filtered supersets, the slices' own top-k bounds, the min-p cut of the row maximum,
+    # and (top-k 200: more merged entries than the all-pairs path takes) the cut to the k best
+    B, V = 3, 128256
+    z = (W.normal(21, 1, B * V) * 3.0).astype(np.float32).reshape(B, V)
+    z[1, ::7] = 2.5  # ties across slices
+    u = W.uniform_f32(21, 2, B)
+    hist = W.randint(21, 3, B * 96, V).astype(np.int32).reshape(B, 96)
+    for p, h in ((dict(temperature=0.7, top_k=200, top_p=0.9), None),
+                 (dict(temperature=0.7, top_k=40), None),
+                 (dict(temperature=0.9, min_p=0.02, top_p=0.95, frequency_penalty=0.4, presence_penalty=0.2), hist),
+                 (dict(temperature=1.0, top_k=8, repetition_penalty=1.3), hist),
+                 (dict(greedy=True), None)):
+        got, ref = run_both(sampler, oracle, z, p, u, hist=h, want_kept=256)
+        assert_parity(got, ref)
+    zb = W.f32_to_bf16_bits((W.normal(22, 1, 2 * 151936) * 2.5).astype(np.float32)).reshape(2, 151936)
+    ub = W.uniform_f32(22, 2, 2)
+    for p in (dict(temperature=1.0, top_k=64, top_p=0.9), dict(temperature=0.8, min_p=0.05)):
+        got, ref = run_both(sampler, oracle, zb, p, ub, want_kept=128)
+        assert_parity(got, ref)
+
+
 def test_invalid_rows_report_status(sampler, oracle):
     B, V = 6, 5000
     z = (W.normal(5, 1, B * V)).astype(np.float32).reshape(B, V)

@@ -48,6 +48,7 @@ struct Handle {
     int* dev_error = nullptr;
     uint8_t* spec_scratch = nullptr;
     size_t spec_scratch_bytes = 0;
+    int64_t spec_layout_key = -1;
     Staging stage[16];
     cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
     float timing[3] = {0, 0, 0};
@@ -219,13 +220,8 @@ int32_t born_sampler_create(int32_t device, int32_t max_batch, int32_t max_vocab
     int rc = dev_alloc(h, (void**)&h->records, (size_t)h->max_records * (size_t)h->record_stride);
     if (rc == BORN_OK) rc = dev_alloc(h, (void**)&h->tickets, sizeof(uint32_t) * (size_t)max_batch * 2);
     if (rc == BORN_OK) rc = dev_alloc(h, (void**)&h->dev_error, sizeof(int));
-    if (rc == BORN_OK) {
-        h->spec_scratch_bytes = spec_scratch_bytes(max_batch);
-        rc = dev_alloc(h, (void**)&h->spec_scratch, h->spec_scratch_bytes);
-    }
     if (rc == BORN_OK && cudaMemset(h->tickets, 0, sizeof(uint32_t) * (size_t)max_batch * 2) != cudaSuccess) rc = BORN_ERR_CUDA;
     if (rc == BORN_OK && cudaMemset(h->dev_error, 0, sizeof(int)) != cudaSuccess) rc = BORN_ERR_CUDA;
-    if (rc == BORN_OK && cudaMemset(h->spec_scratch, 0, h->spec_scratch_bytes) != cudaSuccess) rc = BORN_ERR_CUDA;
     for (int i = 0; i < 4 && rc == BORN_OK; ++i)
         if (cudaEventCreate(&h->ev[i]) != cudaSuccess) rc = BORN_ERR_CUDA;
     if (rc != BORN_OK) {
@@ -465,15 +461,33 @@ int32_t born_spec_verify(void* handle, const born_spec_args* a, void* stream) {
     memset(&A, 0, sizeof A);
     A.B = B; A.K = K; A.V = V; A.target_rows = R;
     A.inv_T = a->temperature == 0.0f ? 1.0f : 1.0f / a->temperature;
-    A.scratch = h->spec_scratch;
+    // scratch of the speculative path (tickets, chunk sums, block results): grown on first use
+    // like the staging mirrors, then reused; the tickets are zero between launches
+    const SpecScratchLayout SL = spec_scratch_layout(B, K, V);
+    if (h->spec_scratch_bytes < SL.total) {
+        CUDA_TRY(h, cudaStreamSynchronize(st));
+        if (h->spec_scratch) { cudaFree(h->spec_scratch); h->workspace -= (int64_t)h->spec_scratch_bytes; h->spec_scratch = nullptr; h->spec_scratch_bytes = 0; }
+        int rc0 = dev_alloc(h, (void**)&h->spec_scratch, SL.total);
+        if (rc0 != BORN_OK) return rc0;
+        h->spec_scratch_bytes = SL.total;
+        h->spec_layout_key = -1;
+    }
+    // the ticket area sits at offset 0 whatever the shape; it is cleared when the layout changes
+    if (h->spec_layout_key != ((int64_t)B << 40 | (int64_t)K << 32 | (int64_t)V)) {
+        CUDA_TRY(h, cudaMemsetAsync(h->spec_scratch, 0, SL.csum, st));
+        h->spec_layout_key = ((int64_t)B << 40 | (int64_t)K << 32 | (int64_t)V);
+    }
+    A.tickets = reinterpret_cast<uint32_t*>(h->spec_scratch + SL.tickets);
+    A.csum = reinterpret_cast<unsigned long long*>(h->spec_scratch + SL.csum);
+    A.blocks = reinterpret_cast<BlockMass*>(h->spec_scratch + SL.blocks);
     A.dev_error = h->dev_error;
     if (a->memory == BORN_MEM_DEVICE) {
         A.target = a->target_logits; A.draft = a->draft_logits; A.draft_tok = a->draft_tokens;
         A.u_accept = a->u_accept; A.u_resample = a->u_resample;
         A.accept_len = a->out_accept_len; A.out_tok = a->out_tokens; A.status = a->out_status;
-        int rc = launch_spec(A, st);
+        int rc = launch_spec(A, h->num_sms, st);
         if (rc != 0) return fail(h, BORN_ERR_CUDA, "spec kernel launch failed: %s", cudaGetErrorString((cudaError_t)rc));
-        h->launches++;
+        h->launches += 2;
         return BORN_OK;
     }
     if (a->memory != BORN_MEM_HOST) return fail(h, BORN_ERR_INVALID_ARGUMENT, "memory");
@@ -498,9 +512,9 @@ int32_t born_spec_verify(void* handle, const born_spec_args* a, void* stream) {
     A.u_resample = (const float*)h->stage[4].p;
     A.accept_len = (int32_t*)h->stage[6].p; A.out_tok = (int32_t*)h->stage[7].p; A.status = (int32_t*)h->stage[9].p;
     CUDA_TRY(h, cudaEventRecord(h->ev[1], st));
-    rc = launch_spec(A, st);
+    rc = launch_spec(A, h->num_sms, st);
     if (rc != 0) return fail(h, BORN_ERR_CUDA, "spec kernel launch failed: %s", cudaGetErrorString((cudaError_t)rc));
-    h->launches++;
+    h->launches += 2;
     CUDA_TRY(h, cudaEventRecord(h->ev[2], st));
     CUDA_TRY(h, cudaMemcpyAsync(a->out_accept_len, A.accept_len, (size_t)B * 4, cudaMemcpyDeviceToHost, st));
     CUDA_TRY(h, cudaMemcpyAsync(a->out_tokens, A.out_tok, (size_t)B * (K + 1) * 4, cudaMemcpyDeviceToHost, st));

@@ -1,18 +1,20 @@
 // Speculative-decoding verification: accept/reject of K draft tokens per sequence and the
-// resampling draw from the residual distribution max(0, p - q), in one launch.
+// resampling draw from the residual distribution max(0, p - q), in two launches.
 //
-// CTA (j, b) owns draft position j of sequence b.  It streams the target row p_j and the
-// draft row q_j once through a ring of shared-memory tiles filled by 1-D bulk copies
-// (TMA, non-multicast) and computes, per block of 1024 tokens, the block maximum and the
-// exact fixed-point mass of the block relative to it (one warp per block: warp-shuffle
-// max, deterministic exp, integer warp sum).  The row totals follow from the block
-// results with one rescale per block, so the accept test
+// Launch 1 (spec_mass_kernel) treats every row of the call on its own -- (K+1) target rows
+// and K draft rows per sequence -- and cuts it into contiguous ranges of tiles so that the GPU
+// sees a few waves of CTAs whatever the batch.  A CTA streams its tiles through a ring of
+// shared-memory stages filled by 1-D bulk copies (TMA, non-multicast) and leaves, per block of
+// 1024 tokens, the block maximum and the exact fixed-point mass of the block relative to it
+// (one warp per block: warp-shuffle max, deterministic exp, integer warp sum).
+//
+// Launch 2 (spec_draw_kernel) gives every sequence kSpecParts CTAs.  Each of them folds the
+// block results into row maxima and row totals (one rescale per block), runs the accept tests
 //     u * q(x) < p(x)   <=>   (u * wq_x) * S_p < wp_x * S_q
-// needs a single pass over HBM.  A position that rejects draws its replacement token right
-// away (a second pass over its two rows, normally served by L2): per-chunk sums of the
-// residual masses, then a scan inside the one chunk the target falls into.  The extra CTA
-// (K, b) draws the bonus token from the last target row.  The last CTA of a sequence to
-// finish (atomic ticket, no spinning) picks the first rejection and writes the outputs.
+// and so knows the first rejecting position (or that the bonus token is due).  Only that
+// position is drawn: the CTAs share its chunks of 4096 tokens, leave the chunk sums of the
+// residual masses in scratch, and the last one to finish (atomic ticket, no spinning) picks
+// the chunk the target falls into, scans inside it and writes the sequence's outputs.
 //
 // The row arithmetic keeps the reference's shape -- maximum, exp of the shifted logits, sum
 // (born: internal/autodiff/ops/softmax.go:214-238) -- with integer masses in place of the
@@ -30,18 +32,33 @@ constexpr int kMassBlock = 1024;  // tokens per mass block, aligned to the row s
 constexpr int kSpecMaxBlocks = 512;  // => vocab <= 524,288 on this path
 constexpr int kSpecHalf = kSpecTile / 2;  // tokens per chunk in the paired (p, q) pass
 constexpr int kSpecMaxChunks = kSpecMaxBlocks * kMassBlock / kSpecHalf;
+constexpr int kSpecParts = 8;  // CTAs per sequence in the draw launch
+constexpr int kSpecMaxRows = 2 * BORN_MAX_DRAFT + 1;
 constexpr int kRowBadToken = 5;
+static_assert(kSpecThreads == kThreads, "the block helpers in spec.cuh are sized for kThreads");
 
-struct SeqScratch {  // 256 bytes per sequence, zero between launches
-    uint32_t ticket;
-    int32_t pos_status[BORN_MAX_DRAFT + 1];
-    int32_t accept[BORN_MAX_DRAFT];
-    int32_t token[BORN_MAX_DRAFT + 1];
-    int32_t pad[13];
+struct BlockMass {  // result of one 1024-token block
+    float m;               // block maximum (NaN if the block holds one)
+    uint32_t pad;
+    unsigned long long M;  // sum of the fixed-point masses relative to m
 };
-static_assert(sizeof(SeqScratch) == 256, "SeqScratch size");
+static_assert(sizeof(BlockMass) == 16, "BlockMass size");
 
-inline size_t spec_scratch_bytes(int max_batch) { return sizeof(SeqScratch) * (size_t)max_batch; }
+// Scratch of one call: per-sequence tickets (zero between launches), chunk sums of the draw,
+// block results of every row.
+struct SpecScratchLayout {
+    size_t tickets, csum, blocks, total;
+};
+inline SpecScratchLayout spec_scratch_layout(int B, int K, int V) {
+    SpecScratchLayout L;
+    const size_t nblk = (size_t)(V + kMassBlock - 1) / kMassBlock, nchb = (size_t)(V + kSpecHalf - 1) / kSpecHalf;
+    size_t off = 0;
+    L.tickets = off; off += ((size_t)B * 4 + 255) / 256 * 256;
+    L.csum = off; off += ((size_t)B * nchb * 8 + 255) / 256 * 256;
+    L.blocks = off; off += (size_t)B * (2 * K + 1) * nblk * sizeof(BlockMass);
+    L.total = off;
+    return L;
+}
 
 struct SpecKernelArgs {
     const float* target;
@@ -52,26 +69,13 @@ struct SpecKernelArgs {
     int32_t* accept_len;
     int32_t* out_tok;
     int32_t* status;
-    uint8_t* scratch;
+    uint32_t* tickets;
+    unsigned long long* csum;
+    BlockMass* blocks;
     int* dev_error;
     int B, K, V, target_rows;
     float inv_T;
     int tma;
-};
-
-struct SpecShared {
-    unsigned long long bars[kSpecStages];
-    unsigned long long red64[kSpecThreads / 32];
-    unsigned long long scan[kSpecThreads / 32];
-    float blk_m[2][kSpecMaxBlocks];
-    unsigned long long blk_M[2][kSpecMaxBlocks];
-    unsigned long long csum[kSpecMaxChunks];
-    float redf[kSpecThreads / 32];
-    int fail;
-    int last;
-    int pick_chunk;
-    unsigned long long pick_before;
-    int token;
 };
 
 struct SpecPipe {  // ring of tiles; `it` counts every tile ever issued/consumed by this CTA
@@ -92,6 +96,21 @@ __device__ __forceinline__ void spec_issue(SpecPipe& P, const float* src0, int n
     bulk_load(dst, src0, b0, bar);
     if (src1) bulk_load(dst + kSpecHalf, src1, b1, bar);
     P.issued++;
+}
+
+// Consume side: wait for the next tile (or fill it with plain loads when rows are not 16-byte
+// aligned).  A timeout sets *fail.
+__device__ __forceinline__ float* spec_acquire(SpecPipe& P, const float* src0, int n0, const float* src1, int n1, int* fail) {
+    float* t = P.tile(P.consumed);
+    if (P.tma) {
+        if (!mbar_wait(P.bar(P.consumed), (P.consumed / kSpecStages) & 1u)) *fail = 1;
+    } else {
+        for (int i = threadIdx.x; i < n0; i += kSpecThreads) t[i] = src0[i];
+        if (src1) for (int i = threadIdx.x; i < n1; i += kSpecThreads) t[kSpecHalf + i] = src1[i];
+        __syncthreads();
+    }
+    P.consumed++;
+    return t;
 }
 
 // Exclusive block scan helper: returns the exclusive prefix of v over threads, total in *tot.
@@ -117,7 +136,7 @@ __device__ __forceinline__ uint64_t block_excl_scan_u64(uint64_t v, unsigned lon
     return base + incl - v;
 }
 
-// Weight of token i in the draw of this CTA: residual max(0, p - q) or the plain mass of p.
+// Weight of token i in the draw: residual max(0, p - q) or the plain mass of p.
 struct DrawCtx {
     int residual;  // 1: max(0, p_i - q_i); 0: mass of p_i
     float mp, mq, inv_T, invSp, invSq;
@@ -133,14 +152,24 @@ __device__ __forceinline__ uint64_t draw_weight(const DrawCtx& D, float zp, floa
     return mass_of(scaled_shift(zp, D.mp, D.inv_T));
 }
 
-__global__ void __launch_bounds__(kSpecThreads, 2) spec_verify_kernel(const SpecKernelArgs A) {
+// ------------------------------------------------------------------ launch 1: block masses
+struct MassShared {
+    unsigned long long bars[kSpecStages];
+    int fail;
+};
+
+__global__ void __launch_bounds__(kSpecThreads, 2) spec_mass_kernel(const SpecKernelArgs A) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ SpecShared sh;
+    __shared__ MassShared sh;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int j = blockIdx.x, b = blockIdx.y;
-    const int K = A.K, V = A.V;
-    const bool bonus = (j == K);
-    SeqScratch* seq = reinterpret_cast<SeqScratch*>(A.scratch) + b;
+    const int row = blockIdx.y, V = A.V;
+    const int ntarget = A.B * A.target_rows;
+    const float* src_row = row < ntarget ? A.target + (int64_t)row * V : A.draft + (int64_t)(row - ntarget) * V;
+    const int nch = (V + kSpecTile - 1) / kSpecTile;
+    const int nblk = (V + kMassBlock - 1) / kMassBlock;
+    const int per = (nch + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int t_lo = blockIdx.x * per, t_hi = min(nch, t_lo + per);
+    if (t_lo >= t_hi) return;
 
     SpecPipe P;
     P.tiles = reinterpret_cast<float*>(smem);
@@ -151,48 +180,15 @@ __global__ void __launch_bounds__(kSpecThreads, 2) spec_verify_kernel(const Spec
         for (int s = 0; s < kSpecStages; ++s) mbar_init(reinterpret_cast<uint64_t*>(&sh.bars[s]), 1);
         mbar_fence_init();
         sh.fail = 0;
-        sh.last = 0;
     }
     __syncthreads();
-
-    const float* rowp = A.target + ((int64_t)b * A.target_rows + j) * (int64_t)V;
-    const float* rowq = bonus ? nullptr : A.draft + ((int64_t)b * K + j) * (int64_t)V;
-    const int nrows = bonus ? 1 : 2;
-    const int nch = (V + kSpecTile - 1) / kSpecTile;
-    const int nblk = (V + kMassBlock - 1) / kMassBlock;
-
-    // tile `t` of pass A: row t / nch, chunk t % nch
-    auto issue_a = [&](int t) {
-        const int r = t / nch, cc = t % nch;
-        const float* src = (r == 0 ? rowp : rowq) + (size_t)cc * kSpecTile;
-        spec_issue(P, src, min(kSpecTile, V - cc * kSpecTile), nullptr, 0);
-    };
-    // Consume side: wait for tile `it` (or fill it with plain loads when rows are not
-    // 16-byte aligned); returns false on a timeout.
-    auto acquire = [&](const float* src0, int n0, const float* src1, int n1) -> float* {
-        float* t = P.tile(P.consumed);
-        if (P.tma) {
-            if (!mbar_wait(P.bar(P.consumed), (P.consumed / kSpecStages) & 1u)) sh.fail = 1;
-        } else {
-            for (int i = tid; i < n0; i += kSpecThreads) t[i] = src0[i];
-            if (src1) for (int i = tid; i < n1; i += kSpecThreads) t[kSpecHalf + i] = src1[i];
-            __syncthreads();
-        }
-        P.consumed++;
-        return t;
-    };
-
-    int status = BORN_ROW_OK;
-    const int ntile_a = nrows * nch;
+    auto issue = [&](int t) { spec_issue(P, src_row + (size_t)t * kSpecTile, min(kSpecTile, V - t * kSpecTile), nullptr, 0); };
     if (P.tma && tid == 0)
-        for (int t = 0; t < min(kSpecStages, ntile_a); ++t) issue_a(t);
+        for (int t = t_lo; t < min(t_lo + kSpecStages, t_hi); ++t) issue(t);
 
-    // ------------------------------------------------------------ pass A: block masses
-    for (int t = 0; t < ntile_a; ++t) {
-        const int r = t / nch, cc = t % nch;
-        const int nvalid = min(kSpecTile, V - cc * kSpecTile);
-        const float* src = (r == 0 ? rowp : rowq) + (size_t)cc * kSpecTile;
-        const float* tile = acquire(src, nvalid, nullptr, 0);
+    for (int t = t_lo; t < t_hi; ++t) {
+        const int nvalid = min(kSpecTile, V - t * kSpecTile);
+        const float* tile = spec_acquire(P, src_row + (size_t)t * kSpecTile, nvalid, nullptr, 0, &sh.fail);
         const int base = warp * kMassBlock;
         if (base < nvalid) {
             float v[32];
@@ -211,140 +207,265 @@ __global__ void __launch_bounds__(kSpecThreads, 2) spec_verify_kernel(const Spec
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) mc = max_nan(mc, __shfl_xor_sync(0xffffffffu, mc, d));
             uint64_t Mc = 0;
-            if (!bonus) {  // the bonus row only needs its maximum here
 #pragma unroll
-                for (int i = 0; i < 32; ++i) Mc += mass_of(scaled_shift(v[i], mc, A.inv_T));
+            for (int i = 0; i < 32; ++i) Mc += mass_of(scaled_shift(v[i], mc, A.inv_T));
 #pragma unroll
-                for (int d = 16; d > 0; d >>= 1) Mc += shfl_xor_u64(Mc, d);
-            }
-            if (lane == 0) {
-                const int blk = cc * (kSpecTile / kMassBlock) + warp;
-                sh.blk_m[r][blk] = mc;
-                sh.blk_M[r][blk] = Mc;
+            for (int d = 16; d > 0; d >>= 1) Mc += shfl_xor_u64(Mc, d);
+            if (lane == 0 && !sh.fail) {
+                BlockMass r;
+                r.m = mc; r.pad = 0; r.M = Mc;
+                A.blocks[(size_t)row * nblk + t * (kSpecTile / kMassBlock) + warp] = r;
             }
         }
         __syncthreads();
         if (sh.fail) break;
-        if (P.tma && tid == 0 && t + kSpecStages < ntile_a) {
+        if (P.tma && tid == 0 && t + kSpecStages < t_hi) {
             fence_proxy_async();
-            issue_a(t + kSpecStages);
+            issue(t + kSpecStages);
         }
     }
+    if (sh.fail && tid == 0) {
+        if (P.tma)
+            for (uint32_t it = P.consumed; it < P.issued; ++it) mbar_wait(P.bar(it), (it / kSpecStages) & 1u);
+        atomicExch(A.dev_error, 2);
+    }
+}
 
-    // row maxima and totals
-    float mrow[2] = {-INFINITY, -INFINITY};
-    uint64_t Srow[2] = {0, 0};
-    if (!sh.fail) {
-        for (int r = 0; r < nrows; ++r) {
+// ------------------------------------------------------------------ launch 2: accept and draw
+struct DrawShared {
+    unsigned long long bars[kSpecStages];
+    unsigned long long red64[kSpecThreads / 32];
+    unsigned long long scan[kSpecThreads / 32];
+    unsigned long long rowS[kSpecMaxRows];   // row totals of the fixed-point masses
+    unsigned long long csum[kSpecMaxChunks];
+    unsigned long long pick_before;
+    uint32_t rowkey[kSpecMaxRows];           // order-preserving key of the row maximum
+    int rownan[kSpecMaxRows];
+    int accept[BORN_MAX_DRAFT];
+    int pstat[BORN_MAX_DRAFT + 1];
+    int fail, last, pick_chunk, token;
+};
+
+__global__ void __launch_bounds__(kSpecThreads, 2) spec_draw_kernel(const SpecKernelArgs A) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ DrawShared sh;
+    const int tid = threadIdx.x;
+    const int part = blockIdx.x, nparts = gridDim.x, b = blockIdx.y;
+    const int K = A.K, V = A.V, R = A.target_rows;
+    const int nblk = (V + kMassBlock - 1) / kMassBlock;
+    const int nrows = R + K;  // this sequence's rows: r < R target row r, else draft row r - R
+    auto row_id = [&](int r) { return r < R ? b * R + r : A.B * R + b * K + (r - R); };
+
+    SpecPipe P;
+    P.tiles = reinterpret_cast<float*>(smem);
+    P.bars = sh.bars;
+    P.tma = A.tma;
+    P.issued = P.consumed = 0;
+    if (tid == 0) {
+        for (int s = 0; s < kSpecStages; ++s) mbar_init(reinterpret_cast<uint64_t*>(&sh.bars[s]), 1);
+        mbar_fence_init();
+        sh.fail = 0;
+        sh.last = 0;
+        sh.token = -1;
+    }
+    if (tid < kSpecMaxRows) { sh.rowS[tid] = 0; sh.rowkey[tid] = zkey(-INFINITY); sh.rownan[tid] = 0; }
+    __syncthreads();
+
+    // ---- row maxima and totals from the block results (every CTA of the sequence on its own):
+    // one warp per row, the blocks of the row dealt out to its lanes and held in registers, so
+    // that the block results are fetched once, all loads in flight together, and the warp
+    // reduces by shuffles.
+    {
+        constexpr int kPerLane = kSpecMaxBlocks / 32;  // 16 blocks per lane at most
+        const int lane = tid & 31, warp = tid >> 5;
+        for (int r = warp; r < nrows; r += kSpecThreads / 32) {
+            const BlockMass* rb = A.blocks + (size_t)row_id(r) * nblk;
+            float bm[kPerLane];
+            unsigned long long bM[kPerLane];
+#pragma unroll
+            for (int q = 0; q < kPerLane; ++q) {
+                const int blk = lane + 32 * q;
+                bm[q] = -INFINITY;
+                bM[q] = 0;
+                if (blk < nblk) {
+                    const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(rb + blk));
+                    bm[q] = __uint_as_float(raw.x);
+                    bM[q] = ((unsigned long long)raw.w << 32) | raw.z;
+                }
+            }
             float m = -INFINITY;
-            for (int i = tid; i < nblk; i += kSpecThreads) m = max_nan(m, sh.blk_m[r][i]);
+#pragma unroll
+            for (int q = 0; q < kPerLane; ++q) m = max_nan(m, bm[q]);
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) m = max_nan(m, __shfl_xor_sync(0xffffffffu, m, d));
-            __syncthreads();
-            if (lane == 0) sh.redf[warp] = m;
-            __syncthreads();
-            m = sh.redf[0];
-            for (int w = 1; w < kSpecThreads / 32; ++w) m = max_nan(m, sh.redf[w]);
-            mrow[r] = m;
-            uint64_t part = 0;
-            if (!bonus && m == m && m > -INFINITY && m < INFINITY) {
-                for (int i = tid; i < nblk; i += kSpecThreads) {
-                    const float mc = sh.blk_m[r][i];
-                    if (mc == -INFINITY) continue;
-                    const float ef = exp_det(scaled_shift(mc, m, A.inv_T));
-                    part += __double2ull_rn(__dmul_rn(__ull2double_rn(sh.blk_M[r][i]), (double)ef));
+            unsigned long long S = 0;
+            if (m == m && m > -INFINITY && m < INFINITY) {
+#pragma unroll
+                for (int q = 0; q < kPerLane; ++q) {
+                    if (bm[q] == -INFINITY) continue;
+                    const float ef = exp_det(scaled_shift(bm[q], m, A.inv_T));
+                    S += __double2ull_rn(__dmul_rn(__ull2double_rn(bM[q]), (double)ef));
                 }
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) S += shfl_xor_u64(S, d);
             }
-            // block_sum_u64 is sized for kThreads == kSpecThreads
-            Srow[r] = block_sum_u64(part, sh.red64);
-            __syncthreads();
-        }
-        for (int r = 0; r < nrows && status == BORN_ROW_OK; ++r) {
-            if (mrow[r] != mrow[r]) status = BORN_ROW_NAN;
-            else if (mrow[r] == INFINITY) status = BORN_ROW_POS_INF;
-            else if (mrow[r] == -INFINITY) status = BORN_ROW_ALL_MASKED;
+            if (lane == 0) {
+                sh.rownan[r] = (m != m) ? 1 : 0;
+                sh.rowkey[r] = (m != m) ? zkey(-INFINITY) : zkey(m);
+                sh.rowS[r] = S;
+            }
         }
     }
-
-    int accept = 0;
-    int need_draw = 0;
-    DrawCtx D;
-    D.residual = 0; D.mp = mrow[0]; D.mq = mrow[1]; D.inv_T = A.inv_T; D.invSp = 0.0f; D.invSq = 0.0f;
-    if (!sh.fail && status == BORN_ROW_OK) {
-        if (bonus) {
-            need_draw = 1;
-        } else {
+    __syncthreads();
+    auto row_status = [&](int r) {
+        const float m = zkey_to_float(sh.rowkey[r]);
+        if (sh.rownan[r]) return (int)BORN_ROW_NAN;
+        if (m == INFINITY) return (int)BORN_ROW_POS_INF;
+        if (m == -INFINITY) return (int)BORN_ROW_ALL_MASKED;
+        return (int)BORN_ROW_OK;
+    };
+    const bool dev_failed = *reinterpret_cast<volatile int*>(A.dev_error) != 0;  // launch 1 gave up on a copy
+    if (tid < K) {
+        const int j = tid;
+        int st = row_status(j);
+        if (st == BORN_ROW_OK) st = row_status(R + j);
+        if (dev_failed) st = 100 + BORN_ERR_DEVICE_TIMEOUT;
+        int acc = 0;
+        if (st == BORN_ROW_OK) {
             const int x = A.draft_tok[(int64_t)b * K + j];
-            if (x < 0 || x >= V) status = kRowBadToken;
+            if (x < 0 || x >= V) st = kRowBadToken;
             else {
-                const uint64_t wp = mass_of(scaled_shift(rowp[x], mrow[0], A.inv_T));
-                const uint64_t wq = mass_of(scaled_shift(rowq[x], mrow[1], A.inv_T));
+                const float* rowp = A.target + ((int64_t)b * R + j) * (int64_t)V;
+                const float* rowq = A.draft + ((int64_t)b * K + j) * (int64_t)V;
+                const uint64_t wp = mass_of(scaled_shift(rowp[x], zkey_to_float(sh.rowkey[j]), A.inv_T));
+                const uint64_t wq = mass_of(scaled_shift(rowq[x], zkey_to_float(sh.rowkey[R + j]), A.inv_T));
                 const double u = (double)A.u_accept[(int64_t)b * K + j];
-                const double lhs = __dmul_rn(__dmul_rn(u, __ull2double_rn(wq)), __ull2double_rn(Srow[0]));
-                const double rhs = __dmul_rn(__ull2double_rn(wp), __ull2double_rn(Srow[1]));
-                accept = lhs < rhs;
-                if (!accept) {
-                    need_draw = 1;
-                    D.residual = 1;
-                    D.invSp = __double2float_rn(__ddiv_rn(1099511627776.0, __ull2double_rn(Srow[0])));
-                    D.invSq = __double2float_rn(__ddiv_rn(1099511627776.0, __ull2double_rn(Srow[1])));
-                }
+                const double lhs = __dmul_rn(__dmul_rn(u, __ull2double_rn(wq)), __ull2double_rn(sh.rowS[j]));
+                const double rhs = __dmul_rn(__ull2double_rn(wp), __ull2double_rn(sh.rowS[R + j]));
+                acc = lhs < rhs;
             }
         }
+        sh.accept[j] = acc;
+        sh.pstat[j] = st;
+    }
+    if (tid == K) sh.pstat[K] = (R > K) ? (dev_failed ? 100 + BORN_ERR_DEVICE_TIMEOUT : row_status(K)) : BORN_ROW_OK;
+    __syncthreads();
+
+    // ---- the sequence's verdict (same in every thread of every CTA of the sequence)
+    int len = K, seq_status = BORN_ROW_OK, jstar = -1;
+    DrawCtx D;
+    D.residual = 0; D.inv_T = A.inv_T; D.mp = 0.0f; D.mq = 0.0f; D.invSp = 0.0f; D.invSq = 0.0f;
+    for (int i = 0; i < K; ++i) {
+        if (sh.pstat[i] != BORN_ROW_OK) { seq_status = sh.pstat[i]; len = i; break; }
+        if (!sh.accept[i]) { len = i; jstar = i; D.residual = 1; break; }
+    }
+    if (len == K && seq_status == BORN_ROW_OK && R > K) {
+        if (sh.pstat[K] != BORN_ROW_OK) seq_status = sh.pstat[K];
+        else jstar = K;
+    }
+    auto write_outputs = [&](int token) {  // one thread
+        int32_t* out = A.out_tok + (int64_t)b * (K + 1);
+        for (int i = 0; i <= K; ++i) out[i] = -1;
+        for (int i = 0; i < len; ++i) out[i] = A.draft_tok[(int64_t)b * K + i];
+        if (jstar >= 0) out[jstar] = token;
+        A.accept_len[b] = len;
+        A.status[b] = seq_status;
+    };
+    if (jstar < 0) {  // nothing to draw
+        if (part == 0 && tid == 0) write_outputs(-1);
+        return;
+    }
+    const float* rowp = A.target + ((int64_t)b * R + jstar) * (int64_t)V;
+    const float* rowq = D.residual ? A.draft + ((int64_t)b * K + jstar) * (int64_t)V : nullptr;
+    D.mp = zkey_to_float(sh.rowkey[jstar]);
+    if (D.residual) {
+        D.mq = zkey_to_float(sh.rowkey[R + jstar]);
+        D.invSp = __double2float_rn(__ddiv_rn(1099511627776.0, __ull2double_rn(sh.rowS[jstar])));
+        D.invSq = __double2float_rn(__ddiv_rn(1099511627776.0, __ull2double_rn(sh.rowS[R + jstar])));
     }
 
-    // ------------------------------------------------ pass B: draw (rejecting positions, bonus)
-    int token = -1;
-    for (int attempt = 0; attempt < 2 && need_draw && !sh.fail; ++attempt) {
-        const int nchb = (V + kSpecHalf - 1) / kSpecHalf;
-        auto issue_b = [&](int cc) {
-            const int n = min(kSpecHalf, V - cc * kSpecHalf);
-            spec_issue(P, rowp + (size_t)cc * kSpecHalf, n, D.residual ? rowq + (size_t)cc * kSpecHalf : nullptr, n);
-        };
-        // Weights of the 16 tokens a thread owns in a chunk: four strided groups of four when
-        // only the sum matters (conflict-free shared loads), 16 consecutive tokens when the
-        // caller needs them in index order.
-        auto chunk_weights = [&](const float* tile, int nvalid, uint64_t* wts) -> uint64_t {
-            uint64_t s = 0;
+    // ---- chunk sums of the draw weights: this CTA's share of the chunks
+    const int nchb = (V + kSpecHalf - 1) / kSpecHalf;
+    auto issue_b = [&](int cc) {
+        const int n = min(kSpecHalf, V - cc * kSpecHalf);
+        spec_issue(P, rowp + (size_t)cc * kSpecHalf, n, D.residual ? rowq + (size_t)cc * kSpecHalf : nullptr, n);
+    };
+    // Weights of the 16 tokens a thread owns in a chunk: four strided groups of four when only
+    // the sum matters (conflict-free shared loads), 16 consecutive tokens when the caller needs
+    // them in index order.
+    auto chunk_weights = [&](const float* tile, int nvalid, uint64_t* wts) -> uint64_t {
+        uint64_t s = 0;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int e = wts ? 16 * tid + 4 * i : 4 * (tid + kSpecThreads * i);
-                float4 zp = *reinterpret_cast<const float4*>(tile + e);
-                float4 zq = D.residual ? *reinterpret_cast<const float4*>(tile + kSpecHalf + e) : zp;
-                const float ap[4] = {zp.x, zp.y, zp.z, zp.w}, aq[4] = {zq.x, zq.y, zq.z, zq.w};
+        for (int i = 0; i < 4; ++i) {
+            const int e = wts ? 16 * tid + 4 * i : 4 * (tid + kSpecThreads * i);
+            float4 zp = *reinterpret_cast<const float4*>(tile + e);
+            float4 zq = D.residual ? *reinterpret_cast<const float4*>(tile + kSpecHalf + e) : zp;
+            const float ap[4] = {zp.x, zp.y, zp.z, zp.w}, aq[4] = {zq.x, zq.y, zq.z, zq.w};
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    uint64_t wv = (e + k < nvalid) ? draw_weight(D, ap[k], aq[k]) : 0ull;
-                    if (wts) wts[4 * i + k] = wv;
-                    s += wv;
-                }
+            for (int k = 0; k < 4; ++k) {
+                uint64_t wv = (e + k < nvalid) ? draw_weight(D, ap[k], aq[k]) : 0ull;
+                if (wts) wts[4 * i + k] = wv;
+                s += wv;
             }
-            return s;
-        };
-        // tiles issued so far have all been consumed (passes are separated by barriers)
+        }
+        return s;
+    };
+    // sums of chunks [lo, hi) into dst[cc] (thread 0 writes); tiles issued before have all been consumed
+    auto sum_chunks = [&](int lo, int hi, unsigned long long* dst) {
         if (P.tma && tid == 0)
-            for (int cc = 0; cc < min(kSpecStages, nchb); ++cc) issue_b(cc);
-        for (int cc = 0; cc < nchb; ++cc) {
+            for (int cc = lo; cc < min(lo + kSpecStages, hi); ++cc) issue_b(cc);
+        for (int cc = lo; cc < hi; ++cc) {
             const int nvalid = min(kSpecHalf, V - cc * kSpecHalf);
-            const float* tile = acquire(rowp + (size_t)cc * kSpecHalf, nvalid,
-                                        D.residual ? rowq + (size_t)cc * kSpecHalf : nullptr, nvalid);
+            const float* tile = spec_acquire(P, rowp + (size_t)cc * kSpecHalf, nvalid,
+                                             D.residual ? rowq + (size_t)cc * kSpecHalf : nullptr, nvalid, &sh.fail);
             uint64_t s = chunk_weights(tile, nvalid, nullptr);
             s = block_sum_u64(s, sh.red64);
-            if (tid == 0) sh.csum[cc] = s;
+            if (tid == 0) dst[cc] = s;
             __syncthreads();
             if (sh.fail) break;
-            if (P.tma && tid == 0 && cc + kSpecStages < nchb) {
+            if (P.tma && tid == 0 && cc + kSpecStages < hi) {
                 fence_proxy_async();
                 issue_b(cc + kSpecStages);
             }
         }
-        if (sh.fail) break;
+    };
+    unsigned long long* csum_g = A.csum + (size_t)b * nchb;
+    const int per = (nchb + nparts - 1) / nparts;
+    const int lo = min(nchb, part * per), hi = min(nchb, lo + per);
+    sum_chunks(lo, hi, csum_g);
+    if (sh.fail && tid == 0) atomicExch(A.dev_error, 2);
+
+    // ---- ticket: the last CTA of the sequence picks the chunk and the token
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const uint32_t tk = atomicAdd(&A.tickets[b], 1u);
+        sh.last = (tk == (uint32_t)nparts - 1);
+        if (sh.last) A.tickets[b] = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (!sh.last) {
+        if (sh.fail && tid == 0 && P.tma)
+            for (uint32_t it = P.consumed; it < P.issued; ++it) mbar_wait(P.bar(it), (it / kSpecStages) & 1u);
+        return;
+    }
+    __threadfence();
+    int token = -1;
+    bool failed = sh.fail || *reinterpret_cast<volatile int*>(A.dev_error) != 0;
+    for (int attempt = 0; attempt < 2 && !failed; ++attempt) {
+        if (attempt == 0) {
+            for (int cc = tid; cc < nchb; cc += kSpecThreads) sh.csum[cc] = __ldcg(&csum_g[cc]);
+        } else {
+            sum_chunks(0, nchb, sh.csum);  // the residual vanished: the plain masses of p, all chunks
+            if (sh.fail) { failed = true; break; }
+        }
+        __syncthreads();
         if (tid == 0) {
             uint64_t W = 0;
             for (int cc = 0; cc < nchb; ++cc) W += sh.csum[cc];
             sh.pick_chunk = -1;
             if (W > 0) {
-                const float u = A.u_resample[(int64_t)b * (K + 1) + j];
+                const float u = A.u_resample[(int64_t)b * (K + 1) + jstar];
                 uint64_t t = __double2ull_rz(__dmul_rn((double)u, __ull2double_rn(W)));
                 if (t > W - 1) t = W - 1;
                 uint64_t cum = 0;
@@ -363,84 +484,65 @@ __global__ void __launch_bounds__(kSpecThreads, 2) spec_verify_kernel(const Spec
             if (D.residual) { D.residual = 0; continue; }
             break;
         }
-        {
-            const int nvalid = min(kSpecHalf, V - pc * kSpecHalf);
-            if (P.tma && tid == 0) { fence_proxy_async(); issue_b(pc); }
-            const float* tile = acquire(rowp + (size_t)pc * kSpecHalf, nvalid,
-                                        D.residual ? rowq + (size_t)pc * kSpecHalf : nullptr, nvalid);
-            uint64_t wts[16];
-            uint64_t s = chunk_weights(tile, nvalid, wts);
-            uint64_t tot;
-            uint64_t excl = block_excl_scan_u64(s, sh.scan, &tot);
-            const uint64_t t = sh.pick_before;
-            if (t >= excl && t < excl + s) {
-                uint64_t cum = excl;
-                int k = 15;
+        const int nvalid = min(kSpecHalf, V - pc * kSpecHalf);
+        if (P.tma && tid == 0) { fence_proxy_async(); issue_b(pc); }
+        const float* tile = spec_acquire(P, rowp + (size_t)pc * kSpecHalf, nvalid,
+                                         D.residual ? rowq + (size_t)pc * kSpecHalf : nullptr, nvalid, &sh.fail);
+        uint64_t wts[16];
+        uint64_t s = chunk_weights(tile, nvalid, wts);
+        uint64_t tot;
+        uint64_t excl = block_excl_scan_u64(s, sh.scan, &tot);
+        const uint64_t t = sh.pick_before;
+        if (t >= excl && t < excl + s) {
+            uint64_t cum = excl;
+            int k = 15;
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    if (cum + wts[i] > t) { k = i; break; }
-                    cum += wts[i];
-                }
-                sh.token = pc * kSpecHalf + 16 * tid + k;
+            for (int i = 0; i < 16; ++i) {
+                if (cum + wts[i] > t) { k = i; break; }
+                cum += wts[i];
             }
-            __syncthreads();
-            token = sh.token;
+            sh.token = pc * kSpecHalf + 16 * tid + k;
         }
+        __syncthreads();
+        token = sh.token;
+        if (sh.fail) failed = true;
         break;
     }
-
-    if (sh.fail) {
-        if (tid == 0) {
+    if (tid == 0) {
+        if (failed) {
             if (P.tma)
                 for (uint32_t it = P.consumed; it < P.issued; ++it) mbar_wait(P.bar(it), (it / kSpecStages) & 1u);
             atomicExch(A.dev_error, 2);
+            seq_status = 100 + BORN_ERR_DEVICE_TIMEOUT;
+            len = min(len, jstar);
         }
-        status = 100 + BORN_ERR_DEVICE_TIMEOUT;
-    }
-
-    // ------------------------------------------------------------ publish, ticket, finish
-    if (tid == 0) {
-        seq->pos_status[j] = status;
-        if (!bonus) seq->accept[j] = accept;
-        seq->token[j] = token;
-        __threadfence();
-        const uint32_t nct = gridDim.x;
-        const uint32_t tk = atomicAdd(&seq->ticket, 1u);
-        if (tk == nct - 1) {
-            __threadfence();
-            volatile SeqScratch* vs = seq;
-            int32_t* out = A.out_tok + (int64_t)b * (K + 1);
-            for (int i = 0; i <= K; ++i) out[i] = -1;
-            int len = K, st = BORN_ROW_OK;
-            for (int i = 0; i < K; ++i) {
-                const int ps = vs->pos_status[i];
-                if (ps != BORN_ROW_OK) { st = ps; len = i; break; }
-                if (!vs->accept[i]) { len = i; out[i] = vs->token[i]; break; }
-                out[i] = A.draft_tok[(int64_t)b * K + i];
-            }
-            if (len == K && st == BORN_ROW_OK && A.target_rows > K) {
-                const int ps = vs->pos_status[K];
-                if (ps != BORN_ROW_OK) st = ps;
-                else out[K] = vs->token[K];
-            }
-            A.accept_len[b] = len;
-            A.status[b] = st;
-            seq->ticket = 0;
-        }
+        write_outputs(failed ? -1 : token);
     }
 }
 
 inline size_t spec_smem_bytes() { return (size_t)kSpecStages * kSpecTile * sizeof(float); }
 
-// returns 0 or a cudaError_t
-inline int launch_spec(SpecKernelArgs A, cudaStream_t st) {
+// returns 0 or a cudaError_t; `num_sms` sizes the first launch
+inline int launch_spec(SpecKernelArgs A, int num_sms, cudaStream_t st) {
     if (A.V > kSpecMaxBlocks * kMassBlock) return (int)cudaErrorInvalidValue;
     A.tma = ((uintptr_t)A.target % 16 == 0) && ((uintptr_t)A.draft % 16 == 0) && (((int64_t)A.V * 4) % 16 == 0);
-    cudaError_t e = cudaFuncSetAttribute(spec_verify_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)spec_smem_bytes());
+    cudaError_t e = cudaFuncSetAttribute(spec_mass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)spec_smem_bytes());
     if (e != cudaSuccess) return (int)e;
-    dim3 grid((unsigned)(A.target_rows > A.K ? A.K + 1 : A.K), (unsigned)A.B, 1);
-    spec_verify_kernel<<<grid, kSpecThreads, spec_smem_bytes(), st>>>(A);
+    e = cudaFuncSetAttribute(spec_draw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)spec_smem_bytes());
+    if (e != cudaSuccess) return (int)e;
+    const int rows = A.B * (A.target_rows + A.K);
+    const int nch = (A.V + kSpecTile - 1) / kSpecTile;
+    int parts = (4 * num_sms + rows - 1) / rows;  // about two waves of two CTAs per SM
+    if (parts > nch) parts = nch;
+    if (parts < 1) parts = 1;
+    if (const char* e1 = getenv("BORN_SPEC_PARTS1")) parts = atoi(e1);
+    spec_mass_kernel<<<dim3((unsigned)parts, (unsigned)rows, 1), kSpecThreads, spec_smem_bytes(), st>>>(A);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    const int nchb = (A.V + kSpecHalf - 1) / kSpecHalf;
+    int dparts = kSpecParts < nchb ? kSpecParts : nchb;
+    if (const char* e2 = getenv("BORN_SPEC_PARTS2")) dparts = atoi(e2);
+    spec_draw_kernel<<<dim3((unsigned)dparts, (unsigned)A.B, 1), kSpecThreads, spec_smem_bytes(), st>>>(A);
     return (int)cudaGetLastError();
 }
 

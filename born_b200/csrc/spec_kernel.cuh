@@ -195,12 +195,13 @@ __global__ void __launch_bounds__(kSpecThreads, 2) spec_mass_kernel(const SpecKe
             float mc = -INFINITY;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const int e = base + 4 * (lane + 32 * i);
-                float4 q = *reinterpret_cast<const float4*>(tile + e);
-                v[4 * i + 0] = (e + 0 < nvalid) ? q.x : -INFINITY;
-                v[4 * i + 1] = (e + 1 < nvalid) ? q.y : -INFINITY;
-                v[4 * i + 2] = (e + 2 < nvalid) ? q.z : -INFINITY;
-                v[4 * i + 3] = (e + 3 < nvalid) ? q.w : -INFINITY;
+                const float4 q = *reinterpret_cast<const float4*>(tile + base + 4 * (lane + 32 * i));
+                v[4 * i + 0] = q.x; v[4 * i + 1] = q.y; v[4 * i + 2] = q.z; v[4 * i + 3] = q.w;
+            }
+            if (base + kMassBlock > nvalid) {  // the row ends inside this block: nothing beyond it counts
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (base + 4 * (lane + 32 * (i >> 2)) + (i & 3) >= nvalid) v[i] = -INFINITY;
             }
 #pragma unroll
             for (int i = 0; i < 32; ++i) mc = max_nan(mc, v[i]);
@@ -532,16 +533,24 @@ inline int launch_spec(SpecKernelArgs A, int num_sms, cudaStream_t st) {
     if (e != cudaSuccess) return (int)e;
     const int rows = A.B * (A.target_rows + A.K);
     const int nch = (A.V + kSpecTile - 1) / kSpecTile;
-    int parts = (4 * num_sms + rows - 1) / rows;  // about two waves of two CTAs per SM
-    if (parts > nch) parts = nch;
-    if (parts < 1) parts = 1;
-    if (const char* e1 = getenv("BORN_SPEC_PARTS1")) parts = atoi(e1);
+    // CTAs per row: enough for a few full waves of two CTAs per SM, with the last wave as full
+    // as the choice allows, and at least two tiles each
+    int parts = 1;
+    {
+        const int slots = 2 * num_sms;
+        double best = 0.0;
+        for (int p = 1; p <= 8 && 2 * p <= nch + 1; ++p) {
+            const double waves = (double)rows * p / slots;
+            const double fill = waves / (double)((long long)waves + ((double)(long long)waves < waves ? 1 : 0));
+            const double score = (waves >= 2.0 ? 1.0 : waves / 2.0) * fill;
+            if (score > best + 0.02) { best = score; parts = p; }
+        }
+    }
     spec_mass_kernel<<<dim3((unsigned)parts, (unsigned)rows, 1), kSpecThreads, spec_smem_bytes(), st>>>(A);
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     const int nchb = (A.V + kSpecHalf - 1) / kSpecHalf;
     int dparts = kSpecParts < nchb ? kSpecParts : nchb;
-    if (const char* e2 = getenv("BORN_SPEC_PARTS2")) dparts = atoi(e2);
     spec_draw_kernel<<<dim3((unsigned)dparts, (unsigned)A.B, 1), kSpecThreads, spec_smem_bytes(), st>>>(A);
     return (int)cudaGetLastError();
 }

@@ -352,7 +352,7 @@ __global__ void __launch_bounds__(kSpecThreads, 2) spec_draw_kernel(const SpecKe
     if (tid == K) sh.pstat[K] = (R > K) ? (dev_failed ? 100 + BORN_ERR_DEVICE_TIMEOUT : row_status(K)) : BORN_ROW_OK;
     __syncthreads();
 
-    // ---- the sequence's verdict (same in every thread of every CTA of the sequence)
+    // ---- the outcome for the sequence (same in every thread of every CTA of the sequence)
     int len = K, seq_status = BORN_ROW_OK, jstar = -1;
     DrawCtx D;
     D.residual = 0; D.inv_T = A.inv_T; D.mp = 0.0f; D.mq = 0.0f; D.invSp = 0.0f; D.invSq = 0.0f;

@@ -1513,8 +1513,15 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             for (int d = 16; d > 0; d >>= 1) v += shfl_xor_u64(v, d);
             if ((tid & 31) == 0 && v) atomicAdd(&bs.acc[slot], (unsigned long long)v);
         };
+        // (the all-pairs passes read two entries per 16-byte shared load)
+        const ulonglong2* sel2 = reinterpret_cast<const ulonglong2*>(sel);
+        const ulonglong2* selq2 = reinterpret_cast<const ulonglong2*>(selq);
         int rank = 0;
-        for (int j = part; j < na; j += P) rank += (sel[j] > ck) ? 1 : 0;
+        for (int jj = part; jj < (na >> 1); jj += P) {
+            const ulonglong2 k2 = sel2[jj];
+            rank += (k2.x > ck ? 1 : 0) + (k2.y > ck ? 1 : 0);
+        }
+        if ((na & 1) && part == 0) rank += (sel[na - 1] > ck) ? 1 : 0;
         rank = (int)group_sum((uint64_t)rank);
         bool kept = mine && (A.segment_mode || rank < cx.k_eff);
         uint64_t q = 0;
@@ -1571,7 +1578,12 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         };
         if (rp.top_p > 0.0f && rp.top_p < 1.0f) {
             uint64_t before = 0;  // mass ahead in rank order = mass of the entries in front
-            for (int j = part2; j < ent2 && j < nk; j += P2) before += selq[j];
+            const int lim = min(ent2, nk);
+            for (int jj = part2; jj < (lim >> 1); jj += P2) {
+                const ulonglong2 v2 = selq2[jj];
+                before += v2.x + v2.y;
+            }
+            if ((lim & 1) && part2 == 0) before += selq[lim - 1];
             before = group_sum2(before);
             uint64_t Tp = __double2ull_rz(__dmul_rn((double)rp.top_p, __ull2double_rn(S)));
             if (Tp < 1) Tp = 1;
@@ -1588,7 +1600,11 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         BORN_PROF(26);
         const uint32_t my_low = (uint32_t)(ck2 & kIdxMask);  // larger low bits = smaller token index
         uint64_t pre = 0;
-        for (int j = part2; j < nk; j += P2) pre += ((uint32_t)(sel[j] & kIdxMask) > my_low) ? selq[j] : 0ull;
+        for (int jj = part2; jj < (nk >> 1); jj += P2) {
+            const ulonglong2 k2 = sel2[jj], v2 = selq2[jj];
+            pre += (((uint32_t)(k2.x & kIdxMask) > my_low) ? v2.x : 0ull) + (((uint32_t)(k2.y & kIdxMask) > my_low) ? v2.y : 0ull);
+        }
+        if ((nk & 1) && part2 == 0) pre += ((uint32_t)(sel[nk - 1] & kIdxMask) > my_low) ? selq[nk - 1] : 0ull;
         pre = group_sum2(pre);
         if (S == 0) {  // cannot happen while the row maximum is finite; never divide by it
             if (tid == 0) { A.out_token[row] = -1; A.out_status[row] = BORN_ROW_ALL_MASKED; }
@@ -1605,7 +1621,12 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         if (A.out_kept_count || A.out_kept_ids) {
             if (A.out_kept_ids) {
                 int kr = 0;  // kept entries ahead in rank order
-                for (int j = part2; j < ent2 && j < nk; j += P2) kr += ck_alive(sel[j]) ? 1 : 0;
+                const int lim = min(ent2, nk);
+                for (int jj = part2; jj < (lim >> 1); jj += P2) {
+                    const ulonglong2 k2 = sel2[jj];
+                    kr += (ck_alive(k2.x) ? 1 : 0) + (ck_alive(k2.y) ? 1 : 0);
+                }
+                if ((lim & 1) && part2 == 0) kr += ck_alive(sel[lim - 1]) ? 1 : 0;
                 kr = (int)group_sum2((uint64_t)kr);
                 if (lead2 && kept2 && kr < A.kept_stride) A.out_kept_ids[(int64_t)row * A.kept_stride + kr] = ck_idx(ck2);
             }

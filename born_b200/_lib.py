@@ -22,6 +22,7 @@ MAX_SHARDS = 16
 DTYPE_F32, DTYPE_BF16 = 0, 1
 MEM_DEVICE, MEM_HOST = 0, 1
 FLAG_GREEDY = 1
+FLAG_FULL_VOCAB = 2
 
 
 class RowParams(C.Structure):

@@ -16,6 +16,7 @@
 #include "../../include/born_sampler.h"
 #include "sample_kernel.cuh"
 #include "spec_kernel.cuh"
+#include "fullrow_kernel.cuh"
 
 using namespace born;
 
@@ -49,6 +50,10 @@ struct Handle {
     uint8_t* spec_scratch = nullptr;
     size_t spec_scratch_bytes = 0;
     int64_t spec_layout_key = -1;
+    uint8_t* fr_scratch = nullptr;  // full-vocabulary path: tickets, range statistics, chunk sums
+    size_t fr_scratch_bytes = 0;
+    int64_t fr_layout_key = -1;
+    bool is_static = false;  // the handle of born_sample_static: may not allocate
     Staging stage[16];
     cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
     float timing[3] = {0, 0, 0};
@@ -242,6 +247,7 @@ int32_t born_sampler_destroy(void* handle) {
     cudaFree(h->tickets);
     cudaFree(h->dev_error);
     cudaFree(h->spec_scratch);
+    cudaFree(h->fr_scratch);
     cudaFree(h->gathered);
     cudaFree(h->packed);
     for (auto& s : h->stage) cudaFree(s.p);
@@ -258,7 +264,65 @@ int32_t born_last_timing(void* handle, float* out3) {
     return BORN_OK;
 }
 
+// Rows that neither top-k nor top-p narrows have no small candidate set: temperature-only
+// sampling always, min-p when the caller asks for it with BORN_FLAG_FULL_VOCAB (without the
+// flag min-p goes through the one-pass kernel, which serves up to 1024 survivors).  Uniform
+// parameters only, no history penalties, no kept-id list.
+static bool wants_full_row(const Handle* h, const born_sample_args* a) {
+    if (h->is_static || a->row_params || a->vocab_segments > 1 || a->out_kept_ids) return false;
+    const born_row_params& p = a->params;
+    if ((p.flags & BORN_FLAG_GREEDY) || p.temperature == 0.0f) return false;
+    if (p.top_k > 0 || (p.top_p > 0.0f && p.top_p < 1.0f)) return false;
+    if (p.min_p > 0.0f && !(p.flags & BORN_FLAG_FULL_VOCAB)) return false;
+    const bool pen_on = (p.repetition_penalty != 1.0f && p.repetition_penalty != 0.0f) || p.frequency_penalty != 0.0f ||
+                        p.presence_penalty != 0.0f;
+    if (a->history && pen_on) return false;
+    return true;
+}
+
+static int sample_full_row(Handle* h, const born_sample_args* a, cudaStream_t st) {
+    const int B = a->batch, V = a->vocab;
+    const int esz = a->logits_dtype == BORN_DTYPE_F32 ? 4 : 2;
+    const int parts = fullrow_parts(B, V, h->num_sms);
+    const FullRowScratchLayout L = fullrow_scratch_layout(B, V, parts);
+    if (h->fr_scratch_bytes < L.total) {  // grown on first use, like the staging mirrors
+        CUDA_TRY(h, cudaStreamSynchronize(st));
+        if (h->fr_scratch) { cudaFree(h->fr_scratch); h->workspace -= (int64_t)h->fr_scratch_bytes; h->fr_scratch = nullptr; h->fr_scratch_bytes = 0; }
+        int rc0 = dev_alloc(h, (void**)&h->fr_scratch, L.total);
+        if (rc0 != BORN_OK) return rc0;
+        h->fr_scratch_bytes = L.total;
+        h->fr_layout_key = -1;
+    }
+    const int64_t key = ((int64_t)B << 32) | (int64_t)V;
+    if (h->fr_layout_key != key) {  // the tickets sit at offset 0 and are zero between launches
+        CUDA_TRY(h, cudaMemsetAsync(h->fr_scratch, 0, L.stat, st));
+        h->fr_layout_key = key;
+    }
+    FullRowArgs F;
+    memset(&F, 0, sizeof F);
+    F.logits = a->logits;
+    F.mask = a->mask;
+    F.uniforms = a->uniforms;
+    F.out_token = a->out_token; F.out_prob = a->out_prob; F.out_lse = a->out_lse; F.out_status = a->out_status;
+    F.out_kept_count = a->out_kept_count;
+    F.tickets = reinterpret_cast<uint32_t*>(h->fr_scratch + L.tickets);
+    F.stat = reinterpret_cast<float2*>(h->fr_scratch + L.stat);
+    F.csum = reinterpret_cast<unsigned long long*>(h->fr_scratch + L.csum);
+    F.ccount = reinterpret_cast<uint32_t*>(h->fr_scratch + L.ccount);
+    F.row_stride = a->logits_row_stride;
+    F.mask_stride = a->mask_row_stride;
+    F.B = B; F.V = V; F.parts1 = parts;
+    F.temperature = a->params.temperature;
+    F.min_p = a->params.min_p;
+    F.vec_ok = ((uintptr_t)a->logits % 16 == 0) && ((a->logits_row_stride * esz) % 16 == 0);
+    int rc = launch_fullrow(F, a->logits_dtype, parts, st);
+    if (rc != 0) return fail(h, BORN_ERR_CUDA, "full-vocabulary kernel launch failed: %s", cudaGetErrorString((cudaError_t)rc));
+    h->launches += 2;
+    return BORN_OK;
+}
+
 static int sample_device(Handle* h, const born_sample_args* a, cudaStream_t st) {
+    if (wants_full_row(h, a)) return sample_full_row(h, a, st);
     SampleKernelArgs A;
     memset(&A, 0, sizeof A);
     A.logits = a->logits;
@@ -746,6 +810,7 @@ extern "C" int32_t born_sample_static(const born_sample_args* a, void* stream) {
             return fail(nullptr, BORN_ERR_CUDA, "cudaDeviceGetAttribute failed");
         if (major != 10) return fail(nullptr, BORN_ERR_NO_DEVICE, "device %d is not sm_100; this library is built for sm_100a only", dev);
         h->device = dev;
+        h->is_static = true;
         h->max_batch = kStaticMaxBatch;
         h->max_vocab = BORN_MAX_VOCAB;
         h->max_k = BORN_MAX_TOP_K;

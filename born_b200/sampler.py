@@ -60,10 +60,14 @@ class SamplingConfig:
     frequency_penalty: float = 0.0
     presence_penalty: float = 0.0
     greedy: bool = False
+    full_vocab: bool = False  # min-p over the whole vocabulary (no survivor limit); top-k and top-p off
+
+    def flags(self):
+        return (L.FLAG_GREEDY if self.greedy else 0) | (L.FLAG_FULL_VOCAB if self.full_vocab else 0)
 
     def to_struct(self):
         return L.RowParams(self.temperature, self.top_p, self.min_p, int(self.top_k), self.repetition_penalty,
-                           self.frequency_penalty, self.presence_penalty, L.FLAG_GREEDY if self.greedy else 0)
+                           self.frequency_penalty, self.presence_penalty, self.flags())
 
 
 ROW_PARAMS_DTYPE = np.dtype([
@@ -77,7 +81,7 @@ def row_params_array(configs):
     a = np.zeros(len(configs), dtype=ROW_PARAMS_DTYPE)
     for i, c in enumerate(configs):
         a[i] = (c.temperature, c.top_p, c.min_p, c.top_k, c.repetition_penalty, c.frequency_penalty,
-                c.presence_penalty, L.FLAG_GREEDY if c.greedy else 0)
+                c.presence_penalty, c.flags())
     return a
 
 
@@ -184,7 +188,7 @@ class Sampler:
     # -- sampling -------------------------------------------------------------------------
     def sample(self, logits, uniforms=None, config=None, row_params=None, mask=None, history=None,
                history_len=None, want_prob=True, want_lse=False, want_kept=0, vocab_segments=0, stream=None,
-               bf16=False, out=None):
+               bf16=False, out=None, want_kept_count=False):
         """Sample one token per row of `logits` [batch, vocab].
 
         row_params: optional per-row array (numpy structured `ROW_PARAMS_DTYPE` on the host, or a
@@ -239,6 +243,8 @@ class Sampler:
                     res["kept_ids"] = torch.full((B, want_kept), -1, dtype=torch.int32, device=f"cuda:{self.device}")
                 else:
                     res["kept_ids"] = np.full((B, want_kept), -1, dtype=np.int32)
+                res["kept_count"] = self._new(dev, (B,), np.int32, torch.int32 if torch else None)
+            elif want_kept_count:  # the size of the kept set without the id list
                 res["kept_count"] = self._new(dev, (B,), np.int32, torch.int32 if torch else None)
         a.out_token = _ptr(res["token"])
         a.out_status = _ptr(res["status"])

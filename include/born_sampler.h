@@ -69,6 +69,7 @@ extern "C" {
                              out and returns after the stream has drained */
 
 #define BORN_FLAG_GREEDY 1u
+#define BORN_FLAG_FULL_VOCAB 2u /* min-p over the whole vocabulary (two passes, no 1024-survivor limit); top-k and top-p off */
 
 /* Sampling parameters of one row (32 bytes).  Zero means "off" for every filter, as in
  * the reference's config structs (internal/optim/adam.go:78-91). */
@@ -80,7 +81,7 @@ typedef struct born_row_params {
     float repetition_penalty; /* > 0; 1 or 0 => off; z>0 ? z/r : z*r once per distinct token */
     float frequency_penalty;  /* z -= f * count */
     float presence_penalty;   /* z -= p once per distinct token */
-    uint32_t flags;           /* BORN_FLAG_GREEDY */
+    uint32_t flags;           /* BORN_FLAG_GREEDY, BORN_FLAG_FULL_VOCAB */
 } born_row_params;
 
 /* Arguments of born_sample.  Pipeline per row: upcast -> penalties over the token

@@ -479,3 +479,53 @@ def test_argument_errors_are_raised_not_ignored(sampler):
     out = sampler.sample(z, config=SamplingConfig(greedy=True))  # greedy needs no uniforms
     torch.cuda.synchronize()
     assert out["token"].cpu().tolist() == [0, 0]
+
+
+def test_whole_vocabulary_sampling(sampler, oracle):
+    # no top-k and no top-p: temperature-only sampling, and min-p with more than 1024 survivors
+    # when the caller asks for the two-pass path -- every token of the row can be drawn
+    B, V = 9, 50257
+    z = (W.normal(31, 1, B * V) * 1.5).astype(np.float32).reshape(B, V)
+    z[2, ::5] = -np.inf
+    z[3] = np.round(z[3])
+    z[4, :] = -np.inf
+    z[4, 77] = 0.5
+    z[5, 1234] = np.nan
+    z[6, :] = -np.inf
+    u = W.uniform_f32(31, 2, B)
+    u[7] = 0.0
+    u[8] = np.float32(1.0 - 2.0 ** -24)
+    words = (V + 31) // 32
+    bits = W.uniform(31, 3, B * words * 32).reshape(B, words * 32) < 0.4
+    bits[:, V:] = False
+    bits[:, 5] = True
+    mask = np.packbits(bits.reshape(B, words, 32), axis=-1, bitorder="little").view(np.uint32).reshape(B, words)
+    for dtype in ("f32", "bf16"):
+        logits = z if dtype == "f32" else W.f32_to_bf16_bits(z).reshape(B, V)
+        for m in (None, mask):
+            for p in (dict(temperature=1.0), dict(temperature=0.6), dict(temperature=1.5, min_p=0.01, full_vocab=True),
+                      dict(temperature=2.0, top_p=1.0)):
+                op = {k: v for k, v in p.items() if k != "full_vocab"}
+                got, ref = run_both_full(sampler, oracle, logits, p, op, u, m)
+                assert np.array_equal(got["status"], ref["status"]), (dtype, p, got["status"], ref["status"])
+                assert np.array_equal(got["token"], ref["token"]), (dtype, p)
+                assert np.array_equal(got["prob"].view(np.uint32), ref["prob"].view(np.uint32)), (dtype, p)
+                assert np.array_equal(got["kept_count"], ref["kept_count"]), (dtype, p)
+                ok = ref["status"] == 0
+                assert np.allclose(got["lse"][ok], ref["lse"][ok], rtol=1e-4, atol=2e-3)
+    # odd sizes and rows that are not 16-byte aligned
+    for V2 in (1, 3, 1025, 4097, 12345):
+        z2 = (W.normal(32, V2, 3 * V2) * 2.0).astype(np.float32).reshape(3, V2)
+        got, ref = run_both_full(sampler, oracle, z2, dict(temperature=0.9), dict(temperature=0.9), W.uniform_f32(32, 5, 3), None)
+        assert np.array_equal(got["token"], ref["token"]) and np.array_equal(got["status"], ref["status"]), V2
+        assert np.array_equal(got["prob"].view(np.uint32), ref["prob"].view(np.uint32)), V2
+
+
+def run_both_full(sampler, oracle, logits, gpu_params, oracle_params, u, mask):
+    from born_b200 import SamplingConfig
+    torch = torch_mod()
+    ref = oracle.sample(logits, oracle.make_params(**oracle_params), uniforms=u, mask=mask, want_kept=8, nthreads=8)
+    out = sampler.sample(to_dev(logits), uniforms=to_dev(u), config=SamplingConfig(**gpu_params), mask=to_dev(mask),
+                         want_lse=True, want_kept_count=True)
+    torch.cuda.synchronize()
+    return {k: v.cpu().numpy() for k, v in out.items()}, ref

@@ -513,6 +513,12 @@ def test_whole_vocabulary_sampling(sampler, oracle):
                 assert np.array_equal(got["kept_count"], ref["kept_count"]), (dtype, p)
                 ok = ref["status"] == 0
                 assert np.allclose(got["lse"][ok], ref["lse"][ok], rtol=1e-4, atol=2e-3)
+    # the host-memory call takes the same route
+    from born_b200 import SamplingConfig
+    hout = sampler.sample(z, uniforms=u, config=SamplingConfig(temperature=0.6), want_lse=True, want_kept_count=True)
+    href = oracle.sample(z, oracle.make_params(temperature=0.6), uniforms=u, want_kept=8, nthreads=8)
+    assert np.array_equal(hout["token"], href["token"]) and np.array_equal(hout["status"], href["status"])
+    assert np.array_equal(hout["kept_count"], href["kept_count"])
     # odd sizes and rows that are not 16-byte aligned
     for V2 in (1, 3, 1025, 4097, 12345):
         z2 = (W.normal(32, V2, 3 * V2) * 2.0).astype(np.float32).reshape(3, V2)

@@ -280,7 +280,24 @@ static bool wants_full_row(const Handle* h, const born_sample_args* a) {
     return true;
 }
 
-static int sample_full_row(Handle* h, const born_sample_args* a, cudaStream_t st) {
+// Top-p without top-k: the one-pass kernel keeps the 1024 best, which hold the nucleus of any
+// peaked distribution, but the nucleus is defined against the total mass of all survivors.
+// That total comes from the two passes of the whole-vocabulary path (run in sum-only mode).
+static bool wants_survivor_total(const Handle* h, const born_sample_args* a) {
+    if (h->is_static || a->row_params || a->vocab_segments > 1) return false;
+    const born_row_params& p = a->params;
+    if ((p.flags & BORN_FLAG_GREEDY) || p.temperature == 0.0f) return false;
+    if (p.top_k > 0 || !(p.top_p > 0.0f && p.top_p < 1.0f)) return false;
+    const bool pen_on = (p.repetition_penalty != 1.0f && p.repetition_penalty != 0.0f) || p.frequency_penalty != 0.0f ||
+                        p.presence_penalty != 0.0f;
+    if (a->history && pen_on) return false;
+    return true;
+}
+
+// Both launches of the whole-vocabulary path; with `totals_only` the second one leaves each row's
+// total survivor mass in *totals and writes no outputs.
+static int run_full_row(Handle* h, const born_sample_args* a, cudaStream_t st, bool totals_only,
+                        const unsigned long long** totals) {
     const int B = a->batch, V = a->vocab;
     const int esz = a->logits_dtype == BORN_DTYPE_F32 ? 4 : 2;
     const int parts = fullrow_parts(B, V, h->num_sms);
@@ -309,6 +326,8 @@ static int sample_full_row(Handle* h, const born_sample_args* a, cudaStream_t st
     F.stat = reinterpret_cast<float2*>(h->fr_scratch + L.stat);
     F.csum = reinterpret_cast<unsigned long long*>(h->fr_scratch + L.csum);
     F.ccount = reinterpret_cast<uint32_t*>(h->fr_scratch + L.ccount);
+    F.total_out = totals_only ? reinterpret_cast<unsigned long long*>(h->fr_scratch + L.totals) : nullptr;
+    if (totals_only) F.out_kept_count = nullptr;
     F.row_stride = a->logits_row_stride;
     F.mask_stride = a->mask_row_stride;
     F.B = B; F.V = V; F.parts1 = parts;
@@ -318,13 +337,24 @@ static int sample_full_row(Handle* h, const born_sample_args* a, cudaStream_t st
     int rc = launch_fullrow(F, a->logits_dtype, parts, st);
     if (rc != 0) return fail(h, BORN_ERR_CUDA, "full-vocabulary kernel launch failed: %s", cudaGetErrorString((cudaError_t)rc));
     h->launches += 2;
+    if (totals) *totals = F.total_out;
     return BORN_OK;
+}
+
+static int sample_full_row(Handle* h, const born_sample_args* a, cudaStream_t st) {
+    return run_full_row(h, a, st, false, nullptr);
 }
 
 static int sample_device(Handle* h, const born_sample_args* a, cudaStream_t st) {
     if (wants_full_row(h, a)) return sample_full_row(h, a, st);
+    const unsigned long long* survivor_total = nullptr;
+    if (wants_survivor_total(h, a)) {
+        int rc0 = run_full_row(h, a, st, true, &survivor_total);
+        if (rc0 != BORN_OK) return rc0;
+    }
     SampleKernelArgs A;
     memset(&A, 0, sizeof A);
+    A.ext_total = survivor_total;
     A.logits = a->logits;
     A.row_stride = a->logits_row_stride;
     A.mask = a->mask;

@@ -37,6 +37,7 @@ struct FullRowArgs {
     unsigned long long* csum;   // [B, nchunks]
     uint32_t* ccount;           // [B, nchunks]
     uint32_t* tickets;          // [B], zero between launches
+    unsigned long long* total_out;  // when set: launch 2 only leaves the row's total mass here (no draw, no outputs)
     int64_t row_stride, mask_stride;
     int B, V, parts1;
     float temperature, min_p;
@@ -170,7 +171,7 @@ __global__ void __launch_bounds__(kFrThreads) fullrow_draw_kernel(const FullRowA
     else if (m_row == INFINITY) status = BORN_ROW_POS_INF;
     else if (m_row == -INFINITY) status = BORN_ROW_ALL_MASKED;
     if (status != BORN_ROW_OK) {
-        if (part == 0 && tid == 0) {
+        if (part == 0 && tid == 0 && !A.total_out) {
             A.out_token[row_i] = -1;
             A.out_status[row_i] = status;
             if (A.out_prob) A.out_prob[row_i] = 0.0f;
@@ -229,6 +230,10 @@ __global__ void __launch_bounds__(kFrThreads) fullrow_draw_kernel(const FullRowA
         for (int cc = tid; cc < nchunks; cc += kFrThreads) { s += __ldcg(&csum[cc]); nk += __ldcg(&ccount[cc]); }
         const uint64_t S = block_sum_u64(s, sh.red64);
         const uint64_t NK = block_sum_u64((uint64_t)nk, sh.red64);
+        if (A.total_out) {  // the caller only wants the total (top-p over the whole vocabulary)
+            if (tid == 0) A.total_out[row_i] = S;
+            return;
+        }
         if (tid == 0) {
             sh.total = S;
             sh.kept_total = (uint32_t)NK;
@@ -317,7 +322,7 @@ __global__ void __launch_bounds__(kFrThreads) fullrow_draw_kernel(const FullRowA
 }
 
 struct FullRowScratchLayout {
-    size_t tickets, stat, csum, ccount, total;
+    size_t tickets, stat, csum, ccount, totals, total;
 };
 inline FullRowScratchLayout fullrow_scratch_layout(int B, int V, int parts1) {
     FullRowScratchLayout L;
@@ -327,6 +332,7 @@ inline FullRowScratchLayout fullrow_scratch_layout(int B, int V, int parts1) {
     L.stat = off; off += ((size_t)B * parts1 * 8 + 255) / 256 * 256;
     L.csum = off; off += ((size_t)B * nchunks * 8 + 255) / 256 * 256;
     L.ccount = off; off += ((size_t)B * nchunks * 4 + 255) / 256 * 256;
+    L.totals = off; off += ((size_t)B * 8 + 255) / 256 * 256;
     L.total = off;
     return L;
 }

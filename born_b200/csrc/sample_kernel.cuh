@@ -71,6 +71,7 @@ struct SampleKernelArgs {
     int segment_mode;  // 1: each slice keeps its own top-k, the merge takes the union
     int idx_offset;    // added to token indices written to records (shard offset)
     int tma_logits, tma_mask;
+    const unsigned long long* ext_total;  // per row: total mass of all survivors (top-p without top-k), or null
     uint8_t* records;  // record (row, slice) at row*rec_row_stride + slice*rec_slice_stride
     int64_t rec_row_stride, rec_slice_stride;
     uint32_t* tickets;
@@ -1462,7 +1463,12 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     uint64_t* sel = reinterpret_cast<uint64_t*>(smem + L.search);  // kSmallSet keys, then kSmallSet masses
     unsigned long long* selq = reinterpret_cast<unsigned long long*>(sel + kSmallSet);
     const bool own_row = (A.mode == kModeFull && A.S == 1);
-    const bool need_low = (rp.top_k <= 0 && dropped);  // the set's lowest entry must be seen unpruned
+    // With top-k off and entries dropped the kept set is exact only if min-p cuts inside the
+    // buffer -- unless the caller supplied the total mass of all survivors: then top-p is taken
+    // against that total and the row is exact whenever its nucleus fits into the buffer.
+    const bool have_total = A.ext_total != nullptr && rp.top_k <= 0 && rp.top_p > 0.0f && rp.top_p < 1.0f;
+    const bool need_low = (rp.top_k <= 0 && dropped && !have_total);  // the set's lowest entry must be seen unpruned
+    const uint64_t S_all = have_total ? __ldcg(&A.ext_total[row]) : 0ull;
     float tau_g = (own_row && cx.k_eff <= kThreads) ? zkey_to_float(bs.taubits) : -INFINITY;
     if (cx.minp_on && !need_low && !A.segment_mode) tau_g = fmaxf(tau_g, m_row + cx.delta_minp);
     // a merged row whose records hold far more than k entries is cut to its k best first
@@ -1585,8 +1591,17 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             }
             if ((lim & 1) && part2 == 0) before += selq[lim - 1];
             before = group_sum2(before);
-            uint64_t Tp = __double2ull_rz(__dmul_rn((double)rp.top_p, __ull2double_rn(S)));
+            uint64_t Tp = __double2ull_rz(__dmul_rn((double)rp.top_p, __ull2double_rn(have_total ? S_all : S)));
             if (Tp < 1) Tp = 1;
+            if (have_total && dropped && S < Tp) {  // the nucleus does not fit into the buffer
+                if (tid == 0) {
+                    A.out_token[row] = -1;
+                    A.out_status[row] = BORN_ROW_OVERFLOW;
+                    if (A.out_prob) A.out_prob[row] = 0.0f;
+                    if (A.out_kept_count) A.out_kept_count[row] = 0;
+                }
+                return;
+            }
             if (kept2 && !(before < Tp)) { kept2 = false; q2 = 0; }
             cta_sync();
             if (lead2) {
@@ -1669,7 +1684,7 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
             qbuf[i] = 0ull;
         }
     }
-    if (rp.top_k <= 0 && dropped) {
+    if (rp.top_k <= 0 && dropped && !have_total) {
         // survivor limit reached with top-k off: exact only if min-p cuts inside the buffer
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) low_ck = min(low_ck, shfl_xor_u64(low_ck, d));
@@ -1700,8 +1715,17 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
         uint64_t part = 0;
         for (int i = tid; i < n; i += kThreads) part += qbuf[i];
         uint64_t S = block_sum_u64(part, bs.red64);
-        uint64_t Tp = __double2ull_rz(__dmul_rn((double)rp.top_p, __ull2double_rn(S)));
+        uint64_t Tp = __double2ull_rz(__dmul_rn((double)rp.top_p, __ull2double_rn(have_total ? S_all : S)));
         if (Tp < 1) Tp = 1;
+        if (have_total && dropped && S < Tp) {  // the nucleus does not fit into the buffer
+            if (tid == 0) {
+                A.out_token[row] = -1;
+                A.out_status[row] = BORN_ROW_OVERFLOW;
+                if (A.out_prob) A.out_prob[row] = 0.0f;
+                if (A.out_kept_count) A.out_kept_count[row] = 0;
+            }
+            return;
+        }
         uint64_t C = block_radix_search<true, 56, false>(
             n, Tp - 1, [&](int i) { return cand[i]; }, [&](int i) { return qbuf[i]; }, *cx.sc);
         for (int i = tid; i < n; i += kThreads)

@@ -535,3 +535,42 @@ def run_both_full(sampler, oracle, logits, gpu_params, oracle_params, u, mask):
                          want_lse=True, want_kept_count=True)
     torch.cuda.synchronize()
     return {k: v.cpu().numpy() for k, v in out.items()}, ref
+
+
+def test_top_p_without_top_k_is_taken_against_all_survivors(sampler, oracle):
+    # top-p with top-k off: the nucleus is defined against the total mass of every survivor; the
+    # kernel gets that total from the whole-vocabulary passes and is exact whenever the nucleus
+    # fits into the 1024 best, and says BORN_ROW_OVERFLOW when it does not
+    V = 128256
+    for B in (3, 160):  # sliced rows with a record merge, and one CTA per row
+        z = (W.normal(41, B, B * V) * 3.0).astype(np.float32).reshape(B, V)
+        z[0, ::9] = -np.inf
+        z[1] = np.round(z[1] * 4) / 4  # ties around the boundary
+        u = W.uniform_f32(41, 2, B)
+        for p in (dict(temperature=0.7, top_p=0.9), dict(temperature=1.0, top_p=0.5),
+                  dict(temperature=0.5, top_p=0.95, min_p=0.001), dict(temperature=1.2, top_p=0.95)):
+            got, ref = run_both(sampler, oracle, z, p, u, want_kept=64)
+            fits = ref["kept_count"] <= 1024
+            if p["temperature"] < 1.1:
+                assert fits.sum() >= B // 2, (B, p, ref["kept_count"][:8])
+            assert np.all(got["status"][~fits] == 4), (B, p)
+            for k in ("status", "token", "kept_count"):
+                assert np.array_equal(got[k][fits], ref[k][fits]), (B, p, k)
+            assert np.array_equal(got["prob"][fits].view(np.uint32), ref["prob"][fits].view(np.uint32)), (B, p)
+            assert np.array_equal(got["kept_ids"][fits], ref["kept_ids"][fits]), (B, p)
+    # bf16 with a mask; and a flat row whose nucleus cannot fit
+    B = 5
+    zb = (W.normal(42, 1, B * 151936) * 4.0).astype(np.float32).reshape(B, 151936)
+    zb[4] *= 0.05
+    words = (151936 + 31) // 32
+    bits = W.uniform(42, 3, B * words * 32).reshape(B, words * 32) < 0.5
+    bits[:, 151936:] = False
+    mask = np.packbits(bits.reshape(B, words, 32), axis=-1, bitorder="little").view(np.uint32).reshape(B, words)
+    got, ref = run_both(sampler, oracle, W.f32_to_bf16_bits(zb).reshape(B, 151936), dict(temperature=0.5, top_p=0.9),
+                        W.uniform_f32(42, 5, B), mask=mask, want_kept=64)
+    fits = ref["kept_count"] <= 1024
+    assert fits[:4].all() and not fits[4]
+    assert got["status"][4] == 4
+    for k in ("status", "token", "kept_count"):
+        assert np.array_equal(got[k][fits], ref[k][fits]), k
+    assert np.array_equal(got["kept_ids"][fits], ref["kept_ids"][fits])

@@ -173,7 +173,13 @@ int32_t born_sampler_destroy(void* handle);
 
 /* Replaces nn.Accuracy's per-row argmax (internal/nn/cross_entropy.go:241-284) and the
  * softmax / log-sum-exp row passes (internal/autodiff/ops/softmax.go:214-238,
- * internal/nn/cross_entropy.go:126-153) with the full sampling pipeline.  One kernel launch. */
+ * internal/nn/cross_entropy.go:126-153) with the full sampling pipeline.  One kernel launch
+ * when top-k or min-p narrows the row (at most 1024 survivors reach the selection; beyond
+ * that the row reports BORN_ROW_OVERFLOW).  With uniform parameters and no history
+ * penalties, rows that nothing narrows are served over the whole vocabulary instead:
+ * temperature-only sampling (and min-p under BORN_FLAG_FULL_VOCAB) in two launches, top-p
+ * without top-k in three (the nucleus is taken against the total mass of all survivors and
+ * must fit into the 1024 best). */
 int32_t born_sample(void* handle, const born_sample_args* args, void* stream);
 
 /* No counterpart in the reference (it has no speculative decoding); the row arithmetic is

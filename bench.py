@@ -44,6 +44,10 @@ WORKLOADS = {
                                               presence_penalty=0.3)),
     "headline_topk_b256": dict(B=256, V=128256, dtype="f32", H=0, mask=False,
                                params=dict(temperature=0.7, top_k=50, top_p=0.9)),
+    # nothing narrows the row: the two-pass route over the whole vocabulary
+    "temperature_only_b256": dict(B=256, V=128256, dtype="f32", H=0, mask=False, params=dict(temperature=0.8)),
+    # top-p without top-k: two whole-vocabulary passes for the survivor total, then the one-pass kernel
+    "top_p_only_b256": dict(B=256, V=128256, dtype="f32", H=0, mask=False, params=dict(temperature=0.7, top_p=0.9)),
     "c3_constrained_b256": dict(B=256, V=151936, dtype="bf16", H=0, mask=True, params=None),
     "c5_sharded": dict(B=1024, V=256000, dtype="bf16", H=0, mask=False,
                        params=dict(temperature=1.0, top_k=64, top_p=0.95)),

@@ -1012,6 +1012,18 @@ __global__ void __launch_bounds__(kBlockThreads, 2) sample_kernel(const SampleKe
     cx.c2 = inv_T * 1.44269504f;
     cx.minp_on = !greedy && rp.min_p > 0.0f;
     cx.delta_minp = cx.minp_on ? (__logf(rp.min_p) - 0.05f) * rp.temperature : 0.0f;
+    if (A.ext_total && !greedy && rp.top_k <= 0 && rp.top_p > 0.0f && rp.top_p < 1.0f) {
+        // Top-p against the known total S of all survivors: the tokens lighter than
+        // (1 - P) * S / V weigh less than (1 - P) * S together, so the nucleus lies among the
+        // others -- a cut of the same kind as min-p (relative to the running maximum, with a
+        // margin), which spares the candidate buffer nearly the whole row.
+        const float s_all = (float)__ldcg(&A.ext_total[row]) * (1.0f / 1099511627776.0f);
+        if (s_all > 0.0f) {
+            const float d = (__logf((1.0f - rp.top_p) * s_all / (float)A.V) - 0.05f) * rp.temperature;
+            cx.delta_minp = cx.minp_on ? fmaxf(cx.delta_minp, d) : d;
+            cx.minp_on = true;
+        }
+    }
     cx.k_eff = greedy ? 1 : (rp.top_k > 0 ? min(rp.top_k, kMaxK) : kMaxK);
     cx.psize = (A.mode == kModeMerge) ? 0 : kPrivCap;
     cx.trigger = min(max(2 * cx.k_eff, 512), kCandCap - kPrivCap - 128);  // fill of the shared area that asks for a compaction

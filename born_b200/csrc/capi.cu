@@ -54,6 +54,8 @@ struct Handle {
     size_t fr_scratch_bytes = 0;
     int64_t fr_layout_key = -1;
     bool is_static = false;  // the handle of born_sample_static: may not allocate
+    float* pen_copy = nullptr;  // fp32 copy of the rows with history penalties applied (whole-vocabulary routes)
+    size_t pen_copy_bytes = 0;
     Staging stage[16];
     cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
     float timing[3] = {0, 0, 0};
@@ -248,6 +250,7 @@ int32_t born_sampler_destroy(void* handle) {
     cudaFree(h->dev_error);
     cudaFree(h->spec_scratch);
     cudaFree(h->fr_scratch);
+    cudaFree(h->pen_copy);
     cudaFree(h->gathered);
     cudaFree(h->packed);
     for (auto& s : h->stage) cudaFree(s.p);
@@ -288,6 +291,9 @@ static bool wants_survivor_total(const Handle* h, const born_sample_args* a) {
     const born_row_params& p = a->params;
     if ((p.flags & BORN_FLAG_GREEDY) || p.temperature == 0.0f) return false;
     if (p.top_k > 0 || !(p.top_p > 0.0f && p.top_p < 1.0f)) return false;
+    // min-p already narrows the row for the one-pass kernel (up to 1024 survivors): the extra
+    // passes are only taken when the caller asks for them
+    if (p.min_p > 0.0f && !(p.flags & BORN_FLAG_FULL_VOCAB)) return false;
     const bool pen_on = (p.repetition_penalty != 1.0f && p.repetition_penalty != 0.0f) || p.frequency_penalty != 0.0f ||
                         p.presence_penalty != 0.0f;
     if (a->history && pen_on) return false;
@@ -345,7 +351,47 @@ static int sample_full_row(Handle* h, const born_sample_args* a, cudaStream_t st
     return run_full_row(h, a, st, false, nullptr);
 }
 
-static int sample_device(Handle* h, const born_sample_args* a, cudaStream_t st) {
+static int sample_device(Handle* h, const born_sample_args* a_in, cudaStream_t st) {
+    const born_sample_args* a = a_in;
+    born_sample_args a2;
+    {
+        // The whole-vocabulary routes read the raw logits more than once.  A row with history
+        // penalties that would take one of them is first copied, penalties applied, to fp32
+        // scratch; the routes then see plain rows without a history.
+        const born_row_params& p = a_in->params;
+        const bool pen_on = (p.repetition_penalty != 1.0f && p.repetition_penalty != 0.0f) || p.frequency_penalty != 0.0f ||
+                            p.presence_penalty != 0.0f;
+        if (a_in->history && pen_on && !a_in->row_params) {
+            a2 = *a_in;
+            a2.history = nullptr; a2.history_len = nullptr; a2.history_stride = 0;
+            a2.params.repetition_penalty = 0.0f; a2.params.frequency_penalty = 0.0f; a2.params.presence_penalty = 0.0f;
+            if (wants_full_row(h, &a2) || wants_survivor_total(h, &a2)) {
+                const int64_t v_pad = ((int64_t)a_in->vocab + 3) / 4 * 4;
+                const size_t need = (size_t)a_in->batch * (size_t)v_pad * sizeof(float);
+                if (h->pen_copy_bytes < need) {  // grown on first use, like the staging mirrors
+                    CUDA_TRY(h, cudaStreamSynchronize(st));
+                    if (h->pen_copy) { cudaFree(h->pen_copy); h->workspace -= (int64_t)h->pen_copy_bytes; h->pen_copy = nullptr; h->pen_copy_bytes = 0; }
+                    int rc0 = dev_alloc(h, (void**)&h->pen_copy, need);
+                    if (rc0 != BORN_OK) return rc0;
+                    h->pen_copy_bytes = need;
+                }
+                PenaliseArgs P;
+                memset(&P, 0, sizeof P);
+                P.logits = a_in->logits; P.out = h->pen_copy;
+                P.history = a_in->history; P.history_len = a_in->history_len;
+                P.row_stride = a_in->logits_row_stride; P.out_stride = v_pad;
+                P.B = a_in->batch; P.V = a_in->vocab; P.history_stride = a_in->history_stride;
+                P.repetition = p.repetition_penalty; P.frequency = p.frequency_penalty; P.presence = p.presence_penalty;
+                int rc1 = launch_penalised_copy(P, a_in->logits_dtype, h->num_sms, st);
+                if (rc1 != 0) return fail(h, BORN_ERR_CUDA, "penalised-copy launch failed: %s", cudaGetErrorString((cudaError_t)rc1));
+                h->launches += 2;
+                a2.logits = h->pen_copy;
+                a2.logits_dtype = BORN_DTYPE_F32;
+                a2.logits_row_stride = v_pad;
+                a = &a2;
+            }
+        }
+    }
     if (wants_full_row(h, a)) return sample_full_row(h, a, st);
     const unsigned long long* survivor_total = nullptr;
     if (wants_survivor_total(h, a)) {

@@ -361,3 +361,80 @@ inline int launch_fullrow(const FullRowArgs& A, int dtype, int parts2, cudaStrea
 }
 
 }  // namespace born
+
+// ------------------------------------------------------------------ penalised copy of the rows
+// The whole-vocabulary routes read a row more than once, so for rows with history penalties
+// they work on an fp32 copy that already holds the penalised logits: a vector copy (bf16 is
+// widened, exactly), then one small CTA per row that applies the penalties to the distinct
+// history tokens -- the same operations in the same order as the one-pass kernel:
+// repetition (z > 0 ? z / r : z * r), then z - (frequency * count + presence).
+namespace born {
+
+struct PenaliseArgs {
+    const void* logits;        // [B, row_stride] fp32 or bf16
+    float* out;                // [B, out_stride] fp32
+    const int32_t* history;    // [B, history_stride]
+    const int32_t* history_len;  // [B] or null
+    int64_t row_stride, out_stride;
+    int B, V, history_stride;
+    float repetition, frequency, presence;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kFrThreads) widen_copy_kernel(const PenaliseArgs A) {
+    const int row_i = blockIdx.y;
+    const T* row = reinterpret_cast<const T*>(A.logits) + (int64_t)row_i * A.row_stride;
+    float* out = A.out + (int64_t)row_i * A.out_stride;
+    for (int e = blockIdx.x * kFrThreads + threadIdx.x; e < A.V; e += gridDim.x * kFrThreads) out[e] = fr_load<T>(row + e);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kFrThreads) penalise_patch_kernel(const PenaliseArgs A) {
+    __shared__ int32_t ids[BORN_MAX_HISTORY];
+    const int tid = threadIdx.x, row_i = blockIdx.x;
+    int len = A.history_len ? A.history_len[row_i] : A.history_stride;
+    len = max(0, min(min(len, A.history_stride), (int)BORN_MAX_HISTORY));
+    const int32_t* h = A.history + (int64_t)row_i * A.history_stride;
+    for (int i = tid; i < len; i += kFrThreads) ids[i] = h[i];
+    __syncthreads();
+    const T* row = reinterpret_cast<const T*>(A.logits) + (int64_t)row_i * A.row_stride;
+    float* out = A.out + (int64_t)row_i * A.out_stride;
+    for (int i = tid; i < len; i += kFrThreads) {
+        const int id = ids[i];
+        if (id < 0 || id >= A.V) continue;
+        int cnt = 0;
+        bool first = true;
+        for (int j = 0; j < len; ++j) {
+            const bool eq = (ids[j] == id);
+            cnt += eq ? 1 : 0;
+            if (eq && j < i) first = false;
+        }
+        if (!first) continue;  // once per distinct token
+        float z = fr_load<T>(row + id);
+        if (A.repetition != 1.0f && A.repetition != 0.0f) z = (z > 0.0f) ? __fdiv_rn(z, A.repetition) : __fmul_rn(z, A.repetition);
+        if (A.frequency != 0.0f || A.presence != 0.0f) {
+            float pen = __fmul_rn(A.frequency, (float)cnt);
+            pen = __fadd_rn(pen, A.presence);
+            z = __fsub_rn(z, pen);
+        }
+        out[id] = z;
+    }
+}
+
+// returns 0 or a cudaError_t
+inline int launch_penalised_copy(const PenaliseArgs& A, int dtype, int num_sms, cudaStream_t st) {
+    int parts = (8 * num_sms + A.B - 1) / A.B;
+    const int maxp = (A.V + kFrThreads * 4 - 1) / (kFrThreads * 4);
+    if (parts > maxp) parts = maxp;
+    if (parts < 1) parts = 1;
+    const dim3 g((unsigned)parts, (unsigned)A.B, 1);
+    if (dtype == BORN_DTYPE_F32) widen_copy_kernel<float><<<g, kFrThreads, 0, st>>>(A);
+    else widen_copy_kernel<uint16_t><<<g, kFrThreads, 0, st>>>(A);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    if (dtype == BORN_DTYPE_F32) penalise_patch_kernel<float><<<A.B, kFrThreads, 0, st>>>(A);
+    else penalise_patch_kernel<uint16_t><<<A.B, kFrThreads, 0, st>>>(A);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace born

@@ -69,7 +69,7 @@ extern "C" {
                              out and returns after the stream has drained */
 
 #define BORN_FLAG_GREEDY 1u
-#define BORN_FLAG_FULL_VOCAB 2u /* min-p over the whole vocabulary (two passes, no 1024-survivor limit); top-k and top-p off */
+#define BORN_FLAG_FULL_VOCAB 2u /* with min-p on and top-k off: take the whole-vocabulary passes (no 1024-survivor limit for min-p alone; top-p against all survivors) */
 
 /* Sampling parameters of one row (32 bytes).  Zero means "off" for every filter, as in
  * the reference's config structs (internal/optim/adam.go:78-91). */
@@ -175,8 +175,9 @@ int32_t born_sampler_destroy(void* handle);
  * softmax / log-sum-exp row passes (internal/autodiff/ops/softmax.go:214-238,
  * internal/nn/cross_entropy.go:126-153) with the full sampling pipeline.  One kernel launch
  * when top-k or min-p narrows the row (at most 1024 survivors reach the selection; beyond
- * that the row reports BORN_ROW_OVERFLOW).  With uniform parameters and no history
- * penalties, rows that nothing narrows are served over the whole vocabulary instead:
+ * that the row reports BORN_ROW_OVERFLOW).  With uniform parameters, rows that nothing
+ * narrows are served over the whole vocabulary instead (history penalties are applied to an
+ * fp32 copy of the rows first):
  * temperature-only sampling (and min-p under BORN_FLAG_FULL_VOCAB) in two launches, top-p
  * without top-k in three (the nucleus is taken against the total mass of all survivors and
  * must fit into the 1024 best). */

@@ -574,3 +574,39 @@ def test_top_p_without_top_k_is_taken_against_all_survivors(sampler, oracle):
     for k in ("status", "token", "kept_count"):
         assert np.array_equal(got[k][fits], ref[k][fits]), k
     assert np.array_equal(got["kept_ids"][fits], ref["kept_ids"][fits])
+
+
+def test_whole_vocabulary_routes_with_history_penalties(sampler, oracle):
+    # temperature (+ top-p) with repetition / frequency / presence penalties and no top-k: the
+    # rows are copied with the penalties applied, then take the whole-vocabulary routes
+    B, V = 7, 50257
+    z = (W.normal(51, 1, B * V) * 3.0).astype(np.float32).reshape(B, V)
+    u = W.uniform_f32(51, 2, B)
+    hist = W.randint(51, 3, B * 96, V).astype(np.int32).reshape(B, 96)
+    hist[:, 10:20] = hist[:, 0:10]                      # repeats
+    hist[0, :8] = np.argsort(-z[0])[:8].astype(np.int32)  # the row's best tokens are in its history
+    hist[1, 5] = -3
+    hist[1, 6] = V + 2
+    hl = np.array([96, 96, 0, 1, 50, 96, 17], dtype=np.int32)
+    for dtype in ("f32", "bf16"):
+        logits = z if dtype == "f32" else W.f32_to_bf16_bits(z).reshape(B, V)
+        for p in (dict(temperature=0.9, repetition_penalty=1.3),
+                  dict(temperature=0.7, frequency_penalty=0.4, presence_penalty=0.2),
+                  dict(temperature=0.6, top_p=0.9, repetition_penalty=1.2, frequency_penalty=0.3, presence_penalty=0.1)):
+            want = 32 if "top_p" in p else 0
+            from born_b200 import SamplingConfig
+            torch = torch_mod()
+            ref = oracle.sample(logits, oracle.make_params(**p), uniforms=u, history=hist, history_len=hl, want_kept=max(want, 8),
+                                nthreads=8)
+            out = sampler.sample(to_dev(logits), uniforms=to_dev(u), config=SamplingConfig(**p), history=to_dev(hist),
+                                 history_len=to_dev(hl), want_lse=True, want_kept=want, want_kept_count=True)
+            torch.cuda.synchronize()
+            got = {k: v.cpu().numpy() for k, v in out.items()}
+            fits = ref["kept_count"] <= 1024 if "top_p" in p else np.ones(B, dtype=bool)
+            assert fits.sum() >= B - 1, (dtype, p, ref["kept_count"])
+            for k in ("status", "token", "kept_count"):
+                assert np.array_equal(got[k][fits], ref[k][fits]), (dtype, p, k, got[k], ref[k])
+            assert np.array_equal(got["prob"][fits].view(np.uint32), ref["prob"][fits].view(np.uint32)), (dtype, p)
+            if want:
+                assert np.array_equal(got["kept_ids"][fits], ref["kept_ids"][fits][:, :want]), (dtype, p)
+            assert np.allclose(got["lse"][fits], ref["lse"][fits], rtol=1e-4, atol=2e-3)

@@ -610,3 +610,33 @@ def test_whole_vocabulary_routes_with_history_penalties(sampler, oracle):
             if want:
                 assert np.array_equal(got["kept_ids"][fits], ref["kept_ids"][fits][:, :want]), (dtype, p)
             assert np.allclose(got["lse"][fits], ref["lse"][fits], rtol=1e-4, atol=2e-3)
+
+
+def test_which_parameter_sets_take_which_route(sampler):
+    # one launch whenever top-k or min-p narrows the row (the fast path of the benchmark's
+    # default workload must never drift onto the slower routes); two launches for
+    # temperature-only sampling, three for top-p alone, two more when penalties need the copy
+    from born_b200 import SamplingConfig
+    torch = torch_mod()
+    B, V = 4, 32000
+    z = torch.randn((B, V), device="cuda")
+    u = torch.rand(B, device="cuda").clamp_(max=0.999)
+    hist = torch.randint(0, V, (B, 32), device="cuda", dtype=torch.int32)
+
+    def launches(cfg, history=None):
+        n0 = sampler.launch_count
+        sampler.sample(z, uniforms=u, config=cfg, history=history)
+        torch.cuda.synchronize()
+        return sampler.launch_count - n0
+
+    pen = dict(frequency_penalty=0.5, presence_penalty=0.3)
+    assert launches(SamplingConfig(temperature=0.7, min_p=0.05, top_p=0.9, **pen), hist) == 1
+    assert launches(SamplingConfig(temperature=0.7, min_p=0.05, top_p=0.9)) == 1
+    assert launches(SamplingConfig(temperature=0.7, top_k=50, top_p=0.9)) == 1
+    assert launches(SamplingConfig(temperature=0.7, min_p=0.05)) == 1
+    assert launches(SamplingConfig(greedy=True)) == 1
+    assert launches(SamplingConfig(temperature=0.7)) == 2
+    assert launches(SamplingConfig(temperature=0.7, min_p=0.05, full_vocab=True)) == 2
+    assert launches(SamplingConfig(temperature=0.7, top_p=0.9)) == 3
+    assert launches(SamplingConfig(temperature=0.7, **pen), hist) == 4
+    assert launches(SamplingConfig(temperature=0.7, top_p=0.9, **pen), hist) == 5

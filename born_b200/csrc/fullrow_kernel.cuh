@@ -90,13 +90,25 @@ __global__ void __launch_bounds__(kFrThreads) fullrow_stat_kernel(const FullRowA
     const int lo = part * per, hi = min(nvec, lo + per);
     const float c2 = 1.44269504f / A.temperature;
     float mx = -INFINITY, R = -1e30f, s = 0.0f;
-    for (int g = lo + tid; g < hi; g += kFrThreads) {
-        float v[VEC];
-        fr_load_vec<T>(row, g * VEC, A.V, A.vec_ok != 0, v);
-        if constexpr (kHasMask) fr_apply_mask<VEC>(mrow, g * VEC, v);
-        float m = v[0];
+    constexpr int UN = 4;  // vectors in flight per thread: the loop is bound by load latency otherwise
+    for (int g0 = lo + tid; g0 < hi; g0 += kFrThreads * UN) {
+        float v[UN][VEC];
 #pragma unroll
-        for (int i = 1; i < VEC; ++i) m = max_nan(m, v[i]);
+        for (int k = 0; k < UN; ++k) {
+            const int g = g0 + k * kFrThreads;
+            if (g < hi) {
+                fr_load_vec<T>(row, g * VEC, A.V, A.vec_ok != 0, v[k]);
+                if constexpr (kHasMask) fr_apply_mask<VEC>(mrow, g * VEC, v[k]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) v[k][i] = -INFINITY;
+            }
+        }
+        float m = v[0][0];
+#pragma unroll
+        for (int k = 0; k < UN; ++k)
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) m = max_nan(m, v[k][i]);
         mx = max_nan(mx, m);
         if (m > R) {
             s *= ex2_approx(__fmul_rn(R - m, c2));
@@ -104,7 +116,9 @@ __global__ void __launch_bounds__(kFrThreads) fullrow_stat_kernel(const FullRowA
         }
         const float nRc = -R * c2;
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) s += ex2_approx(fmaf(v[i], c2, nRc));
+        for (int k = 0; k < UN; ++k)
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) s += ex2_approx(fmaf(v[k][i], c2, nRc));
     }
     // block reduce: maximum, then the sums rescaled to it
     float wm = mx;
@@ -206,7 +220,7 @@ __global__ void __launch_bounds__(kFrThreads) fullrow_draw_kernel(const FullRowA
             for (int k = 0; k < VEC; ++k) {
                 bool kept;
                 s += weight(v[k], kept);
-                nk += kept ? 1u : 0u;
+                if (A.out_kept_count) nk += kept ? 1u : 0u;
             }
         }
         const uint64_t tot_s = block_sum_u64(s, sh.red64);

@@ -3,20 +3,23 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
-A step is one pass of the fused sampling kernel over one batch of synthetic logits.  The
-default workload is the batched-decode recipe (fp32 N(0, 3^2) + Zipf-shaped bias,
-temperature 0.7, min-p 0.05, top-p 0.9, frequency 0.5 / presence 0.3 over 512 prior ids)
-at the headline shape batch 256 x vocab 128256.  With N GPUs every rank samples its own
-batch (batch-parallel, no communication): weak scaling.  `--workload c5_sharded` runs the
-vocab-sharded path instead (local top-k + one NCCL all-gather + merge).
+A step is one pass of the sampling kernel over one batch of synthetic logits.  The default
+workload is the batched-decode recipe (fp32 N(0, 3^2) + Zipf-shaped bias, temperature 0.7,
+min-p 0.05, top-p 0.9, frequency 0.5 / presence 0.3 over 512 prior ids) at the headline shape
+batch 256 x vocab 128256.  With N GPUs every rank samples its own batch (batch-parallel, no
+communication): weak scaling.
 
-`value` is device-resident throughput (inputs already in HBM, CUDA events on the launching
-stream, max over ranks); `e2e` is the same metric through the host-memory C-ABI call
-(pinned host buffers, host<->device copies inside the timed region).  Between timed
-iterations the kernel reads a different one of several logits buffers whose total size
-exceeds L2, so no launch finds its input cached.  `--impl reference` times the CPU oracle
-(the reference's sequential algorithm restated in C, one thread per core over rows) on
-this box's host cores.
+`value` is device-resident throughput: inputs already in HBM, the K timed steps recorded
+once into a CUDA graph and replayed between two CUDA events on the launching stream, so that
+the figure does not depend on how fast the host issues launches; max over ranks.  Between
+timed steps the kernel reads a different one of several logits buffers whose total size
+exceeds L2.  `e2e` is the same metric through the host-memory C-ABI call (pinned host
+buffers, host<->device copies inside the timed region).  `workloads` holds the other
+workloads of the same library (top-k, temperature-only, top-p alone, constrained bf16,
+speculative verification; with N > 1 the vocab-sharded path over NCCL), each with its own
+time, roofline fraction and a parity block against the CPU oracle over every row.
+`--impl reference` times the CPU oracle (the reference's sequential algorithm restated in C,
+one thread per core over rows) on the same rows from the same generator.
 """
 import argparse
 import json
@@ -33,27 +36,25 @@ import numpy as np  # noqa: E402
 
 METRIC = "sampled_rows_per_s"
 UNIT = "rows/s"
+DEFAULT = "c2_batched_decode_b256"
 
+PEN = dict(frequency_penalty=0.5, presence_penalty=0.3)
 WORKLOADS = {
-    # name: (batch, vocab, dtype, history, description)
     "c2_batched_decode_b256": dict(B=256, V=128256, dtype="f32", H=512, mask=False,
-                                   params=dict(temperature=0.7, min_p=0.05, top_p=0.9, frequency_penalty=0.5,
-                                               presence_penalty=0.3)),
+                                   params=dict(temperature=0.7, min_p=0.05, top_p=0.9, **PEN)),
     "c2_batched_decode_b64": dict(B=64, V=128256, dtype="f32", H=512, mask=False,
-                                  params=dict(temperature=0.7, min_p=0.05, top_p=0.9, frequency_penalty=0.5,
-                                              presence_penalty=0.3)),
+                                  params=dict(temperature=0.7, min_p=0.05, top_p=0.9, **PEN)),
     "headline_topk_b256": dict(B=256, V=128256, dtype="f32", H=0, mask=False,
                                params=dict(temperature=0.7, top_k=50, top_p=0.9)),
-    # nothing narrows the row: the two-pass route over the whole vocabulary
     "temperature_only_b256": dict(B=256, V=128256, dtype="f32", H=0, mask=False, params=dict(temperature=0.8)),
-    # top-p without top-k: two whole-vocabulary passes for the survivor total, then the one-pass kernel
     "top_p_only_b256": dict(B=256, V=128256, dtype="f32", H=0, mask=False, params=dict(temperature=0.7, top_p=0.9)),
     "c3_constrained_b256": dict(B=256, V=151936, dtype="bf16", H=0, mask=True, params=None),
     "c5_sharded": dict(B=1024, V=256000, dtype="bf16", H=0, mask=False,
                        params=dict(temperature=1.0, top_k=64, top_p=0.95)),
-    # speculative verification: 32 sequences x 5 draft positions (+ bonus row); metric is its own
     "c4_spec_verify": dict(B=32, V=128256, dtype="f32", H=0, mask=False, K=5, params=None),
 }
+EXTRA_N1 = ["headline_topk_b256", "temperature_only_b256", "top_p_only_b256", "c3_constrained_b256",
+            "c2_batched_decode_b64", "c4_spec_verify"]
 
 
 def algorithmic_bytes_per_row(w, V=None):
@@ -171,80 +172,126 @@ def host_copy(torch, buf):
     return out
 
 
-def run_reference(args, w, name):
-    """CPU arm: the oracle on host cores, rank 0 only."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
-    from born_b200 import workloads as W
+def read_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f)
+    except Exception:
+        return {}
+
+
+def roofline(bytes_launch, kernel_ms, name):
+    peaks = read_peaks()
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    achieved = bytes_launch / (kernel_ms * 1e-3) / 1e9
+    traffic = None
+    try:
+        with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+            traffic = json.load(f).get(name)
+    except Exception:
+        pass
+    return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "traffic": traffic, "peak_source": "measured" if peaks else "fallback",
+            "algorithmic_bytes_per_launch": bytes_launch, "frac_of_8TBs": achieved / 8000.0}
+
+
+def timed_steps(torch, stream, calls, steps, warmup, barrier):
+    """Runs warmup steps, then times `steps` steps (calls[i % len(calls)]) between two CUDA events.
+    The timed steps are captured once into a CUDA graph and replayed, so the device never waits
+    for the host; when capture is not possible they are issued directly.  Returns (ms, how)."""
+    n = len(calls)
+    sp = stream.cuda_stream
+    for i in range(warmup):
+        calls[i % n](sp)
+    barrier()
+    graph = None
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            csp = torch.cuda.current_stream().cuda_stream
+            for i in range(steps):
+                calls[i % n](csp)
+        graph.replay()  # one untimed replay: the graph's own first-launch cost
+        torch.cuda.synchronize()
+    except Exception as e:  # pragma: no cover - capture refused
+        sys.stderr.write(f"bench: CUDA graph capture failed ({e!r}); timing direct launches\n")
+        graph = None
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    if graph is not None:
+        graph.replay()
+    else:
+        for i in range(steps):
+            calls[i % n](sp)
+    e1.record(stream)
+    barrier()
+    return e0.elapsed_time(e1), ("cuda-graph of %d steps" % steps) if graph is not None else "direct launches"
+
+
+def parity_block(torch, w, name, buf, out, segments=1):
+    """GPU outputs of one step on `buf` against the CPU oracle over every row."""
     from oracle import born_oracle as O
     O.build()
-    cores = os.cpu_count() or 1
-    B, V = w["B"], w["V"]
-    rows = min(B, max(cores, 64))  # bounded sample of the workload
-    z = (W.normal(0, 10, rows * V) * 3.0).astype(np.float32).reshape(rows, V)
-    if w["dtype"] == "f32":
-        bias = -1.1 * np.log(np.arange(1, V + 1, dtype=np.float64))
-        for b in range(rows):
-            perm = np.argsort(W.raw_u64(0, 1000 + b, V), kind="stable")
-            z[b, perm] += bias.astype(np.float32)
-        logits = z
-    else:
-        logits = W.f32_to_bf16_bits(z)
-    u = W.uniform_f32(0, 12, rows)
-    hist = W.randint(0, 11, rows * w["H"], V).astype(np.int32).reshape(rows, w["H"]) if w["H"] else None
-    mask = None
-    if w["mask"]:
-        words = (V + 31) // 32
-        bits = W.uniform(0, 21, rows * words * 32).reshape(rows, words * 32) < 0.05
-        bits[:, V:] = False
-        bits[:, 0] = True
-        mask = np.packbits(bits.reshape(rows, words, 32), axis=-1, bitorder="little").view(np.uint32).reshape(rows, words)
+    hc = host_copy(torch, buf)
     params = oracle_params_for(w)
-    if params.size > 1:
-        params = params[:rows]
-    seg = 8 if name == "c5_sharded" else 1
-
-    def step():
-        O.sample(logits, params, uniforms=u, mask=mask, history=hist, segments=seg, nthreads=cores)
-
-    for _ in range(args.warmup):
-        step()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        step()
-    dt = time.perf_counter() - t0
-    val = rows * args.steps / dt
-    line = {
-        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
-        "config": {"workload": name, "batch": B, "vocab": V, "sample_rows_per_step": rows},
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"{rows} rows of the workload per step, {args.steps} steps, {cores} threads over rows"},
-        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }
-    print(json.dumps(line), flush=True)
+    ref = O.sample(hc["logits"], params, uniforms=hc["uniforms"], mask=hc["mask"], history=hc["history"],
+                   segments=segments, nthreads=os.cpu_count() or 1)
+    tok = out["token"].cpu().numpy()
+    prob = out["prob"].cpu().numpy()
+    st = out["status"].cpu().numpy()
+    res = {"rows_checked": int(tok.size), "token_mismatches": int((tok != ref["token"]).sum()),
+           "prob_bit_mismatches": int((prob.view(np.uint32) != ref["prob"].view(np.uint32)).sum()),
+           "status_mismatches": int((st != ref["status"]).sum()),
+           "near_cutoff_rows": int((ref["near_cutoff"] != 0).sum()),
+           "row_status_nonzero": int((st != 0).sum())}
+    if "lse" in out:
+        lse = out["lse"].cpu().numpy()
+        ok = ref["status"] == 0
+        res["max_abs_lse_diff_vs_sequential_f32"] = float(np.nanmax(np.abs(lse[ok] - ref["lse"][ok]))) if ok.any() else 0.0
+    return res
 
 
-def run_spec(args, w, name):
-    """Speculative verification (born_spec_verify): one step verifies B sequences of K draft
-    tokens against K+1 target rows.  Every rank verifies its own batch (no communication)."""
-    import torch
-    import torch.distributed as dist
-    from born_b200 import Sampler, build
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the sampling path has no CPU fallback")
-    build.build()
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
+def run_sampling_workload(torch, dist, sampler, name, w, rank, world, device, steps, warmup, small, barrier):
+    """Times one batch-parallel sampling workload; returns a dict with everything the caller reports."""
+    B, V = w["B"], w["V"]
+    esz = 4 if w["dtype"] == "f32" else 2
+    nbuf = 1 if small else max(2, int(np.ceil(400e6 / (B * V * esz))) + 1)
+    bufs = make_inputs(torch, w, seed=1234 + rank, device=device, nbuf=nbuf)
+    cfg, rp = row_params_for(w)
+    rp_dev = torch.from_numpy(rp.view(np.uint8)).to(device) if rp is not None else None
+    stream = torch.cuda.current_stream()
+    out = {}
+    kw = dict(uniforms=bufs[0]["uniforms"], config=cfg, row_params=rp_dev, mask=bufs[0].get("mask"),
+              history=bufs[0].get("history"), want_prob=True, want_lse=True, out=out)
+    sampler.reserve(bufs[0]["logits"], **kw)
+    prepared = [sampler.prepare(b["logits"], **kw) for b in bufs]
+    calls = [p.run for p in prepared]
+    l0 = sampler.launch_count
+    calls[0](stream.cuda_stream)
+    per_step = sampler.launch_count - l0
+    ms, how = timed_steps(torch, stream, calls, steps, warmup, barrier)
+    sampler.check_error()
+    fb = sampler.fallback_rows
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    res = {"ms_per_step": ms / steps, "launches_per_step": int(per_step), "timing": how, "nbuf": nbuf,
+           "bytes_launch": algorithmic_bytes_per_row(w) * B, "bufs": bufs, "out": out, "prepared": prepared,
+           "cfg": cfg, "rp": rp, "fallback_rows_in_timed_steps": fb}
+    if rank == 0:
+        calls[0](stream.cuda_stream)
+        torch.cuda.synchronize()
+        res["parity"] = parity_block(torch, w, name, bufs[0], out)
+    return res
+
+
+def run_spec_workload(torch, dist, sampler, w, rank, world, device, steps, warmup, small, barrier, cpu_baseline):
+    """Speculative verification (born_spec_verify): one step verifies B sequences of K draft tokens."""
     B, V, K = w["B"], w["V"], w["K"]
-    nbuf = 1 if args.small else 3
+    nbuf = 1 if small else 3
     g = torch.Generator(device=device).manual_seed(4321 + rank)
     sets = []
     for _ in range(nbuf):
@@ -254,104 +301,186 @@ def run_spec(args, w, name):
         sets.append(dict(target=tgt, draft=drf, tok=tok.contiguous(),
                          ua=torch.rand((B, K), generator=g, device=device),
                          ur=torch.rand((B, K + 1), generator=g, device=device).clamp_(max=1.0 - 2.0 ** -24)))
-    sampler = Sampler(device=local, max_batch=B, max_vocab=V)
     stream = torch.cuda.current_stream()
-    sp = stream.cuda_stream
+    holder = {}
 
-    def step(i):
-        s_ = sets[i % nbuf]
-        return sampler.spec_verify(s_["target"], s_["draft"], s_["tok"], s_["ua"], s_["ur"], stream=sp)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for i in range(args.warmup):
-        step(i)
-    barrier()
-    clocks = ClockSampler(local)
-    clocks.start()
+    def mk(s_):
+        def call(sp):
+            holder["res"] = sampler.spec_verify(s_["target"], s_["draft"], s_["tok"], s_["ua"], s_["ur"], stream=sp)
+        return call
+    calls = [mk(s_) for s_ in sets]
     l0 = sampler.launch_count
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    calls[0](stream.cuda_stream)
+    per_step = sampler.launch_count - l0
+    # (spec_verify allocates its outputs per call: direct launches, no graph)
+    for i in range(warmup):
+        calls[i % nbuf](stream.cuda_stream)
     barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
-    for i in range(args.steps):
-        step(i)
+    for i in range(steps):
+        calls[i % nbuf](stream.cuda_stream)
     e1.record(stream)
     barrier()
     ms = e0.elapsed_time(e1)
-    launches = sampler.launch_count - l0
-    t_end = time.time() + 0.6
-    i = 0
-    while time.time() < t_end:
-        step(i)
-        i += 1
-        if i % 16 == 0:
-            torch.cuda.synchronize()
-    torch.cuda.synchronize()
-    clocks.stop_flag = True
-    clocks.join(timeout=3)
     t = torch.tensor([ms], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
+    res = {"ms_per_step": ms / steps, "launches_per_step": int(per_step), "timing": "direct launches",
+           "bytes_launch": B * (2 * K + 1) * V * 4, "sequences": B}
     if rank == 0:
         from oracle import born_oracle as O
         O.build()
-        res = step(0)
+        calls[0](stream.cuda_stream)
         torch.cuda.synchronize()
-        nchk = min(B, 8)
+        r = holder["res"]
         s0 = sets[0]
-        ref = O.spec_verify(s0["target"][:nchk].cpu().numpy(), s0["draft"][:nchk].cpu().numpy(),
-                            s0["tok"][:nchk].cpu().numpy(), s0["ua"][:nchk].cpu().numpy(),
-                            s0["ur"][:nchk].cpu().numpy(), nthreads=os.cpu_count() or 1)
-        alen = res["accept_len"][:nchk].cpu().numpy()
-        toks = res["tokens"][:nchk].cpu().numpy()
+        hs = {k: v.cpu().numpy() for k, v in s0.items()}
+        ref = O.spec_verify(hs["target"], hs["draft"], hs["tok"], hs["ua"], hs["ur"], nthreads=os.cpu_count() or 1)
+        alen = r["accept_len"].cpu().numpy()
+        toks = r["tokens"].cpu().numpy()
         mism = 0
-        for b in range(nchk):
+        for b in range(B):
             n = int(ref["accept_len"][b]) + 1
             mism += int(alen[b] != ref["accept_len"][b]) + int((toks[b, :n] != ref["tokens"][b, :n]).any())
-        cpu = None
-        if world == 1 and not args.no_cpu_baseline:
+        res["parity"] = {"sequences_checked": B, "mismatches": mism}
+        if cpu_baseline:
             cores = os.cpu_count() or 1
-            hs = {k: v[:nchk].cpu().numpy() for k, v in s0.items()}
             t0 = time.perf_counter()
             reps = 0
-            while time.perf_counter() - t0 < 10.0:
+            while time.perf_counter() - t0 < 5.0:
                 O.spec_verify(hs["target"], hs["draft"], hs["tok"], hs["ua"], hs["ur"], nthreads=cores)
                 reps += 1
             dt = time.perf_counter() - t0
-            cpu = {"value": nchk * reps / dt, "unit": "sequences/s", "cores": cores, "kind": "port",
-                   "sample": f"{nchk} sequences of the workload x {reps} passes, {cores} threads over sequences"}
-        peaks = {}
-        try:
-            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-                peaks = json.load(f)
-        except Exception:
-            pass
-        peak = float(peaks.get("hbm_gbs", 6650.0))
-        bytes_launch = B * (2 * K + 1) * V * 4
-        kernel_ms = ms / args.steps
-        achieved = bytes_launch / (kernel_ms * 1e-3) / 1e9
-        line = {
-            "metric": "spec_verified_sequences_per_s", "value": B * args.steps * world / (ms * 1e-3),
-            "unit": "sequences/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": kernel_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
-            "config": {"workload": name, "batch_per_gpu": B, "draft_len": K, "vocab": V,
-                       "parallelism": "batch-parallel x%d" % world,
-                       "l2": f"{nbuf} rotating input sets, {nbuf * bytes_launch / 1e6:.0f} MB > L2"},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": "measured" if peaks else "fallback",
-                         "algorithmic_bytes_per_launch": bytes_launch, "frac_of_8TBs": achieved / 8000.0},
-            "cpu_baseline": cpu, "e2e": None, "gpu_launches": int(launches), "clocks": clocks.summary(),
-            "parity": {"sequences_checked": nchk, "mismatches": mism},
-        }
-        print(json.dumps(line), flush=True)
-    sampler.close()
-    if world > 1:
-        dist.destroy_process_group()
+            res["cpu_baseline"] = {"value": B * reps / dt, "unit": "sequences/s", "cores": cores, "kind": "port",
+                                   "sample": f"all {B} sequences of the workload x {reps} passes, {cores} threads over sequences"}
+    return res
+
+
+def run_sharded(torch, dist, sampler, w, rank, world, device, steps, warmup, barrier):
+    """Vocab-sharded sampling (local top-k -> NCCL all-gather -> merge) over all ranks, with a
+    parity block against the oracle's segmented sampling over every row."""
+    from born_b200 import Sampler
+    B, V = w["B"], w["V"]
+    Vl = V // world
+    wl = dict(w)
+    wl["V"] = Vl
+    esz = 2
+    nbuf = max(2, int(np.ceil(400e6 / (B * Vl * esz))) + 1)
+    bufs = make_inputs(torch, wl, seed=977 + rank, device=device, nbuf=nbuf)
+    dist.broadcast(bufs[0]["uniforms"], src=0)
+    uid = [Sampler.nccl_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(uid, src=0)
+    sampler.shard_init(uid[0], rank, world)
+    out = {}
+    stream = torch.cuda.current_stream()
+    p = w["params"]
+
+    def mk(b):
+        def call(sp):
+            sampler.sample_sharded(b["logits"], bufs[0]["uniforms"], rank, world, p["top_k"],
+                                   temperature=p["temperature"], top_p=p["top_p"], stream=sp, out=out)
+        return call
+    calls = [mk(b) for b in bufs]
+    l0 = sampler.launch_count
+    calls[0](stream.cuda_stream)
+    per_step = sampler.launch_count - l0
+    torch.cuda.synchronize()
+    for i in range(warmup):
+        calls[i % nbuf](stream.cuda_stream)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(steps):
+        calls[i % nbuf](stream.cuda_stream)
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    # parity: rank 0 gathers the shards of buffer 0 once, outside the timed region
+    calls[0](stream.cuda_stream)
+    torch.cuda.synchronize()
+    shard = bufs[0]["logits"].view(torch.int16)
+    gathered = [torch.empty_like(shard) for _ in range(world)] if rank == 0 else None
+    dist.gather(shard, gathered, dst=0)
+    toks = [torch.empty_like(out["token"]) for _ in range(world)] if rank == 0 else None
+    dist.gather(out["token"], toks, dst=0)
+    res = None
+    if rank == 0:
+        from oracle import born_oracle as O
+        O.build()
+        full = torch.cat(gathered, dim=1).cpu().numpy().view(np.uint16)
+        u = bufs[0]["uniforms"].cpu().numpy()
+        ref = O.sample(np.ascontiguousarray(full), O.make_params(**p), uniforms=u, segments=world,
+                       nthreads=os.cpu_count() or 1)
+        tok = out["token"].cpu().numpy()
+        prob = out["prob"].cpu().numpy()
+        st = out["status"].cpu().numpy()
+        same = all(bool((tk == toks[0]).all().item()) for tk in toks)
+        kernel_ms = ms / steps
+        bytes_gpu = Vl * esz * B
+        res = {"workload": "c5_sharded", "ms_per_step": kernel_ms, "rows_per_s": B / (kernel_ms * 1e-3),
+               "launches_per_step": int(per_step), "collective": "one ncclAllGather of %d bytes per rank" % (B * (32 + 8 * p["top_k"])),
+               "vocab_per_gpu": Vl, "roofline_per_gpu": roofline(bytes_gpu, kernel_ms, "c5_sharded"),
+               "parity": {"rows_checked": int(B), "token_mismatches": int((tok != ref["token"]).sum()),
+                          "prob_bit_mismatches": int((prob.view(np.uint32) != ref["prob"].view(np.uint32)).sum()),
+                          "status_mismatches": int((st != ref["status"]).sum()),
+                          "all_ranks_agree": bool(same)}}
+    return res
+
+
+def reference_inputs(w, rows):
+    """The first `rows` rows of the GPU arm's first input buffer (same generator, same seed): made
+    on the GPU when there is one, so that both arms see identical rows."""
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --impl reference needs the GPU box: it samples the rows the GPU arm samples")
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    buf = make_inputs(torch, w, seed=1234, device=device, nbuf=1)[0]
+    hc = host_copy(torch, buf)
+    return {k: (None if v is None else np.ascontiguousarray(v[:rows])) for k, v in hc.items()}
+
+
+def run_reference(args, w, name):
+    """CPU arm: the oracle on host cores, rank 0 only, on the rows the GPU arm samples."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import born_oracle as O
+    O.build()
+    cores = os.cpu_count() or 1
+    B, V = w["B"], w["V"]
+    hc = reference_inputs(w, B)
+    params = oracle_params_for(w)
+    seg = 8 if name == "c5_sharded" else 1
+
+    def step():
+        O.sample(hc["logits"], params, uniforms=hc["uniforms"], mask=hc["mask"], history=hc["history"], segments=seg,
+                 nthreads=cores)
+
+    for _ in range(args.warmup):
+        step()
+    # at least `steps` steps and at least 3 s of CPU work
+    t0 = time.perf_counter()
+    n = 0
+    while n < args.steps or time.perf_counter() - t0 < 3.0:
+        step()
+        n += 1
+    dt = time.perf_counter() - t0
+    val = B * n / dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": n,
+        "warmup": args.warmup, "ms_per_step": 1e3 * dt / n, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "config": {"workload": name, "batch_per_gpu": B, "vocab": V, "same_rows_as_gpu_arm": True},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"all {B} rows of the workload per step, {n} steps, {cores} threads over rows"},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
 
 
 def main():
@@ -359,10 +488,11 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
-    ap.add_argument("--workload", default="c2_batched_decode_b256", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="born_b200", choices=["born_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the other workloads of the `workloads` key")
     ap.add_argument("--small", action="store_true", help="one input buffer, for profiler captures")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
@@ -375,8 +505,6 @@ def main():
         return run_reference(args, w, name)
     args.steps = args.steps or 200
     args.warmup = 20 if args.warmup is None else args.warmup
-    if name == "c4_spec_verify":
-        return run_spec(args, w, name)
 
     import torch
     import torch.distributed as dist
@@ -392,93 +520,54 @@ def main():
     device = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    sharded = name == "c5_sharded" and world > 1
-    B, V = w["B"], w["V"]
-    V_local = V // world if sharded else V
-
-    nbuf = 1 if args.small else max(2, int(np.ceil(400e6 / (B * V_local * (4 if w["dtype"] == "f32" else 2)))) + 1)
-    wl = dict(w)
-    if sharded:
-        wl["V"] = V_local
-    bufs = make_inputs(torch, wl, seed=1234 + (0 if sharded else rank), device=device, nbuf=nbuf)
-    if sharded:  # uniforms must be identical on every rank
-        dist.broadcast(bufs[0]["uniforms"], src=0)
-    # the one-GPU form of the sharded workload cuts every row into 8 vocab segments (8 records a row)
-    sampler = Sampler(device=local, max_batch=B * (2 if name == "c5_sharded" and not sharded else 1),
-                      max_vocab=max(V_local, 1024))
-    cfg, rp = row_params_for(w)
-    rp_dev = torch.from_numpy(rp.view(np.uint8)).to(device) if rp is not None else None
-    stream = torch.cuda.current_stream()
-    sp = stream.cuda_stream
-    if sharded:
-        uid = [Sampler.nccl_unique_id() if rank == 0 else None]
-        dist.broadcast_object_list(uid, src=0)
-        sampler.shard_init(uid[0], rank, world)
-    out = {}
-
-    def step(i):
-        b = bufs[i % nbuf]
-        if sharded:
-            sampler.sample_sharded(b["logits"], b["uniforms"], rank, world, w["params"]["top_k"],
-                                   temperature=w["params"]["temperature"], top_p=w["params"]["top_p"], stream=sp, out=out)
-        else:
-            sampler.sample(b["logits"], uniforms=b["uniforms"], config=cfg, row_params=rp_dev, mask=b.get("mask"),
-                           history=b.get("history"), want_prob=True, want_lse=True, stream=sp, out=out,
-                           vocab_segments=8 if name == "c5_sharded" else 0)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
-        step(i)
-    barrier()
+    sampler = Sampler(device=local, max_batch=1024, max_vocab=262144)
+    stream = torch.cuda.current_stream()
     clocks = ClockSampler(local)
     clocks.start()
-    l0 = sampler.launch_count
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record(stream)
-    for i in range(args.steps):
-        step(i)
-    e1.record(stream)
-    barrier()
-    ms = e0.elapsed_time(e1)
-    launches = sampler.launch_count - l0
-    # keep the GPU under the same load a little longer so that the clock sampler sees it
-    t_end = time.time() + 0.6
-    i = 0
-    while time.time() < t_end:
-        step(i)
-        i += 1
-        if i % 64 == 0:
-            torch.cuda.synchronize()
-    torch.cuda.synchronize()
+    spec = name == "c4_spec_verify"
+    if spec:
+        r = run_spec_workload(torch, dist, sampler, w, rank, world, device, args.steps, args.warmup, args.small, barrier,
+                              world == 1 and not args.no_cpu_baseline)
+    elif name == "c5_sharded" and world > 1:
+        r = None
+    else:
+        if name == "c5_sharded":
+            raise SystemExit("c5_sharded needs --gpus N > 1 (on one GPU its vocab-segment form is covered by the tests)")
+        r = run_sampling_workload(torch, dist, sampler, name, w, rank, world, device, args.steps, args.warmup, args.small,
+                                  barrier)
+        # keep the GPU under the same load a little longer so that the clock sampler sees it
+        t_end = time.time() + 0.6
+        i = 0
+        while time.time() < t_end:
+            r["prepared"][i % len(r["prepared"])].run(stream.cuda_stream)
+            i += 1
+            if i % 64 == 0:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
     clocks.stop_flag = True
     clocks.join(timeout=3)
-    t = torch.tensor([ms], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    rows_total = B * args.steps * (1 if sharded else world)
-    value = rows_total / (ms * 1e-3)
 
     # ---- end to end through the host-memory call (pinned host buffers) ----
     e2e = None
-    if not args.no_e2e and not sharded:
-        hb = {k: (v.cpu().pin_memory() if hasattr(v, "cpu") else v) for k, v in bufs[0].items()}
-        hrp = rp
+    if r is not None and not spec and not args.no_e2e:
+        B = w["B"]
+        hb = {k: (v.cpu().pin_memory() if hasattr(v, "cpu") else v) for k, v in r["bufs"][0].items()}
         hout = {}
         esteps = max(3, min(args.steps, 20))
 
         def estep():
-            sampler.sample(hb["logits"], uniforms=hb["uniforms"], config=cfg, row_params=hrp, mask=hb.get("mask"),
-                           history=hb.get("history"), want_prob=True, want_lse=True, stream=sp, out=hout,
-                           vocab_segments=8 if name == "c5_sharded" else 0)
+            sampler.sample(hb["logits"], uniforms=hb["uniforms"], config=r["cfg"], row_params=r["rp"], mask=hb.get("mask"),
+                           history=hb.get("history"), want_prob=True, want_lse=True, stream=stream.cuda_stream, out=hout)
         for _ in range(3):
             estep()
         barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         t0 = time.perf_counter()
         for _ in range(esteps):
@@ -491,91 +580,95 @@ def main():
         if world > 1:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
         h2d = sum(v.numel() * v.element_size() for k, v in hb.items() if hasattr(v, "numel"))
-        if hrp is not None:
-            h2d += hrp.nbytes
+        if r["rp"] is not None:
+            h2d += r["rp"].nbytes
         d2h = sum(v.nbytes for v in hout.values())
         e2e = {"value": B * esteps * world / (float(te.item()) * 1e-3), "unit": UNIT, "h2d_bytes_per_step": int(h2d),
                "d2h_bytes_per_step": int(d2h), "steps": esteps, "split_ms": sampler.last_timing_ms()}
 
-    # ---- parity spot-check and CPU baseline (rank 0, N == 1 only for the timing) ----
-    parity = None
+    # ---- CPU baseline: the oracle on the same rows (rank 0, N == 1) ----
     cpu = None
-    if rank == 0 and not sharded:
+    if r is not None and not spec and rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle import born_oracle as O
         O.build()
-        hc = host_copy(torch, bufs[0])
-        nchk = min(B, 32)
-        step(0)
-        torch.cuda.synchronize()
+        cores = os.cpu_count() or 1
+        hc = host_copy(torch, r["bufs"][0])
         params = oracle_params_for(w)
-        pr = params if params.size == 1 else params[:nchk]
-        ref = O.sample(np.ascontiguousarray(hc["logits"][:nchk]), pr, uniforms=hc["uniforms"][:nchk],
-                       mask=None if hc["mask"] is None else np.ascontiguousarray(hc["mask"][:nchk]),
-                       history=None if hc["history"] is None else np.ascontiguousarray(hc["history"][:nchk]),
-                       segments=8 if name == "c5_sharded" else 1, nthreads=os.cpu_count() or 1)
-        tok = out["token"][:nchk].cpu().numpy()
-        prob = out["prob"][:nchk].cpu().numpy()
-        lse = out["lse"][:nchk].cpu().numpy()
-        parity = {"rows_checked": nchk, "token_mismatches": int((tok != ref["token"]).sum()),
-                  "prob_bit_mismatches": int((prob.view(np.uint32) != ref["prob"].view(np.uint32)).sum()),
-                  "max_abs_lse_diff_vs_sequential_f32": float(np.nanmax(np.abs(lse - ref["lse"]))),
-                  "near_cutoff_rows": int((ref["near_cutoff"] != 0).sum()),
-                  "row_status_nonzero": int((out["status"].cpu().numpy() != 0).sum())}
-        if world == 1 and not args.no_cpu_baseline:
-            cores = os.cpu_count() or 1
-            nrows = min(B, max(cores, 64))
-            lg = np.ascontiguousarray(hc["logits"][:nrows])
-            pr = params if params.size == 1 else params[:nrows]
-            kw = dict(uniforms=hc["uniforms"][:nrows],
-                      mask=None if hc["mask"] is None else np.ascontiguousarray(hc["mask"][:nrows]),
-                      history=None if hc["history"] is None else np.ascontiguousarray(hc["history"][:nrows]),
-                      segments=8 if name == "c5_sharded" else 1)
-            O.sample(lg, pr, nthreads=cores, **kw)
-            t0 = time.perf_counter()
-            reps = 0
-            while time.perf_counter() - t0 < 10.0:
-                O.sample(lg, pr, nthreads=cores, **kw)
-                reps += 1
-            dt = time.perf_counter() - t0
-            t1 = time.perf_counter()
-            O.sample(lg[:8], pr if pr.size == 1 else pr[:8], nthreads=1,
-                     **{k: (None if v is None else v[:8]) if k != "segments" else v for k, v in kw.items()})
-            single = 8 / (time.perf_counter() - t1)
-            cpu = {"value": nrows * reps / dt, "unit": UNIT, "cores": cores, "kind": "port",
-                   "sample": f"{nrows} rows of the workload x {reps} passes, {cores} threads over rows",
-                   "single_thread_rows_per_s": single}
+        kw = dict(uniforms=hc["uniforms"], mask=hc["mask"], history=hc["history"])
+        O.sample(hc["logits"], params, nthreads=cores, **kw)
+        t0 = time.perf_counter()
+        reps = 0
+        while time.perf_counter() - t0 < 10.0:
+            O.sample(hc["logits"], params, nthreads=cores, **kw)
+            reps += 1
+        dt = time.perf_counter() - t0
+        cpu = {"value": w["B"] * reps / dt, "unit": UNIT, "cores": cores, "kind": "port",
+               "sample": f"all {w['B']} rows of the workload x {reps} passes, {cores} threads over rows"}
 
-    if rank == 0:
-        bytes_launch = algorithmic_bytes_per_row(w, V_local) * B
-        kernel_ms = ms / args.steps
-        peaks = {}
-        try:
-            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-                peaks = json.load(f)
-        except Exception:
-            pass
-        peak = float(peaks.get("hbm_gbs", 6650.0))
-        achieved = bytes_launch / (kernel_ms * 1e-3) / 1e9
-        traffic = None
-        try:
-            with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
-                traffic = json.load(f).get(name)
-        except Exception:
-            pass
-        line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": kernel_ms, "higher_is_better": True,
-            "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
-            "config": {"workload": name, "batch_per_gpu": B, "vocab": V, "vocab_per_gpu": V_local,
-                       "parallelism": ("vocab-sharded x%d (NCCL all-gather)" % world) if sharded else "batch-parallel x%d" % world,
-                       "l2": f"{nbuf} rotating input buffers, {nbuf * B * V_local * (4 if w['dtype'] == 'f32' else 2) / 1e6:.0f} MB > L2",
-                       "outputs": "token, prob, lse, status"},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": traffic, "peak_source": "measured" if peaks else "fallback",
-                         "algorithmic_bytes_per_launch": bytes_launch, "frac_of_8TBs": achieved / 8000.0},
-            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary(),
-            "parity": parity,
-        }
+    # ---- the other workloads of the library, each timed and checked the same way ----
+    extra = {}
+    if not args.no_extra and not args.small and name == DEFAULT:
+        if world == 1:
+            for en in EXTRA_N1:
+                ew = WORKLOADS[en]
+                es, ewm = max(10, min(args.steps, 50)), max(3, min(args.warmup, 5))
+                try:
+                    if en == "c4_spec_verify":
+                        x = run_spec_workload(torch, dist, sampler, ew, rank, world, device, es, ewm, False, barrier, False)
+                        extra[en] = {"us_per_step": 1e3 * x["ms_per_step"], "sequences_per_s": x["sequences"] / (x["ms_per_step"] * 1e-3),
+                                     "frac_of_measured_peak": roofline(x["bytes_launch"], x["ms_per_step"], en)["frac"],
+                                     "launches_per_step": x["launches_per_step"], "parity": x.get("parity")}
+                    else:
+                        x = run_sampling_workload(torch, dist, sampler, en, ew, rank, world, device, es, ewm, False, barrier)
+                        extra[en] = {"us_per_step": 1e3 * x["ms_per_step"], "rows_per_s": ew["B"] / (x["ms_per_step"] * 1e-3),
+                                     "frac_of_measured_peak": roofline(x["bytes_launch"], x["ms_per_step"], en)["frac"],
+                                     "launches_per_step": x["launches_per_step"], "timing": x["timing"],
+                                     "fallback_rows_in_timed_steps": x["fallback_rows_in_timed_steps"],
+                                     "parity": x.get("parity")}
+                        del x
+                    torch.cuda.empty_cache()
+                except Exception as e:  # a failing extra must not lose the headline line
+                    extra[en] = {"error": repr(e)}
+        else:
+            try:
+                x = run_sharded(torch, dist, sampler, WORKLOADS["c5_sharded"], rank, world, device,
+                                max(10, min(args.steps, 50)), max(3, min(args.warmup, 5)), barrier)
+                if rank == 0:
+                    extra["c5_sharded"] = x
+            except Exception as e:
+                extra["c5_sharded"] = {"error": repr(e)}
+    if name == "c5_sharded" and world > 1:
+        x = run_sharded(torch, dist, sampler, w, rank, world, device, args.steps, args.warmup, barrier)
+        if rank == 0:
+            line = {"metric": METRIC, "value": x["rows_per_s"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                    "warmup": args.warmup, "ms_per_step": x["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+                    "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                    "config": {"workload": name, "batch": w["B"], "vocab": w["V"], "vocab_per_gpu": x["vocab_per_gpu"],
+                               "parallelism": "vocab-sharded x%d (NCCL all-gather)" % world},
+                    "roofline": x["roofline_per_gpu"], "cpu_baseline": None, "e2e": None,
+                    "gpu_launches": x["launches_per_step"] * args.steps, "clocks": clocks.summary(), "parity": x["parity"]}
+            print(json.dumps(line), flush=True)
+    elif rank == 0:
+        B, V = w["B"], w["V"]
+        kernel_ms = r["ms_per_step"]
+        if spec:
+            line = {"metric": "spec_verified_sequences_per_s", "value": B * world / (kernel_ms * 1e-3), "unit": "sequences/s",
+                    "dtype": "f32", "config": {"workload": name, "batch_per_gpu": B, "draft_len": w["K"], "vocab": V,
+                                               "parallelism": "batch-parallel x%d" % world, "timing": r["timing"]},
+                    "cpu_baseline": r.get("cpu_baseline")}
+        else:
+            esz = 4 if w["dtype"] == "f32" else 2
+            line = {"metric": METRIC, "value": B * world / (kernel_ms * 1e-3), "unit": UNIT, "dtype": w["dtype"],
+                    "config": {"workload": name, "batch_per_gpu": B, "vocab": V, "vocab_per_gpu": V,
+                               "parallelism": "batch-parallel x%d" % world,
+                               "l2": f"{r['nbuf']} rotating input buffers, {r['nbuf'] * B * V * esz / 1e6:.0f} MB > L2",
+                               "timing": r["timing"], "outputs": "token, prob, lse, status"},
+                    "cpu_baseline": cpu, "fallback_rows_in_timed_steps": r["fallback_rows_in_timed_steps"]}
+        line.update({"n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": kernel_ms,
+                     "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic",
+                     "roofline": roofline(r["bytes_launch"], kernel_ms, name), "e2e": e2e,
+                     "gpu_launches": int(r["launches_per_step"]) * args.steps, "clocks": clocks.summary(),
+                     "parity": r.get("parity"), "workloads": extra})
         print(json.dumps(line), flush=True)
     sampler.close()
     if world > 1:

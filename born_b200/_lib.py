@@ -117,6 +117,10 @@ SYMBOLS = {
     "born_sampler_destroy": (C.c_int32, [C.c_void_p]),
     "born_sample": (C.c_int32, [C.c_void_p, C.POINTER(SampleArgs), C.c_void_p]),
     "born_sample_static": (C.c_int32, [C.POINTER(SampleArgs), C.c_void_p]),
+    "born_sampler_reserve": (C.c_int32, [C.c_void_p, C.POINTER(SampleArgs)]),
+    "born_check_error": (C.c_int32, [C.c_void_p]),
+    "born_fallback_rows": (C.c_int64, [C.c_void_p]),
+    "born_debug_expire_wait": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "born_spec_verify": (C.c_int32, [C.c_void_p, C.POINTER(SpecArgs), C.c_void_p]),
     "born_shard_record_bytes": (C.c_int32, [C.c_int32]),
     "born_shard_unique_id": (C.c_int32, [C.c_void_p]),

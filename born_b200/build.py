@@ -13,7 +13,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 SRC = os.path.join(HERE, "csrc", "capi.cu")
-DEPS = [os.path.join(HERE, "csrc", f) for f in ("capi.cu", "spec.cuh", "sample_kernel.cuh", "spec_kernel.cuh", "fullrow_kernel.cuh")]
+DEPS = [os.path.join(HERE, "csrc", f) for f in ("capi.cu", "spec.cuh", "scan_common.cuh", "scan_kernel.cuh", "finish.cuh", "fallback.cuh", "merge_kernel.cuh",
+                                                   "prepass.cuh", "spec_kernel.cuh")]
 DEPS.append(os.path.join(ROOT, "include", "born_sampler.h"))
 OUT = os.path.join(HERE, "libborn_sampler.so")
 

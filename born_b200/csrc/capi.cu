@@ -14,9 +14,11 @@
 #include <string.h>
 
 #include "../../include/born_sampler.h"
-#include "sample_kernel.cuh"
+#include "scan_kernel.cuh"
+#include "fallback.cuh"
+#include "merge_kernel.cuh"
+#include "prepass.cuh"
 #include "spec_kernel.cuh"
-#include "fullrow_kernel.cuh"
 
 using namespace born;
 
@@ -42,26 +44,32 @@ struct Handle {
     int device = 0;
     int max_batch = 0, max_vocab = 0, max_k = 0;
     int num_sms = 0;
-    int max_records = 0;
-    int64_t record_stride = 0;
-    uint8_t* records = nullptr;
-    uint32_t* tickets = nullptr;
+    int max_grid = 0;              // CTAs of the streaming kernel (two per SM)
+    int max_rows = 0;              // virtual rows (caller rows x vocabulary segments) a call may stream
+    int rec_cap = 0;               // entries per segment record
+    int64_t rec_stride = 0;
+    size_t records_bytes = 0;
+    uint8_t* records = nullptr;    // segment records, indexed by row + cta
+    MassBlock* blocks = nullptr;   // mass blocks of the whole-vocabulary routes
+    int64_t blocks_cap = 0;
+    uint32_t* tickets = nullptr;   // [max_rows] tickets, then [max_rows] deferred-fallback owners
+    unsigned long long* hist_lists = nullptr;  // [max_batch, BORN_MAX_HISTORY] distinct history ids with counts
+    uint32_t* hist_counts = nullptr;           // [max_batch]
+    uint8_t* seg_packed = nullptr; // packed records of the one-GPU vocabulary-segment form
+    size_t seg_packed_bytes = 0;
     int* dev_error = nullptr;
+    unsigned long long timeout_ns = kMbarTimeoutNs;
     uint8_t* spec_scratch = nullptr;
     size_t spec_scratch_bytes = 0;
     int64_t spec_layout_key = -1;
-    uint8_t* fr_scratch = nullptr;  // full-vocabulary path: tickets, range statistics, chunk sums
-    size_t fr_scratch_bytes = 0;
-    int64_t fr_layout_key = -1;
     bool is_static = false;  // the handle of born_sample_static: may not allocate
-    float* pen_copy = nullptr;  // fp32 copy of the rows with history penalties applied (whole-vocabulary routes)
-    size_t pen_copy_bytes = 0;
+    float* clean_copy = nullptr;  // aligned fp32 copy of the rows (mask and penalties applied)
+    size_t clean_copy_bytes = 0;
     Staging stage[16];
     cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
     float timing[3] = {0, 0, 0};
     int64_t launches = 0;
     int64_t workspace = 0;
-    int force_slices = 0;
     // vocab-sharded path
     NcclApi nccl;
     void* comm = nullptr;
@@ -92,19 +100,41 @@ int fail(Handle* h, int code, const char* fmt, ...) {
     } while (0)
 
 int dev_alloc(Handle* h, void** p, size_t bytes) {
+    if (h->is_static) return fail(h, BORN_ERR_UNSUPPORTED, "this call needs %zu bytes of scratch that the allocation-free entry point may not allocate", bytes);
     cudaError_t e = cudaMalloc(p, bytes);
     if (e != cudaSuccess) return fail(h, BORN_ERR_CUDA, "cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
     h->workspace += (int64_t)bytes;
     return BORN_OK;
 }
 
+// Grow-only scratch: allocated at the size of the largest request seen (born_sampler_reserve
+// makes that request ahead of time), never per call afterwards.
+int grow(Handle* h, void** p, size_t* have, size_t need, cudaStream_t st) {
+    if (*have >= need) return BORN_OK;
+    if (h->is_static) return fail(h, BORN_ERR_UNSUPPORTED, "this call needs %zu bytes of scratch that the allocation-free entry point may not allocate", need);
+    if (*p) {
+        cudaError_t e = cudaStreamSynchronize(st);
+        if (e != cudaSuccess) return fail(h, BORN_ERR_CUDA, "cudaStreamSynchronize failed: %s", cudaGetErrorString(e));
+        cudaFree(*p);
+        h->workspace -= (int64_t)*have;
+        *p = nullptr;
+        *have = 0;
+    }
+    int rc = dev_alloc(h, p, need);
+    if (rc == BORN_OK) *have = need;
+    return rc;
+}
+
 int stage_reserve(Handle* h, int slot, size_t bytes) {
     Staging& s = h->stage[slot];
-    if (s.bytes >= bytes) return BORN_OK;
-    if (s.p) { cudaFree(s.p); h->workspace -= (int64_t)s.bytes; s.p = nullptr; s.bytes = 0; }
-    int rc = dev_alloc(h, &s.p, bytes);
-    if (rc == BORN_OK) s.bytes = bytes;
-    return rc;
+    return grow(h, &s.p, &s.bytes, bytes, nullptr);
+}
+
+int use_device(Handle* h) {
+    int cur = -1;
+    if (cudaGetDevice(&cur) == cudaSuccess && cur == h->device) return BORN_OK;
+    CUDA_TRY(h, cudaSetDevice(h->device));
+    return BORN_OK;
 }
 
 bool params_ok(const born_row_params& p) {
@@ -118,22 +148,40 @@ bool params_ok(const born_row_params& p) {
     return true;
 }
 
-template <typename T, bool M, bool Lse>
-int launch_variant(Handle* h, const SampleKernelArgs& A, dim3 grid, size_t smem, cudaStream_t st) {
-    auto kern = sample_kernel<T, M, Lse>;
-    CUDA_TRY(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, kBlockThreads, smem, st>>>(A);
-    CUDA_TRY(h, cudaGetLastError());
-    h->launches++;
-    return BORN_OK;
+bool host_penalties_on(const born_row_params& p) {
+    return (p.repetition_penalty != 1.0f && p.repetition_penalty != 0.0f) || p.frequency_penalty != 0.0f ||
+           p.presence_penalty != 0.0f;
+}
+// no top-k and no min-p: the row total comes from the mass blocks (temperature-only, top-p alone)
+bool host_need_mass(const born_row_params& p) {
+    const bool greedy = (p.flags & BORN_FLAG_GREEDY) || p.temperature == 0.0f;
+    return !greedy && p.top_k <= 0 && !(p.min_p > 0.0f);
 }
 
-int launch_sample(Handle* h, const SampleKernelArgs& A, int dtype, cudaStream_t st) {
-    const bool has_mask = A.mask != nullptr, lse = A.out_lse != nullptr;
-    const SmemLayout L = smem_layout(dtype == BORN_DTYPE_F32 ? 4 : 2, has_mask, A.history != nullptr);
-    dim3 grid((unsigned)(A.mode == kModeMerge ? 1 : A.S), (unsigned)A.B, 1);
-    const size_t smem = (size_t)L.total;
-#define V_(T, M, Lq) return launch_variant<T, M, Lq>(h, A, grid, smem, st)
+template <typename T, bool M, bool Lse>
+cudaError_t scan_attr() {
+    return cudaFuncSetAttribute(scan_kernel<T, M, Lse>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                scan_smem_layout((int)sizeof(T), M, true).total);
+}
+// The dynamic shared-memory limit of every variant is raised once (at create / first static call).
+cudaError_t scan_attrs_all() {
+    cudaError_t e;
+    if ((e = scan_attr<float, false, false>()) != cudaSuccess) return e;
+    if ((e = scan_attr<float, false, true>()) != cudaSuccess) return e;
+    if ((e = scan_attr<float, true, false>()) != cudaSuccess) return e;
+    if ((e = scan_attr<float, true, true>()) != cudaSuccess) return e;
+    if ((e = scan_attr<uint16_t, false, false>()) != cudaSuccess) return e;
+    if ((e = scan_attr<uint16_t, false, true>()) != cudaSuccess) return e;
+    if ((e = scan_attr<uint16_t, true, false>()) != cudaSuccess) return e;
+    if ((e = scan_attr<uint16_t, true, true>()) != cudaSuccess) return e;
+    return cudaSuccess;
+}
+
+int launch_scan(Handle* h, const ScanArgs& A, int dtype, int grid, cudaStream_t st) {
+    const bool has_mask = A.mask != nullptr;
+    const bool lse = A.out_lse != nullptr || A.want_lse;
+    const size_t smem = (size_t)scan_smem_layout(dtype == BORN_DTYPE_F32 ? 4 : 2, has_mask, A.history != nullptr).total;
+#define V_(T, M, Lq) scan_kernel<T, M, Lq><<<grid, kScanThreads, smem, st>>>(A)
     if (dtype == BORN_DTYPE_F32) {
         if (has_mask) { if (lse) V_(float, true, true); else V_(float, true, false); }
         else { if (lse) V_(float, false, true); else V_(float, false, false); }
@@ -142,37 +190,64 @@ int launch_sample(Handle* h, const SampleKernelArgs& A, int dtype, cudaStream_t 
         else { if (lse) V_(uint16_t, false, true); else V_(uint16_t, false, false); }
     }
 #undef V_
+    CUDA_TRY(h, cudaGetLastError());
+    h->launches++;
+    return BORN_OK;
 }
 
-// Slices per row.  With at least one row per SM every row is one CTA (a slice costs a
-// threshold bootstrap and a record merge); smaller batches are cut so that about two CTAs
-// per SM exist, but never below four tiles per slice.
-void choose_slices(const Handle* h, int B, int V, int elem_bytes, int* S, int* slice_len) {
-    const int kChunk = kTileBytes / elem_bytes;  // logits per pipeline stage
-    const int nchunks = (V + kChunk - 1) / kChunk;
-    int s = 1;
-    if (h->force_slices > 0) s = h->force_slices;
-    else if (B < h->num_sms) {
-        s = (2 * h->num_sms + B - 1) / B;
-        int cap = nchunks / 4;
-        if (cap < 1) cap = 1;
-        if (s > cap) s = cap;
-    }
-    if (s > 64) s = 64;
-    if (s > nchunks) s = nchunks;
-    while (s > 1 && (int64_t)s * B > h->max_records) --s;
-    if (s < 1) s = 1;
-    int per = (nchunks + s - 1) / s;
-    *slice_len = per * kChunk;
-    *S = (nchunks + per - 1) / per;
+int launch_merge(Handle* h, const MergeArgs& M, cudaStream_t st) {
+    merge_kernel<<<M.B, kThreads, 2 * kSelCap * 8, st>>>(M);
+    CUDA_TRY(h, cudaGetLastError());
+    h->launches++;
+    return BORN_OK;
+}
+
+// Geometry and scratch of one streaming launch over B x G virtual rows of V tokens.
+int fill_scan(Handle* h, ScanArgs& A, int B, int G, int V, int dtype, const void* logits, int64_t row_stride,
+              const uint32_t* mask, int64_t mask_stride, int* grid) {
+    const int esz = dtype == BORN_DTYPE_F32 ? 4 : 2;
+    if ((uintptr_t)logits % esz) return fail(h, BORN_ERR_INVALID_ARGUMENT, "logits pointer is not aligned to its element size");
+    if (mask && (uintptr_t)mask % 4) return fail(h, BORN_ERR_INVALID_ARGUMENT, "mask pointer is not 4-byte aligned");
+    bool fast = ((uintptr_t)logits % 16 == 0) && ((row_stride * esz) % 16 == 0) && (G == 1 || ((int64_t)V * esz) % 16 == 0);
+    if (mask) fast = fast && ((uintptr_t)mask % 16 == 0) && ((mask_stride * 4) % 16 == 0) && (G == 1 || V % 128 == 0);
+    const int tile = kTileBytes / esz;
+    const int lead_max = fast ? 0 : 16 / esz - 1;
+    A.B = B; A.G = G; A.V = V;
+    A.tpr = (int)(((int64_t)V + lead_max + tile - 1) / tile);
+    A.fast = fast ? 1 : 0;
+    A.logits = logits; A.row_stride = row_stride;
+    A.mask = mask; A.mask_stride = mask_stride;
+    const int64_t rows = (int64_t)B * G;
+    if (rows > h->max_rows) return fail(h, BORN_ERR_UNSUPPORTED, "%lld rows (batch x segments) exceed the workspace of %d", (long long)rows, h->max_rows);
+    A.nblk = (V + kMassBlock - 1) / kMassBlock;
+    if (rows * A.nblk > h->blocks_cap) return fail(h, BORN_ERR_UNSUPPORTED, "batch x vocab exceeds the workspace");
+    const int64_t tiles = rows * A.tpr;
+    *grid = (int)(tiles < h->max_grid ? tiles : h->max_grid);
+    // entries per segment record: as many as the record area gives every (row + cta) slot
+    int64_t cap = ((int64_t)(h->records_bytes / (size_t)(rows + *grid)) - kRecordHdrBytes) / 8;
+    cap = (cap < h->rec_cap ? cap : h->rec_cap) & ~(int64_t)1;
+    if (cap < 64) return fail(h, BORN_ERR_UNSUPPORTED, "%lld rows (batch x segments) exceed the record workspace", (long long)rows);
+    A.records = h->records; A.rec_cap = (int)cap; A.rec_stride = kRecordHdrBytes + cap * 8;
+    A.blocks = h->blocks;
+    A.tickets = h->tickets; A.deferred = h->tickets + h->max_rows;
+    A.dev_error = h->dev_error;
+    A.timeout_ns = h->timeout_ns;
+    A.debug_skip_tile = -1;
+#ifdef BORN_PROFILE
+    A.prof = nullptr;
+    if (const char* pp = getenv("BORN_PROF_PTR")) A.prof = (unsigned long long*)strtoull(pp, nullptr, 0);
+#endif
+    return BORN_OK;
 }
 
 int check_device_error(Handle* h) {
     int e = 0;
     CUDA_TRY(h, cudaMemcpy(&e, h->dev_error, sizeof(int), cudaMemcpyDeviceToHost));
     if (e) {
+        // tickets of rows that were left unfinished must not leak into the next launch
+        cudaMemset(h->tickets, 0, sizeof(uint32_t) * 2 * (size_t)h->max_rows);
         cudaMemset(h->dev_error, 0, sizeof(int));
-        return fail(h, BORN_ERR_DEVICE_TIMEOUT, "a bounded on-device wait gave up (code %d); outputs are invalid", e);
+        return fail(h, BORN_ERR_DEVICE_TIMEOUT, "a bounded on-device wait gave up (code %d); outputs of that call are invalid", e);
     }
     return BORN_OK;
 }
@@ -186,11 +261,35 @@ __global__ void debug_mass_kernel(const float* x, unsigned long long* q, int64_t
     if (i < n) q[i] = mass_of(x[i]);
 }
 
+// scratch sizes of a handle for max_batch rows of max_vocab tokens
+struct ScratchPlan {
+    int max_rows, rec_cap;
+    int64_t rec_stride, blocks_cap;
+    size_t records, blocks, tickets, seg_packed, hist, total;
+};
+ScratchPlan scratch_plan(int max_batch, int max_vocab, int max_grid, int rec_cap) {
+    ScratchPlan p;
+    // virtual rows (caller rows x vocabulary segments); the record area is sized for full-size
+    // records of 2 * max_batch rows and is cut finer when a call streams more rows than that
+    p.max_rows = max_batch * BORN_MAX_SHARDS > 1024 ? max_batch * BORN_MAX_SHARDS : 1024;
+    p.rec_cap = rec_cap;
+    p.rec_stride = kRecordHdrBytes + (int64_t)rec_cap * 8;
+    p.records = (size_t)((max_batch * 2 > 1024 ? max_batch * 2 : 1024) + max_grid) * (size_t)p.rec_stride;
+    // a call of B x G rows of V tokens needs B*G*ceil(V/512) blocks; segments only shorten V
+    p.blocks_cap = (int64_t)max_batch * (((int64_t)max_vocab + kMassBlock - 1) / kMassBlock) + p.max_rows;
+    p.blocks = (size_t)p.blocks_cap * sizeof(MassBlock);
+    p.tickets = sizeof(uint32_t) * 2 * (size_t)p.max_rows;
+    p.seg_packed = (size_t)max_batch * (size_t)(kRecordHdrBytes * BORN_MAX_SHARDS + 8 * BORN_MAX_CANDIDATES);
+    p.hist = (size_t)max_batch * (BORN_MAX_HISTORY * 8 + 4);
+    p.total = p.records + p.blocks + p.tickets + p.seg_packed + p.hist + 256;
+    return p;
+}
+
 }  // namespace
 
 extern "C" {
 
-const char* born_version(void) { return "born-sampler-b200 0.1.0 (sm_100a)"; }
+const char* born_version(void) { return "born-sampler-b200 0.2.0 (sm_100a)"; }
 
 const char* born_last_error(void* handle) { return handle ? ((Handle*)handle)->err : g_err; }
 
@@ -217,22 +316,32 @@ int32_t born_sampler_create(int32_t device, int32_t max_batch, int32_t max_vocab
     h->device = device;
     h->max_batch = max_batch;
     h->max_vocab = max_vocab;
-    h->max_k = max_k;
+    h->max_k = max_k > 0 ? max_k : BORN_MAX_TOP_K;
     h->num_sms = prop.multiProcessorCount;
-    const char* fs = getenv("BORN_SLICES");
-    if (fs) h->force_slices = atoi(fs);
+    h->max_grid = 2 * h->num_sms;
     if (cudaSetDevice(device) != cudaSuccess) { delete h; return fail(nullptr, BORN_ERR_CUDA, "cudaSetDevice failed"); }
-    h->max_records = max_batch * 4 > 2048 ? max_batch * 4 : 2048;
-    h->record_stride = kRecordHdrBytes + (int64_t)kMaxK * 8;
-    int rc = dev_alloc(h, (void**)&h->records, (size_t)h->max_records * (size_t)h->record_stride);
-    if (rc == BORN_OK) rc = dev_alloc(h, (void**)&h->tickets, sizeof(uint32_t) * (size_t)max_batch * 2);
-    if (rc == BORN_OK) rc = dev_alloc(h, (void**)&h->dev_error, sizeof(int));
-    if (rc == BORN_OK && cudaMemset(h->tickets, 0, sizeof(uint32_t) * (size_t)max_batch * 2) != cudaSuccess) rc = BORN_ERR_CUDA;
-    if (rc == BORN_OK && cudaMemset(h->dev_error, 0, sizeof(int)) != cudaSuccess) rc = BORN_ERR_CUDA;
+    const ScratchPlan sp = scratch_plan(max_batch, max_vocab, h->max_grid, 2048);
+    h->max_rows = sp.max_rows;
+    h->rec_cap = sp.rec_cap;
+    h->rec_stride = sp.rec_stride;
+    h->records_bytes = sp.records;
+    h->blocks_cap = sp.blocks_cap;
+    h->seg_packed_bytes = sp.seg_packed;
+    int rc = dev_alloc(h, (void**)&h->records, sp.records);
+    if (rc == BORN_OK) rc = dev_alloc(h, (void**)&h->blocks, sp.blocks);
+    if (rc == BORN_OK) rc = dev_alloc(h, (void**)&h->tickets, sp.tickets);
+    if (rc == BORN_OK) rc = dev_alloc(h, (void**)&h->seg_packed, sp.seg_packed);
+    if (rc == BORN_OK) rc = dev_alloc(h, (void**)&h->hist_lists, sp.hist);
+    if (rc == BORN_OK) h->hist_counts = reinterpret_cast<uint32_t*>(h->hist_lists + (size_t)max_batch * BORN_MAX_HISTORY);
+    if (rc == BORN_OK) rc = dev_alloc(h, (void**)&h->dev_error, 2 * sizeof(int));
+    if (rc == BORN_OK && cudaMemset(h->tickets, 0, sp.tickets) != cudaSuccess) rc = BORN_ERR_CUDA;
+    if (rc == BORN_OK && cudaMemset(h->dev_error, 0, 2 * sizeof(int)) != cudaSuccess) rc = BORN_ERR_CUDA;
+    if (rc == BORN_OK && scan_attrs_all() != cudaSuccess) rc = BORN_ERR_CUDA;
+    if (rc == BORN_OK && spec_attrs_all() != cudaSuccess) rc = BORN_ERR_CUDA;
     for (int i = 0; i < 4 && rc == BORN_OK; ++i)
         if (cudaEventCreate(&h->ev[i]) != cudaSuccess) rc = BORN_ERR_CUDA;
     if (rc != BORN_OK) {
-        snprintf(g_err, sizeof g_err, "create failed: %.480s", h->err[0] ? h->err : "CUDA error");
+        snprintf(g_err, sizeof g_err, "create failed: %.480s", h->err[0] ? h->err : cudaGetErrorString(cudaGetLastError()));
         born_sampler_destroy(h);
         return rc;
     }
@@ -246,11 +355,13 @@ int32_t born_sampler_destroy(void* handle) {
     cudaSetDevice(h->device);
     if (h->comm && h->nccl.CommDestroy) h->nccl.CommDestroy(h->comm);
     cudaFree(h->records);
+    cudaFree(h->blocks);
     cudaFree(h->tickets);
+    cudaFree(h->seg_packed);
+    cudaFree(h->hist_lists);
     cudaFree(h->dev_error);
     cudaFree(h->spec_scratch);
-    cudaFree(h->fr_scratch);
-    cudaFree(h->pen_copy);
+    cudaFree(h->clean_copy);
     cudaFree(h->gathered);
     cudaFree(h->packed);
     for (auto& s : h->stage) cudaFree(s.p);
@@ -267,149 +378,88 @@ int32_t born_last_timing(void* handle, float* out3) {
     return BORN_OK;
 }
 
-// Rows that neither top-k nor top-p narrows have no small candidate set: temperature-only
-// sampling always, min-p when the caller asks for it with BORN_FLAG_FULL_VOCAB (without the
-// flag min-p goes through the one-pass kernel, which serves up to 1024 survivors).  Uniform
-// parameters only, no history penalties, no kept-id list.
-static bool wants_full_row(const Handle* h, const born_sample_args* a) {
-    if (h->is_static || a->row_params || a->vocab_segments > 1 || a->out_kept_ids) return false;
-    const born_row_params& p = a->params;
-    if ((p.flags & BORN_FLAG_GREEDY) || p.temperature == 0.0f) return false;
-    if (p.top_k > 0 || (p.top_p > 0.0f && p.top_p < 1.0f)) return false;
-    if (p.min_p > 0.0f && !(p.flags & BORN_FLAG_FULL_VOCAB)) return false;
-    const bool pen_on = (p.repetition_penalty != 1.0f && p.repetition_penalty != 0.0f) || p.frequency_penalty != 0.0f ||
-                        p.presence_penalty != 0.0f;
-    if (a->history && pen_on) return false;
-    return true;
+int64_t born_fallback_rows(void* handle) {
+    Handle* h = (Handle*)handle;
+    if (!h || h->is_static) return -1;
+    if (use_device(h)) return -1;
+    int n = 0;
+    if (cudaMemcpy(&n, h->dev_error + 1, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    cudaMemset(h->dev_error + 1, 0, sizeof(int));
+    return n;
 }
 
-// Top-p without top-k: the one-pass kernel keeps the 1024 best, which hold the nucleus of any
-// peaked distribution, but the nucleus is defined against the total mass of all survivors.
-// That total comes from the two passes of the whole-vocabulary path (run in sum-only mode).
-static bool wants_survivor_total(const Handle* h, const born_sample_args* a) {
-    if (h->is_static || a->row_params || a->vocab_segments > 1) return false;
-    const born_row_params& p = a->params;
-    if ((p.flags & BORN_FLAG_GREEDY) || p.temperature == 0.0f) return false;
-    if (p.top_k > 0 || !(p.top_p > 0.0f && p.top_p < 1.0f)) return false;
-    // min-p already narrows the row for the one-pass kernel (up to 1024 survivors): the extra
-    // passes are only taken when the caller asks for them
-    if (p.min_p > 0.0f && !(p.flags & BORN_FLAG_FULL_VOCAB)) return false;
-    const bool pen_on = (p.repetition_penalty != 1.0f && p.repetition_penalty != 0.0f) || p.frequency_penalty != 0.0f ||
-                        p.presence_penalty != 0.0f;
-    if (a->history && pen_on) return false;
-    return true;
+int32_t born_check_error(void* handle) {
+    Handle* h = (Handle*)handle;
+    if (!h) return fail(nullptr, BORN_ERR_INVALID_ARGUMENT, "handle is NULL");
+    if (h->is_static) return BORN_ERR_INVALID_ARGUMENT;
+    int rc = use_device(h);
+    if (rc) return rc;
+    return check_device_error(h);
 }
 
-// Both launches of the whole-vocabulary path; with `totals_only` the second one leaves each row's
-// total survivor mass in *totals and writes no outputs.
-static int run_full_row(Handle* h, const born_sample_args* a, cudaStream_t st, bool totals_only,
-                        const unsigned long long** totals) {
-    const int B = a->batch, V = a->vocab;
-    const int esz = a->logits_dtype == BORN_DTYPE_F32 ? 4 : 2;
-    const int parts = fullrow_parts(B, V, h->num_sms);
-    const FullRowScratchLayout L = fullrow_scratch_layout(B, V, parts);
-    if (h->fr_scratch_bytes < L.total) {  // grown on first use, like the staging mirrors
-        CUDA_TRY(h, cudaStreamSynchronize(st));
-        if (h->fr_scratch) { cudaFree(h->fr_scratch); h->workspace -= (int64_t)h->fr_scratch_bytes; h->fr_scratch = nullptr; h->fr_scratch_bytes = 0; }
-        int rc0 = dev_alloc(h, (void**)&h->fr_scratch, L.total);
-        if (rc0 != BORN_OK) return rc0;
-        h->fr_scratch_bytes = L.total;
-        h->fr_layout_key = -1;
-    }
-    const int64_t key = ((int64_t)B << 32) | (int64_t)V;
-    if (h->fr_layout_key != key) {  // the tickets sit at offset 0 and are zero between launches
-        CUDA_TRY(h, cudaMemsetAsync(h->fr_scratch, 0, L.stat, st));
-        h->fr_layout_key = key;
-    }
-    FullRowArgs F;
-    memset(&F, 0, sizeof F);
-    F.logits = a->logits;
-    F.mask = a->mask;
-    F.uniforms = a->uniforms;
-    F.out_token = a->out_token; F.out_prob = a->out_prob; F.out_lse = a->out_lse; F.out_status = a->out_status;
-    F.out_kept_count = a->out_kept_count;
-    F.tickets = reinterpret_cast<uint32_t*>(h->fr_scratch + L.tickets);
-    F.stat = reinterpret_cast<float2*>(h->fr_scratch + L.stat);
-    F.csum = reinterpret_cast<unsigned long long*>(h->fr_scratch + L.csum);
-    F.ccount = reinterpret_cast<uint32_t*>(h->fr_scratch + L.ccount);
-    F.total_out = totals_only ? reinterpret_cast<unsigned long long*>(h->fr_scratch + L.totals) : nullptr;
-    if (totals_only) F.out_kept_count = nullptr;
-    F.row_stride = a->logits_row_stride;
-    F.mask_stride = a->mask_row_stride;
-    F.B = B; F.V = V; F.parts1 = parts;
-    F.temperature = a->params.temperature;
-    F.min_p = a->params.min_p;
-    F.vec_ok = ((uintptr_t)a->logits % 16 == 0) && ((a->logits_row_stride * esz) % 16 == 0);
-    int rc = launch_fullrow(F, a->logits_dtype, parts, st);
-    if (rc != 0) return fail(h, BORN_ERR_CUDA, "full-vocabulary kernel launch failed: %s", cudaGetErrorString((cudaError_t)rc));
-    h->launches += 2;
-    if (totals) *totals = F.total_out;
-    return BORN_OK;
+// Does this call have to go through the clean fp32 copy first?  Only rows whose total comes
+// from the mass blocks are concerned (no top-k, no min-p); with per-row parameter arrays on
+// the device the host cannot tell, so it assumes that some row is.
+static bool wants_clean_copy(const born_sample_args* a, bool fast) {
+    if (a->vocab_segments > 1) return false;  // segments need top-k
+    const bool may_mass = a->row_params ? true : host_need_mass(a->params);
+    if (!may_mass) return false;
+    if (!fast) return true;
+    const bool pen = a->history && (a->row_params ? true : host_penalties_on(a->params));
+    return pen && a->logits_dtype == BORN_DTYPE_BF16;
 }
 
-static int sample_full_row(Handle* h, const born_sample_args* a, cudaStream_t st) {
-    return run_full_row(h, a, st, false, nullptr);
-}
-
-static int sample_device(Handle* h, const born_sample_args* a_in, cudaStream_t st) {
+static int sample_device(Handle* h, const born_sample_args* a_in, cudaStream_t st, bool reserve_only) {
     const born_sample_args* a = a_in;
     born_sample_args a2;
-    {
-        // The whole-vocabulary routes read the raw logits more than once.  A row with history
-        // penalties that would take one of them is first copied, penalties applied, to fp32
-        // scratch; the routes then see plain rows without a history.
-        const born_row_params& p = a_in->params;
-        const bool pen_on = (p.repetition_penalty != 1.0f && p.repetition_penalty != 0.0f) || p.frequency_penalty != 0.0f ||
-                            p.presence_penalty != 0.0f;
-        if (a_in->history && pen_on && !a_in->row_params) {
-            a2 = *a_in;
-            a2.history = nullptr; a2.history_len = nullptr; a2.history_stride = 0;
-            a2.params.repetition_penalty = 0.0f; a2.params.frequency_penalty = 0.0f; a2.params.presence_penalty = 0.0f;
-            if (wants_full_row(h, &a2) || wants_survivor_total(h, &a2)) {
-                const int64_t v_pad = ((int64_t)a_in->vocab + 3) / 4 * 4;
-                const size_t need = (size_t)a_in->batch * (size_t)v_pad * sizeof(float);
-                if (h->pen_copy_bytes < need) {  // grown on first use, like the staging mirrors
-                    CUDA_TRY(h, cudaStreamSynchronize(st));
-                    if (h->pen_copy) { cudaFree(h->pen_copy); h->workspace -= (int64_t)h->pen_copy_bytes; h->pen_copy = nullptr; h->pen_copy_bytes = 0; }
-                    int rc0 = dev_alloc(h, (void**)&h->pen_copy, need);
-                    if (rc0 != BORN_OK) return rc0;
-                    h->pen_copy_bytes = need;
-                }
-                PenaliseArgs P;
-                memset(&P, 0, sizeof P);
-                P.logits = a_in->logits; P.out = h->pen_copy;
-                P.history = a_in->history; P.history_len = a_in->history_len;
-                P.row_stride = a_in->logits_row_stride; P.out_stride = v_pad;
-                P.B = a_in->batch; P.V = a_in->vocab; P.history_stride = a_in->history_stride;
-                P.repetition = p.repetition_penalty; P.frequency = p.frequency_penalty; P.presence = p.presence_penalty;
-                int rc1 = launch_penalised_copy(P, a_in->logits_dtype, h->num_sms, st);
-                if (rc1 != 0) return fail(h, BORN_ERR_CUDA, "penalised-copy launch failed: %s", cudaGetErrorString((cudaError_t)rc1));
-                h->launches += 2;
-                a2.logits = h->pen_copy;
-                a2.logits_dtype = BORN_DTYPE_F32;
-                a2.logits_row_stride = v_pad;
-                a = &a2;
-            }
-        }
-    }
-    if (wants_full_row(h, a)) return sample_full_row(h, a, st);
-    const unsigned long long* survivor_total = nullptr;
-    if (wants_survivor_total(h, a)) {
-        int rc0 = run_full_row(h, a, st, true, &survivor_total);
-        if (rc0 != BORN_OK) return rc0;
-    }
-    SampleKernelArgs A;
+    ScanArgs A;
     memset(&A, 0, sizeof A);
-    A.ext_total = survivor_total;
-    A.logits = a->logits;
-    A.row_stride = a->logits_row_stride;
-    A.mask = a->mask;
-    A.mask_stride = a->mask_row_stride;
+    int grid = 0;
+    const int G = a->vocab_segments > 1 ? a->vocab_segments : 1;
+    int rc = fill_scan(h, A, a->batch, G, a->vocab / G, a->logits_dtype, a->logits, a->logits_row_stride, a->mask,
+                       a->mask_row_stride, &grid);
+    if (rc) return rc;
+    if (wants_clean_copy(a, A.fast != 0)) {
+        const int64_t v_pad = ((int64_t)a->vocab + 3) / 4 * 4;
+        const size_t need = (size_t)a->batch * (size_t)v_pad * sizeof(float);
+        if ((rc = grow(h, (void**)&h->clean_copy, &h->clean_copy_bytes, need, st))) return rc;
+        if (!reserve_only) {
+            CopyArgs C;
+            memset(&C, 0, sizeof C);
+            C.logits = a->logits; C.out = h->clean_copy; C.mask = a->mask;
+            C.history = a->history; C.history_len = a->history_len; C.history_stride = a->history_stride;
+            C.row_params = a->row_params; C.params = a->params;
+            C.row_stride = a->logits_row_stride; C.out_stride = v_pad; C.mask_stride = a->mask_row_stride;
+            C.B = a->batch; C.V = a->vocab;
+            int nl = 0;
+            const int e = launch_clean_copy(C, a->logits_dtype, h->num_sms, st, &nl);
+            h->launches += nl;
+            if (e != 0) return fail(h, BORN_ERR_CUDA, "clean-copy launch failed: %s", cudaGetErrorString((cudaError_t)e));
+        }
+        a2 = *a;
+        a2.logits = h->clean_copy; a2.logits_dtype = BORN_DTYPE_F32; a2.logits_row_stride = v_pad;
+        a2.mask = nullptr; a2.mask_row_stride = 0;
+        a2.history = nullptr; a2.history_len = nullptr; a2.history_stride = 0;
+        a = &a2;
+        rc = fill_scan(h, A, a->batch, 1, a->vocab, a->logits_dtype, a->logits, a->logits_row_stride, nullptr, 0, &grid);
+        if (rc) return rc;
+    }
+    if (reserve_only) return BORN_OK;
     A.history = a->history;
     A.history_len = a->history_len;
     A.history_stride = a->history_stride;
-    A.B = a->batch;
-    A.V = a->vocab;
+    if (a->history) {
+        if (!h->hist_lists) return fail(h, BORN_ERR_UNSUPPORTED, "token histories need scratch that the allocation-free entry point does not have");
+        HistPrepArgs P;
+        P.history = a->history; P.history_len = a->history_len; P.history_stride = a->history_stride;
+        P.B = a->batch; P.vocab = a->vocab;
+        P.lists = h->hist_lists; P.counts = h->hist_counts;
+        hist_prep_kernel<<<a->batch, kThreads, 0, st>>>(P);
+        CUDA_TRY(h, cudaGetLastError());
+        h->launches++;
+        A.hist_lists = h->hist_lists;
+        A.hist_counts = h->hist_counts;
+    }
     A.row_params = a->row_params;
     A.params = a->params;
     A.uniforms = a->uniforms;
@@ -420,41 +470,40 @@ static int sample_device(Handle* h, const born_sample_args* a_in, cudaStream_t s
     A.out_kept_ids = a->out_kept_ids;
     A.out_kept_count = a->out_kept_count;
     A.kept_stride = a->kept_stride;
-    A.mode = kModeFull;
-    A.records = h->records;
-    A.rec_slice_stride = h->record_stride;
-    A.tickets = h->tickets;
-    A.dev_error = h->dev_error;
-#ifdef BORN_PROFILE
-    if (const char* pp = getenv("BORN_PROF_PTR")) A.prof = (unsigned long long*)strtoull(pp, nullptr, 0);
-#endif
-    const int esz = a->logits_dtype == BORN_DTYPE_F32 ? 4 : 2;
-    if (a->vocab_segments > 1) {
-        A.S = a->vocab_segments;
-        A.slice_len = a->vocab / a->vocab_segments;
-        A.segment_mode = 1;
-    } else {
-        choose_slices(h, a->batch, a->vocab, esz, &A.S, &A.slice_len);
+    A.mode = kScanFull;
+    if (G > 1) {
+        // vocabulary segments on one GPU: the k best of every (row, segment), then the merge --
+        // the same two steps as the vocab-sharded path, without the all-gather in between
+        const int64_t rec = kRecordHdrBytes + 8 * (int64_t)a->params.top_k;
+        A.mode = kScanLocal;
+        A.want_lse = a->out_lse != nullptr;
+        A.out_lse = nullptr;
+        A.packed = h->seg_packed;
+        A.packed_row_stride = rec;
+        A.packed_seg_stride = rec * a->batch;
+        if ((size_t)(rec * a->batch * G) > h->seg_packed_bytes) return fail(h, BORN_ERR_UNSUPPORTED, "batch x segments x top_k exceeds the workspace");
+        if ((rc = launch_scan(h, A, a->logits_dtype, grid, st))) return rc;
+        MergeArgs M;
+        memset(&M, 0, sizeof M);
+        M.gathered = h->seg_packed; M.row_stride = rec; M.seg_stride = rec * a->batch;
+        M.B = a->batch; M.G = G;
+        M.temperature = a->params.temperature; M.top_p = a->params.top_p;
+        M.uniforms = a->uniforms;
+        M.out_token = a->out_token; M.out_prob = a->out_prob; M.out_lse = a->out_lse; M.out_status = a->out_status;
+        M.out_kept_ids = a->out_kept_ids; M.out_kept_count = a->out_kept_count; M.kept_stride = a->kept_stride;
+        return launch_merge(h, M, st);
     }
-    A.rec_row_stride = h->record_stride * A.S;
-    A.tma_logits = ((uintptr_t)a->logits % 16 == 0) && ((a->logits_row_stride * esz) % 16 == 0) &&
-                   (((int64_t)A.slice_len * esz) % 16 == 0);
-    A.tma_mask = a->mask && ((uintptr_t)a->mask % 16 == 0) && ((a->mask_row_stride * 4) % 16 == 0) &&
-                 (A.slice_len % 128 == 0);
-    if (getenv("BORN_NO_TMA")) A.tma_logits = A.tma_mask = 0;
-    return launch_sample(h, A, a->logits_dtype, st);
+    return launch_scan(h, A, a->logits_dtype, grid, st);
 }
 
-int32_t born_sample(void* handle, const born_sample_args* a, void* stream) {
-    Handle* h = (Handle*)handle;
-    if (!h) return fail(nullptr, BORN_ERR_INVALID_ARGUMENT, "handle is NULL");
+static int sample_check(Handle* h, const born_sample_args* a) {
     if (!a) return fail(h, BORN_ERR_INVALID_ARGUMENT, "args is NULL");
     if (a->struct_size != sizeof(born_sample_args))
         return fail(h, BORN_ERR_INVALID_ARGUMENT, "struct_size %u != %zu", a->struct_size, sizeof(born_sample_args));
     if (a->batch <= 0 || a->vocab <= 0) return fail(h, BORN_ERR_INVALID_ARGUMENT, "batch and vocab must be positive");
     if (a->batch > h->max_batch || a->vocab > h->max_vocab)
-        return fail(h, BORN_ERR_INVALID_ARGUMENT, "batch %d / vocab %d exceed the handle's %d / %d", a->batch, a->vocab,
-                    h->max_batch, h->max_vocab);
+        return fail(h, h->is_static ? BORN_ERR_UNSUPPORTED : BORN_ERR_INVALID_ARGUMENT,
+                    "batch %d / vocab %d exceed the limit of %d / %d", a->batch, a->vocab, h->max_batch, h->max_vocab);
     if (a->logits_dtype != BORN_DTYPE_F32 && a->logits_dtype != BORN_DTYPE_BF16)
         return fail(h, BORN_ERR_INVALID_ARGUMENT, "unknown logits_dtype %d", a->logits_dtype);
     if (!a->logits || !a->out_token || !a->out_status)
@@ -467,7 +516,9 @@ int32_t born_sample(void* handle, const born_sample_args* a, void* stream) {
                     "history_stride %d outside 1..%d", a->history_stride, BORN_MAX_HISTORY);
     if (a->memory != BORN_MEM_DEVICE && a->memory != BORN_MEM_HOST)
         return fail(h, BORN_ERR_INVALID_ARGUMENT, "memory must be BORN_MEM_DEVICE or BORN_MEM_HOST");
-    if (a->out_kept_ids && a->kept_stride <= 0) return fail(h, BORN_ERR_INVALID_ARGUMENT, "kept_stride must be positive");
+    if (a->out_kept_ids && (a->kept_stride <= 0 || a->kept_stride > BORN_MAX_CANDIDATES))
+        return fail(h, a->kept_stride > BORN_MAX_CANDIDATES ? BORN_ERR_UNSUPPORTED : BORN_ERR_INVALID_ARGUMENT,
+                    "kept_stride must be in 1..%d", BORN_MAX_CANDIDATES);
     bool need_u = true;
     if (!a->row_params || a->memory == BORN_MEM_HOST) {
         const born_row_params* rp = a->row_params ? a->row_params : &a->params;
@@ -485,13 +536,50 @@ int32_t born_sample(void* handle, const born_sample_args* a, void* stream) {
         if (a->row_params) return fail(h, BORN_ERR_UNSUPPORTED, "vocab_segments needs uniform parameters");
         if (a->params.top_k <= 0 || a->params.top_k * G > BORN_MAX_CANDIDATES)
             return fail(h, BORN_ERR_UNSUPPORTED, "vocab_segments needs 1 <= top_k*segments <= %d", BORN_MAX_CANDIDATES);
-        if (a->mask && (a->vocab / G) % 32)
-            return fail(h, BORN_ERR_UNSUPPORTED, "with a mask the segment length must be a multiple of 32");
-        if ((int64_t)G * a->batch > h->max_records) return fail(h, BORN_ERR_UNSUPPORTED, "batch*segments exceeds the workspace");
+        if (a->params.top_k > kThreads) return fail(h, BORN_ERR_UNSUPPORTED, "vocab_segments needs top_k <= %d per segment", kThreads);
+        if ((a->params.flags & BORN_FLAG_GREEDY) || a->params.temperature == 0.0f || a->params.min_p > 0.0f)
+            return fail(h, BORN_ERR_UNSUPPORTED, "vocab_segments takes temperature > 0, top-k and top-p only");
+        if ((int64_t)G * a->batch > h->max_rows) return fail(h, BORN_ERR_UNSUPPORTED, "batch*segments exceeds the workspace");
+        if (h->is_static) return fail(h, BORN_ERR_UNSUPPORTED, "vocab_segments needs scratch that the allocation-free entry point does not have");
     }
-    CUDA_TRY(h, cudaSetDevice(h->device));
+    return BORN_OK;
+}
+
+int32_t born_sampler_reserve(void* handle, const born_sample_args* a) {
+    Handle* h = (Handle*)handle;
+    if (!h) return fail(nullptr, BORN_ERR_INVALID_ARGUMENT, "handle is NULL");
+    int rc = sample_check(h, a);
+    if (rc) return rc;
+    if ((rc = use_device(h))) return rc;
+    if (a->memory == BORN_MEM_HOST) {
+        const int B = a->batch, V = a->vocab;
+        const size_t esz = a->logits_dtype == BORN_DTYPE_F32 ? 4 : 2;
+        const size_t v_pad = ((size_t)V * esz + 15) / 16 * 16 / esz, w_pad = ((size_t)(V + 31) / 32 + 3) / 4 * 4;
+        if ((rc = stage_reserve(h, 0, (size_t)B * v_pad * esz))) return rc;
+        if (a->mask && (rc = stage_reserve(h, 1, (size_t)B * w_pad * 4))) return rc;
+        if (a->history && (rc = stage_reserve(h, 2, (size_t)B * a->history_stride * 4))) return rc;
+        for (int s = 3; s <= 11; ++s) {
+            size_t need = (size_t)B * (s == 4 ? sizeof(born_row_params) : s == 10 ? (size_t)(a->kept_stride > 0 ? a->kept_stride : 1) * 4 : 4);
+            if ((rc = stage_reserve(h, s, need))) return rc;
+        }
+        // the device form of the call: aligned staging rows
+        born_sample_args d = *a;
+        d.memory = BORN_MEM_DEVICE;
+        d.logits = h->stage[0].p; d.logits_row_stride = (int64_t)v_pad;
+        if (a->mask) { d.mask = (const uint32_t*)h->stage[1].p; d.mask_row_stride = (int64_t)w_pad; }
+        return sample_device(h, &d, nullptr, true);
+    }
+    return sample_device(h, a, nullptr, true);
+}
+
+int32_t born_sample(void* handle, const born_sample_args* a, void* stream) {
+    Handle* h = (Handle*)handle;
+    if (!h) return fail(nullptr, BORN_ERR_INVALID_ARGUMENT, "handle is NULL");
+    int rc = sample_check(h, a);
+    if (rc) return rc;
+    if ((rc = use_device(h))) return rc;
     cudaStream_t st = (cudaStream_t)stream;
-    if (a->memory == BORN_MEM_DEVICE) return sample_device(h, a, st);
+    if (a->memory == BORN_MEM_DEVICE) return sample_device(h, a, st, false);
 
     // ---- host-memory call: copy in, run, copy out, wait ----
     const int B = a->batch, V = a->vocab;
@@ -499,7 +587,6 @@ int32_t born_sample(void* handle, const born_sample_args* a, void* stream) {
     const size_t words = (size_t)(V + 31) / 32;
     born_sample_args d = *a;
     d.memory = BORN_MEM_DEVICE;
-    int rc;
     // tight device copies: row strides become vocab (padded to 16 bytes)
     const size_t v_pad = ((size_t)V * esz + 15) / 16 * 16 / esz;
     const size_t w_pad = (words + 3) / 4 * 4;
@@ -551,7 +638,7 @@ int32_t born_sample(void* handle, const born_sample_args* a, void* stream) {
     d.out_kept_count = a->out_kept_count ? (int32_t*)h->stage[11].p : nullptr;
     if (d.out_kept_ids) CUDA_TRY(h, cudaMemsetAsync(d.out_kept_ids, 0xFF, (size_t)B * a->kept_stride * 4, st));
     CUDA_TRY(h, cudaEventRecord(h->ev[1], st));
-    if ((rc = sample_device(h, &d, st))) return rc;
+    if ((rc = sample_device(h, &d, st, false))) return rc;
     CUDA_TRY(h, cudaEventRecord(h->ev[2], st));
     CUDA_TRY(h, cudaMemcpyAsync(a->out_token, d.out_token, (size_t)B * 4, cudaMemcpyDeviceToHost, st));
     CUDA_TRY(h, cudaMemcpyAsync(a->out_status, d.out_status, (size_t)B * 4, cudaMemcpyDeviceToHost, st));
@@ -566,6 +653,33 @@ int32_t born_sample(void* handle, const born_sample_args* a, void* stream) {
     cudaEventElapsedTime(&h->timing[0], h->ev[0], h->ev[1]);
     cudaEventElapsedTime(&h->timing[1], h->ev[1], h->ev[2]);
     cudaEventElapsedTime(&h->timing[2], h->ev[2], h->ev[3]);
+    return check_device_error(h);
+}
+
+int32_t born_debug_expire_wait(void* handle, void* stream) {
+    Handle* h = (Handle*)handle;
+    if (!h || h->is_static) return fail(nullptr, BORN_ERR_INVALID_ARGUMENT, "handle is NULL");
+    int rc = use_device(h);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    // three tiles of zeros, one row, greedy: three CTAs of one tile each; the middle one's copy is withheld
+    const int V = 3 * (kTileBytes / 4);
+    const size_t bytes = (size_t)V * 4 + 64;
+    if ((rc = stage_reserve(h, 15, bytes))) return rc;
+    uint8_t* buf = (uint8_t*)h->stage[15].p;
+    CUDA_TRY(h, cudaMemsetAsync(buf, 0, bytes, st));
+    ScanArgs A;
+    memset(&A, 0, sizeof A);
+    int grid = 0;
+    if ((rc = fill_scan(h, A, 1, 1, V, BORN_DTYPE_F32, buf, V, nullptr, 0, &grid))) return rc;
+    A.params.flags = BORN_FLAG_GREEDY;
+    A.out_token = (int32_t*)(buf + (size_t)V * 4);
+    A.out_status = (int32_t*)(buf + (size_t)V * 4 + 16);
+    A.mode = kScanFull;
+    A.timeout_ns = 1000000ull;
+    A.debug_skip_tile = 1;
+    if ((rc = launch_scan(h, A, BORN_DTYPE_F32, grid, st))) return rc;
+    CUDA_TRY(h, cudaStreamSynchronize(st));
     return check_device_error(h);
 }
 
@@ -595,7 +709,10 @@ int32_t born_spec_verify(void* handle, const born_spec_args* a, void* stream) {
         !a->out_accept_len || !a->out_tokens || !a->out_status)
         return fail(h, BORN_ERR_INVALID_ARGUMENT, "spec_verify: a required pointer is NULL");
     if (!(a->temperature >= 0.0f) || !isfinite(a->temperature)) return fail(h, BORN_ERR_INVALID_ARGUMENT, "temperature");
-    CUDA_TRY(h, cudaSetDevice(h->device));
+    if (V > kSpecMaxBlocks * kSpecMassBlock)
+        return fail(h, BORN_ERR_UNSUPPORTED, "spec_verify: vocab %d exceeds %d", V, kSpecMaxBlocks * kSpecMassBlock);
+    if (a->memory != BORN_MEM_DEVICE && a->memory != BORN_MEM_HOST) return fail(h, BORN_ERR_INVALID_ARGUMENT, "memory");
+    { int rcd = use_device(h); if (rcd) return rcd; }
     cudaStream_t st = (cudaStream_t)stream;
     SpecKernelArgs A;
     memset(&A, 0, sizeof A);
@@ -605,11 +722,8 @@ int32_t born_spec_verify(void* handle, const born_spec_args* a, void* stream) {
     // like the staging mirrors, then reused; the tickets are zero between launches
     const SpecScratchLayout SL = spec_scratch_layout(B, K, V);
     if (h->spec_scratch_bytes < SL.total) {
-        CUDA_TRY(h, cudaStreamSynchronize(st));
-        if (h->spec_scratch) { cudaFree(h->spec_scratch); h->workspace -= (int64_t)h->spec_scratch_bytes; h->spec_scratch = nullptr; h->spec_scratch_bytes = 0; }
-        int rc0 = dev_alloc(h, (void**)&h->spec_scratch, SL.total);
+        int rc0 = grow(h, (void**)&h->spec_scratch, &h->spec_scratch_bytes, SL.total, st);
         if (rc0 != BORN_OK) return rc0;
-        h->spec_scratch_bytes = SL.total;
         h->spec_layout_key = -1;
     }
     // the ticket area sits at offset 0 whatever the shape; it is cleared when the layout changes
@@ -706,13 +820,17 @@ int32_t born_shard_init(void* handle, const void* id, int32_t rank, int32_t nran
         return fail(h, BORN_ERR_INVALID_ARGUMENT, "shard_init: rank %d of %d", rank, nranks);
     int rc = nccl_load(h);
     if (rc) return rc;
-    CUDA_TRY(h, cudaSetDevice(h->device));
+    { int rcd = use_device(h); if (rcd) return rcd; }
     Id128 u;
     memcpy(&u, id, sizeof u);
     int e = h->nccl.CommInitRank(&h->comm, nranks, u, rank);
     if (e != 0) return fail(h, BORN_ERR_NCCL, "ncclCommInitRank: %s", h->nccl.GetErrorString ? h->nccl.GetErrorString(e) : "error");
     h->rank = rank;
     h->nranks = nranks;
+    // exchange buffers for the handle's limits (top_k <= 256 per shard): nothing is allocated per call
+    const size_t pk = (size_t)h->max_batch * (size_t)(kRecordHdrBytes + 8 * kThreads);
+    if ((rc = grow(h, (void**)&h->packed, &h->packed_bytes, pk, nullptr))) return rc;
+    if ((rc = grow(h, (void**)&h->gathered, &h->gathered_bytes, pk * (size_t)nranks, nullptr))) return rc;
     return BORN_OK;
 }
 
@@ -720,13 +838,14 @@ static int shard_check(Handle* h, const born_shard_args* a, bool local, bool mer
     if (!h) return fail(nullptr, BORN_ERR_INVALID_ARGUMENT, "handle is NULL");
     if (!a || a->struct_size != sizeof(born_shard_args)) return fail(h, BORN_ERR_INVALID_ARGUMENT, "args NULL or wrong struct_size");
     if (a->memory != BORN_MEM_DEVICE) return fail(h, BORN_ERR_UNSUPPORTED, "the sharded path takes device memory only");
-    if (a->batch <= 0 || a->batch > h->max_batch || a->vocab_local <= 0 || a->vocab_local > h->max_vocab)
+    if (a->batch <= 0 || a->batch > h->max_rows || a->vocab_local <= 0 || a->vocab_local > h->max_vocab)
         return fail(h, BORN_ERR_INVALID_ARGUMENT, "batch/vocab_local out of range");
     if (a->nranks < 1 || a->nranks > BORN_MAX_SHARDS || a->rank < 0 || a->rank >= a->nranks)
         return fail(h, BORN_ERR_INVALID_ARGUMENT, "rank %d of %d", a->rank, a->nranks);
     if ((int64_t)a->vocab_local * a->nranks > BORN_MAX_VOCAB) return fail(h, BORN_ERR_UNSUPPORTED, "global vocab too large");
     if (a->top_k <= 0 || (int64_t)a->top_k * a->nranks > BORN_MAX_CANDIDATES)
         return fail(h, BORN_ERR_UNSUPPORTED, "need 1 <= top_k*nranks <= %d", BORN_MAX_CANDIDATES);
+    if (a->top_k > kThreads) return fail(h, BORN_ERR_UNSUPPORTED, "the sharded path takes top_k <= %d per shard", kThreads);
     if (!(a->temperature > 0.0f) || !isfinite(a->temperature) || !(a->top_p >= 0.0f))
         return fail(h, BORN_ERR_INVALID_ARGUMENT, "temperature must be > 0 and top_p >= 0");
     if (local) {
@@ -737,55 +856,38 @@ static int shard_check(Handle* h, const born_shard_args* a, bool local, bool mer
     return BORN_OK;
 }
 
-static void shard_fill(const born_shard_args* a, SampleKernelArgs& A, Handle* h) {
+// Local pass of one shard: the k best of every row (global token ids), the shard's maximum
+// and its share of the log-sum-exp, one packed record per row.
+static int shard_local(Handle* h, const born_shard_args* a, void* packed, bool want_lse, cudaStream_t st) {
+    ScanArgs A;
     memset(&A, 0, sizeof A);
-    A.B = a->batch;
+    int grid = 0;
+    int rc = fill_scan(h, A, a->batch, 1, a->vocab_local, a->logits_dtype, a->logits, a->logits_row_stride, nullptr, 0, &grid);
+    if (rc) return rc;
     A.params.temperature = a->temperature;
     A.params.top_p = a->top_p;
     A.params.top_k = a->top_k;
     A.params.repetition_penalty = 1.0f;
-    A.uniforms = a->uniforms;
-    A.out_token = a->out_token;
-    A.out_prob = a->out_prob;
-    A.out_lse = a->out_lse;
-    A.out_status = a->out_status;
-    A.tickets = h->tickets;
-    A.dev_error = h->dev_error;
-    A.segment_mode = 1;
-}
-
-static int shard_local(Handle* h, const born_shard_args* a, void* packed, bool want_lse, cudaStream_t st) {
-    SampleKernelArgs A;
-    shard_fill(a, A, h);
-    const int esz = a->logits_dtype == BORN_DTYPE_F32 ? 4 : 2;
-    A.logits = a->logits;
-    A.row_stride = a->logits_row_stride;
-    A.V = a->vocab_local;
-    A.mode = kModeLocal;
-    A.S = 1;
-    A.slice_len = (a->vocab_local + kTileBytes / esz - 1) / (kTileBytes / esz) * (kTileBytes / esz);
-    A.idx_offset = a->rank * a->vocab_local;
-    A.records = (uint8_t*)packed;
-    A.rec_row_stride = born_shard_record_bytes(a->top_k);
-    A.rec_slice_stride = 0;
-    A.tma_logits = ((uintptr_t)a->logits % 16 == 0) && ((a->logits_row_stride * esz) % 16 == 0);
-    static float dummy_lse_flag;  // only its non-NULL-ness matters in local mode
-    A.out_lse = want_lse ? &dummy_lse_flag : nullptr;
-    A.out_token = nullptr;
-    A.out_status = nullptr;
-    return launch_sample(h, A, a->logits_dtype, st);
+    A.mode = kScanLocal;
+    A.want_lse = want_lse ? 1 : 0;
+    A.idx_base = a->rank * a->vocab_local;
+    A.packed = (uint8_t*)packed;
+    A.packed_row_stride = born_shard_record_bytes(a->top_k);
+    A.packed_seg_stride = 0;
+    return launch_scan(h, A, a->logits_dtype, grid, st);
 }
 
 static int shard_merge(Handle* h, const born_shard_args* a, const void* gathered, cudaStream_t st) {
-    SampleKernelArgs A;
-    shard_fill(a, A, h);
-    A.V = a->vocab_local * a->nranks;
-    A.mode = kModeMerge;
-    A.S = a->nranks;
-    A.records = (uint8_t*)gathered;
-    A.rec_row_stride = born_shard_record_bytes(a->top_k);
-    A.rec_slice_stride = A.rec_row_stride * a->batch;
-    return launch_sample(h, A, BORN_DTYPE_F32, st);
+    MergeArgs M;
+    memset(&M, 0, sizeof M);
+    M.gathered = (const uint8_t*)gathered;
+    M.row_stride = born_shard_record_bytes(a->top_k);
+    M.seg_stride = M.row_stride * a->batch;
+    M.B = a->batch; M.G = a->nranks;
+    M.temperature = a->temperature; M.top_p = a->top_p;
+    M.uniforms = a->uniforms;
+    M.out_token = a->out_token; M.out_prob = a->out_prob; M.out_lse = a->out_lse; M.out_status = a->out_status;
+    return launch_merge(h, M, st);
 }
 
 int32_t born_shard_local(void* handle, const born_shard_args* a, void* stream) {
@@ -793,7 +895,7 @@ int32_t born_shard_local(void* handle, const born_shard_args* a, void* stream) {
     int rc = shard_check(h, a, true, false);
     if (rc) return rc;
     if (!a->packed) return fail(h, BORN_ERR_INVALID_ARGUMENT, "packed is NULL");
-    CUDA_TRY(h, cudaSetDevice(h->device));
+    if ((rc = use_device(h))) return rc;
     return shard_local(h, a, a->packed, true, (cudaStream_t)stream);
 }
 
@@ -802,7 +904,7 @@ int32_t born_shard_merge(void* handle, const born_shard_args* a, void* stream) {
     int rc = shard_check(h, a, false, true);
     if (rc) return rc;
     if (!a->gathered) return fail(h, BORN_ERR_INVALID_ARGUMENT, "gathered is NULL");
-    CUDA_TRY(h, cudaSetDevice(h->device));
+    if ((rc = use_device(h))) return rc;
     return shard_merge(h, a, a->gathered, (cudaStream_t)stream);
 }
 
@@ -812,20 +914,13 @@ int32_t born_sample_sharded(void* handle, const born_shard_args* a, void* stream
     if (rc) return rc;
     if (!h->comm) return fail(h, BORN_ERR_NCCL, "born_shard_init has not been called on this handle");
     if (a->nranks != h->nranks || a->rank != h->rank) return fail(h, BORN_ERR_INVALID_ARGUMENT, "rank/nranks differ from born_shard_init");
-    CUDA_TRY(h, cudaSetDevice(h->device));
+    if ((rc = use_device(h))) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     const size_t rec = (size_t)born_shard_record_bytes(a->top_k);
     const size_t pk = rec * (size_t)a->batch, ga = pk * (size_t)a->nranks;
-    if (h->packed_bytes < pk) {  // grows once to the largest request seen
-        cudaFree(h->packed); h->packed = nullptr; h->packed_bytes = 0;
-        if ((rc = dev_alloc(h, (void**)&h->packed, pk))) return rc;
-        h->packed_bytes = pk;
-    }
-    if (h->gathered_bytes < ga) {
-        cudaFree(h->gathered); h->gathered = nullptr; h->gathered_bytes = 0;
-        if ((rc = dev_alloc(h, (void**)&h->gathered, ga))) return rc;
-        h->gathered_bytes = ga;
-    }
+    // exchange buffers: sized by born_shard_init for the handle's limits, grown here only by a larger request
+    if ((rc = grow(h, (void**)&h->packed, &h->packed_bytes, pk, st))) return rc;
+    if ((rc = grow(h, (void**)&h->gathered, &h->gathered_bytes, ga, st))) return rc;
     if ((rc = shard_local(h, a, h->packed, a->out_lse != nullptr, st))) return rc;
     int e = h->nccl.AllGather(h->packed, h->gathered, pk, /*ncclInt8*/ 0, h->comm, st);
     if (e != 0) return fail(h, BORN_ERR_NCCL, "ncclAllGather: %s", h->nccl.GetErrorString ? h->nccl.GetErrorString(e) : "error");
@@ -835,15 +930,20 @@ int32_t born_sample_sharded(void* handle, const born_shard_args* a, void* stream
 }  // extern "C"
 
 // ------------------------------------------------------------------ allocation-free entry
-// Scratch for born_sample_static: slice records, row tickets and the device error word in
-// one file-scope array that every GPU loading this library holds until exit.
+// Scratch for born_sample_static: segment records, mass blocks, row tickets and the device
+// error word in one file-scope array that every GPU loading this library holds until exit.
 namespace {
 constexpr int kStaticMaxBatch = BORN_STATIC_MAX_BATCH;
-constexpr int kStaticMaxRecords = 2 * BORN_STATIC_MAX_BATCH;
-constexpr size_t kStaticRecordStride = kRecordHdrBytes + (size_t)kMaxK * 8;
-constexpr size_t kStaticRecordsBytes = kStaticMaxRecords * kStaticRecordStride;
+constexpr int kStaticRecCap = 512;
+constexpr int kStaticMaxGrid = 512;  // >= two CTAs per SM on any sm_100 part
+constexpr size_t kStaticRecStride = kRecordHdrBytes + (size_t)kStaticRecCap * 8;
+constexpr size_t kStaticRecordsBytes = (size_t)(kStaticMaxBatch + kStaticMaxGrid) * kStaticRecStride;
+constexpr size_t kStaticBlocks = BORN_STATIC_MAX_BLOCKS;
+constexpr size_t kStaticBlocksBytes = kStaticBlocks * sizeof(MassBlock);
 constexpr size_t kStaticTicketsBytes = sizeof(uint32_t) * 2 * kStaticMaxBatch;
-constexpr size_t kStaticBytes = kStaticRecordsBytes + kStaticTicketsBytes + 256;
+constexpr size_t kStaticHistBytes = (size_t)kStaticMaxBatch * (BORN_MAX_HISTORY * 8 + 4);
+constexpr size_t kStaticBytes = kStaticRecordsBytes + kStaticBlocksBytes + kStaticHistBytes + kStaticTicketsBytes + 256;
+static_assert(kStaticBytes <= BORN_STATIC_SCRATCH_BYTES, "the header promises at most BORN_STATIC_SCRATCH_BYTES");
 constexpr int kStaticMaxDevices = 64;
 }  // namespace
 
@@ -865,9 +965,10 @@ extern "C" int32_t born_sample_static(const born_sample_args* a, void* stream) {
     if (a->batch > kStaticMaxBatch)
         return fail(nullptr, BORN_ERR_UNSUPPORTED, "born_sample_static: batch %d exceeds the static scratch limit of %d rows",
                     a->batch, kStaticMaxBatch);
-    if (a->vocab_segments > 1 && (int64_t)a->vocab_segments * a->batch > kStaticMaxRecords)
-        return fail(nullptr, BORN_ERR_UNSUPPORTED, "born_sample_static: batch*vocab_segments exceeds %d scratch records",
-                    kStaticMaxRecords);
+    if (a->batch > 0 && a->vocab > 0 &&
+        (int64_t)a->batch * (((int64_t)a->vocab + kMassBlock - 1) / kMassBlock) > (int64_t)kStaticBlocks)
+        return fail(nullptr, BORN_ERR_UNSUPPORTED, "born_sample_static: batch x ceil(vocab/%d) exceeds %d mass blocks of static scratch",
+                    kMassBlock, (int)kStaticBlocks);
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return fail(nullptr, BORN_ERR_NO_DEVICE, "no CUDA device: %s", cudaGetErrorString(e));
@@ -885,17 +986,26 @@ extern "C" int32_t born_sample_static(const born_sample_args* a, void* stream) {
             cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
             return fail(nullptr, BORN_ERR_CUDA, "cudaDeviceGetAttribute failed");
         if (major != 10) return fail(nullptr, BORN_ERR_NO_DEVICE, "device %d is not sm_100; this library is built for sm_100a only", dev);
+        if ((e = scan_attrs_all()) != cudaSuccess)
+            return fail(nullptr, BORN_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
         h->device = dev;
         h->is_static = true;
         h->max_batch = kStaticMaxBatch;
         h->max_vocab = BORN_MAX_VOCAB;
         h->max_k = BORN_MAX_TOP_K;
         h->num_sms = sms;
-        h->max_records = kStaticMaxRecords;
-        h->record_stride = (int64_t)kStaticRecordStride;
+        h->max_grid = 2 * sms < kStaticMaxGrid ? 2 * sms : kStaticMaxGrid;
+        h->max_rows = kStaticMaxBatch;
+        h->rec_cap = kStaticRecCap;
+        h->rec_stride = (int64_t)kStaticRecStride;
+        h->records_bytes = kStaticRecordsBytes;
         h->records = base;
-        h->tickets = reinterpret_cast<uint32_t*>(base + kStaticRecordsBytes);
-        h->dev_error = reinterpret_cast<int*>(base + kStaticRecordsBytes + kStaticTicketsBytes);
+        h->blocks = reinterpret_cast<MassBlock*>(base + kStaticRecordsBytes);
+        h->blocks_cap = (int64_t)kStaticBlocks;
+        h->hist_lists = reinterpret_cast<unsigned long long*>(base + kStaticRecordsBytes + kStaticBlocksBytes);
+        h->hist_counts = reinterpret_cast<uint32_t*>(h->hist_lists + (size_t)kStaticMaxBatch * BORN_MAX_HISTORY);
+        h->tickets = reinterpret_cast<uint32_t*>(base + kStaticRecordsBytes + kStaticBlocksBytes + kStaticHistBytes);
+        h->dev_error = reinterpret_cast<int*>(base + kStaticRecordsBytes + kStaticBlocksBytes + kStaticHistBytes + kStaticTicketsBytes);
         g_static_ready[dev] = true;
     }
     // The array keeps whatever the previous call left; the tickets and the error word

@@ -1,0 +1,688 @@
+// Finishing a row: merge the segment records, select (top-k -> min-p -> top-p on exact
+// integer masses) and draw by inverse CDF in ascending token index.  Runs in the CTA that
+// completes the row (scan_kernel) or in merge_kernel over all-gathered shard records.
+//
+// Every decision sum is an exact integer sum of fixed-point masses
+// q = rne(exp_det((z - m) * inv_T) * 2^40), so thread order cannot matter.  Rank order is
+// (value descending, token index ascending): the first maximum wins, as in the reference's
+// argmax (born: internal/nn/cross_entropy.go:241-251).
+#pragma once
+#include "scan_common.cuh"
+
+namespace born {
+
+struct PackedHdr {  // 32 bytes: header of a packed shard / segment record (the all-gather payload)
+    float m;        // maximum of the shard's row (NaN if a NaN was seen)
+    float lse_s;    // sum of 2^((z - m) * c2)
+    uint32_t count; // entries that follow: rank keys, best first
+    uint32_t flags; // bit 0: the shard held more than `count` candidates; bit 1: the record is not exact
+    float bound;
+    uint32_t pad[3];
+};
+static_assert(sizeof(PackedHdr) == kRecordHdrBytes, "packed header size");
+
+struct RowOut {   // where a finished row reports
+    int32_t* token; float* prob; float* lse; int32_t* status; int32_t* kept_ids; int32_t* kept_count;
+    int kept_stride;
+    int row;
+};
+__device__ __forceinline__ void row_fail(const RowOut& o, int status) {
+    if (threadIdx.x == 0) {
+        o.token[o.row] = -1;
+        o.status[o.row] = status;
+        if (o.prob) o.prob[o.row] = 0.0f;
+        if (o.kept_count) o.kept_count[o.row] = 0;
+    }
+}
+
+struct SelectIn {
+    int n;          // entries in sel[]: rank keys, all alive
+    int k;          // keep the k best first (0: keep all)
+    unsigned long long Qa;     // min-p threshold on the masses (0: off)
+    float top_p;    // (0,1): on
+    unsigned long long S_ext;  // top-p total when the candidates are only the heavy part of the row (0: their own sum)
+    bool complete;  // the candidates hold every token the row can keep
+    float m_row, inv_T, u;
+};
+
+// Selection and draw over n <= kSelCap candidates in shared memory (sel: rank keys; selq:
+// scratch for their masses).  Returns false when the nucleus is not inside the candidates
+// (the caller then takes the exact fallback); all threads get the same answer.
+__device__ __noinline__ bool select_and_draw(const SelectIn in, uint64_t* sel, unsigned long long* selq, ScanShared& sh,
+                                             const RowOut o) {
+    const int tid = threadIdx.x;
+    const int n = in.n;
+    const int k_eff = in.k > 0 ? in.k : 0x7fffffff;
+    const bool topp = in.top_p > 0.0f && in.top_p < 1.0f;
+    if (tid == 0) { sh.acc[0] = 0; sh.acc[1] = 0; sh.acc[2] = 0; sh.flag = 0; }
+    cta_sync();
+    if (n <= kThreads) {
+        // ---- small set: everything by all-pairs comparison.  An entry is shared by P = 2^lg
+        // adjacent threads, each walking every P-th entry; partial counts meet by shuffles.
+        int lg = 0;
+        while (lg < 5 && (n << (lg + 1)) <= kThreads) ++lg;
+        const int P = 1 << lg, part = tid & (P - 1), ent = tid >> lg;
+        const bool mine = ent < n;
+        const bool lead = mine && part == 0;
+        const uint64_t ck = mine ? sel[ent] : 0ull;
+        auto group_sum = [&](uint64_t v, int PP) {
+            for (int d = 1; d < PP; d <<= 1) v += shfl_xor_u64(v, d);
+            return v;
+        };
+        auto block_add = [&](uint64_t v, int slot) {
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) v += shfl_xor_u64(v, d);
+            if ((tid & 31) == 0 && v) atomicAdd(&sh.acc[slot], (unsigned long long)v);
+        };
+        int rank = 0;
+        for (int j = part; j < n; j += P) rank += (sel[j] > ck) ? 1 : 0;
+        rank = (int)group_sum((uint64_t)rank, P);
+        bool kept = mine && rank < k_eff;
+        uint64_t q = 0;
+        if (kept) {
+            const float x = scaled_shift(ck_z(ck), in.m_row, in.inv_T);
+            q = (x < -30.0f) ? 0ull : mass_of(x);
+        }
+        if (in.Qa && q < in.Qa) { kept = false; q = 0; }
+        cta_sync();  // every thread has read sel[] for its rank
+        // the nk best entries go to sel[0..nk) in rank order; one that min-p removed stays as a dead entry
+        const int nk = min(n, k_eff);
+        if (lead && rank < nk) {
+            sel[rank] = kept ? ck : (ck & (uint64_t)kIdxMask);
+            selq[rank] = q;
+        }
+        block_add(lead ? q : 0ull, 0);
+        cta_sync();
+        uint64_t S = sh.acc[0];
+        int lg2 = 0;
+        while (lg2 < 5 && (nk << (lg2 + 1)) <= kThreads) ++lg2;
+        const int P2 = 1 << lg2, part2 = tid & (P2 - 1), ent2 = tid >> lg2;
+        const bool mine2 = ent2 < nk;
+        const bool lead2 = mine2 && part2 == 0;
+        const uint64_t ck2 = mine2 ? sel[ent2] : 0ull;
+        uint64_t q2 = mine2 ? (uint64_t)selq[ent2] : 0ull;
+        bool kept2 = mine2 && ck_alive(ck2);
+        if (topp) {
+            uint64_t before = 0;  // mass ahead in rank order
+            for (int j = part2; j < min(ent2, nk); j += P2) before += selq[j];
+            before = group_sum(before, P2);
+            uint64_t Tp = __double2ull_rz(__dmul_rn((double)in.top_p, __ull2double_rn(in.S_ext ? in.S_ext : S)));
+            if (Tp < 1) Tp = 1;
+            if (in.S_ext && !in.complete && S < Tp) return false;  // (uniform: S and Tp are)
+            if (kept2 && !(before < Tp)) { kept2 = false; q2 = 0; }
+            cta_sync();
+            if (lead2) {
+                sel[ent2] = kept2 ? ck2 : (ck2 & (uint64_t)kIdxMask);
+                selq[ent2] = q2;
+            }
+            block_add(lead2 ? q2 : 0ull, 1);
+            cta_sync();
+            S = sh.acc[1];
+        }
+        if (S == 0) {  // cannot happen while the row maximum is finite; never divide by it
+            row_fail(o, BORN_ROW_ALL_MASKED);
+            return true;
+        }
+        const uint32_t my_low = (uint32_t)(ck2 & kIdxMask);  // larger low bits = smaller token index
+        uint64_t pre = 0;
+        for (int j = part2; j < nk; j += P2) pre += ((uint32_t)(sel[j] & kIdxMask) > my_low) ? selq[j] : 0ull;
+        pre = group_sum(pre, P2);
+        uint64_t t = __double2ull_rz(__dmul_rn((double)in.u, __ull2double_rn(S)));
+        if (t > S - 1) t = S - 1;
+        if (lead2 && kept2 && pre <= t && t < pre + q2) {
+            o.token[o.row] = ck_idx(ck2);
+            o.status[o.row] = BORN_ROW_OK;
+            if (o.prob) o.prob[o.row] = __double2float_rn(__ddiv_rn(__ull2double_rn(q2), __ull2double_rn(S)));
+        }
+        if (o.kept_count || o.kept_ids) {
+            if (o.kept_ids) {
+                int kr = 0;  // kept entries ahead in rank order
+                for (int j = part2; j < min(ent2, nk); j += P2) kr += ck_alive(sel[j]) ? 1 : 0;
+                kr = (int)group_sum((uint64_t)kr, P2);
+                if (lead2 && kept2 && kr < o.kept_stride) o.kept_ids[(int64_t)o.row * o.kept_stride + kr] = ck_idx(ck2);
+            }
+            if (o.kept_count) {
+                block_add((lead2 && kept2) ? 1ull : 0ull, 2);
+                cta_sync();
+                if (tid == 0) o.kept_count[o.row] = (int)sh.acc[2];
+            }
+        }
+        return true;
+    }
+
+    // ---- large set: radix select, then mass-weighted radix threshold searches
+    if (n > k_eff) {
+        const uint64_t T = block_radix_search<true, 56, true>(
+            n, (unsigned long long)(k_eff - 1), [&](int i) { return sel[i]; }, [&](int) { return 1ull; }, sh.sc);
+        for (int i = tid; i < n; i += kThreads)
+            if (sel[i] < T) sel[i] &= (uint64_t)kIdxMask;
+        cta_sync();
+    }
+    for (int i = tid; i < n; i += kThreads) {
+        const uint64_t c = sel[i];
+        uint64_t q = 0;
+        if (ck_alive(c)) {
+            const float x = scaled_shift(ck_z(c), in.m_row, in.inv_T);
+            q = (x < -30.0f) ? 0ull : mass_of(x);
+            if (in.Qa && q < in.Qa) { q = 0; sel[i] = c & (uint64_t)kIdxMask; }
+        }
+        selq[i] = q;
+    }
+    cta_sync();
+    if (topp) {
+        uint64_t part = 0;
+        for (int i = tid; i < n; i += kThreads) part += selq[i];
+        const uint64_t S = block_sum_u64(part, sh.red64);
+        uint64_t Tp = __double2ull_rz(__dmul_rn((double)in.top_p, __ull2double_rn(in.S_ext ? in.S_ext : S)));
+        if (Tp < 1) Tp = 1;
+        if (in.S_ext && !in.complete && S < Tp) return false;
+        if (S >= Tp) {
+            // dead entries take part with weight 0 (their keys are unique small numbers)
+            const uint64_t C = block_radix_search<true, 56, false>(
+                n, Tp - 1, [&](int i) { return sel[i]; }, [&](int i) { return selq[i]; }, sh.sc);
+            for (int i = tid; i < n; i += kThreads)
+                if (sel[i] < C && ck_alive(sel[i])) { selq[i] = 0; sel[i] &= (uint64_t)kIdxMask; }
+            cta_sync();
+        }
+    }
+    uint64_t part = 0;
+    for (int i = tid; i < n; i += kThreads) part += selq[i];
+    const uint64_t S = block_sum_u64(part, sh.red64);
+    if (S == 0) {
+        row_fail(o, BORN_ROW_ALL_MASKED);
+        return true;
+    }
+    uint64_t t = __double2ull_rz(__dmul_rn((double)in.u, __ull2double_rn(S)));
+    if (t > S - 1) t = S - 1;
+    // walk in ascending token index: key = index; dead entries weigh nothing but need unique keys
+    const uint64_t tok64 = block_radix_search<false, 25, false>(
+        n, t, [&](int i) { return ck_alive(sel[i]) ? (uint64_t)ck_idx(sel[i]) : ((1ull << 24) | (uint64_t)i); },
+        [&](int i) { return selq[i]; }, sh.sc);
+    const int tok = (int)tok64;
+    for (int i = tid; i < n; i += kThreads) {
+        if (ck_alive(sel[i]) && ck_idx(sel[i]) == tok) {
+            o.token[o.row] = tok;
+            o.status[o.row] = BORN_ROW_OK;
+            if (o.prob) o.prob[o.row] = __double2float_rn(__ddiv_rn(__ull2double_rn(selq[i]), __ull2double_rn(S)));
+        }
+    }
+    if (o.kept_count || o.kept_ids) {
+        int alive = 0;
+        for (int i = tid; i < n; i += kThreads) {
+            const uint64_t c = sel[i];
+            if (!ck_alive(c)) continue;
+            ++alive;
+            if (o.kept_ids) {
+                int rank = 0;
+                for (int j = 0; j < n; ++j) rank += (sel[j] > c) ? 1 : 0;
+                if (rank < o.kept_stride) o.kept_ids[(int64_t)o.row * o.kept_stride + rank] = ck_idx(c);
+            }
+        }
+        const uint64_t tot = block_sum_u64((uint64_t)alive, sh.red64);
+        if (tid == 0 && o.kept_count) o.kept_count[o.row] = (int)tot;
+    }
+    return true;
+}
+
+// Block-wide reductions of the compute threads (results to every thread).
+__device__ __forceinline__ float block_max_nan(float v, float* buf) {
+    v = warp_max_nan(v);
+    cta_sync();
+    if ((threadIdx.x & 31) == 0) buf[threadIdx.x >> 5] = v;
+    cta_sync();
+    float r = buf[0];
+#pragma unroll
+    for (int w = 1; w < kScanWarps; ++w) r = max_nan(r, buf[w]);
+    return r;
+}
+__device__ __forceinline__ float block_sum_f32(float v, float* buf) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+    cta_sync();
+    if ((threadIdx.x & 31) == 0) buf[threadIdx.x >> 5] = v;
+    cta_sync();
+    float r = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kScanWarps; ++w) r += buf[w];
+    return r;
+}
+
+__device__ __forceinline__ MassBlock load_block(const MassBlock* p) {
+    const ulonglong2 v = __ldcg(reinterpret_cast<const ulonglong2*>(p));
+    MassBlock b;
+    b.m = __uint_as_float((uint32_t)v.x);
+    b.pad = (uint32_t)(v.x >> 32);
+    b.M = v.y;
+    return b;
+}
+
+// One mass block's contribution to the row total: rne_u64((double)M_c * (double)exp_det((m_c - m) * inv_T)).
+__device__ __forceinline__ unsigned long long block_share(const MassBlock& bk, float m, float inv_T) {
+    if (!(bk.m > -INFINITY) || bk.M == 0) return 0ull;
+    const float ef = exp_det(scaled_shift(bk.m, m, inv_T));
+    return __double2ull_rn(__dmul_rn(__ull2double_rn(bk.M), (double)ef));
+}
+
+// Logit of token `tok` of virtual row (b, g) as the sampler sees it: upcast, history
+// penalties, grammar mask.  O(history) per call; used by the paths that look at few tokens.
+template <typename T>
+__device__ __forceinline__ float token_logit(const ScanArgs& A, const born_row_params& rp, int b, int g, int tok) {
+    const T* row = reinterpret_cast<const T*>(A.logits) + (int64_t)b * A.row_stride + (int64_t)g * A.V;
+    float z;
+    if constexpr (sizeof(T) == 4) z = __ldg(reinterpret_cast<const float*>(row) + tok);
+    else z = bf16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t*>(row) + tok));
+    if (A.history && penalties_on(rp)) {
+        int len = A.history_len ? A.history_len[b] : A.history_stride;
+        len = max(0, min(min(len, A.history_stride), BORN_MAX_HISTORY));
+        const int32_t* gh = A.history + (int64_t)b * A.history_stride;
+        const int id = g * A.V + tok;
+        int cnt = 0;
+        for (int p = 0; p < len; ++p) cnt += (__ldg(gh + p) == id) ? 1 : 0;
+        if (cnt > 0) z = penalise(rp, z, cnt);
+    }
+    if (A.mask) {
+        const int64_t bi = (int64_t)g * A.V + tok;
+        if (!((__ldg(A.mask + (int64_t)b * A.mask_stride + (bi >> 5)) >> (bi & 31)) & 1u)) z = -INFINITY;
+    }
+    return z;
+}
+
+// Temperature-only rows: the draw descends the mass blocks.  t = min(floor(u * S), S - 1)
+// picks the block (ascending order, shares S_c), then the token inside it by the block's own
+// masses: t'' = min(floor((t - before) * M_c / S_c), M_c - 1) in float64.
+template <typename T>
+__device__ __forceinline__ void draw_whole_row(const ScanArgs& A, ScanShared& sh, uint8_t* scratch, const RowOut& o,
+                                               const born_row_params& rp, int b, int g, int row, float m, float inv_T,
+                                               unsigned long long S, float u) {
+    const int tid = threadIdx.x;
+    const MassBlock* blocks = A.blocks + (int64_t)row * A.nblk;
+    unsigned long long t = __double2ull_rz(__dmul_rn((double)u, __ull2double_rn(S)));
+    if (t > S - 1) t = S - 1;
+    unsigned long long run = 0;
+    if (tid == 0) sh.found = -1;
+    cta_sync();
+    for (int base = 0; base < A.nblk; base += kThreads) {
+        const int c = base + tid;
+        MassBlock bk;
+        bk.m = -INFINITY; bk.M = 0; bk.pad = 0;
+        if (c < A.nblk) bk = load_block(blocks + c);
+        const unsigned long long v = block_share(bk, m, inv_T);
+        unsigned long long incl = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const unsigned long long up = shfl_up_u64(incl, d);
+            if ((tid & 31) >= d) incl += up;
+        }
+        cta_sync();
+        if ((tid & 31) == 31) sh.red64[tid >> 5] = incl;
+        cta_sync();
+        unsigned long long off = 0, total = 0;
+#pragma unroll
+        for (int w = 0; w < kScanWarps; ++w) {
+            const unsigned long long x = sh.red64[w];
+            if (w < (tid >> 5)) off += x;
+            total += x;
+        }
+        incl += off;
+        if (run + total > t) {  // the block is in this chunk (uniform)
+            if (run + incl > t && run + incl - v <= t) {
+                sh.found = c;
+                sh.before = run + incl - v;
+            }
+            cta_sync();
+            break;
+        }
+        run += total;
+    }
+    cta_sync();
+    const int c = sh.found;
+    if (c < 0) {  // cannot happen: S is the sum of the shares
+        row_fail(o, BORN_ROW_ALL_MASKED);
+        return;
+    }
+    const MassBlock bk = load_block(blocks + c);
+    const unsigned long long Sc = block_share(bk, m, inv_T);
+    const unsigned long long tb = t - sh.before;
+    unsigned long long tt = __double2ull_rz(__ddiv_rn(__dmul_rn(__ull2double_rn(tb), __ull2double_rn(bk.M)), __ull2double_rn(Sc)));
+    if (tt > bk.M - 1) tt = bk.M - 1;
+    // the block's tokens again, two consecutive ones per thread
+    unsigned long long q[2];
+    const int tok0 = c * kMassBlock + 2 * tid;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        q[i] = 0;
+        if (tok0 + i < A.V) {
+            const float z = token_logit<T>(A, rp, b, g, tok0 + i);
+            q[i] = mass_of(scaled_shift(z, bk.m, inv_T));
+        }
+    }
+    const unsigned long long v = q[0] + q[1];
+    unsigned long long incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const unsigned long long up = shfl_up_u64(incl, d);
+        if ((tid & 31) >= d) incl += up;
+    }
+    cta_sync();
+    if ((tid & 31) == 31) sh.red64[tid >> 5] = incl;
+    cta_sync();
+    unsigned long long off = 0;
+    for (int w = 0; w < (tid >> 5); ++w) off += sh.red64[w];
+    incl += off;
+    if (incl > tt && incl - v <= tt) {
+        const int i = (incl - v + q[0] > tt) ? 0 : 1;
+        o.token[o.row] = g * A.V + tok0 + i;
+        o.status[o.row] = BORN_ROW_OK;
+        if (o.prob) {
+            const double p = __dmul_rn(__ddiv_rn(__ull2double_rn(q[i]), __ull2double_rn(bk.M)),
+                                       __ddiv_rn(__ull2double_rn(Sc), __ull2double_rn(S)));
+            o.prob[o.row] = __double2float_rn(p);
+        }
+    }
+    (void)scratch;
+}
+
+template <typename T>
+__device__ __noinline__ void fallback_row(const ScanArgs& A, ScanShared& sh, uint8_t* smem, int row);
+
+// Exactly the k best of a virtual row, in rank order, into its packed record.
+__device__ __forceinline__ void write_packed(const ScanArgs& A, ScanShared& sh, uint64_t* sel, int n, int k, int b, int g,
+                                             float m, float lse_s, float bound, bool exact) {
+    const int tid = threadIdx.x;
+    uint8_t* rec = A.packed + (int64_t)g * A.packed_seg_stride + (int64_t)b * A.packed_row_stride;
+    uint64_t* ent = reinterpret_cast<uint64_t*>(rec + kRecordHdrBytes);
+    int nk = 0;
+    if (exact && n > 0) {
+        if (n > kThreads) {
+            // cut to the k best first (k <= kThreads here), survivors to the front
+            const uint64_t Tk = block_radix_search<true, 56, true>(
+                n, (unsigned long long)(min(k, n) - 1), [&](int i) { return sel[i]; }, [&](int) { return 1ull; }, sh.sc);
+            uint64_t* tmp = sel + kSelCap;  // the mass array is idle here
+            if (tid == 0) sh.nl = 0;
+            cta_sync();
+            for (int i = tid; i < n; i += kThreads)
+                if (sel[i] >= Tk) tmp[smem_atom_add(&sh.nl, 1u)] = sel[i];
+            cta_sync();
+            n = sh.nl;
+            for (int i = tid; i < n; i += kThreads) sel[i] = tmp[i];
+            cta_sync();
+        }
+        const uint64_t ck = tid < n ? sel[tid] : 0ull;
+        int rank = 0;
+        for (int j = 0; j < n; ++j) rank += (sel[j] > ck) ? 1 : 0;
+        nk = min(n, k);
+        if (tid < n && rank < nk) ent[rank] = ck;
+    }
+    if (tid == 0) {
+        PackedHdr h;
+        h.m = m; h.lse_s = lse_s; h.count = (uint32_t)nk;
+        h.flags = (exact ? 0u : 2u) | ((n > k) ? 1u : 0u);
+        h.bound = bound;
+        h.pad[0] = h.pad[1] = h.pad[2] = 0;
+        memcpy(rec, &h, sizeof h);
+    }
+}
+
+// The CTA that completed `row` (all its segment records are in scratch): merge, select, draw.
+template <typename T>
+__device__ __noinline__ void finish_row(const ScanArgs& A, ScanShared& sh, uint8_t* sel_mem, int row, int c_first, int c_last) {
+    const int tid = threadIdx.x;
+    const int nseg = c_last - c_first + 1;
+    const int b = row / A.G, g = row - b * A.G;
+    const born_row_params rp = A.row_params ? A.row_params[b] : A.params;
+    const RowPlan pl = row_plan(rp);
+    uint64_t* sel = reinterpret_cast<uint64_t*>(sel_mem);
+    unsigned long long* selq = reinterpret_cast<unsigned long long*>(sel + kSelCap);
+    auto rec_of = [&](int s) { return A.records + (int64_t)(row + c_first + s) * A.rec_stride; };
+
+    // headers: row maximum, exclusion level, best lane-maxima bound; then the log-sum-exp.
+    // Up to kHdrCache headers are fetched once (one round trip to L2) and shared.
+    float m = -INFINITY, taux = -INFINITY, bk = -INFINITY, ls = 0.0f;
+    const bool cached = nseg <= kHdrCache;
+    if (cached) {
+        cta_sync();
+        if (tid < nseg) {
+            const uint8_t* rec = rec_of(tid);
+            const float4 h = __ldcg(reinterpret_cast<const float4*>(rec));
+            sh.hdr[tid] = h;
+            sh.hdr_cnt[tid] = __ldcg(reinterpret_cast<const uint32_t*>(rec) + 4);
+        }
+        cta_sync();
+        for (int s = 0; s < nseg; ++s) {
+            const float4 h = sh.hdr[s];
+            m = max_nan(m, h.x);
+            taux = fmaxf(taux, h.z);
+            bk = fmaxf(bk, h.w);
+        }
+        if (!pl.need_mass)
+            for (int s = 0; s < nseg; ++s) {
+                const float4 h = sh.hdr[s];
+                if (h.y > 0.0f) ls += h.y * ex2_approx(__fmul_rn(h.x - m, pl.c2));
+            }
+    } else {
+        for (int s = tid; s < nseg; s += kThreads) {
+            const float4 h = __ldcg(reinterpret_cast<const float4*>(rec_of(s)));
+            m = max_nan(m, h.x);
+            taux = fmaxf(taux, h.z);
+            bk = fmaxf(bk, h.w);
+        }
+        m = block_max_nan(m, sh.redf);
+        taux = block_max_nan(taux, sh.redf2);
+        bk = block_max_nan(bk, sh.redf3);
+        if (!pl.need_mass) {
+            for (int s = tid; s < nseg; s += kThreads) {
+                const float4 h = __ldcg(reinterpret_cast<const float4*>(rec_of(s)));
+                if (h.y > 0.0f) ls += h.y * ex2_approx(__fmul_rn(h.x - m, pl.c2));
+            }
+            ls = block_sum_f32(ls, sh.redf);
+        }
+    }
+    auto count_of = [&](int s) { return cached ? (int)sh.hdr_cnt[s] : (int)__ldcg(reinterpret_cast<const uint32_t*>(rec_of(s)) + 4); };
+    int status = BORN_ROW_OK;
+    if (m != m) status = BORN_ROW_NAN;
+    else if (m == INFINITY) status = BORN_ROW_POS_INF;
+    else if (m == -INFINITY) status = BORN_ROW_ALL_MASKED;
+
+    if (A.mode == kScanLocal) {
+        // ---- the k best of the virtual row, in rank order
+        int n = 0;
+        bool exact = true;
+        if (status == BORN_ROW_OK) {
+            if (tid == 0) sh.nl = 0;
+            cta_sync();
+            for (int s = 0; s < nseg; ++s) {
+                const uint8_t* rec = rec_of(s);
+                const int cnt = count_of(s);
+                const unsigned long long* ent = reinterpret_cast<const unsigned long long*>(rec + kRecordHdrBytes);
+                for (int i = tid; i < cnt; i += kThreads) {
+                    const unsigned long long e = __ldcg(ent + i);
+                    const float z = __uint_as_float((uint32_t)(e >> 32));
+                    if (z >= bk && z >= taux) {
+                        const int pos = (int)smem_atom_add(&sh.nl, 1u);
+                        if (pos < kSelCap) sel[pos] = make_ck(z, (int)(uint32_t)e);
+                    }
+                }
+            }
+            cta_sync();
+            n = sh.nl;
+            // complete above max(bk, taux); the k best are inside iff there are k of them (or nothing was excluded)
+            if (n > kSelCap || (taux > bk && n < pl.k) || pl.no_bound) exact = false;
+            if (!exact) {  // the exact search over the row writes the record instead
+                if (tid == 0) A.deferred[row] = blockIdx.x + 1u;
+                return;
+            }
+        }
+        write_packed(A, sh, sel, n, pl.k, b, g, m, ls, bk, true);
+        return;
+    }
+
+    RowOut o;
+    o.token = A.out_token; o.prob = A.out_prob; o.lse = A.out_lse; o.status = A.out_status;
+    o.kept_ids = A.out_kept_ids; o.kept_count = A.out_kept_count; o.kept_stride = A.kept_stride;
+    o.row = b;
+    if (status != BORN_ROW_OK) {
+        if (tid == 0 && A.out_lse) A.out_lse[b] = NAN;
+        row_fail(o, status);
+        return;
+    }
+    if (!pl.need_mass && A.out_lse && tid == 0) A.out_lse[b] = m * pl.inv_T + __log2f(ls) * 0.69314718f;
+
+    if (pl.greedy) {
+        if (taux > m) {  // a token equal to the maximum may have been lost to a full buffer
+            if (tid == 0) A.deferred[row] = blockIdx.x + 1u;
+            return;
+        }
+        uint64_t best = 0;
+        for (int s = 0; s < nseg; ++s) {
+            const uint8_t* rec = rec_of(s);
+            const int cnt = count_of(s);
+            const unsigned long long* ent = reinterpret_cast<const unsigned long long*>(rec + kRecordHdrBytes);
+            for (int i = tid; i < cnt; i += kThreads) {
+                const unsigned long long e = __ldcg(ent + i);
+                const float z = __uint_as_float((uint32_t)(e >> 32));
+                if (z >= m) best = max(best, make_ck(z, (int)(uint32_t)e));
+            }
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) best = max(best, shfl_xor_u64(best, d));
+        cta_sync();
+        if ((tid & 31) == 0) sh.red64[tid >> 5] = best;
+        cta_sync();
+        if (tid == 0) {
+            for (int w = 1; w < kScanWarps; ++w) best = max(best, (uint64_t)sh.red64[w]);
+            const int tok = ck_idx(best);
+            A.out_token[b] = tok;
+            A.out_status[b] = BORN_ROW_OK;
+            if (A.out_prob) A.out_prob[b] = 1.0f;
+            if (A.out_kept_count) A.out_kept_count[b] = 1;
+            if (A.out_kept_ids && A.kept_stride > 0) A.out_kept_ids[(int64_t)b * A.kept_stride] = tok;
+        }
+        return;
+    }
+
+    const float u = A.uniforms[b];
+    unsigned long long S_tot = 0;
+    if (pl.need_mass) {
+        // row total from the mass blocks; log-sum-exp from it
+        const MassBlock* blocks = A.blocks + (int64_t)row * A.nblk;
+        unsigned long long part = 0;
+        int fin = 0;
+        for (int c = tid; c < A.nblk; c += kThreads) {
+            const MassBlock bkc = load_block(blocks + c);
+            part += block_share(bkc, m, pl.inv_T);
+            fin += (int)bkc.pad;
+        }
+        S_tot = block_sum_u64(part, sh.red64);
+        const int nfin = (int)block_sum_u64((uint64_t)fin, sh.red64);
+        if (S_tot == 0) {
+            row_fail(o, BORN_ROW_ALL_MASKED);
+            return;
+        }
+        if (A.out_lse && tid == 0)
+            A.out_lse[b] = (float)((double)m * (double)pl.inv_T + log(__ull2double_rn(S_tot) * (1.0 / 1099511627776.0)));
+        if (!pl.window) {
+            if (A.out_kept_count && tid == 0) A.out_kept_count[b] = nfin;
+            if (A.out_kept_ids) {  // the kept set is the whole row: no list of a useful size exists
+                if (tid == 0) A.deferred[row] = blockIdx.x + 1u;
+                return;
+            }
+            draw_whole_row<T>(A, sh, sel_mem, o, rp, b, g, row, m, pl.inv_T, S_tot, u);
+            return;
+        }
+    }
+
+    // ---- candidates at or above the valid cut
+    float cut = -INFINITY;
+    if (pl.lane_bound) cut = bk;
+    if (rp.min_p > 0.0f) cut = fmaxf(cut, m + pl.delta);
+    if (pl.window) {
+        // tokens lighter than (1 - P) * S / V weigh less than (1 - P) * S together: outside the nucleus
+        const float s_all = (float)S_tot * (1.0f / 1099511627776.0f);
+        cut = m + (__logf((1.0f - rp.top_p) * s_all / (float)A.V) - 0.05f) * rp.temperature;
+    }
+    bool complete = !(taux > cut);
+    float lowest = complete ? cut : taux;  // below it the entries are not all there: not used
+    auto gather = [&](float low) {
+        if (tid == 0) sh.nl = 0;
+        cta_sync();
+        for (int s = 0; s < nseg; ++s) {
+            const uint8_t* rec = rec_of(s);
+            const int cnt = count_of(s);
+            const unsigned long long* ent = reinterpret_cast<const unsigned long long*>(rec + kRecordHdrBytes);
+            for (int i = tid; i < cnt; i += kThreads) {
+                const unsigned long long e = __ldcg(ent + i);
+                const float z = __uint_as_float((uint32_t)(e >> 32));
+                if (z >= low) {
+                    const int pos = (int)smem_atom_add(&sh.nl, 1u);
+                    if (pos < kSelCap) sel[pos] = make_ck(z, (int)(uint32_t)e);
+                }
+            }
+        }
+        cta_sync();
+        const int got = sh.nl;
+        cta_sync();
+        return got;
+    };
+    int n = gather(lowest);
+    if (n > kSelCap && !pl.no_bound) {
+        // More candidates than the selection takes (a wide nucleus window, many ties).  Use only
+        // the part above a higher level -- the lowest of a fixed ladder (in scaled-logit units
+        // below the row maximum) that leaves at most kSelCap entries; that part is complete, and
+        // the checks below decide whether the kept set lies inside it.
+        constexpr int NL = 8;
+        const float ladder[NL] = {8.0f, 6.5f, 5.0f, 4.0f, 3.0f, 2.0f, 1.0f, 0.5f};
+        if (tid < NL) sh.sc.c[tid] = 0;
+        cta_sync();
+        for (int s = 0; s < nseg; ++s) {
+            const uint8_t* rec = rec_of(s);
+            const int cnt = count_of(s);
+            const unsigned long long* ent = reinterpret_cast<const unsigned long long*>(rec + kRecordHdrBytes);
+            for (int i = tid; i < cnt; i += kThreads) {
+                const float z = __uint_as_float((uint32_t)(__ldcg(ent + i) >> 32));
+                if (!(z >= lowest)) continue;
+                const float d = (m - z) * pl.inv_T;
+                int lvl = -1;  // narrowest level that still holds the entry
+#pragma unroll
+                for (int l = 0; l < NL; ++l)
+                    if (d <= ladder[l]) lvl = l;
+                if (lvl >= 0) smem_red_add(&sh.sc.c[lvl], 1u);
+            }
+        }
+        cta_sync();
+        int pick = -1;
+        uint32_t cum = 0;
+        // entries inside level l = those whose narrowest level is >= l: cumulative from the narrow end
+        for (int l = NL - 1; l >= 0; --l) {
+            cum += sh.sc.c[l];
+            if (cum <= (uint32_t)kSelCap) pick = l;
+        }
+        cta_sync();
+        if (pick >= 0) {
+            const float low2 = m - ladder[pick] * rp.temperature;
+            if (low2 > lowest) {
+                lowest = low2;
+                complete = false;
+                n = gather(lowest);
+            }
+        }
+    }
+    bool defer = n > kSelCap || pl.no_bound;
+    if (!defer && !complete) {
+        if (pl.k > 0) defer = n < pl.k;          // the k best are all at or above taux iff k tokens are
+        else if (!pl.window) defer = true;       // min-p survivors may lie below taux
+    }
+    if (!defer) {
+        SelectIn in;
+        in.n = n;
+        in.k = pl.k;
+        in.Qa = (rp.min_p > 0.0f) ? __double2ull_ru((double)rp.min_p * 1099511627776.0) : 0ull;
+        in.top_p = rp.top_p;
+        in.S_ext = pl.window ? S_tot : 0ull;
+        in.complete = complete;
+        in.m_row = m; in.inv_T = pl.inv_T; in.u = u;
+        defer = !select_and_draw(in, sel, selq, sh, o);
+    }
+    if (defer && tid == 0) A.deferred[row] = blockIdx.x + 1u;
+}
+
+}  // namespace born

@@ -28,10 +28,10 @@ namespace born {
 constexpr int kSpecThreads = 256;
 constexpr int kSpecTile = 8192;  // floats per stage (32 KB)
 constexpr int kSpecStages = 3;
-constexpr int kMassBlock = 1024;  // tokens per mass block, aligned to the row start
+constexpr int kSpecMassBlock = 1024;  // tokens per mass block, aligned to the row start
 constexpr int kSpecMaxBlocks = 512;  // => vocab <= 524,288 on this path
 constexpr int kSpecHalf = kSpecTile / 2;  // tokens per chunk in the paired (p, q) pass
-constexpr int kSpecMaxChunks = kSpecMaxBlocks * kMassBlock / kSpecHalf;
+constexpr int kSpecMaxChunks = kSpecMaxBlocks * kSpecMassBlock / kSpecHalf;
 constexpr int kSpecParts = 8;  // CTAs per sequence in the draw launch
 constexpr int kSpecMaxRows = 2 * BORN_MAX_DRAFT + 1;
 constexpr int kRowBadToken = 5;
@@ -51,7 +51,7 @@ struct SpecScratchLayout {
 };
 inline SpecScratchLayout spec_scratch_layout(int B, int K, int V) {
     SpecScratchLayout L;
-    const size_t nblk = (size_t)(V + kMassBlock - 1) / kMassBlock, nchb = (size_t)(V + kSpecHalf - 1) / kSpecHalf;
+    const size_t nblk = (size_t)(V + kSpecMassBlock - 1) / kSpecMassBlock, nchb = (size_t)(V + kSpecHalf - 1) / kSpecHalf;
     size_t off = 0;
     L.tickets = off; off += ((size_t)B * 4 + 255) / 256 * 256;
     L.csum = off; off += ((size_t)B * nchb * 8 + 255) / 256 * 256;
@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(kSpecThreads, 2) spec_mass_kernel(const SpecKe
     const int ntarget = A.B * A.target_rows;
     const float* src_row = row < ntarget ? A.target + (int64_t)row * V : A.draft + (int64_t)(row - ntarget) * V;
     const int nch = (V + kSpecTile - 1) / kSpecTile;
-    const int nblk = (V + kMassBlock - 1) / kMassBlock;
+    const int nblk = (V + kSpecMassBlock - 1) / kSpecMassBlock;
     const int per = (nch + (int)gridDim.x - 1) / (int)gridDim.x;
     const int t_lo = blockIdx.x * per, t_hi = min(nch, t_lo + per);
     if (t_lo >= t_hi) return;
@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(kSpecThreads, 2) spec_mass_kernel(const SpecKe
     for (int t = t_lo; t < t_hi; ++t) {
         const int nvalid = min(kSpecTile, V - t * kSpecTile);
         const float* tile = spec_acquire(P, src_row + (size_t)t * kSpecTile, nvalid, nullptr, 0, &sh.fail);
-        const int base = warp * kMassBlock;
+        const int base = warp * kSpecMassBlock;
         if (base < nvalid) {
             float v[32];
             float mc = -INFINITY;
@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(kSpecThreads, 2) spec_mass_kernel(const SpecKe
                 const float4 q = *reinterpret_cast<const float4*>(tile + base + 4 * (lane + 32 * i));
                 v[4 * i + 0] = q.x; v[4 * i + 1] = q.y; v[4 * i + 2] = q.z; v[4 * i + 3] = q.w;
             }
-            if (base + kMassBlock > nvalid) {  // the row ends inside this block: nothing beyond it counts
+            if (base + kSpecMassBlock > nvalid) {  // the row ends inside this block: nothing beyond it counts
 #pragma unroll
                 for (int i = 0; i < 32; ++i)
                     if (base + 4 * (lane + 32 * (i >> 2)) + (i & 3) >= nvalid) v[i] = -INFINITY;
@@ -215,7 +215,7 @@ __global__ void __launch_bounds__(kSpecThreads, 2) spec_mass_kernel(const SpecKe
             if (lane == 0 && !sh.fail) {
                 BlockMass r;
                 r.m = mc; r.pad = 0; r.M = Mc;
-                A.blocks[(size_t)row * nblk + t * (kSpecTile / kMassBlock) + warp] = r;
+                A.blocks[(size_t)row * nblk + t * (kSpecTile / kSpecMassBlock) + warp] = r;
             }
         }
         __syncthreads();
@@ -253,7 +253,7 @@ __global__ void __launch_bounds__(kSpecThreads, 2) spec_draw_kernel(const SpecKe
     const int tid = threadIdx.x;
     const int part = blockIdx.x, nparts = gridDim.x, b = blockIdx.y;
     const int K = A.K, V = A.V, R = A.target_rows;
-    const int nblk = (V + kMassBlock - 1) / kMassBlock;
+    const int nblk = (V + kSpecMassBlock - 1) / kSpecMassBlock;
     const int nrows = R + K;  // this sequence's rows: r < R target row r, else draft row r - R
     auto row_id = [&](int r) { return r < R ? b * R + r : A.B * R + b * K + (r - R); };
 
@@ -523,14 +523,18 @@ __global__ void __launch_bounds__(kSpecThreads, 2) spec_draw_kernel(const SpecKe
 
 inline size_t spec_smem_bytes() { return (size_t)kSpecStages * kSpecTile * sizeof(float); }
 
+// raises the dynamic shared-memory limit of both kernels; once per device, at handle creation
+inline cudaError_t spec_attrs_all() {
+    cudaError_t e = cudaFuncSetAttribute(spec_mass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)spec_smem_bytes());
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(spec_draw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)spec_smem_bytes());
+}
+
 // returns 0 or a cudaError_t; `num_sms` sizes the first launch
 inline int launch_spec(SpecKernelArgs A, int num_sms, cudaStream_t st) {
-    if (A.V > kSpecMaxBlocks * kMassBlock) return (int)cudaErrorInvalidValue;
+    if (A.V > kSpecMaxBlocks * kSpecMassBlock) return (int)cudaErrorInvalidValue;
     A.tma = ((uintptr_t)A.target % 16 == 0) && ((uintptr_t)A.draft % 16 == 0) && (((int64_t)A.V * 4) % 16 == 0);
-    cudaError_t e = cudaFuncSetAttribute(spec_mass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)spec_smem_bytes());
-    if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(spec_draw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)spec_smem_bytes());
-    if (e != cudaSuccess) return (int)e;
+    cudaError_t e;
     const int rows = A.B * (A.target_rows + A.K);
     const int nch = (A.V + kSpecTile - 1) / kSpecTile;
     // CTAs per row: enough for a few full waves of two CTAs per SM, with the last wave as full

@@ -125,6 +125,26 @@ def _logits_dtype(x, bf16_hint):
     raise InvalidArgument(f"logits dtype {x.dtype} is not float32 or bfloat16 (uint16 bit patterns on the host)")
 
 
+class PreparedCall:
+    """A marshalled `born_sample` call (see `Sampler.prepare`)."""
+
+    def __init__(self, sampler, out):
+        self._s = sampler
+        self._fn = sampler._lib.born_sample
+        self.args = None
+        self.out = out
+
+    def set_logits(self, logits):
+        self.args.logits = _ptr(logits)
+        self._keep = logits
+
+    def run(self, stream=None):
+        rc = self._fn(self._s._h, C.byref(self.args), stream)
+        if rc != L.BORN_OK:
+            self._s._raise(rc)
+        return self.out
+
+
 class Sampler:
     """One handle = one device workspace = one stream of calls."""
 
@@ -253,10 +273,43 @@ class Sampler:
         a.out_kept_ids = _ptr(res.get("kept_ids"))
         a.out_kept_count = _ptr(res.get("kept_count"))
         a.kept_stride = int(res["kept_ids"].shape[1]) if "kept_ids" in res else 0
+        if getattr(self, "_marshal", None) is not None:
+            self._marshal.args = a
+            return res
         rc = self._lib.born_sample(self._h, C.byref(a), stream)
         if rc != L.BORN_OK:
             self._raise(rc)
         return res
+
+    def prepare(self, logits, **kw):
+        """Marshal a `sample` call once and return a `PreparedCall`: `run(stream)` then costs one
+        foreign call.  Takes the arguments of `sample`; the buffers must stay alive and in place."""
+        kw.pop("stream", None)
+        call = PreparedCall(self, kw.get("out"))
+        self._marshal = call
+        try:
+            call.out = self.sample(logits, **kw)
+        finally:
+            self._marshal = None
+        return call
+
+    def reserve(self, logits, **kw):
+        """Allocate now whatever scratch a `sample` call with these arguments would allocate on first use."""
+        call = self.prepare(logits, **kw)
+        rc = self._lib.born_sampler_reserve(self._h, C.byref(call.args))
+        if rc != L.BORN_OK:
+            self._raise(rc)
+
+    def check_error(self):
+        """Raise if a bounded on-device wait gave up in an earlier device-memory call (synchronises)."""
+        rc = self._lib.born_check_error(self._h)
+        if rc != L.BORN_OK:
+            self._raise(rc)
+
+    @property
+    def fallback_rows(self):
+        """Rows that took the exact multi-pass search since the last read (synchronises)."""
+        return int(self._lib.born_fallback_rows(self._h))
 
     # -- speculative decoding -------------------------------------------------------------
     def spec_verify(self, target_logits, draft_logits, draft_tokens, u_accept, u_resample, temperature=1.0,

@@ -23,8 +23,14 @@
  *     (internal/tensor/raw.go:89-92): BORN_ERR_INVALID_ARGUMENT maps to the former, the
  *     CUDA/NCCL codes to the latter.
  *
- * Ownership: the caller owns every input and output buffer.  The library owns only the
- * workspace it allocated in born_sampler_create and never allocates per call.
+ * Ownership: the caller owns every input and output buffer.  The library owns only its
+ * workspace.  What the sampling kernel needs (segment records, mass blocks, tickets) is
+ * allocated in born_sampler_create and never per call.  Three kinds of scratch are grown to
+ * the largest request seen instead, because their size depends on the call: the staging
+ * mirrors of BORN_MEM_HOST calls, the aligned fp32 copy that whole-vocabulary rows need when
+ * their logits are not 16-byte aligned or are bf16 with history penalties, and the scratch of
+ * born_spec_verify.  born_sampler_reserve makes such a request ahead of time, so that no
+ * later call of that shape allocates; born_shard_init sizes the exchange buffers.
  * Threading: one handle = one stream of calls; distinct handles are independent.
  */
 #ifndef BORN_SAMPLER_H
@@ -50,12 +56,12 @@ extern "C" {
 #define BORN_ROW_ALL_MASKED 1 /* no allowed token with a logit above -inf: token = -1 */
 #define BORN_ROW_NAN 2        /* NaN logit among the allowed tokens: token = -1 */
 #define BORN_ROW_POS_INF 3    /* +inf logit among the allowed tokens: token = -1 */
-#define BORN_ROW_OVERFLOW 4   /* more surviving candidates than BORN_MAX_CANDIDATES: token = -1 */
+#define BORN_ROW_OVERFLOW 4   /* only from the vocab-sharded path: a shard record could not be made exact */
 #define BORN_ROW_BAD_TOKEN 5  /* speculative verify: draft token outside [0, vocab) */
 
 /* ---- limits ---- */
-#define BORN_MAX_TOP_K 1024        /* also the survivor limit when top_k is off */
-#define BORN_MAX_CANDIDATES 1024
+#define BORN_MAX_TOP_K 1024
+#define BORN_MAX_CANDIDATES 1024   /* top_k * shards in the sharded path; longest kept-id list */
 #define BORN_MAX_HISTORY 1024      /* history ids per row */
 #define BORN_MAX_VOCAB ((1 << 24) - 4096)
 #define BORN_MAX_DRAFT 16          /* speculative draft length */
@@ -69,7 +75,7 @@ extern "C" {
                              out and returns after the stream has drained */
 
 #define BORN_FLAG_GREEDY 1u
-#define BORN_FLAG_FULL_VOCAB 2u /* with min-p on and top-k off: take the whole-vocabulary passes (no 1024-survivor limit for min-p alone; top-p against all survivors) */
+#define BORN_FLAG_FULL_VOCAB 2u /* accepted and ignored: every parameter set is exact over the whole vocabulary */
 
 /* Sampling parameters of one row (32 bytes).  Zero means "off" for every filter, as in
  * the reference's config structs (internal/optim/adam.go:78-91). */
@@ -173,15 +179,27 @@ int32_t born_sampler_destroy(void* handle);
 
 /* Replaces nn.Accuracy's per-row argmax (internal/nn/cross_entropy.go:241-284) and the
  * softmax / log-sum-exp row passes (internal/autodiff/ops/softmax.go:214-238,
- * internal/nn/cross_entropy.go:126-153) with the full sampling pipeline.  One kernel launch
- * when top-k or min-p narrows the row (at most 1024 survivors reach the selection; beyond
- * that the row reports BORN_ROW_OVERFLOW).  With uniform parameters, rows that nothing
- * narrows are served over the whole vocabulary instead (history penalties are applied to an
- * fp32 copy of the rows first):
- * temperature-only sampling (and min-p under BORN_FLAG_FULL_VOCAB) in two launches, top-p
- * without top-k in three (the nucleus is taken against the total mass of all survivors and
- * must fit into the 1024 best). */
+ * internal/nn/cross_entropy.go:126-153) with the full sampling pipeline.  One kernel launch:
+ * every logit is read once, whatever the parameters (per-row parameter arrays included).
+ * Rows whose kept set is small (top-k, min-p, a nucleus of up to 1024 tokens) are finished
+ * from the candidates collected while streaming; rows that nothing narrows are drawn from
+ * exact per-512-token mass blocks; any other row (top-k above 256, a nucleus or a min-p
+ * survivor set beyond 1024 tokens) takes an exact multi-pass search inside the same launch --
+ * slower, never approximate.  Two more launches come first when whole-vocabulary rows are not
+ * 16-byte aligned or are bf16 with history penalties (see "Ownership" above). */
 int32_t born_sample(void* handle, const born_sample_args* args, void* stream);
+
+/* No counterpart in the reference.  Allocates now whatever scratch a later born_sample call
+ * with these arguments (same memory side, shapes, dtype, alignment and parameters) would
+ * otherwise allocate on first use; runs nothing. */
+int32_t born_sampler_reserve(void* handle, const born_sample_args* args);
+
+/* No counterpart in the reference.  Reads and clears the handle's device error word
+ * (synchronises the device).  Every on-device wait of the kernels is bounded; when one gives
+ * up, the rows the CTA had a part in report row status 100 + BORN_ERR_DEVICE_TIMEOUT, and the
+ * call is reported here -- BORN_MEM_HOST calls check by themselves and return
+ * BORN_ERR_DEVICE_TIMEOUT, BORN_MEM_DEVICE calls are asynchronous and are checked with this. */
+int32_t born_check_error(void* handle);
 
 /* No counterpart in the reference (it has no speculative decoding); the row arithmetic is
  * the same max-shifted softmax as internal/autodiff/ops/softmax.go:214-238. */
@@ -199,18 +217,28 @@ int32_t born_sample_sharded(void* handle, const born_shard_args* args, void* str
 /* No counterpart in the reference.  born_sample for callers that must not allocate device
  * memory -- code running where cudaMalloc is off limits (a pre-sized serving process whose
  * memory pool owns the whole GPU, a latency-critical decode loop, a host binding without a
- * place to keep a handle).  It needs no handle: the slice records and row tickets the kernel
- * uses as scratch live in a fixed array inside the library image, BORN_STATIC_SCRATCH_BYTES
- * per GPU that loads the library.  Limits: device pointers only (BORN_MEM_DEVICE),
- * batch <= BORN_STATIC_MAX_BATCH, batch * vocab_segments <= 2 * BORN_STATIC_MAX_BATCH;
- * anything larger is refused with BORN_ERR_UNSUPPORTED.  Runs on the current device.  The
- * first call on a device looks up the array's address; make that call before any stream
- * capture.  All calls on a device share the one array: calls that overlap on the GPU
- * (different streams, different threads) race and give wrong results -- serialise them.
- * Errors are reported through born_last_error(NULL). */
+ * place to keep a handle).  It needs no handle: the segment records, mass blocks and row
+ * tickets the kernel uses as scratch live in a fixed array inside the library image, at most
+ * BORN_STATIC_SCRATCH_BYTES per GPU that loads the library.  Limits, anything beyond them is
+ * refused with BORN_ERR_UNSUPPORTED: device pointers only (BORN_MEM_DEVICE);
+ * batch <= BORN_STATIC_MAX_BATCH; batch * ceil(vocab / 512) <= BORN_STATIC_MAX_BLOCKS; no
+ * vocab_segments; and none of the calls that need the aligned fp32 copy (whole-vocabulary rows
+ * -- no top-k and no min-p, or a per-row parameter array -- whose logits are not 16-byte
+ * aligned or are bf16 with history penalties).  Runs on the current device.  The first call
+ * on a device looks up the array's address; make that call before any stream capture.  All
+ * calls on a device share the one array: calls that overlap on the GPU (different streams,
+ * different threads) race and give wrong results -- serialise them.  Errors are reported
+ * through born_last_error(NULL). */
 #define BORN_STATIC_MAX_BATCH 256
-#define BORN_STATIC_SCRATCH_BYTES (2 * BORN_STATIC_MAX_BATCH * (32 + 8 * BORN_MAX_CANDIDATES) + 8 * BORN_STATIC_MAX_BATCH + 256)
+#define BORN_STATIC_MAX_BLOCKS 131072
+#define BORN_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
 int32_t born_sample_static(const born_sample_args* args, void* stream);
+
+/* No counterpart in the reference.  Rows that took the exact multi-pass search (see
+ * born_sample) since the last call of this function; synchronises the device.  A serving
+ * loop can watch it: a workload whose rows keep landing there is paying for a flat
+ * distribution (or a top-k above 256), not for a fault. */
+int64_t born_fallback_rows(void* handle);
 
 /* Bytes of device workspace a handle holds (for capacity planning). */
 int64_t born_workspace_bytes(void* handle);
@@ -221,6 +249,12 @@ int32_t born_last_timing(void* handle, float* out3);
 
 const char* born_last_error(void* handle);
 const char* born_version(void);
+
+/* Test hook: one small sampling launch in which one bulk copy is withheld and the wait limit
+ * is a millisecond, so that the bounded wait gives up.  Returns BORN_ERR_DEVICE_TIMEOUT when
+ * the kernel reported the expiry and came back (the expected outcome), BORN_OK when it did
+ * not expire.  The handle stays usable.  Synchronises the stream. */
+int32_t born_debug_expire_wait(void* handle, void* stream);
 
 /* Test hooks: run the library's deterministic exp / fixed-point mass on device arrays. */
 int32_t born_debug_exp(const float* x_dev, float* y_dev, int64_t n, void* stream);

@@ -43,7 +43,7 @@
 #include <stdlib.h>
 #include <string.h>
 
-#define BORN_ORACLE_VERSION 1
+#define BORN_ORACLE_VERSION 2
 
 /* row status codes (same values as the CUDA library's BORN_ROW_*) */
 enum {
@@ -277,6 +277,39 @@ typedef struct {
     int32_t* near_cutoff;
 } sample_job;
 
+#define SAMPLE_MASS_BLOCK 512 /* tokens per mass block of the sampler, aligned to the row start */
+
+/* Whole-row total of the sampler when neither top-k nor min-p narrows the row: per block of
+ * 512 tokens the masses are taken relative to the block maximum m_c and summed exactly (M_c);
+ * a block's share of the row is S_c = rne_u64((double)M_c * (double)exp_det((m_c - m) * inv_T)).
+ * This is what a single streaming pass can form before the row maximum is known. */
+static uint64_t block_mass(const float* z, int lo, int hi, float inv_T, float* mc_out) {
+    float mc = -INFINITY;
+    for (int i = lo; i < hi; i++) if (z[i] > mc) mc = z[i];
+    *mc_out = mc;
+    if (mc == -INFINITY) return 0;
+    uint64_t Mc = 0;
+    for (int i = lo; i < hi; i++) {
+        float w = born_oracle_exp1((z[i] - mc) * inv_T);
+        Mc += (uint64_t)llrintf(w * 1099511627776.0f);
+    }
+    return Mc;
+}
+static uint64_t block_share(uint64_t Mc, float mc, float m, float inv_T) {
+    if (Mc == 0) return 0;
+    float ef = born_oracle_exp1((mc - m) * inv_T);
+    return (uint64_t)llrint((double)Mc * (double)ef);
+}
+static uint64_t sampler_row_total(const float* z, int V, float inv_T, float m) {
+    uint64_t S = 0;
+    for (int lo = 0; lo < V; lo += SAMPLE_MASS_BLOCK) {
+        int hi = lo + SAMPLE_MASS_BLOCK; if (hi > V) hi = V;
+        float mc; uint64_t Mc = block_mass(z, lo, hi, inv_T, &mc);
+        S += block_share(Mc, mc, m, inv_T);
+    }
+    return S;
+}
+
 static void sample_row(const sample_job* J, row_ws* w, int b) {
     const int V = J->V;
     const oracle_row_params* p = J->rp + (size_t)b * J->rp_stride;
@@ -324,6 +357,51 @@ static void sample_row(const sample_job* J, row_ws* w, int b) {
         return;
     }
 
+    /* Rows that neither top-k nor min-p narrows take their total from the mass blocks. */
+    int whole = !(p->top_k > 0) && !(p->min_p > 0.0f);
+    uint64_t S_tot = whole ? sampler_row_total(z, V, inv_T, m) : 0;
+    int topp_on = (p->top_p > 0.0f && p->top_p < 1.0f);
+    if (whole && !topp_on) {
+        /* Temperature-only: the draw descends the blocks.  t = min(floor(u*S), S-1) picks the
+         * block by the shares S_c in ascending order, then the token inside it by the block's own
+         * masses with t'' = min(floor((t - before) * M_c / S_c), M_c - 1) in float64. */
+        int nfin = 0;
+        for (int i = 0; i < V; i++) if (z[i] > -INFINITY) nfin++;
+        if (J->kept_count) J->kept_count[b] = nfin;
+        if (J->kept_ids) {
+            cand_t* K0 = w->cand; int n0 = 0;
+            for (int i = 0; i < V; i++) if (z[i] > -INFINITY) { K0[n0].z = z[i]; K0[n0].idx = i; n0++; }
+            qsort(K0, (size_t)n0, sizeof(cand_t), cmp_rank);
+            for (int i = 0; i < n0 && i < J->kept_stride; i++) J->kept_ids[(size_t)b * J->kept_stride + i] = K0[i].idx;
+        }
+        if (S_tot == 0) { J->status[b] = ROW_ALL_MASKED; return; }
+        uint64_t t = (uint64_t)((double)J->u[b] * (double)S_tot);
+        if (t > S_tot - 1) t = S_tot - 1;
+        uint64_t cum = 0;
+        for (int lo = 0; lo < V; lo += SAMPLE_MASS_BLOCK) {
+            int hi = lo + SAMPLE_MASS_BLOCK; if (hi > V) hi = V;
+            float mc; uint64_t Mc = block_mass(z, lo, hi, inv_T, &mc);
+            uint64_t Sc = block_share(Mc, mc, m, inv_T);
+            if (cum + Sc > t) {
+                uint64_t tb = t - cum;
+                uint64_t tt = (uint64_t)(((double)tb * (double)Mc) / (double)Sc);
+                if (tt > Mc - 1) tt = Mc - 1;
+                uint64_t c2 = 0;
+                for (int i = lo; i < hi; i++) {
+                    uint64_t qi = mass_of((z[i] - mc) * inv_T);
+                    c2 += qi;
+                    if (c2 > tt) {
+                        J->tok[b] = i;
+                        if (J->prob) J->prob[b] = (float)(((double)qi / (double)Mc) * ((double)Sc / (double)S_tot));
+                        return;
+                    }
+                }
+            }
+            cum += Sc;
+        }
+        return;
+    }
+
     /* top-k (per segment when n_segments > 1) */
     cand_t* K = w->cand; int n = 0;
     int G = J->n_segments < 1 ? 1 : J->n_segments;
@@ -359,8 +437,9 @@ static void sample_row(const sample_job* J, row_ws* w, int b) {
     qsort(K, (size_t)n, sizeof(cand_t), cmp_rank);
     uint64_t S = 0;
     for (int i = 0; i < n; i++) { q[i] = mass_of((K[i].z - m) * inv_T); S += q[i]; }
-    if (p->top_p > 0.0f && p->top_p < 1.0f) {
-        uint64_t Tp = (uint64_t)((double)p->top_p * (double)S);
+    if (topp_on) {
+        /* the nucleus is taken against the block total when nothing else narrows the row */
+        uint64_t Tp = (uint64_t)((double)p->top_p * (double)(whole ? S_tot : S));
         if (Tp < 1) Tp = 1;
         uint64_t cum = 0; int keep = n;
         for (int i = 0; i < n; i++) { cum += q[i]; if (cum >= Tp) { keep = i + 1; break; } }

@@ -238,23 +238,32 @@ def test_invalid_rows_report_status(sampler, oracle):
     assert got["token"][3] == 169 and list(got["token"][[0, 1, 2, 4]]) == [-1] * 4
 
 
-def test_survivor_limit_without_top_k(sampler, oracle):
-    # top-k off: exact while min-p cuts inside the 1024 best, BORN_ROW_OVERFLOW otherwise
+def test_rows_beyond_the_candidate_limit_are_exact(sampler, oracle):
+    # top-k off: whatever the number of min-p survivors or the size of the nucleus, the row is
+    # answered exactly (the kernel falls to its multi-pass search over the row); nothing reports
+    # BORN_ROW_OVERFLOW
     B, V = 4, 30000
     z = (W.normal(6, 1, B * V) * 3.0).astype(np.float32).reshape(B, V)
     u = W.uniform_f32(6, 2, B)
     got, ref = run_both(sampler, oracle, z, dict(temperature=0.7, min_p=0.05, top_p=0.9), u, want_kept=1024)
     assert_parity(got, ref)
-    flat = np.zeros((2, V), dtype=np.float32)
-    torch = torch_mod()
-    from born_b200 import SamplingConfig
-    out = sampler.sample(to_dev(flat), uniforms=to_dev(u[:2]), config=SamplingConfig(temperature=1.0, top_p=0.9))
-    torch.cuda.synchronize()
-    assert out["status"].cpu().tolist() == [4, 4] and out["token"].cpu().tolist() == [-1, -1]
-    small = (W.normal(6, 3, 2 * 900) * 2).astype(np.float32).reshape(2, 900)  # fits: exact without filters
+    flat = np.zeros((2, V), dtype=np.float32)  # an all-zeros row: the nucleus is 90 % of the vocabulary
+    for p in (dict(temperature=1.0, top_p=0.9), dict(temperature=1.0, min_p=0.5), dict(temperature=2.0, min_p=1e-4, top_p=0.5),
+              dict(temperature=1.0, top_k=1000), dict(temperature=1.0)):
+        got, ref = run_both(sampler, oracle, flat, p, u[:2], want_kept=64)
+        assert_parity(got, ref)
+    n0 = sampler.fallback_rows
+    for T in (1.2, 1.6, 2.0):  # flat distributions: thousands of min-p survivors / nucleus tokens
+        for p in (dict(temperature=T, top_p=0.9), dict(temperature=T, min_p=0.001), dict(temperature=T, min_p=0.002, top_p=0.95)):
+            got, ref = run_both(sampler, oracle, z, p, u, want_kept=1024)
+            assert (ref["kept_count"] > 1024).any(), (T, p)
+            assert_parity(got, ref)
+    assert sampler.fallback_rows > 0  # these rows did take the exact search
+    small = (W.normal(6, 3, 2 * 900) * 2).astype(np.float32).reshape(2, 900)
     for p in (dict(temperature=1.0), dict(temperature=1.0, top_p=0.7)):
         got, ref = run_both(sampler, oracle, small, p, u[:2], want_kept=1024)
         assert_parity(got, ref)
+    assert n0 >= 0
 
 
 def test_lse_within_tolerance_of_float64(sampler, oracle):
@@ -349,22 +358,25 @@ def test_config5_single_gpu_segmented(sampler, oracle):
     assert_parity(got, ref)
 
 
-def test_shard_local_and_merge_equal_segmented_sampling(sampler, oracle):
+@pytest.mark.parametrize("k", [64, 5, 1])
+def test_shard_local_and_merge_equal_segmented_sampling(sampler, oracle, k):
     """The vocab-sharded pipeline on one GPU: G local passes, records concatenated the way an
-    all-gather lays them out, one merge.  Must equal the oracle's segmented sampling."""
+    all-gather lays them out, one merge.  Must equal the oracle's segmented sampling.  An odd k
+    makes every second record start off a 16-byte boundary."""
     torch = torch_mod()
     c = W.config5(seed=1, batch=48, vocab=64000, shards=8)
     G, B = 8, 48
     Vl = 64000 // G
     ld = to_dev(c["logits_bf16"])
-    k = c["params"]["top_k"]
+    params = dict(c["params"], top_k=k)
     gathered = torch.empty((G, B, sampler.record_bytes(k)), dtype=torch.uint8, device="cuda")
     for g in range(G):
         shard = ld[:, g * Vl:(g + 1) * Vl].contiguous()
         sampler.shard_local(shard, g, G, k, temperature=1.0, top_p=0.95, packed=gathered[g])
     out = sampler.shard_merge(gathered, to_dev(c["uniforms"]), Vl, 0, G, k, temperature=1.0, top_p=0.95)
     torch.cuda.synchronize()
-    ref = oracle.sample(c["logits_bf16"], oracle.make_params(**c["params"]), uniforms=c["uniforms"], segments=G)
+    ref = oracle.sample(c["logits_bf16"], oracle.make_params(**params), uniforms=c["uniforms"], segments=G)
+    assert np.array_equal(out["status"].cpu().numpy(), ref["status"])
     assert np.array_equal(out["token"].cpu().numpy(), ref["token"])
     assert np.array_equal(out["prob"].cpu().numpy().view(np.uint32), ref["prob"].view(np.uint32))
     z = W.bf16_bits_to_f32(c["logits_bf16"]).astype(np.float64)
@@ -537,28 +549,22 @@ def run_both_full(sampler, oracle, logits, gpu_params, oracle_params, u, mask):
     return {k: v.cpu().numpy() for k, v in out.items()}, ref
 
 
-def test_top_p_without_top_k_is_taken_against_all_survivors(sampler, oracle):
-    # top-p with top-k off: the nucleus is defined against the total mass of every survivor; the
-    # kernel gets that total from the whole-vocabulary passes and is exact whenever the nucleus
-    # fits into the 1024 best, and says BORN_ROW_OVERFLOW when it does not
+def test_top_p_without_top_k_is_taken_against_the_row_total(sampler, oracle):
+    # top-p with top-k off: the nucleus is defined against the row total (mass blocks); exact on
+    # every row, whether the nucleus fits the candidates collected while streaming or not
     V = 128256
-    for B in (3, 160):  # sliced rows with a record merge, and one CTA per row
+    for B in (3, 160):  # rows cut into many segments, and rows that share CTAs
         z = (W.normal(41, B, B * V) * 3.0).astype(np.float32).reshape(B, V)
         z[0, ::9] = -np.inf
         z[1] = np.round(z[1] * 4) / 4  # ties around the boundary
         u = W.uniform_f32(41, 2, B)
         for p in (dict(temperature=0.7, top_p=0.9), dict(temperature=1.0, top_p=0.5),
                   dict(temperature=0.5, top_p=0.95, min_p=0.001), dict(temperature=1.2, top_p=0.95)):
+            if B == 160 and p["temperature"] > 1.1:
+                continue  # (every row takes the exact search there: covered with B = 3, slow with 160)
             got, ref = run_both(sampler, oracle, z, p, u, want_kept=64)
-            fits = ref["kept_count"] <= 1024
-            if p["temperature"] < 1.1:
-                assert fits.sum() >= B // 2, (B, p, ref["kept_count"][:8])
-            assert np.all(got["status"][~fits] == 4), (B, p)
-            for k in ("status", "token", "kept_count"):
-                assert np.array_equal(got[k][fits], ref[k][fits]), (B, p, k)
-            assert np.array_equal(got["prob"][fits].view(np.uint32), ref["prob"][fits].view(np.uint32)), (B, p)
-            assert np.array_equal(got["kept_ids"][fits], ref["kept_ids"][fits]), (B, p)
-    # bf16 with a mask; and a flat row whose nucleus cannot fit
+            assert_parity(got, ref)
+    # bf16 with a mask; and a flat row whose nucleus is far beyond the candidate limit
     B = 5
     zb = (W.normal(42, 1, B * 151936) * 4.0).astype(np.float32).reshape(B, 151936)
     zb[4] *= 0.05
@@ -568,17 +574,13 @@ def test_top_p_without_top_k_is_taken_against_all_survivors(sampler, oracle):
     mask = np.packbits(bits.reshape(B, words, 32), axis=-1, bitorder="little").view(np.uint32).reshape(B, words)
     got, ref = run_both(sampler, oracle, W.f32_to_bf16_bits(zb).reshape(B, 151936), dict(temperature=0.5, top_p=0.9),
                         W.uniform_f32(42, 5, B), mask=mask, want_kept=64)
-    fits = ref["kept_count"] <= 1024
-    assert fits[:4].all() and not fits[4]
-    assert got["status"][4] == 4
-    for k in ("status", "token", "kept_count"):
-        assert np.array_equal(got[k][fits], ref[k][fits]), k
-    assert np.array_equal(got["kept_ids"][fits], ref["kept_ids"][fits])
+    assert ref["kept_count"][4] > 1024
+    assert_parity(got, ref)
 
 
 def test_whole_vocabulary_routes_with_history_penalties(sampler, oracle):
-    # temperature (+ top-p) with repetition / frequency / presence penalties and no top-k: the
-    # rows are copied with the penalties applied, then take the whole-vocabulary routes
+    # temperature (+ top-p) with repetition / frequency / presence penalties and no top-k: fp32
+    # rows are patched in the streaming tiles, bf16 rows go through the clean fp32 copy first
     B, V = 7, 50257
     z = (W.normal(51, 1, B * V) * 3.0).astype(np.float32).reshape(B, V)
     u = W.uniform_f32(51, 2, B)
@@ -602,8 +604,7 @@ def test_whole_vocabulary_routes_with_history_penalties(sampler, oracle):
                                  history_len=to_dev(hl), want_lse=True, want_kept=want, want_kept_count=True)
             torch.cuda.synchronize()
             got = {k: v.cpu().numpy() for k, v in out.items()}
-            fits = ref["kept_count"] <= 1024 if "top_p" in p else np.ones(B, dtype=bool)
-            assert fits.sum() >= B - 1, (dtype, p, ref["kept_count"])
+            fits = np.ones(B, dtype=bool)
             for k in ("status", "token", "kept_count"):
                 assert np.array_equal(got[k][fits], ref[k][fits]), (dtype, p, k, got[k], ref[k])
             assert np.array_equal(got["prob"][fits].view(np.uint32), ref["prob"][fits].view(np.uint32)), (dtype, p)
@@ -612,10 +613,10 @@ def test_whole_vocabulary_routes_with_history_penalties(sampler, oracle):
             assert np.allclose(got["lse"][fits], ref["lse"][fits], rtol=1e-4, atol=2e-3)
 
 
-def test_which_parameter_sets_take_which_route(sampler):
-    # one launch whenever top-k or min-p narrows the row (the fast path of the benchmark's
-    # default workload must never drift onto the slower routes); two launches for
-    # temperature-only sampling, three for top-p alone, two more when penalties need the copy
+def test_launch_counts(sampler):
+    # one launch for every parameter set; one more (the history dedupe) when a token history is
+    # given; two more instead (the clean fp32 copy and its penalty patch) when whole-vocabulary
+    # rows are bf16 with history penalties, or one more when they are not 16-byte aligned
     from born_b200 import SamplingConfig
     torch = torch_mod()
     B, V = 4, 32000
@@ -623,20 +624,90 @@ def test_which_parameter_sets_take_which_route(sampler):
     u = torch.rand(B, device="cuda").clamp_(max=0.999)
     hist = torch.randint(0, V, (B, 32), device="cuda", dtype=torch.int32)
 
-    def launches(cfg, history=None):
+    def launches(cfg, history=None, logits=z):
         n0 = sampler.launch_count
-        sampler.sample(z, uniforms=u, config=cfg, history=history)
+        sampler.sample(logits, uniforms=u, config=cfg, history=history)
         torch.cuda.synchronize()
         return sampler.launch_count - n0
 
     pen = dict(frequency_penalty=0.5, presence_penalty=0.3)
-    assert launches(SamplingConfig(temperature=0.7, min_p=0.05, top_p=0.9, **pen), hist) == 1
+    assert launches(SamplingConfig(temperature=0.7, min_p=0.05, top_p=0.9, **pen), hist) == 2
     assert launches(SamplingConfig(temperature=0.7, min_p=0.05, top_p=0.9)) == 1
     assert launches(SamplingConfig(temperature=0.7, top_k=50, top_p=0.9)) == 1
     assert launches(SamplingConfig(temperature=0.7, min_p=0.05)) == 1
     assert launches(SamplingConfig(greedy=True)) == 1
-    assert launches(SamplingConfig(temperature=0.7)) == 2
-    assert launches(SamplingConfig(temperature=0.7, min_p=0.05, full_vocab=True)) == 2
-    assert launches(SamplingConfig(temperature=0.7, top_p=0.9)) == 3
-    assert launches(SamplingConfig(temperature=0.7, **pen), hist) == 4
-    assert launches(SamplingConfig(temperature=0.7, top_p=0.9, **pen), hist) == 5
+    assert launches(SamplingConfig(temperature=0.7)) == 1
+    assert launches(SamplingConfig(temperature=0.7, min_p=0.05, full_vocab=True)) == 1
+    assert launches(SamplingConfig(temperature=0.7, top_p=0.9)) == 1
+    assert launches(SamplingConfig(temperature=0.7, **pen), hist) == 2
+    assert launches(SamplingConfig(temperature=0.7, top_p=0.9, **pen), hist) == 2
+    zb = z.to(torch.bfloat16)
+    assert launches(SamplingConfig(temperature=0.7, top_k=50, **pen), hist, zb) == 2
+    assert launches(SamplingConfig(temperature=0.7, **pen), hist, zb) == 3
+    odd = torch.randn((B, V + 1), device="cuda")[:, :V]  # rows of 32001 floats: not 16-byte aligned
+    assert launches(SamplingConfig(temperature=0.7, top_k=50), None, odd) == 1
+    assert launches(SamplingConfig(temperature=0.7), None, odd) == 2
+
+
+def test_bounded_wait_expires_and_the_handle_stays_usable(sampler, oracle, lib):
+    # A kernel wait that cannot be satisfied (the test hook withholds one bulk copy and sets the
+    # limit to a millisecond) must give up, report through the error word and leave the handle in
+    # working order -- no trap, no hang.
+    from born_b200 import _lib as L
+    from born_b200.sampler import SamplerError
+    torch = torch_mod()
+    rc = lib.born_debug_expire_wait(sampler._h, None)
+    assert rc == L.ERR_DEVICE_TIMEOUT, rc
+    assert b"bounded on-device wait" in lib.born_last_error(sampler._h)
+    assert lib.born_check_error(sampler._h) == L.BORN_OK  # reported once, then clear
+    B, V = 6, 50000
+    z = (W.normal(61, 1, B * V) * 3.0).astype(np.float32).reshape(B, V)
+    u = W.uniform_f32(61, 2, B)
+    for p in (dict(temperature=0.8, top_k=40, top_p=0.95), dict(temperature=0.9), dict(greedy=True)):
+        got, ref = run_both(sampler, oracle, z, p, u)
+        assert_parity(got, ref)
+    sampler.check_error()
+    assert SamplerError is not None and torch is not None
+
+
+def test_reserve_leaves_nothing_to_allocate(sampler):
+    from born_b200 import SamplingConfig
+    torch = torch_mod()
+    B, V = 8, 40001
+    zb = torch.randn((B, V), device="cuda").to(torch.bfloat16)
+    u = torch.rand(B, device="cuda").clamp_(max=0.999)
+    hist = torch.randint(0, V, (B, 16), device="cuda", dtype=torch.int32)
+    cfg = SamplingConfig(temperature=0.9, repetition_penalty=1.2)  # whole-vocabulary bf16 rows with penalties: clean copy
+    sampler.reserve(zb, uniforms=u, config=cfg, history=hist)
+    w0 = sampler.workspace_bytes
+    free0 = torch.cuda.mem_get_info()[0]
+    for _ in range(3):
+        sampler.sample(zb, uniforms=u, config=cfg, history=hist)
+    torch.cuda.synchronize()
+    assert sampler.workspace_bytes == w0
+    assert torch.cuda.mem_get_info()[0] == free0
+
+
+FULL_SIZE_SETTINGS = [
+    ("default", dict(temperature=0.7, min_p=0.05, top_p=0.9, frequency_penalty=0.5, presence_penalty=0.3), 512),
+    ("topk_topp", dict(temperature=0.7, top_k=50, top_p=0.9), 0),
+    ("temperature_only", dict(temperature=0.8), 0),
+    ("top_p_only", dict(temperature=0.7, top_p=0.9), 0),
+]
+
+
+@pytest.mark.parametrize("label,params,H", FULL_SIZE_SETTINGS, ids=[x[0] for x in FULL_SIZE_SETTINGS])
+def test_headline_batch_every_row_against_the_oracle(sampler, oracle, label, params, H):
+    """B=256 x V=128256 fp32 (the headline shape, the benchmark's value distribution): every row."""
+    c = W.config2(seed=7, batch=256)
+    hist = c["history"] if H else None
+    got, ref = run_both(sampler, oracle, c["logits"], params, c["uniforms"], hist=hist, want_kept=0)
+    assert_parity(got, ref, check_kept=False)
+    assert (ref["status"] == 0).all()
+
+
+def test_config5_full_batch_on_one_gpu(sampler, oracle):
+    """Config 5 at its stated batch (1024 rows x 256000 bf16, 8 vocabulary segments) on one GPU."""
+    c = W.config5(seed=0, batch=1024)
+    got, ref = run_both(sampler, oracle, c["logits_bf16"], c["params"], c["uniforms"], segments=c["shards"], want_kept=0)
+    assert_parity(got, ref, check_kept=False)

@@ -91,7 +91,7 @@ def test_random_configurations_match_the_oracle(sampler, oracle, seed):
         seg = 1
         if (not per_row and hist is None and 0 < params.get("top_k", 0) <= 128 and V >= 4096 and rng.random() < 0.3):
             for g in (2, 4, 8):
-                if V % g == 0 and (V // g) % 32 == 0 and (V // g * (2 if bf else 4)) % 16 == 0 and params["top_k"] * g <= 1024:
+                if V % g == 0 and params["top_k"] * g <= 1024:
                     seg = g
         op = oracle.params_from_rows(rows) if per_row else oracle.make_params(**params)
         ref = oracle.sample(logits, op, uniforms=u, mask=mask, history=hist, history_len=hl, segments=seg, want_kept=64,
@@ -106,12 +106,7 @@ def test_random_configurations_match_the_oracle(sampler, oracle, seed):
                              history_len=_dev(hl), want_lse=True, want_kept=64, vocab_segments=seg, **kw)
         torch.cuda.synchronize()
         got = {k: v.cpu().numpy() for k, v in out.items()}
-        # the survivor limit (see the module docstring): only possible with top-k off
-        lim = (got["status"] == ROW_OVERFLOW) & (ref["status"] == 0)
-        for b in np.nonzero(lim)[0]:
-            assert used[b if per_row else 0].get("top_k", 0) == 0, (seed, it, b)
-        limit_rows += int(lim.sum())
-        keep = ~lim
+        keep = np.ones(B, dtype=bool)  # every row the oracle answers is answered, exactly
         ctx = (seed, it, B, V, bf, kind, seg, used[:3])
         assert np.array_equal(got["status"][keep], ref["status"][keep]), ctx
         assert np.array_equal(got["token"][keep], ref["token"][keep]), ctx
@@ -121,4 +116,4 @@ def test_random_configurations_match_the_oracle(sampler, oracle, seed):
         fin = keep & np.isfinite(ref["lse"]) & (ref["status"] == 0)
         if fin.any():  # both sides sum in fp32, in different orders
             assert np.allclose(got["lse"][fin], ref["lse"][fin], rtol=1e-4, atol=2e-3), ctx
-    assert limit_rows < 80 * 64 // 10
+    assert limit_rows == 0

@@ -2,11 +2,12 @@
 
 Some hosts of this library run where cudaMalloc is off limits: a serving process whose
 memory pool has already claimed the whole GPU, or a decode loop that must not hit the
-allocator.  For them the library keeps the kernel's scratch (slice records, row tickets)
-in a fixed device array inside its own image.  This test drives the entry point through
-the C ABI twice in a row -- the second call finds the array as the first one left it -- and
-holds the results against the regular born_sample entry point on the same inputs.
-It lives in a file of its own that pytest collects last.
+allocator.  For them the library keeps the kernel's scratch (segment records, mass blocks,
+history lists, row tickets) in a fixed device array inside its own image.  This test drives
+the entry point through the C ABI twice in a row -- the second call finds the array as the
+first one left it -- and holds the results against the regular born_sample entry point and
+against the CPU oracle on the same inputs; it also checks that the calls leave the amount of
+free device memory unchanged.  It lives in a file of its own that pytest collects last.
 """
 import ctypes as C
 
@@ -37,13 +38,19 @@ def _args(L, logits, u, hist, cfg, out, V):
     return a
 
 
-def test_static_entry_matches_regular_entry_twice(lib):
+@pytest.mark.parametrize("B,params", [
+    (12, dict(temperature=0.8, top_k=40, top_p=0.95, repetition_penalty=1.1)),  # few rows: every row is many segments
+    (256, dict(temperature=0.7, min_p=0.05, top_p=0.9, frequency_penalty=0.5, presence_penalty=0.3)),  # the row limit
+    (7, dict(temperature=0.9)),               # whole-vocabulary rows: mass blocks in the static array
+    (5, dict(temperature=1.6, top_p=0.9)),    # a nucleus beyond the candidates: the exact search, still no allocation
+])
+def test_static_entry_matches_regular_entry_twice(lib, oracle, B, params):
     import torch
     from born_b200 import Sampler, SamplingConfig, _lib as L
     assert torch.cuda.is_available(), "needs a CUDA device"
     torch.cuda.set_device(0)
-    B, V, H = 12, 128256, 64  # few rows of a large vocabulary: rows are cut into slices, so scratch records are used
-    cfg = SamplingConfig(temperature=0.8, top_k=40, top_p=0.95, repetition_penalty=1.1)
+    V, H = 128256, 64
+    cfg = SamplingConfig(**params)
     with Sampler(device=0, max_batch=B, max_vocab=V) as regular:
         for call in range(2):
             z = torch.from_numpy((W.normal(900 + call, 1, B * V) * 3.0).astype(np.float32).reshape(B, V)).cuda()
@@ -55,9 +62,17 @@ def test_static_entry_matches_regular_entry_twice(lib):
                    "prob": torch.zeros(B, dtype=torch.float32, device="cuda"),
                    "lse": torch.zeros(B, dtype=torch.float32, device="cuda")}
             a = _args(L, z, u, hist, cfg, got, V)
+            torch.cuda.synchronize()
+            free0 = torch.cuda.mem_get_info()[0] if call == 1 else None  # (the first call may load the kernels)
             rc = lib.born_sample_static(C.byref(a), None)
             assert rc == 0, lib.born_last_error(None)
             torch.cuda.synchronize()
+            if free0 is not None:
+                assert torch.cuda.mem_get_info()[0] == free0
+            ref = oracle.sample(z.cpu().numpy(), oracle.make_params(**params), uniforms=u.cpu().numpy(),
+                                history=hist.cpu().numpy(), nthreads=8)
+            assert np.array_equal(got["token"].cpu().numpy(), ref["token"])
+            assert np.array_equal(got["prob"].cpu().numpy().view(np.uint32), ref["prob"].view(np.uint32))
             assert torch.equal(got["status"], want["status"]) and int(got["status"].abs().sum()) == 0
             assert torch.equal(got["token"], want["token"])
             assert torch.equal(got["prob"], want["prob"])  # integer masses: bit-exact
@@ -80,3 +95,19 @@ def test_static_entry_rejects_what_it_cannot_hold(lib):
     a.batch = 4
     a.memory = L.MEM_HOST
     assert lib.born_sample_static(C.byref(a), None) == L.ERR_UNSUPPORTED
+    a.memory = L.MEM_DEVICE
+    a.vocab_segments = 2
+    assert lib.born_sample_static(C.byref(a), None) == L.ERR_UNSUPPORTED  # needs scratch it does not have
+    a.vocab_segments = 0
+    # whole-vocabulary bf16 rows with history penalties need the clean fp32 copy: refused, not allocated
+    zb = torch.zeros((4, V), dtype=torch.bfloat16, device="cuda")
+    b = _args(L, zb, u, hist, SamplingConfig(temperature=1.0, repetition_penalty=1.2), out, V)
+    b.batch = 4
+    b.logits_dtype = L.DTYPE_BF16
+    assert lib.born_sample_static(C.byref(b), None) == L.ERR_UNSUPPORTED
+    assert b"may not allocate" in lib.born_last_error(None)
+    # and the mass-block limit: batch x ceil(vocab / 512) beyond BORN_STATIC_MAX_BLOCKS
+    big = _args(L, z, u, hist, SamplingConfig(temperature=1.0, top_k=5), out, V)
+    big.batch, big.vocab, big.logits_row_stride = 256, 1 << 20, 1 << 20
+    assert lib.born_sample_static(C.byref(big), None) == L.ERR_UNSUPPORTED
+    assert b"mass blocks" in lib.born_last_error(None)

@@ -53,8 +53,6 @@ struct Handle {
     MassBlock* blocks = nullptr;   // mass blocks of the whole-vocabulary routes
     int64_t blocks_cap = 0;
     uint32_t* tickets = nullptr;   // [max_rows] tickets, then [max_rows] deferred-fallback owners
-    unsigned long long* hist_lists = nullptr;  // [max_batch, BORN_MAX_HISTORY] distinct history ids with counts
-    uint32_t* hist_counts = nullptr;           // [max_batch]
     uint8_t* seg_packed = nullptr; // packed records of the one-GPU vocabulary-segment form
     size_t seg_packed_bytes = 0;
     int* dev_error = nullptr;
@@ -177,11 +175,18 @@ cudaError_t scan_attrs_all() {
     return cudaSuccess;
 }
 
+template <typename T, bool M, bool Lq>
+cudaError_t launch_scan_variant(const ScanArgs& A, int grid, size_t smem, cudaStream_t st) {
+    scan_kernel<T, M, Lq><<<grid, kScanThreads, smem, st>>>(A);
+    return cudaGetLastError();
+}
+
 int launch_scan(Handle* h, const ScanArgs& A, int dtype, int grid, cudaStream_t st) {
     const bool has_mask = A.mask != nullptr;
     const bool lse = A.out_lse != nullptr || A.want_lse;
     const size_t smem = (size_t)scan_smem_layout(dtype == BORN_DTYPE_F32 ? 4 : 2, has_mask, A.history != nullptr).total;
-#define V_(T, M, Lq) scan_kernel<T, M, Lq><<<grid, kScanThreads, smem, st>>>(A)
+    cudaError_t e;
+#define V_(T, M, Lq) e = launch_scan_variant<T, M, Lq>(A, grid, smem, st)
     if (dtype == BORN_DTYPE_F32) {
         if (has_mask) { if (lse) V_(float, true, true); else V_(float, true, false); }
         else { if (lse) V_(float, false, true); else V_(float, false, false); }
@@ -190,7 +195,7 @@ int launch_scan(Handle* h, const ScanArgs& A, int dtype, int grid, cudaStream_t 
         else { if (lse) V_(uint16_t, false, true); else V_(uint16_t, false, false); }
     }
 #undef V_
-    CUDA_TRY(h, cudaGetLastError());
+    if (e != cudaSuccess) return fail(h, BORN_ERR_CUDA, "scan kernel launch failed: %s", cudaGetErrorString(e));
     h->launches++;
     return BORN_OK;
 }
@@ -223,6 +228,14 @@ int fill_scan(Handle* h, ScanArgs& A, int B, int G, int V, int dtype, const void
     if (rows * A.nblk > h->blocks_cap) return fail(h, BORN_ERR_UNSUPPORTED, "batch x vocab exceeds the workspace");
     const int64_t tiles = rows * A.tpr;
     *grid = (int)(tiles < h->max_grid ? tiles : h->max_grid);
+    // When a whole number S of equal slices per row nearly fills the GPU, every CTA gets exactly
+    // one slice: no CTA meets a row boundary in mid-stream, and with S = 1 a row is finished from
+    // the shared memory of the CTA that streamed it.
+#if defined(BORN_EXP) || defined(BORN_PROFILE)
+    if (!getenv("BORN_NO_SLICES"))
+#endif
+    for (int S = 1; S <= 64 && rows * S <= h->max_grid; ++S)
+        if (A.tpr % S == 0 && rows * S * 20 >= (int64_t)h->max_grid * 17) { *grid = (int)(rows * S); break; }
     // entries per segment record: as many as the record area gives every (row + cta) slot
     int64_t cap = ((int64_t)(h->records_bytes / (size_t)(rows + *grid)) - kRecordHdrBytes) / 8;
     cap = (cap < h->rec_cap ? cap : h->rec_cap) & ~(int64_t)1;
@@ -280,8 +293,7 @@ ScratchPlan scratch_plan(int max_batch, int max_vocab, int max_grid, int rec_cap
     p.blocks = (size_t)p.blocks_cap * sizeof(MassBlock);
     p.tickets = sizeof(uint32_t) * 2 * (size_t)p.max_rows;
     p.seg_packed = (size_t)max_batch * (size_t)(kRecordHdrBytes * BORN_MAX_SHARDS + 8 * BORN_MAX_CANDIDATES);
-    p.hist = (size_t)max_batch * (BORN_MAX_HISTORY * 8 + 4);
-    p.total = p.records + p.blocks + p.tickets + p.seg_packed + p.hist + 256;
+    p.total = p.records + p.blocks + p.tickets + p.seg_packed + 256;
     return p;
 }
 
@@ -331,11 +343,9 @@ int32_t born_sampler_create(int32_t device, int32_t max_batch, int32_t max_vocab
     if (rc == BORN_OK) rc = dev_alloc(h, (void**)&h->blocks, sp.blocks);
     if (rc == BORN_OK) rc = dev_alloc(h, (void**)&h->tickets, sp.tickets);
     if (rc == BORN_OK) rc = dev_alloc(h, (void**)&h->seg_packed, sp.seg_packed);
-    if (rc == BORN_OK) rc = dev_alloc(h, (void**)&h->hist_lists, sp.hist);
-    if (rc == BORN_OK) h->hist_counts = reinterpret_cast<uint32_t*>(h->hist_lists + (size_t)max_batch * BORN_MAX_HISTORY);
-    if (rc == BORN_OK) rc = dev_alloc(h, (void**)&h->dev_error, 2 * sizeof(int));
+    if (rc == BORN_OK) rc = dev_alloc(h, (void**)&h->dev_error, 32 * sizeof(int));
     if (rc == BORN_OK && cudaMemset(h->tickets, 0, sp.tickets) != cudaSuccess) rc = BORN_ERR_CUDA;
-    if (rc == BORN_OK && cudaMemset(h->dev_error, 0, 2 * sizeof(int)) != cudaSuccess) rc = BORN_ERR_CUDA;
+    if (rc == BORN_OK && cudaMemset(h->dev_error, 0, 32 * sizeof(int)) != cudaSuccess) rc = BORN_ERR_CUDA;
     if (rc == BORN_OK && scan_attrs_all() != cudaSuccess) rc = BORN_ERR_CUDA;
     if (rc == BORN_OK && spec_attrs_all() != cudaSuccess) rc = BORN_ERR_CUDA;
     for (int i = 0; i < 4 && rc == BORN_OK; ++i)
@@ -358,7 +368,6 @@ int32_t born_sampler_destroy(void* handle) {
     cudaFree(h->blocks);
     cudaFree(h->tickets);
     cudaFree(h->seg_packed);
-    cudaFree(h->hist_lists);
     cudaFree(h->dev_error);
     cudaFree(h->spec_scratch);
     cudaFree(h->clean_copy);
@@ -382,10 +391,14 @@ int64_t born_fallback_rows(void* handle) {
     Handle* h = (Handle*)handle;
     if (!h || h->is_static) return -1;
     if (use_device(h)) return -1;
-    int n = 0;
-    if (cudaMemcpy(&n, h->dev_error + 1, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-    cudaMemset(h->dev_error + 1, 0, sizeof(int));
-    return n;
+    int n[24];
+    if (cudaMemcpy(n, h->dev_error + 1, sizeof n, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    cudaMemset(h->dev_error + 1, 0, sizeof n);
+    // by reason: 1 greedy tie lost, 2 kept-id list of a whole row, 3 more than 1024 candidates, 4 top-k above 256,
+    // 5 / 6 top-k / min-p set not provably complete, 7 nucleus below the candidates, 8 shard record not exact
+    snprintf(h->err, sizeof h->err, "exact-search rows by reason 1..8: %d %d %d %d %d %d %d %d", n[8], n[9], n[10], n[11], n[12],
+             n[13], n[14], n[15]);
+    return n[0];
 }
 
 int32_t born_check_error(void* handle) {
@@ -448,18 +461,6 @@ static int sample_device(Handle* h, const born_sample_args* a_in, cudaStream_t s
     A.history = a->history;
     A.history_len = a->history_len;
     A.history_stride = a->history_stride;
-    if (a->history) {
-        if (!h->hist_lists) return fail(h, BORN_ERR_UNSUPPORTED, "token histories need scratch that the allocation-free entry point does not have");
-        HistPrepArgs P;
-        P.history = a->history; P.history_len = a->history_len; P.history_stride = a->history_stride;
-        P.B = a->batch; P.vocab = a->vocab;
-        P.lists = h->hist_lists; P.counts = h->hist_counts;
-        hist_prep_kernel<<<a->batch, kThreads, 0, st>>>(P);
-        CUDA_TRY(h, cudaGetLastError());
-        h->launches++;
-        A.hist_lists = h->hist_lists;
-        A.hist_counts = h->hist_counts;
-    }
     A.row_params = a->row_params;
     A.params = a->params;
     A.uniforms = a->uniforms;
@@ -941,8 +942,7 @@ constexpr size_t kStaticRecordsBytes = (size_t)(kStaticMaxBatch + kStaticMaxGrid
 constexpr size_t kStaticBlocks = BORN_STATIC_MAX_BLOCKS;
 constexpr size_t kStaticBlocksBytes = kStaticBlocks * sizeof(MassBlock);
 constexpr size_t kStaticTicketsBytes = sizeof(uint32_t) * 2 * kStaticMaxBatch;
-constexpr size_t kStaticHistBytes = (size_t)kStaticMaxBatch * (BORN_MAX_HISTORY * 8 + 4);
-constexpr size_t kStaticBytes = kStaticRecordsBytes + kStaticBlocksBytes + kStaticHistBytes + kStaticTicketsBytes + 256;
+constexpr size_t kStaticBytes = kStaticRecordsBytes + kStaticBlocksBytes + kStaticTicketsBytes + 256;  // (the last 256: error word and counters)
 static_assert(kStaticBytes <= BORN_STATIC_SCRATCH_BYTES, "the header promises at most BORN_STATIC_SCRATCH_BYTES");
 constexpr int kStaticMaxDevices = 64;
 }  // namespace
@@ -1002,10 +1002,8 @@ extern "C" int32_t born_sample_static(const born_sample_args* a, void* stream) {
         h->records = base;
         h->blocks = reinterpret_cast<MassBlock*>(base + kStaticRecordsBytes);
         h->blocks_cap = (int64_t)kStaticBlocks;
-        h->hist_lists = reinterpret_cast<unsigned long long*>(base + kStaticRecordsBytes + kStaticBlocksBytes);
-        h->hist_counts = reinterpret_cast<uint32_t*>(h->hist_lists + (size_t)kStaticMaxBatch * BORN_MAX_HISTORY);
-        h->tickets = reinterpret_cast<uint32_t*>(base + kStaticRecordsBytes + kStaticBlocksBytes + kStaticHistBytes);
-        h->dev_error = reinterpret_cast<int*>(base + kStaticRecordsBytes + kStaticBlocksBytes + kStaticHistBytes + kStaticTicketsBytes);
+        h->tickets = reinterpret_cast<uint32_t*>(base + kStaticRecordsBytes + kStaticBlocksBytes);
+        h->dev_error = reinterpret_cast<int*>(base + kStaticRecordsBytes + kStaticBlocksBytes + kStaticTicketsBytes);
         g_static_ready[dev] = true;
     }
     // The array keeps whatever the previous call left; the tickets and the error word

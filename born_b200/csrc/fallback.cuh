@@ -242,7 +242,7 @@ __device__ __noinline__ void fallback_row(const ScanArgs& A, ScanShared& sh, uin
             if (h.y > 0.0f) ls += h.y * ex2_approx(__fmul_rn(h.x - c.m, pl.c2));
         }
         ls = block_sum_f32(ls, sh.redf);
-        write_packed(A, sh, sel, n, pl.k, c.b, c.g, c.m, ls, -INFINITY, true);
+        write_packed(A, sh, sel, reinterpret_cast<unsigned long long*>(sel + kSelCap), n, pl.k, c.b, c.g, c.m, ls, -INFINITY, true);
         return;
     }
 

@@ -45,111 +45,122 @@ struct SelectIn {
     float m_row, inv_T, u;
 };
 
-// Selection and draw over n <= kSelCap candidates in shared memory (sel: rank keys; selq:
-// scratch for their masses).  Returns false when the nucleus is not inside the candidates
-// (the caller then takes the exact fallback); all threads get the same answer.
+// Selection and draw over n <= kThreads candidates in shared memory (sel: rank keys, all alive;
+// selq: scratch for their masses), one candidate per thread.  The rank of a candidate is the
+// number of larger keys (keys are unique: the token index is part of them); candidates and
+// masses are then re-written in rank order, and since a mass never grows along that order the
+// kept set of every filter is a prefix of it, which every thread finds by walking the sorted
+// masses itself.  Returns false when the nucleus is not inside the candidates (the caller then
+// takes the exact fallback); all threads get the same answer.
+__device__ __forceinline__ bool select_small(const SelectIn& in, uint64_t* sel, unsigned long long* selq, ScanShared& sh,
+                                             const RowOut& o) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n = in.n;
+    const int k_eff = in.k > 0 ? in.k : 0x7fffffff;
+    const bool topp = in.top_p > 0.0f && in.top_p < 1.0f;
+    const bool mine = tid < n;
+    uint64_t ck = mine ? sel[tid] : 0ull;
+    int rank = 0;
+    {   // (eight broadcast loads in flight: the loop is bound by latency otherwise)
+        int j = 0;
+        for (; j + 8 <= n; j += 8) {
+            uint64_t v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = sel[j + i];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) rank += (v[i] > ck) ? 1 : 0;
+        }
+        for (; j < n; ++j) rank += (sel[j] > ck) ? 1 : 0;
+    }
+    uint64_t q = 0;
+    if (mine && rank < k_eff) {
+        const float x = scaled_shift(ck_z(ck), in.m_row, in.inv_T);
+        q = (x < -30.0f) ? 0ull : mass_of(x);
+        if (in.Qa && q < in.Qa) { q = 0; ck &= (uint64_t)kIdxMask; }  // min-p: a dead entry keeps its index only
+    }
+    PROFG(15);
+    cta_sync();  // every thread has read sel[] for its rank
+    const int nk = min(n, k_eff);
+    if (mine && rank < nk) { sel[rank] = ck; selq[rank] = q; }
+    if (tid == 0) { sh.acc[0] = 0; sh.nw = 0; }
+    cta_sync();
+    PROFG(16);
+    // the entry of rank `tid`, and the mass ahead of it
+    const uint64_t c2 = tid < nk ? sel[tid] : 0ull;
+    const uint64_t q2 = tid < nk ? (uint64_t)selq[tid] : 0ull;
+    uint64_t incl = q2;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint64_t up = shfl_up_u64(incl, d);
+        if (lane >= d) incl += up;
+    }
+    if (lane == 31) sh.red64[warp] = incl;
+    cta_sync();
+    uint64_t off = 0, tot = 0;
+#pragma unroll
+    for (int w = 0; w < kScanWarps; ++w) {
+        const uint64_t x = sh.red64[w];
+        if (w < warp) off += x;
+        tot += x;
+    }
+    const uint64_t before = off + incl - q2;
+    uint64_t Tp = ~0ull;
+    if (topp) {
+        Tp = __double2ull_rz(__dmul_rn((double)in.top_p, __ull2double_rn(in.S_ext ? in.S_ext : tot)));
+        if (Tp < 1) Tp = 1;
+    }
+    // kept: alive and the mass ahead still short of the nucleus -- a prefix of the rank order;
+    // its last entry of every warp reports the prefix's length and mass
+    const bool kept = tid < nk && ck_alive(c2) && before < Tp;
+    const uint32_t kb = __ballot_sync(0xffffffffu, kept);
+    if (kb && lane == 31 - __clz(kb)) {
+        atomicMax(&sh.nw, tid + 1);
+        atomicMax(&sh.acc[0], (unsigned long long)(before + q2));
+    }
+    cta_sync();
+    const int R = sh.nw;
+    PROFG(17);
+    const uint64_t S = sh.acc[0];
+    if (topp && in.S_ext && !in.complete && S < Tp) return false;  // (uniform)
+    if (S == 0) {  // cannot happen while the row maximum is finite; never divide by it
+        row_fail(o, BORN_ROW_ALL_MASKED);
+        return true;
+    }
+    uint64_t t = __double2ull_rz(__dmul_rn((double)in.u, __ull2double_rn(S)));
+    if (t > S - 1) t = S - 1;
+    if (tid < R) {
+        const uint32_t my_low = (uint32_t)(c2 & kIdxMask);  // larger low bits = smaller token index
+        uint64_t pre = 0;
+        int j = 0;
+        for (; j + 8 <= R; j += 8) {
+            uint64_t cj[8], qj[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { cj[i] = sel[j + i]; qj[i] = selq[j + i]; }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) pre += ((uint32_t)(cj[i] & kIdxMask) > my_low) ? qj[i] : 0ull;
+        }
+        for (; j < R; ++j) pre += ((uint32_t)(sel[j] & kIdxMask) > my_low) ? (uint64_t)selq[j] : 0ull;
+        if (pre <= t && t < pre + q2) {
+            o.token[o.row] = ck_idx(c2);
+            o.status[o.row] = BORN_ROW_OK;
+            if (o.prob) o.prob[o.row] = __double2float_rn(__ddiv_rn(__ull2double_rn(q2), __ull2double_rn(S)));
+        }
+        if (o.kept_ids && tid < o.kept_stride) o.kept_ids[(int64_t)o.row * o.kept_stride + tid] = ck_idx(c2);
+    }
+    if (o.kept_count && tid == 0) o.kept_count[o.row] = R;
+    PROFG(18);
+    return true;
+}
+
+// Selection and draw over kThreads < n <= kSelCap candidates: radix select, then mass-weighted
+// radix threshold searches.  Same rules, same answer convention as select_small.
 __device__ __noinline__ bool select_and_draw(const SelectIn in, uint64_t* sel, unsigned long long* selq, ScanShared& sh,
                                              const RowOut o) {
     const int tid = threadIdx.x;
     const int n = in.n;
     const int k_eff = in.k > 0 ? in.k : 0x7fffffff;
     const bool topp = in.top_p > 0.0f && in.top_p < 1.0f;
-    if (tid == 0) { sh.acc[0] = 0; sh.acc[1] = 0; sh.acc[2] = 0; sh.flag = 0; }
     cta_sync();
-    if (n <= kThreads) {
-        // ---- small set: everything by all-pairs comparison.  An entry is shared by P = 2^lg
-        // adjacent threads, each walking every P-th entry; partial counts meet by shuffles.
-        int lg = 0;
-        while (lg < 5 && (n << (lg + 1)) <= kThreads) ++lg;
-        const int P = 1 << lg, part = tid & (P - 1), ent = tid >> lg;
-        const bool mine = ent < n;
-        const bool lead = mine && part == 0;
-        const uint64_t ck = mine ? sel[ent] : 0ull;
-        auto group_sum = [&](uint64_t v, int PP) {
-            for (int d = 1; d < PP; d <<= 1) v += shfl_xor_u64(v, d);
-            return v;
-        };
-        auto block_add = [&](uint64_t v, int slot) {
-#pragma unroll
-            for (int d = 16; d > 0; d >>= 1) v += shfl_xor_u64(v, d);
-            if ((tid & 31) == 0 && v) atomicAdd(&sh.acc[slot], (unsigned long long)v);
-        };
-        int rank = 0;
-        for (int j = part; j < n; j += P) rank += (sel[j] > ck) ? 1 : 0;
-        rank = (int)group_sum((uint64_t)rank, P);
-        bool kept = mine && rank < k_eff;
-        uint64_t q = 0;
-        if (kept) {
-            const float x = scaled_shift(ck_z(ck), in.m_row, in.inv_T);
-            q = (x < -30.0f) ? 0ull : mass_of(x);
-        }
-        if (in.Qa && q < in.Qa) { kept = false; q = 0; }
-        cta_sync();  // every thread has read sel[] for its rank
-        // the nk best entries go to sel[0..nk) in rank order; one that min-p removed stays as a dead entry
-        const int nk = min(n, k_eff);
-        if (lead && rank < nk) {
-            sel[rank] = kept ? ck : (ck & (uint64_t)kIdxMask);
-            selq[rank] = q;
-        }
-        block_add(lead ? q : 0ull, 0);
-        cta_sync();
-        uint64_t S = sh.acc[0];
-        int lg2 = 0;
-        while (lg2 < 5 && (nk << (lg2 + 1)) <= kThreads) ++lg2;
-        const int P2 = 1 << lg2, part2 = tid & (P2 - 1), ent2 = tid >> lg2;
-        const bool mine2 = ent2 < nk;
-        const bool lead2 = mine2 && part2 == 0;
-        const uint64_t ck2 = mine2 ? sel[ent2] : 0ull;
-        uint64_t q2 = mine2 ? (uint64_t)selq[ent2] : 0ull;
-        bool kept2 = mine2 && ck_alive(ck2);
-        if (topp) {
-            uint64_t before = 0;  // mass ahead in rank order
-            for (int j = part2; j < min(ent2, nk); j += P2) before += selq[j];
-            before = group_sum(before, P2);
-            uint64_t Tp = __double2ull_rz(__dmul_rn((double)in.top_p, __ull2double_rn(in.S_ext ? in.S_ext : S)));
-            if (Tp < 1) Tp = 1;
-            if (in.S_ext && !in.complete && S < Tp) return false;  // (uniform: S and Tp are)
-            if (kept2 && !(before < Tp)) { kept2 = false; q2 = 0; }
-            cta_sync();
-            if (lead2) {
-                sel[ent2] = kept2 ? ck2 : (ck2 & (uint64_t)kIdxMask);
-                selq[ent2] = q2;
-            }
-            block_add(lead2 ? q2 : 0ull, 1);
-            cta_sync();
-            S = sh.acc[1];
-        }
-        if (S == 0) {  // cannot happen while the row maximum is finite; never divide by it
-            row_fail(o, BORN_ROW_ALL_MASKED);
-            return true;
-        }
-        const uint32_t my_low = (uint32_t)(ck2 & kIdxMask);  // larger low bits = smaller token index
-        uint64_t pre = 0;
-        for (int j = part2; j < nk; j += P2) pre += ((uint32_t)(sel[j] & kIdxMask) > my_low) ? selq[j] : 0ull;
-        pre = group_sum(pre, P2);
-        uint64_t t = __double2ull_rz(__dmul_rn((double)in.u, __ull2double_rn(S)));
-        if (t > S - 1) t = S - 1;
-        if (lead2 && kept2 && pre <= t && t < pre + q2) {
-            o.token[o.row] = ck_idx(ck2);
-            o.status[o.row] = BORN_ROW_OK;
-            if (o.prob) o.prob[o.row] = __double2float_rn(__ddiv_rn(__ull2double_rn(q2), __ull2double_rn(S)));
-        }
-        if (o.kept_count || o.kept_ids) {
-            if (o.kept_ids) {
-                int kr = 0;  // kept entries ahead in rank order
-                for (int j = part2; j < min(ent2, nk); j += P2) kr += ck_alive(sel[j]) ? 1 : 0;
-                kr = (int)group_sum((uint64_t)kr, P2);
-                if (lead2 && kept2 && kr < o.kept_stride) o.kept_ids[(int64_t)o.row * o.kept_stride + kr] = ck_idx(ck2);
-            }
-            if (o.kept_count) {
-                block_add((lead2 && kept2) ? 1ull : 0ull, 2);
-                cta_sync();
-                if (tid == 0) o.kept_count[o.row] = (int)sh.acc[2];
-            }
-        }
-        return true;
-    }
-
     // ---- large set: radix select, then mass-weighted radix threshold searches
     if (n > k_eff) {
         const uint64_t T = block_radix_search<true, 56, true>(
@@ -386,7 +397,7 @@ template <typename T>
 __device__ __noinline__ void fallback_row(const ScanArgs& A, ScanShared& sh, uint8_t* smem, int row);
 
 // Exactly the k best of a virtual row, in rank order, into its packed record.
-__device__ __forceinline__ void write_packed(const ScanArgs& A, ScanShared& sh, uint64_t* sel, int n, int k, int b, int g,
+__device__ __forceinline__ void write_packed(const ScanArgs& A, ScanShared& sh, uint64_t* sel, unsigned long long* tmp_mem, int n, int k, int b, int g,
                                              float m, float lse_s, float bound, bool exact) {
     const int tid = threadIdx.x;
     uint8_t* rec = A.packed + (int64_t)g * A.packed_seg_stride + (int64_t)b * A.packed_row_stride;
@@ -397,7 +408,7 @@ __device__ __forceinline__ void write_packed(const ScanArgs& A, ScanShared& sh, 
             // cut to the k best first (k <= kThreads here), survivors to the front
             const uint64_t Tk = block_radix_search<true, 56, true>(
                 n, (unsigned long long)(min(k, n) - 1), [&](int i) { return sel[i]; }, [&](int) { return 1ull; }, sh.sc);
-            uint64_t* tmp = sel + kSelCap;  // the mass array is idle here
+            uint64_t* tmp = reinterpret_cast<uint64_t*>(tmp_mem);  // the mass array is idle here
             if (tid == 0) sh.nl = 0;
             cta_sync();
             for (int i = tid; i < n; i += kThreads)
@@ -423,61 +434,93 @@ __device__ __forceinline__ void write_packed(const ScanArgs& A, ScanShared& sh, 
     }
 }
 
-// The CTA that completed `row` (all its segment records are in scratch): merge, select, draw.
+// Where a finished row's statistics and candidates come from: the segment records in scratch
+// (a row streamed by several CTAs), or -- when one CTA streamed the whole row -- that CTA's
+// own shared memory, without a round trip through L2.
+struct RowSrc {
+    bool direct;
+    float m, ls, taux, bk;       // direct: the row's maximum, log-sum-exp sum, exclusion level, lane-maxima bound
+    const uint64_t* wbuf;        // direct: the warps' candidate buffers (kScanWarps x kWarpCand raw entries)
+    const uint32_t* wcount;
+    int c_first, nseg;           // records: CTAs that hold a segment of the row
+    int b, g;                    // the row: caller row and vocabulary segment
+    float u;                     // the caller row's uniform, fetched while the row was streamed
+    born_row_params rp;
+    RowPlan plan;
+};
+
+// A row is complete: merge its statistics, select, draw.
 template <typename T>
-__device__ __noinline__ void finish_row(const ScanArgs& A, ScanShared& sh, uint8_t* sel_mem, int row, int c_first, int c_last) {
+__device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, uint64_t* sel, unsigned long long* selq, int row,
+                                           const RowSrc& src) {
     const int tid = threadIdx.x;
-    const int nseg = c_last - c_first + 1;
-    const int b = row / A.G, g = row - b * A.G;
-    const born_row_params rp = A.row_params ? A.row_params[b] : A.params;
-    const RowPlan pl = row_plan(rp);
-    uint64_t* sel = reinterpret_cast<uint64_t*>(sel_mem);
-    unsigned long long* selq = reinterpret_cast<unsigned long long*>(sel + kSelCap);
+    const int nseg = src.nseg, c_first = src.c_first;
+    const int b = src.b, g = src.g;
+    const born_row_params& rp = src.rp;
+    const RowPlan& pl = src.plan;
     auto rec_of = [&](int s) { return A.records + (int64_t)(row + c_first + s) * A.rec_stride; };
 
-    // headers: row maximum, exclusion level, best lane-maxima bound; then the log-sum-exp.
-    // Up to kHdrCache headers are fetched once (one round trip to L2) and shared.
-    float m = -INFINITY, taux = -INFINITY, bk = -INFINITY, ls = 0.0f;
+    // statistics: row maximum, exclusion level, best lane-maxima bound, log-sum-exp sum
+    float m = src.m, taux = src.taux, bk = src.bk, ls = src.ls;
     const bool cached = nseg <= kHdrCache;
-    if (cached) {
-        cta_sync();
-        if (tid < nseg) {
-            const uint8_t* rec = rec_of(tid);
-            const float4 h = __ldcg(reinterpret_cast<const float4*>(rec));
-            sh.hdr[tid] = h;
-            sh.hdr_cnt[tid] = __ldcg(reinterpret_cast<const uint32_t*>(rec) + 4);
-        }
-        cta_sync();
-        for (int s = 0; s < nseg; ++s) {
-            const float4 h = sh.hdr[s];
-            m = max_nan(m, h.x);
-            taux = fmaxf(taux, h.z);
-            bk = fmaxf(bk, h.w);
-        }
-        if (!pl.need_mass)
+    if (!src.direct) {
+        m = -INFINITY; taux = -INFINITY; bk = -INFINITY; ls = 0.0f;
+        if (cached) {  // the headers are fetched once (one round trip to L2) and shared
+            cta_sync();
+            if (tid < nseg) {
+                const uint8_t* rec = rec_of(tid);
+                const float4 h = __ldcg(reinterpret_cast<const float4*>(rec));
+                sh.hdr[tid] = h;
+                sh.hdr_cnt[tid] = __ldcg(reinterpret_cast<const uint32_t*>(rec) + 4);
+            }
+            cta_sync();
             for (int s = 0; s < nseg; ++s) {
                 const float4 h = sh.hdr[s];
-                if (h.y > 0.0f) ls += h.y * ex2_approx(__fmul_rn(h.x - m, pl.c2));
+                m = max_nan(m, h.x);
+                taux = fmaxf(taux, h.z);
+                bk = fmaxf(bk, h.w);
             }
-    } else {
-        for (int s = tid; s < nseg; s += kThreads) {
-            const float4 h = __ldcg(reinterpret_cast<const float4*>(rec_of(s)));
-            m = max_nan(m, h.x);
-            taux = fmaxf(taux, h.z);
-            bk = fmaxf(bk, h.w);
-        }
-        m = block_max_nan(m, sh.redf);
-        taux = block_max_nan(taux, sh.redf2);
-        bk = block_max_nan(bk, sh.redf3);
-        if (!pl.need_mass) {
+            if (!pl.need_mass)
+                for (int s = 0; s < nseg; ++s) {
+                    const float4 h = sh.hdr[s];
+                    if (h.y > 0.0f) ls += h.y * ex2_approx(__fmul_rn(h.x - m, pl.c2));
+                }
+        } else {
             for (int s = tid; s < nseg; s += kThreads) {
                 const float4 h = __ldcg(reinterpret_cast<const float4*>(rec_of(s)));
-                if (h.y > 0.0f) ls += h.y * ex2_approx(__fmul_rn(h.x - m, pl.c2));
+                m = max_nan(m, h.x);
+                taux = fmaxf(taux, h.z);
+                bk = fmaxf(bk, h.w);
             }
-            ls = block_sum_f32(ls, sh.redf);
+            m = block_max_nan(m, sh.redf);
+            taux = block_max_nan(taux, sh.redf2);
+            bk = block_max_nan(bk, sh.redf3);
+            if (!pl.need_mass) {
+                for (int s = tid; s < nseg; s += kThreads) {
+                    const float4 h = __ldcg(reinterpret_cast<const float4*>(rec_of(s)));
+                    if (h.y > 0.0f) ls += h.y * ex2_approx(__fmul_rn(h.x - m, pl.c2));
+                }
+                ls = block_sum_f32(ls, sh.redf);
+            }
         }
     }
     auto count_of = [&](int s) { return cached ? (int)sh.hdr_cnt[s] : (int)__ldcg(reinterpret_cast<const uint32_t*>(rec_of(s)) + 4); };
+    // every raw entry (value bits << 32 | token id) of the row, dealt over the threads
+    auto for_entries = [&](auto f) {
+        if (src.direct) {
+            for (int idx = tid; idx < kScanWarps * kWarpCand; idx += kThreads) {
+                const int w = idx / kWarpCand, i = idx - w * kWarpCand;
+                if (i < (int)min(src.wcount[w], (uint32_t)kWarpCand)) f(src.wbuf[idx]);
+            }
+        } else {
+            for (int s = 0; s < nseg; ++s) {
+                const int cnt = count_of(s);
+                const unsigned long long* ent = reinterpret_cast<const unsigned long long*>(rec_of(s) + kRecordHdrBytes);
+                for (int i = tid; i < cnt; i += kThreads) f(__ldcg(ent + i));
+            }
+        }
+    };
+    PROF(20);
     int status = BORN_ROW_OK;
     if (m != m) status = BORN_ROW_NAN;
     else if (m == INFINITY) status = BORN_ROW_POS_INF;
@@ -486,33 +529,26 @@ __device__ __noinline__ void finish_row(const ScanArgs& A, ScanShared& sh, uint8
     if (A.mode == kScanLocal) {
         // ---- the k best of the virtual row, in rank order
         int n = 0;
-        bool exact = true;
         if (status == BORN_ROW_OK) {
             if (tid == 0) sh.nl = 0;
             cta_sync();
-            for (int s = 0; s < nseg; ++s) {
-                const uint8_t* rec = rec_of(s);
-                const int cnt = count_of(s);
-                const unsigned long long* ent = reinterpret_cast<const unsigned long long*>(rec + kRecordHdrBytes);
-                for (int i = tid; i < cnt; i += kThreads) {
-                    const unsigned long long e = __ldcg(ent + i);
-                    const float z = __uint_as_float((uint32_t)(e >> 32));
-                    if (z >= bk && z >= taux) {
-                        const int pos = (int)smem_atom_add(&sh.nl, 1u);
-                        if (pos < kSelCap) sel[pos] = make_ck(z, (int)(uint32_t)e);
-                    }
+            for_entries([&](unsigned long long e) {
+                const float z = __uint_as_float((uint32_t)(e >> 32));
+                if (z >= bk && z >= taux) {
+                    const int pos = (int)smem_atom_add(&sh.nl, 1u);
+                    if (pos < kSelCap) sel[pos] = make_ck(z, (int)(uint32_t)e);
                 }
-            }
+            });
             cta_sync();
             n = sh.nl;
             // complete above max(bk, taux); the k best are inside iff there are k of them (or nothing was excluded)
-            if (n > kSelCap || (taux > bk && n < pl.k) || pl.no_bound) exact = false;
-            if (!exact) {  // the exact search over the row writes the record instead
-                if (tid == 0) A.deferred[row] = blockIdx.x + 1u;
+            if (n > kSelCap || (taux > bk && n < pl.k) || pl.no_bound) {
+                // the exact search over the row writes the record instead
+                if (tid == 0) A.deferred[row] = (8u << 24) | (blockIdx.x + 1u);
                 return;
             }
         }
-        write_packed(A, sh, sel, n, pl.k, b, g, m, ls, bk, true);
+        write_packed(A, sh, sel, selq, n, pl.k, b, g, m, ls, bk, true);
         return;
     }
 
@@ -529,20 +565,14 @@ __device__ __noinline__ void finish_row(const ScanArgs& A, ScanShared& sh, uint8
 
     if (pl.greedy) {
         if (taux > m) {  // a token equal to the maximum may have been lost to a full buffer
-            if (tid == 0) A.deferred[row] = blockIdx.x + 1u;
+            if (tid == 0) A.deferred[row] = (1u << 24) | (blockIdx.x + 1u);
             return;
         }
         uint64_t best = 0;
-        for (int s = 0; s < nseg; ++s) {
-            const uint8_t* rec = rec_of(s);
-            const int cnt = count_of(s);
-            const unsigned long long* ent = reinterpret_cast<const unsigned long long*>(rec + kRecordHdrBytes);
-            for (int i = tid; i < cnt; i += kThreads) {
-                const unsigned long long e = __ldcg(ent + i);
-                const float z = __uint_as_float((uint32_t)(e >> 32));
-                if (z >= m) best = max(best, make_ck(z, (int)(uint32_t)e));
-            }
-        }
+        for_entries([&](unsigned long long e) {
+            const float z = __uint_as_float((uint32_t)(e >> 32));
+            if (z >= m) best = max(best, make_ck(z, (int)(uint32_t)e));
+        });
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) best = max(best, shfl_xor_u64(best, d));
         cta_sync();
@@ -560,7 +590,8 @@ __device__ __noinline__ void finish_row(const ScanArgs& A, ScanShared& sh, uint8
         return;
     }
 
-    const float u = A.uniforms[b];
+    const float u = src.u;
+    PROF(21);
     unsigned long long S_tot = 0;
     if (pl.need_mass) {
         // row total from the mass blocks; log-sum-exp from it
@@ -583,10 +614,10 @@ __device__ __noinline__ void finish_row(const ScanArgs& A, ScanShared& sh, uint8
         if (!pl.window) {
             if (A.out_kept_count && tid == 0) A.out_kept_count[b] = nfin;
             if (A.out_kept_ids) {  // the kept set is the whole row: no list of a useful size exists
-                if (tid == 0) A.deferred[row] = blockIdx.x + 1u;
+                if (tid == 0) A.deferred[row] = (2u << 24) | (blockIdx.x + 1u);
                 return;
             }
-            draw_whole_row<T>(A, sh, sel_mem, o, rp, b, g, row, m, pl.inv_T, S_tot, u);
+            draw_whole_row<T>(A, sh, nullptr, o, rp, b, g, row, m, pl.inv_T, S_tot, u);
             return;
         }
     }
@@ -602,28 +633,40 @@ __device__ __noinline__ void finish_row(const ScanArgs& A, ScanShared& sh, uint8
     }
     bool complete = !(taux > cut);
     float lowest = complete ? cut : taux;  // below it the entries are not all there: not used
+    // (sh.nl is zero on entry: the caller's last barrier saw to it)
     auto gather = [&](float low) {
-        if (tid == 0) sh.nl = 0;
-        cta_sync();
-        for (int s = 0; s < nseg; ++s) {
-            const uint8_t* rec = rec_of(s);
-            const int cnt = count_of(s);
-            const unsigned long long* ent = reinterpret_cast<const unsigned long long*>(rec + kRecordHdrBytes);
-            for (int i = tid; i < cnt; i += kThreads) {
-                const unsigned long long e = __ldcg(ent + i);
+        if (src.direct) {
+            // a warp compacts its own buffer: one reservation per 32 entries
+            const int lane = tid & 31, w = tid >> 5;
+            const uint32_t cnt = min(src.wcount[w], (uint32_t)kWarpCand);
+            const uint64_t* buf = src.wbuf + w * kWarpCand;
+            for (uint32_t base = 0; base < cnt; base += 32) {
+                const uint32_t i = base + lane;
+                const uint64_t e = i < cnt ? buf[i] : 0ull;
+                const float z = __uint_as_float((uint32_t)(e >> 32));
+                const bool ok = i < cnt && z >= low;
+                const uint32_t okb = __ballot_sync(0xffffffffu, ok);
+                if (!okb) continue;
+                uint32_t pos0 = 0;
+                if (lane == 0) pos0 = smem_atom_add(&sh.nl, (uint32_t)__popc(okb));
+                pos0 = __shfl_sync(0xffffffffu, pos0, 0);
+                const uint32_t pos = pos0 + __popc(okb & ((1u << lane) - 1u));
+                if (ok && pos < (uint32_t)kSelCap) sel[pos] = make_ck(z, (int)(uint32_t)e);
+            }
+        } else {
+            for_entries([&](unsigned long long e) {
                 const float z = __uint_as_float((uint32_t)(e >> 32));
                 if (z >= low) {
                     const int pos = (int)smem_atom_add(&sh.nl, 1u);
                     if (pos < kSelCap) sel[pos] = make_ck(z, (int)(uint32_t)e);
                 }
-            }
+            });
         }
         cta_sync();
-        const int got = sh.nl;
-        cta_sync();
-        return got;
+        return (int)sh.nl;
     };
     int n = gather(lowest);
+    PROF(23);
     if (n > kSelCap && !pl.no_bound) {
         // More candidates than the selection takes (a wide nucleus window, many ties).  Use only
         // the part above a higher level -- the lowest of a fixed ladder (in scaled-logit units
@@ -633,21 +676,16 @@ __device__ __noinline__ void finish_row(const ScanArgs& A, ScanShared& sh, uint8
         const float ladder[NL] = {8.0f, 6.5f, 5.0f, 4.0f, 3.0f, 2.0f, 1.0f, 0.5f};
         if (tid < NL) sh.sc.c[tid] = 0;
         cta_sync();
-        for (int s = 0; s < nseg; ++s) {
-            const uint8_t* rec = rec_of(s);
-            const int cnt = count_of(s);
-            const unsigned long long* ent = reinterpret_cast<const unsigned long long*>(rec + kRecordHdrBytes);
-            for (int i = tid; i < cnt; i += kThreads) {
-                const float z = __uint_as_float((uint32_t)(__ldcg(ent + i) >> 32));
-                if (!(z >= lowest)) continue;
-                const float d = (m - z) * pl.inv_T;
-                int lvl = -1;  // narrowest level that still holds the entry
+        for_entries([&](unsigned long long e) {
+            const float z = __uint_as_float((uint32_t)(e >> 32));
+            if (!(z >= lowest)) return;
+            const float d = (m - z) * pl.inv_T;
+            int lvl = -1;  // narrowest level that still holds the entry
 #pragma unroll
-                for (int l = 0; l < NL; ++l)
-                    if (d <= ladder[l]) lvl = l;
-                if (lvl >= 0) smem_red_add(&sh.sc.c[lvl], 1u);
-            }
-        }
+            for (int l = 0; l < NL; ++l)
+                if (d <= ladder[l]) lvl = l;
+            if (lvl >= 0) smem_red_add(&sh.sc.c[lvl], 1u);
+        });
         cta_sync();
         int pick = -1;
         uint32_t cum = 0;
@@ -662,15 +700,21 @@ __device__ __noinline__ void finish_row(const ScanArgs& A, ScanShared& sh, uint8
             if (low2 > lowest) {
                 lowest = low2;
                 complete = false;
+                if (tid == 0) sh.nl = 0;
+                cta_sync();
                 n = gather(lowest);
             }
         }
     }
-    bool defer = n > kSelCap || pl.no_bound;
-    if (!defer && !complete) {
-        if (pl.k > 0) defer = n < pl.k;          // the k best are all at or above taux iff k tokens are
-        else if (!pl.window) defer = true;       // min-p survivors may lie below taux
+    // why a row goes to the exact search (kept in the upper byte of its `deferred` word)
+    uint32_t why = 0;
+    if (pl.no_bound) why = 4;
+    else if (n > kSelCap) why = 3;
+    else if (!complete) {
+        if (pl.k > 0) { if (n < pl.k) why = 5; }   // the k best are all at or above taux iff k tokens are
+        else if (!pl.window) why = 6;              // min-p survivors may lie below taux
     }
+    bool defer = why != 0;
     if (!defer) {
         SelectIn in;
         in.n = n;
@@ -680,9 +724,12 @@ __device__ __noinline__ void finish_row(const ScanArgs& A, ScanShared& sh, uint8
         in.S_ext = pl.window ? S_tot : 0ull;
         in.complete = complete;
         in.m_row = m; in.inv_T = pl.inv_T; in.u = u;
-        defer = !select_and_draw(in, sel, selq, sh, o);
+        if (n <= kThreads) defer = !select_small(in, sel, selq, sh, o);
+        else defer = !select_and_draw(in, sel, selq, sh, o);
+        if (defer) why = 7;                        // the nucleus reaches below the candidates
     }
-    if (defer && tid == 0) A.deferred[row] = blockIdx.x + 1u;
+    PROF(24);
+    if (defer && tid == 0) A.deferred[row] = (why << 24) | (blockIdx.x + 1u);
 }
 
 }  // namespace born

@@ -82,7 +82,8 @@ __global__ void __launch_bounds__(kThreads) merge_kernel(const __grid_constant__
     in.S_ext = 0;
     in.complete = true;
     in.m_row = m; in.inv_T = inv_T; in.u = A.uniforms[b];
-    select_and_draw(in, sel, selq, sh, o);
+    if (n <= kThreads) select_small(in, sel, selq, sh, o);
+    else select_and_draw(in, sel, selq, sh, o);
 }
 
 }  // namespace born

@@ -73,48 +73,6 @@ __global__ void __launch_bounds__(kThreads) clean_patch_kernel(const CopyArgs A)
     }
 }
 
-// The distinct token ids of every row's history with their multiplicities, once per call, so
-// that the streaming kernel's producer warp only has to read a short list per segment:
-// lists[b][i] = (count << 32) | id for i < counts[b]; ids outside [0, vocab) are dropped.
-struct HistPrepArgs {
-    const int32_t* history;
-    const int32_t* history_len;
-    int history_stride, B, vocab;
-    unsigned long long* lists;
-    uint32_t* counts;
-};
-__global__ void __launch_bounds__(kThreads) hist_prep_kernel(const HistPrepArgs A) {
-    __shared__ unsigned long long table[kHashSlots];
-    __shared__ uint32_t n_out;
-    const int tid = threadIdx.x, b = blockIdx.x;
-    for (int i = tid; i < kHashSlots; i += kThreads) table[i] = ~0ull;
-    if (tid == 0) n_out = 0;
-    __syncthreads();
-    int len = A.history_len ? A.history_len[b] : A.history_stride;
-    len = max(0, min(min(len, A.history_stride), (int)BORN_MAX_HISTORY));
-    const int32_t* gh = A.history + (int64_t)b * A.history_stride;
-    for (int p = tid; p < len; p += kThreads) {
-        const int id = gh[p];
-        if (id < 0 || id >= A.vocab) continue;
-        const uint32_t key = (uint32_t)id;
-        uint32_t slot = (key * 2654435761u) >> 21;  // 11 bits
-        for (int probe = 0; probe < kHashSlots; ++probe) {
-            const unsigned long long old = atomicCAS(&table[slot], ~0ull, (1ull << 32) | key);
-            if (old == ~0ull) break;
-            if ((uint32_t)old == key) { atomicAdd(&table[slot], 1ull << 32); break; }
-            slot = (slot + 1) & (kHashSlots - 1);
-        }
-    }
-    __syncthreads();
-    unsigned long long* out = A.lists + (int64_t)b * BORN_MAX_HISTORY;
-    for (int i = tid; i < kHashSlots; i += kThreads) {
-        const unsigned long long e = table[i];
-        if (e != ~0ull) out[atomicAdd(&n_out, 1u)] = e;
-    }
-    __syncthreads();
-    if (tid == 0) A.counts[b] = n_out;
-}
-
 // returns 0 or a cudaError_t; `launches` counts what was launched
 inline int launch_clean_copy(const CopyArgs& A, int dtype, int num_sms, cudaStream_t st, int* launches) {
     int parts = (8 * num_sms + A.B - 1) / A.B;

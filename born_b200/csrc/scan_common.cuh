@@ -58,8 +58,6 @@ struct ScanArgs {
     const int32_t* history;
     const int32_t* history_len;
     int history_stride;
-    const unsigned long long* hist_lists;  // [B, BORN_MAX_HISTORY] distinct ids with counts (hist_prep_kernel)
-    const uint32_t* hist_counts;           // [B]
     const born_row_params* row_params;
     born_row_params params;
     const float* uniforms;
@@ -88,7 +86,7 @@ struct ScanArgs {
     int nblk;
     uint32_t* tickets;          // [rows] zero between launches
     uint32_t* deferred;         // [rows] zero between launches: cta+1 that owes the row its exact fallback
-    int* dev_error;                 // [0] error word, [1] rows that took the exact fallback
+    int* dev_error;                 // [0] error word, [1] rows that took the exact search, [8..16] ... by reason
     unsigned long long timeout_ns;  // limit of every on-device wait
     long long debug_skip_tile;      // test hook: the bulk copy of this tile is never issued (-1: none)
 #ifdef BORN_PROFILE
@@ -97,9 +95,12 @@ struct ScanArgs {
 };
 #ifdef BORN_PROFILE
 #define PROF(i) do { if (A.prof && threadIdx.x == 0) A.prof[(size_t)blockIdx.x * 32 + (i)] = (unsigned long long)clock64(); } while (0)
+__device__ unsigned long long* g_prof_ptr;
+#define PROFG(i) do { if (g_prof_ptr && threadIdx.x == 0) g_prof_ptr[(size_t)blockIdx.x * 32 + (i)] = (unsigned long long)clock64(); } while (0)
 #define PROF_ADD(i, v) do { if (A.prof && threadIdx.x == 0) A.prof[(size_t)blockIdx.x * 32 + (i)] += (unsigned long long)(v); } while (0)
 #else
 #define PROF(i) do { } while (0)
+#define PROFG(i) do { } while (0)
 #define PROF_ADD(i, v) do { } while (0)
 #endif
 
@@ -159,7 +160,7 @@ __host__ __device__ inline int cta_of_tile(long long t, long long T, long long G
 
 // Shared-memory layout (dynamic part), computed identically on host and device.
 struct ScanSmem {
-    int tiles, masks, cand, hist, total;
+    int tiles, masks, cand, sel, hist, total;
 };
 __host__ __device__ inline ScanSmem scan_smem_layout(int elem_bytes, bool has_mask, bool has_hist) {
     ScanSmem L;
@@ -167,17 +168,17 @@ __host__ __device__ inline ScanSmem scan_smem_layout(int elem_bytes, bool has_ma
     L.tiles = off; off += kScanStages * kTileBytes;
     L.masks = off; off += has_mask ? kScanStages * ((kTileBytes / elem_bytes / 32 + 8) * 4) : 0;
     off = (off + 127) & ~127;
-    L.cand = off; off += kScanWarps * kWarpCand * 8;  // also the selection's key and mass arrays (2 * kSelCap * 8)
-    L.hist = off; off += has_hist ? BORN_MAX_HISTORY * 8 : 0;
+    L.cand = off; off += kScanWarps * kWarpCand * 8;  // the warps' candidate buffers; the selection's masses once they are read
+    L.sel = off; off += kSelCap * 8;                   // the selection's rank keys
+    L.hist = off; off += has_hist ? BORN_MAX_HISTORY * 8 : 0;  // the segment's distinct history tokens, by tile
     L.total = off;
     return L;
 }
-static_assert(kScanWarps * kWarpCand * 8 >= 2 * kSelCap * 8, "the selection arrays alias the candidate buffers");
+static_assert(kScanWarps * kWarpCand * 8 >= kSelCap * 8, "the selection's masses alias the candidate buffers");
 
 // Static shared state of a CTA of scan_kernel (and of merge_kernel, which uses the selection part).
 struct ScanShared {
     unsigned long long full_bar[kScanStages];
-    unsigned long long ready_bar[kScanStages];
     unsigned long long empty_bar[kScanStages];
     // segment state of the compute threads
     uint32_t maxbits;               // key of the running maximum (only ever raised)
@@ -186,10 +187,6 @@ struct ScanShared {
     float wbound[kScanWarps];       // per warp: its share of the lane-maxima bound
     uint32_t wcount[kScanWarps];    // candidates in each warp's buffer
     float wmax[kScanWarps], wsum[kScanWarps];
-    struct Side {                   // penalised tokens the producer took out of bf16 tiles, per segment
-        float m, s;
-        uint32_t n;
-    } side[kScanStages + 1];
     int fail;
     int prod_done;                  // the producer warp has left its loop
     long long issued;               // ... having issued the tiles below this one

@@ -44,7 +44,6 @@ struct ThreadStats {
     float nRc;  // -R * c2
     float2 s;   // two partial sums of 2^((z - R) * c2)
     float pub;  // largest maximum this thread has published
-    float lost; // largest candidate that found the warp's buffer full
 };
 __device__ __forceinline__ void stats_reset(ThreadStats& st, float c2) {
     st.mx = -INFINITY;
@@ -52,7 +51,6 @@ __device__ __forceinline__ void stats_reset(ThreadStats& st, float c2) {
     st.nRc = 1e30f * c2;
     st.s = make_float2(0.0f, 0.0f);
     st.pub = -INFINITY;
-    st.lost = -INFINITY;
 }
 template <bool kLse>
 __device__ __forceinline__ void stats_one(ThreadStats& st, float z, float c2) {
@@ -89,11 +87,13 @@ __device__ __forceinline__ void lse16(ThreadStats& st, const float (&v)[16], flo
     st.s = __fadd2_rn(st.s, s1);
 }
 
-// One candidate from the lane that found it, into the warp's own buffer.
-__device__ __forceinline__ void push_cand(uint64_t* wbuf, uint32_t* wcount, ThreadStats& st, float z, int id) {
+// One candidate from the lane that found it, into the warp's own buffer.  A candidate that finds
+// the buffer full raises the CTA's exclusion level above itself: nothing at or below that level
+// counts as collected any more, and every warp's threshold follows (current_tau).
+__device__ __forceinline__ void push_cand(uint64_t* wbuf, uint32_t* wcount, uint32_t* excl, float z, int id) {
     const uint32_t pos = smem_atom_add(wcount, 1u);
     if (pos < (uint32_t)kWarpCand) wbuf[pos] = ((uint64_t)__float_as_uint(z) << 32) | (uint32_t)id;
-    else st.lost = fmaxf(st.lost, z);
+    else smem_red_max(excl, key_above(z));
 }
 
 struct SegCtx {   // what the compute threads know about the segment they are in (block-uniform)
@@ -103,9 +103,10 @@ struct SegCtx {   // what the compute threads know about the segment they are in
 };
 
 __device__ __forceinline__ float current_tau(const SegCtx& sg, const ScanShared& sh) {
-    float tau = sg.tau_fix;
-    if (sg.plan.use_max)
-        tau = fmaxf(tau, zkey_to_float(*reinterpret_cast<const volatile uint32_t*>(&sh.maxbits)) + sg.plan.delta);
+    // (maxbits, excl_bits) sit side by side: one 8-byte read
+    const unsigned long long both = *reinterpret_cast<const volatile unsigned long long*>(&sh.maxbits);
+    float tau = fmaxf(sg.tau_fix, zkey_to_float((uint32_t)(both >> 32)));
+    if (sg.plan.use_max) tau = fmaxf(tau, zkey_to_float((uint32_t)both) + sg.plan.delta);
     return tau;
 }
 __device__ __forceinline__ void publish_max(ThreadStats& st, ScanShared& sh) {
@@ -178,11 +179,30 @@ __device__ __forceinline__ void load16(const T* tile, const uint32_t* smask, int
     }
 }
 
+// Element e of a tile as the candidate buffer wants it (the value is re-read from shared
+// memory: a hit is rare, and this keeps the hot loop free of sixteen copies of the push).
+template <typename T>
+__device__ __forceinline__ float tile_elem(const T* tile, int e) {
+    if constexpr (sizeof(T) == 4) return reinterpret_cast<const float*>(tile)[e];
+    else return bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(tile)[e]);
+}
+template <typename T>
+__device__ __forceinline__ void push_hits(uint32_t hits, const T* tile, int h, int id_tile0, ThreadStats& st,
+                                          uint64_t* wbuf, uint32_t* wcount, uint32_t* excl) {
+    constexpr int VEC = VecOf<T>::n, NV = 16 / VEC;
+#pragma unroll 1
+    while (hits) {
+        const int i = __ffs(hits) - 1;
+        hits &= hits - 1;
+        const int e = ((int)threadIdx.x + kThreads * (h * NV + i / VEC)) * VEC + (i % VEC);
+        push_cand(wbuf, wcount, excl, tile_elem<T>(tile, e), id_tile0 + e);
+    }
+}
+
 // A full tile of a 16-byte-aligned row: straight-line code, one compare per 16 values.
-// kStats / kCollect select what the pass does (the first tile of a segment is taken twice).
-template <typename T, bool kMask, bool kLse, bool kStats, bool kCollect>
+template <typename T, bool kMask, bool kLse>
 __device__ __forceinline__ void fast_tile(const T* tile, const uint32_t* smask, int id_tile0, float tau, float c2,
-                                          ThreadStats& st, uint64_t* wbuf, uint32_t* wcount) {
+                                          ThreadStats& st, uint64_t* wbuf, uint32_t* wcount, uint32_t* excl) {
     constexpr int VEC = VecOf<T>::n, NV = 16 / VEC, NB = TileOf<T>::n / (kThreads * 16);
 #pragma unroll
     for (int h = 0; h < NB; ++h) {
@@ -193,16 +213,33 @@ __device__ __forceinline__ void fast_tile(const T* tile, const uint32_t* smask, 
 #pragma unroll
         for (int i = 0; i < 4; ++i) m4[i] = max_nan(max3_nan(v[4 * i], v[4 * i + 1], v[4 * i + 2]), v[4 * i + 3]);
         const float mt = max_nan(max3_nan(m4[0], m4[1], m4[2]), m4[3]);
-        if constexpr (kStats) {
-            st.mx = max_nan(st.mx, mt);
-            if constexpr (kLse) lse16(st, v, mt, c2);
-        }
-        if constexpr (kCollect) {
-            if (mt >= tau) {  // rare per lane
+        st.mx = max_nan(st.mx, mt);
+        if constexpr (kLse) lse16(st, v, mt, c2);
+        if (mt >= tau) {  // rare per lane
+            uint32_t hits = 0;
 #pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    if (v[i] >= tau && v[i] > -INFINITY) push_cand(wbuf, wcount, st, v[i], id_tile0 + e0[i / VEC] + (i % VEC));
-            }
+            for (int i = 0; i < 16; ++i) hits |= (v[i] >= tau && v[i] > -INFINITY) ? (1u << i) : 0u;
+            push_hits<T>(hits, tile, h, id_tile0, st, wbuf, wcount, excl);
+        }
+    }
+    __syncwarp();
+}
+
+// Candidates of a full tile whose statistics were taken before (the first tile of a segment,
+// once its threshold exists): compact code, run once per segment.
+template <typename T, bool kMask>
+__device__ __forceinline__ void collect_tile(const T* tile, const uint32_t* smask, int id_tile0, float tau,
+                                             ThreadStats& st, uint64_t* wbuf, uint32_t* wcount, uint32_t* excl) {
+    constexpr int VEC = VecOf<T>::n, ITER = TileOf<T>::n / (kThreads * VEC);
+#pragma unroll 1
+    for (int j = 0; j < ITER; ++j) {
+        const int e0 = ((int)threadIdx.x + kThreads * j) * VEC;
+        uint32_t bits = 0xFFFFFFFFu;
+        if constexpr (kMask) bits = smask[e0 >> 5] >> (e0 & 31);
+#pragma unroll 1
+        for (int i = 0; i < VEC; ++i) {
+            const float z = tile_elem<T>(tile, e0 + i);
+            if (((bits >> i) & 1u) && z >= tau && z > -INFINITY) push_cand(wbuf, wcount, excl, z, id_tile0 + e0 + i);
         }
     }
     __syncwarp();
@@ -213,11 +250,12 @@ __device__ __forceinline__ void fast_tile(const T* tile, const uint32_t* smask, 
 template <typename T, bool kMask, bool kLse>
 __device__ __forceinline__ void slow_tile(const T* tile, const uint32_t* smask, int64_t mb_rel, int lo, int hi,
                                           int id_tile0, float tau, float c2, bool stats, bool collect,
-                                          ThreadStats& st, uint64_t* wbuf, uint32_t* wcount) {
+                                          ThreadStats& st, uint64_t* wbuf, uint32_t* wcount, uint32_t* excl) {
     constexpr int VEC = VecOf<T>::n, ITER = TileOf<T>::n / (kThreads * VEC);
+#pragma unroll 1
     for (int j = 0; j < ITER; ++j) {
         const int vi = (int)threadIdx.x + kThreads * j;
-#pragma unroll
+#pragma unroll 1
         for (int i = 0; i < VEC; ++i) {
             const int e = vi * VEC + i;
             if (e < lo || e >= hi) continue;
@@ -229,7 +267,7 @@ __device__ __forceinline__ void slow_tile(const T* tile, const uint32_t* smask, 
                 if (!((smask[bi >> 5] >> (bi & 31)) & 1u)) z = -INFINITY;
             }
             if (stats) stats_one<kLse>(st, z, c2);
-            if (collect && z >= tau && z > -INFINITY) push_cand(wbuf, wcount, st, z, id_tile0 + e);
+            if (collect && z >= tau && z > -INFINITY) push_cand(wbuf, wcount, excl, z, id_tile0 + e);
         }
     }
     __syncwarp();
@@ -241,7 +279,7 @@ __device__ __forceinline__ void slow_tile(const T* tile, const uint32_t* smask, 
 template <typename T, bool kMask>
 __device__ __forceinline__ void mass_tile(const T* tile, const uint32_t* smask, int hi, int tok_tile0, int id_tile0,
                                           float tau, float inv_T, bool collect, MassBlock* row_blocks, int nblk,
-                                          ThreadStats& st, ScanShared& sh, uint64_t* wbuf, uint32_t* wcount) {
+                                          ThreadStats& st, ScanShared& sh, uint64_t* wbuf, uint32_t* wcount, uint32_t* excl) {
     constexpr int VEC = VecOf<T>::n, NV = 16 / VEC, NB = TileOf<T>::n / (kThreads * 16);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
@@ -279,9 +317,16 @@ __device__ __forceinline__ void mass_tile(const T* tile, const uint32_t* smask, 
         if (collect) {
             publish_max(st, sh);
             if (mt >= tau) {
+                uint32_t hits = 0;
 #pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    if (v[i] >= tau && v[i] > -INFINITY) push_cand(wbuf, wcount, st, v[i], id_tile0 + e0[i / VEC] + (i % VEC));
+                for (int i = 0; i < 16; ++i) hits |= (v[i] >= tau && v[i] > -INFINITY) ? (1u << i) : 0u;
+#pragma unroll 1
+                while (hits) {
+                    const int i = __ffs(hits) - 1;
+                    hits &= hits - 1;
+                    const int e = (warp * 128 + lane + 32 * (h * NV + i / VEC)) * VEC + (i % VEC);
+                    push_cand(wbuf, wcount, excl, tile_elem<T>(tile, e), id_tile0 + e);
+                }
             }
         }
     }
@@ -331,180 +376,25 @@ __device__ __forceinline__ void producer_issue(const ScanArgs& A, ScanShared& sh
     }
 }
 
-// The distinct history tokens of caller row q.b (hist_prep_kernel left them in scratch with their
-// multiplicities) that fall into tokens [tok_lo, tok_hi) of the virtual row, as
-// (count << 32) | token-within-the-virtual-row.
-__device__ __forceinline__ int producer_history(const ScanArgs& A, const RowGeom& q, unsigned long long* list,
-                                                int tok_lo, int tok_hi) {
-    const int lane = threadIdx.x & 31;
-    const int n = min((int)__ldg(A.hist_counts + q.b), BORN_MAX_HISTORY);
-    const unsigned long long* src = A.hist_lists + (int64_t)q.b * BORN_MAX_HISTORY;
-    int out = 0;
-    // all loads of a round are issued before any is used: one trip to L2 for up to 512 entries
-    for (int base = 0; base < n; base += 512) {
-        unsigned long long e[16];
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-            const int i = base + 32 * k + lane;
-            e[k] = (i < n) ? __ldg(src + i) : ~0ull;
-        }
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-            if (base + 32 * k >= n) break;  // (uniform)
-            const long long tok = (long long)(uint32_t)e[k] - (long long)q.g * A.V;
-            const bool in = e[k] != ~0ull && tok >= tok_lo && tok < tok_hi;
-            const uint32_t inb = __ballot_sync(0xffffffffu, in);
-            if (in) list[out + __popc(inb & ((1u << lane) - 1u))] = (e[k] & 0xFFFFFFFF00000000ull) | (uint32_t)tok;
-            out += __popc(inb);
-        }
-    }
-    __syncwarp();
-    return out;
-}
-
-template <typename T, bool kMask, bool kLse>
+// The producer warp: keeps the ring full.  Step n waits (bounded) for the stage of tile n to be
+// handed back by the compute warps and issues its copy.
+template <typename T, bool kMask>
 __device__ __forceinline__ void producer_loop(const ScanArgs& A, ScanShared& sh, uint8_t* smem, const ScanSmem& L,
                                               long long t0, long long t1) {
-    constexpr int TILE = TileOf<T>::n;
     const int lane = threadIdx.x & 31;
-    const bool use_ready = A.history != nullptr;
-    const int cta = blockIdx.x;
-    unsigned long long* table = reinterpret_cast<unsigned long long*>(smem + L.hist);
-    long long issue_t = t0, patch_t = t0;
-    int cur_row = -1, nlist = 0, seg_ord = -1;
-    RowGeom q = {};
-    born_row_params rp = {};
-    RowPlan plan = {};
-    bool pen = false;
-    // statistics of the penalised tokens that were taken out of bf16 tiles
-    float p_mx = -INFINITY, p_R = -1e30f, p_s = 0.0f;
-    uint32_t p_n = 0;
-    // A software pipeline with blocking (bounded) waits: step n first patches tile n - lag, whose
-    // copy was issued lag steps ago, and releases it to the compute warps; then it waits for the
-    // stage of tile n to be handed back and issues its copy.  The tile the compute warps need
-    // next is therefore patched while they still work on the one before.
-    constexpr int lag = kScanStages - 1;
+    long long issue_t = t0;
     const long long n_tiles = t1 - t0;
     bool ok = true;
-    for (long long n = 0; ok && n < n_tiles + (use_ready ? lag : 0); ++n) {
-        if (use_ready && n >= lag) {
-            {
-                const long long i = n - lag;
-                const int stage = (int)(i % kScanStages);
-                if (!mbar_wait_limit(reinterpret_cast<uint64_t*>(&sh.full_bar[stage]), (uint32_t)(i / kScanStages) & 1u, A.timeout_ns,
-                                     &sh.fail)) {
-                    ok = false;
-                    break;
-                }
-                patch_t = t0 + i;
-                const TilePos p = tile_pos(patch_t, A.tpr);
-                if (p.row != cur_row) {  // first tile of a segment: its history list
-                    cur_row = p.row;
-                    ++seg_ord;
-                    q = row_geom<T>(A, p.row);
-                    rp = A.row_params ? A.row_params[q.b] : A.params;
-                    plan = row_plan(rp);
-                    pen = penalties_on(rp);
-                    nlist = 0;
-                    if (pen) {
-                        const long long seg_t0 = max(t0, (long long)p.row * A.tpr), seg_t1 = min(t1, (long long)(p.row + 1) * A.tpr);
-                        const long long e_lo = (seg_t0 - (long long)p.row * A.tpr) * TILE, e_hi = (seg_t1 - (long long)p.row * A.tpr) * TILE;
-                        const int tok_lo = (int)max(0ll, e_lo - q.lead), tok_hi = (int)min((long long)A.V, e_hi - q.lead);
-                        nlist = producer_history(A, q, table, tok_lo, tok_hi);
-                    }
-                    p_mx = -INFINITY; p_R = -1e30f; p_s = 0.0f; p_n = 0;
-                }
-                T* tile = reinterpret_cast<T*>(smem + L.tiles + (size_t)stage * kTileBytes);
-                const int n_el = min(TILE, q.lead + A.V - p.j * TILE);
-                const int lo = max(0, q.lead - p.j * TILE);
-                bool wrote = false;
-                if (nlist > 0 && n_el > lo) {
-                    const uint32_t* smask = reinterpret_cast<const uint32_t*>(smem + L.masks + (size_t)stage * (mask_stage_words<T>() * 4));
-                    MaskTile mt = {};
-                    if constexpr (kMask) mt = mask_tile<T>(A, q, p.j, lo, n_el);
-                    uint64_t* rec_ent = reinterpret_cast<uint64_t*>(A.records + (int64_t)(p.row + cta) * A.rec_stride + kRecordHdrBytes);
-                    const int id0 = A.idx_base + q.g * A.V;
-                    for (int base = 0; base < nlist; base += 32) {
-                        const int i2 = base + lane;
-                        bool side = false;
-                        float zp = -INFINITY;
-                        int tok = 0;
-                        if (i2 < nlist) {
-                            const unsigned long long e = table[i2];
-                            tok = (int)(uint32_t)e;
-                            const int cnt = (int)(e >> 32);
-                            const int off = tok + q.lead - p.j * TILE;
-                            if (off >= lo && off < n_el) {
-                                float z;
-                                if constexpr (sizeof(T) == 4) z = reinterpret_cast<float*>(tile)[off];
-                                else z = bf16_bits_to_f32(reinterpret_cast<uint16_t*>(tile)[off]);
-                                zp = penalise(rp, z, cnt);
-                                if constexpr (sizeof(T) == 4) {
-                                    reinterpret_cast<float*>(tile)[off] = zp;
-                                } else {
-                                    reinterpret_cast<uint16_t*>(tile)[off] = 0xFF80u;  // -inf: the token leaves the tile
-                                    if constexpr (kMask) {
-                                        const int64_t bi = mt.mb0 + off - 32 * mt.w0a;
-                                        if (!((smask[bi >> 5] >> (bi & 31)) & 1u)) zp = -INFINITY;
-                                    }
-                                    side = true;
-                                }
-                                wrote = true;
-                            }
-                        }
-                        if constexpr (sizeof(T) == 2) {
-                            // the penalised value joins the segment's statistics and, if it can matter, its record
-                            if (side) {
-                                p_mx = max_nan(p_mx, zp);
-                                if (kLse && zp > -INFINITY && zp < INFINITY) {
-                                    if (zp > p_R) { p_s *= ex2_approx(__fmul_rn(p_R - zp, plan.c2)); p_R = zp; }
-                                    p_s += ex2_approx(__fmul_rn(zp - p_R, plan.c2));
-                                }
-                            }
-                            const bool keep = side && plan.collect && zp > -INFINITY;
-                            const uint32_t kb = __ballot_sync(0xffffffffu, keep);
-                            if (keep) {
-                                const uint32_t pos = p_n + __popc(kb & ((1u << lane) - 1u));
-                                if (pos < (uint32_t)A.rec_cap)
-                                    rec_ent[pos] = ((uint64_t)__float_as_uint(zp) << 32) | (uint32_t)(id0 + tok);
-                            }
-                            p_n += __popc(kb);
-                        }
-                    }
-                }
-                if constexpr (sizeof(T) == 2) {
-                    // last tile of the segment: leave the side statistics where the compute threads find them
-                    const bool seg_end = (patch_t + 1 == t1) || (tile_pos(patch_t + 1, A.tpr).row != cur_row);
-                    if (seg_end) {
-                        const float wm = warp_max_nan(p_mx);
-                        float ws = 0.0f;
-                        if (kLse) {
-                            ws = (p_s > 0.0f && wm == wm) ? p_s * ex2_approx(__fmul_rn(p_R - wm, plan.c2)) : 0.0f;
-#pragma unroll
-                            for (int d = 16; d > 0; d >>= 1) ws += __shfl_xor_sync(0xffffffffu, ws, d);
-                        }
-                        if (lane == 0) {
-                            ScanShared::Side& sd = sh.side[seg_ord % (kScanStages + 1)];
-                            sd.m = wm; sd.s = ws; sd.n = p_n;
-                        }
-                    }
-                }
-                if (wrote) fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(&sh.ready_bar[stage]));
-            }
+    for (long long n = 0; n < n_tiles; ++n) {
+        const int stage = (int)(n % kScanStages);
+        if (n >= kScanStages &&
+            !mbar_wait_limit(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage]), (uint32_t)((n / kScanStages) - 1) & 1u,
+                             A.timeout_ns, &sh.fail)) {
+            ok = false;
+            break;
         }
-        if (n < n_tiles) {
-            const int stage = (int)(n % kScanStages);
-            if (n >= kScanStages &&
-                !mbar_wait_limit(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage]), (uint32_t)((n / kScanStages) - 1) & 1u,
-                                 A.timeout_ns, &sh.fail)) {
-                ok = false;
-                break;
-            }
-            if (lane == 0) producer_issue<T, kMask>(A, sh, smem, L, t0 + n, stage);
-            issue_t = t0 + n + 1;
-        }
+        if (lane == 0) producer_issue<T, kMask>(A, sh, smem, L, t0 + n, stage);
+        issue_t = t0 + n + 1;
     }
     if (!ok) sh.fail = 1;
     // what the failure path of the compute threads needs to know (see the end of scan_kernel)
@@ -513,6 +403,192 @@ __device__ __forceinline__ void producer_loop(const ScanArgs& A, ScanShared& sh,
         __threadfence_block();
         *reinterpret_cast<volatile int*>(&sh.prod_done) = 1;
     }
+}
+
+// ---- token history -----------------------------------------------------------------------------
+// Penalties touch at most BORN_MAX_HISTORY tokens of a row.  At the start of a segment the
+// compute threads turn the row's history into a list of its distinct tokens with their
+// multiplicities, grouped by the tile they fall into (only the tiles of this segment): a hash
+// table in the candidate area (empty at that point) removes the repeats, counters in the
+// selection area -- per (tile, warp) while the tiles are few, so that the warps do not meet on
+// the same word -- drive a counting sort into the list.  The global read of the ids is the only
+// memory round trip; it leaves before the CTA's first copies.
+//
+// While streaming, every warp walks the list in step with the tiles: the entries of tile j sit
+// at the cursor, a warp applies those that fall into its own share of the tile -- the warp that
+// reads an element is the only one that ever touches it, so a warp-level sync is all it takes.
+// fp32: the penalised value replaces the logit in the tile.  bf16 (a bf16 tile cannot hold it):
+// the token is taken out of the tile (-inf) and its penalised value goes to the statistics and
+// the candidates directly.
+constexpr int kHistPer = BORN_MAX_HISTORY / kThreads;  // history ids per compute thread
+struct HistCursor {
+    int n, pos;
+};
+
+__device__ __forceinline__ void hist_ids(const ScanArgs& A, int b, int (&ids)[kHistPer]) {
+    // the ids do not wait for the length: both reads leave together, the length cuts afterwards
+    const int cap = min(A.history_stride, (int)BORN_MAX_HISTORY);
+    const int32_t* gh = A.history + (int64_t)b * A.history_stride;
+#pragma unroll
+    for (int r = 0; r < kHistPer; ++r) {
+        const int p = (int)threadIdx.x + r * kThreads;
+        ids[r] = p < cap ? __ldg(gh + p) : -1;
+    }
+    const int len = A.history_len ? __ldg(A.history_len + b) : cap;
+#pragma unroll
+    for (int r = 0; r < kHistPer; ++r)
+        if ((int)threadIdx.x + r * kThreads >= len) ids[r] = -1;
+}
+
+template <int TILE>
+__device__ __forceinline__ int hist_build(const ScanArgs& A, const int (&ids)[kHistPer], int g, int lead, int j_begin, int j_end,
+                                          uint32_t* keys, uint32_t* cnt32, unsigned long long* list, uint32_t* wscr) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int span = j_end - j_begin;
+    // the table: a power of two of at least twice the ids there can be
+    const int cap = min(A.history_stride, (int)BORN_MAX_HISTORY);
+    int lg = 6;
+    while ((1 << lg) < 2 * cap) ++lg;
+    const int slots = 1 << lg;
+    uint32_t* mult = keys + slots;  // repeats, beside the keys
+    const int P = span <= 128 ? kScanWarps : 1;
+    const int nc = span * P;
+    PROF(25);
+    {
+        uint4* k4 = reinterpret_cast<uint4*>(keys);
+        uint4* m4 = reinterpret_cast<uint4*>(mult);
+        for (int i = tid; i < slots / 4; i += kThreads) {
+            k4[i] = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu);
+            m4[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        for (int i = tid; i < nc / 2 + 1; i += kThreads) cnt32[i] = 0;
+    }
+    cta_sync();
+    PROF(26);
+    // (shared-memory atomics are what this build costs: one per id for the table, one per new
+    // token to count it, one to place it)
+    int ctr_of[kHistPer];  // the token's counter if this thread was the first to insert it, else -1
+#pragma unroll
+    for (int r = 0; r < kHistPer; ++r) {
+        ctr_of[r] = -1;
+        const int id = ids[r];
+        if (id < 0) continue;
+        int g2 = 0;
+        uint32_t tok = (uint32_t)id;
+        if (A.G > 1) { g2 = id / A.V; tok = (uint32_t)(id - g2 * A.V); }
+        if (g2 != g || tok >= (uint32_t)A.V) continue;  // another vocabulary segment's token, or an id beyond the vocabulary
+        const int tl = (int)((tok + (uint32_t)lead) / (uint32_t)TILE);
+        if (tl < j_begin || tl >= j_end) continue;
+        uint32_t slot = (tok * 2654435761u) >> (32 - lg);
+        for (int probe = 0; probe < slots; ++probe) {
+            const uint32_t old = atomicCAS(&keys[slot], 0xFFFFFFFFu, tok);
+            if (old == 0xFFFFFFFFu) {  // the first of its kind: this thread will place it
+                const int c = (tl - j_begin) * P + (P > 1 ? warp : 0);
+                smem_red_add(&cnt32[c >> 1], 1u << (16 * (c & 1)));
+                ctr_of[r] = c;
+                break;
+            }
+            if (old == tok) {  // a repeat
+                smem_red_add(&mult[slot], 1u);
+                break;
+            }
+            slot = (slot + 1) & (slots - 1);
+        }
+    }
+    PROF(29);
+    cta_sync();
+    PROF(27);
+    // exclusive scan of the counters (a thread takes `per` consecutive ones)
+    uint16_t* cnt16 = reinterpret_cast<uint16_t*>(cnt32);
+    const int per = (nc + kThreads - 1) / kThreads;
+    const int lo = min(tid * per, nc), hi = min(lo + per, nc);
+    uint32_t loc = 0;
+    for (int i = lo; i < hi; ++i) loc += cnt16[i];
+    uint32_t incl = loc;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t up = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += up;
+    }
+    if (lane == 31) wscr[warp] = incl;
+    cta_sync();
+    uint32_t off = 0, n = 0;
+#pragma unroll
+    for (int w = 0; w < kScanWarps; ++w) {
+        const uint32_t x = wscr[w];
+        if (w < warp) off += x;
+        n += x;
+    }
+    uint32_t run = off + incl - loc;
+    for (int i = lo; i < hi; ++i) {
+        const uint32_t c = cnt16[i];
+        cnt16[i] = (uint16_t)run;  // becomes the counter's write cursor
+        run += c;
+    }
+    cta_sync();
+#pragma unroll
+    for (int r = 0; r < kHistPer; ++r) {
+        const int c = ctr_of[r];
+        if (c < 0) continue;
+        uint32_t tok = (uint32_t)ids[r];
+        if (A.G > 1) tok -= (uint32_t)((ids[r] / A.V) * A.V);
+        uint32_t slot = (tok * 2654435761u) >> (32 - lg);  // (found again: cheaper than carried along)
+        while (keys[slot] != tok) slot = (slot + 1) & (slots - 1);
+        const uint32_t old = smem_atom_add(&cnt32[c >> 1], 1u << (16 * (c & 1)));
+        list[(old >> (16 * (c & 1))) & 0xFFFFu] = ((unsigned long long)(mult[slot] + 1u) << 32) | tok;
+    }
+    cta_sync();
+    PROF(28);
+    return (int)n;
+}
+
+// The history tokens of tile j, by the warp.  Bits of `mode`: 2 statistics of the values taken
+// out of a bf16 tile, 4 their candidates (all of them when tau is -inf).  Returns whether the
+// warp wrote to the tile.
+template <typename T, bool kMask, bool kLse>
+__device__ __forceinline__ bool hist_apply(HistCursor& hc, const unsigned long long* list, const born_row_params& rp, T* tile,
+                                           const uint32_t* smask, int64_t mb_rel, int j, int lead, int lo_el, int n_el,
+                                           bool slices, int mode, int id_row0, float tau, float c2, ThreadStats& st,
+                                           uint64_t* wbuf, uint32_t* wcount, uint32_t* excl) {
+    constexpr int TILE = TileOf<T>::n, VEC = VecOf<T>::n;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    bool wrote = false;
+    int pos = hc.pos;
+    for (;;) {
+        const int idx = pos + lane;
+        const unsigned long long e = idx < hc.n ? list[idx] : ~0ull;
+        const int tok = (int)(uint32_t)e;
+        const int off = tok + lead - j * TILE;
+        const bool in = idx < hc.n && off >= 0 && off < TILE;
+        const int c = __popc(__ballot_sync(0xffffffffu, in));
+        if (in && off >= lo_el && off < n_el) {
+            const int vec = off / VEC;
+            const int owner = slices ? (vec >> 7) : ((vec & (kThreads - 1)) >> 5);
+            if (owner == warp) {
+                const int cnt = (int)(e >> 32);
+                if constexpr (sizeof(T) == 4) {
+                    float* pz = reinterpret_cast<float*>(tile) + off;
+                    *pz = penalise(rp, *pz, cnt);
+                } else {
+                    uint16_t* pz = reinterpret_cast<uint16_t*>(tile) + off;
+                    float zp = penalise(rp, bf16_bits_to_f32(*pz), cnt);
+                    if constexpr (kMask) {
+                        const int64_t bi = mb_rel + off;
+                        if (!((smask[bi >> 5] >> (bi & 31)) & 1u)) zp = -INFINITY;
+                    }
+                    *pz = 0xFF80u;
+                    if (mode & 2) stats_one<kLse>(st, zp, c2);
+                    if ((mode & 4) && zp >= tau && zp > -INFINITY) push_cand(wbuf, wcount, excl, zp, id_row0 + tok);
+                }
+                wrote = true;
+            }
+        }
+        pos += c;
+        if (c < 32) break;
+    }
+    hc.pos = pos;
+    __syncwarp();
+    return __any_sync(0xffffffffu, wrote);
 }
 
 // ---- the kernel -------------------------------------------------------------------------------
@@ -527,12 +603,9 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
     const long long T_total = rows * A.tpr;
     const long long ncta = gridDim.x;
     const long long t0 = range_begin(blockIdx.x, T_total, ncta), t1 = range_begin(blockIdx.x + 1, T_total, ncta);
-    const bool use_ready = A.history != nullptr;
-
     if (tid == 0) {
         for (int s = 0; s < kScanStages; ++s) {
             mbar_init(reinterpret_cast<uint64_t*>(&sh.full_bar[s]), 1);
-            mbar_init(reinterpret_cast<uint64_t*>(&sh.ready_bar[s]), 1);
             mbar_init(reinterpret_cast<uint64_t*>(&sh.empty_bar[s]), kScanWarps);
         }
         mbar_fence_init();
@@ -540,28 +613,42 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
         sh.prod_done = 0;
         sh.issued = t0;
     }
+    // The history ids of the CTA's first row go ahead of the bulk copies: behind them they
+    // would wait in the memory system's queues.
+    int ids[kHistPer];
+#pragma unroll
+    for (int r = 0; r < kHistPer; ++r) ids[r] = -1;
+    if (A.history != nullptr && tid < kThreads && t0 < t1) hist_ids(A, (int)(t0 / A.tpr) / A.G, ids);
     __syncthreads();  // the only barrier all 288 threads share
 
     if (tid >= kThreads) {
-        producer_loop<T, kMask, kLse>(A, sh, smem, L, t0, t1);
+        producer_loop<T, kMask>(A, sh, smem, L, t0, t1);
         return;
     }
 
     // ------------------------------------------------------------------------ compute threads
     PROF(0);
+#ifdef BORN_PROFILE
+    if (tid == 0) g_prof_ptr = A.prof;
+    if (A.prof && tid == 0) A.prof[(size_t)blockIdx.x * 32 + 11] = global_timer_ns();
+#endif
     const int lane = tid & 31, warp = tid >> 5;
     uint64_t* wbuf = reinterpret_cast<uint64_t*>(smem + L.cand) + warp * kWarpCand;
     uint32_t* wcount = &sh.wcount[warp];
+    uint32_t* excl = &sh.excl_bits;
 #ifdef BORN_PROFILE
-    long long pf_wait = 0, pf_proc = 0;
+    long long pf_wait = 0, pf_proc = 0, pf_hist = 0;
 #endif
     bool failed = false;
     int bad = 0;
     int seg_ord = -1;
     long long t = t0;
+    int stage = 0;         // ring stage of tile t
+    uint32_t phase = 0;    // ... and the parity of its use
     while (t < t1) {
         // ---- segment set-up (block-synchronous)
         const TilePos p0 = tile_pos(t, A.tpr);
+        const long long seg_begin = t;
         const long long seg_end = min(t1, (long long)(p0.row + 1) * A.tpr);
         ++seg_ord;
         const RowGeom q = row_geom<T>(A, p0.row);
@@ -577,7 +664,10 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
             sh.maxbits = zkey(-INFINITY);
             sh.excl_bits = zkey(-INFINITY);
             sh.rec_count = 0;
+            sh.nl = 0;  // (the row's finish counts its candidates here)
         }
+        // the row's uniform is wanted at the very end: fetch it now
+        const float u_row = (A.uniforms != nullptr && A.mode == kScanFull) ? __ldg(A.uniforms + q.b) : 0.0f;
         if (tid < kScanWarps) { sh.wbound[tid] = -INFINITY; sh.wcount[tid] = 0; }
         cta_sync();
         ThreadStats st;
@@ -585,16 +675,69 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
         MassBlock* row_blocks = A.blocks + (int64_t)p0.row * A.nblk;
         const bool collect = pl.collect && !pl.no_bound;
         int seen = 0;  // tiles of this segment done
-        for (; t < seg_end; ++t, ++seen) {
-            const long long i = t - t0;
-            const int stage = (int)(i % kScanStages);
-            const int j = (int)(t - (long long)p0.row * A.tpr);
+        int j = (int)(t - (long long)p0.row * A.tpr);       // tile within the row
+        int rem = q.lead + A.V - j * TILE;                  // elements of the row from this tile on
+        const int j_end = (int)(seg_end - (long long)p0.row * A.tpr);
+        HistCursor hc;
+        hc.n = 0; hc.pos = 0;
+        const unsigned long long* hlist = reinterpret_cast<const unsigned long long*>(smem + L.hist);
+        if (A.history != nullptr) {
+            if (seg_ord > 0) hist_ids(A, q.b, ids);  // (those of the CTA's first row were fetched before the first copy)
+            if (penalties_on(rp))
+                hc.n = hist_build<TILE>(A, ids, q.g, q.lead, j, j_end, reinterpret_cast<uint32_t*>(smem + L.cand),
+                                        reinterpret_cast<uint32_t*>(smem + L.sel), reinterpret_cast<unsigned long long*>(smem + L.hist),
+                                        reinterpret_cast<uint32_t*>(sh.red64));
+        }
+        const bool hist_on = hc.n > 0;
+        const bool lean = A.fast && !pl.need_mass;
+        for (; t < seg_end; ++t, ++seen, ++j, rem -= TILE) {
+            // ---- steady state: the full tiles of an aligned row after the segment's first tile.
+            // Everything that is decided per segment stays outside; what is left per tile is the
+            // wait, one read of the thresholds, the straight-line tile body and the hand-back.
+            if (lean && seen > 0 && !failed) {
+                while (t < seg_end && rem >= TILE) {
+#ifdef BORN_PROFILE
+                    const long long qw0 = clock64();
+#endif
+                    uint64_t* fb = reinterpret_cast<uint64_t*>(&sh.full_bar[stage]);
+                    bool here = mbar_try(fb, phase);
+                    if (!here) here = mbar_wait_limit(fb, phase, A.timeout_ns, &sh.fail);
+                    if (!__all_sync(0xffffffffu, here)) {
+                        failed = true;
+                        sh.fail = 1;
+                        break;
+                    }
+#ifdef BORN_PROFILE
+                    const long long qw1 = clock64();
+                    pf_wait += qw1 - qw0;
+#endif
+                    T* tile = reinterpret_cast<T*>(smem + L.tiles + stage * kTileBytes);
+                    const uint32_t* smask = reinterpret_cast<const uint32_t*>(smem + L.masks + stage * (mask_stage_words<T>() * 4));
+                    const float tau = collect ? current_tau(sg, sh) : INFINITY;
+                    bool patched = false;
+                    if (hist_on)
+                        patched = hist_apply<T, kMask, kLse>(hc, hlist, rp, tile, smask, 0, j, 0, 0, TILE, false, 6, sg.id0, tau, pl.c2, st,
+                                                             wbuf, wcount, excl);
+                    fast_tile<T, kMask, kLse>(tile, smask, sg.id0 + j * TILE, tau, pl.c2, st, wbuf, wcount, excl);
+                    if (pl.use_max) publish_max(st, sh);
+                    if (pl.lane_bound && ((seen + 1) & seen) == 0) sg.tau_fix = fmaxf(sg.tau_fix, lane_bound(sh, pl.k, st.mx));
+                    if (patched) fence_proxy_async();  // the stage is next written by a bulk copy
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage]));
+                    if (++stage == kScanStages) { stage = 0; phase ^= 1u; }
+                    ++t; ++seen; ++j; rem -= TILE;
+#ifdef BORN_PROFILE
+                    pf_proc += clock64() - qw1;
+#endif
+                }
+                if (t >= seg_end) break;
+            }
 #ifdef BORN_PROFILE
             const long long pw0 = clock64();
 #endif
             if (!failed) {
-                uint64_t* bar = reinterpret_cast<uint64_t*>(use_ready ? &sh.ready_bar[stage] : &sh.full_bar[stage]);
-                if (!mbar_wait_limit(bar, (uint32_t)(i / kScanStages) & 1u, A.timeout_ns, &sh.fail)) {
+                const bool here = mbar_wait_limit(reinterpret_cast<uint64_t*>(&sh.full_bar[stage]), phase, A.timeout_ns, &sh.fail);
+                if (!__all_sync(0xffffffffu, here)) {  // (the warp gives up as one: what follows votes and shuffles)
                     failed = true;
                     sh.fail = 1;
                 }
@@ -604,9 +747,9 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
             pf_wait += pw1 - pw0;
             if (t == t0) PROF(1);
 #endif
-            const T* tile = reinterpret_cast<const T*>(smem + L.tiles + (size_t)stage * kTileBytes);
-            const uint32_t* smask = reinterpret_cast<const uint32_t*>(smem + L.masks + (size_t)stage * (mask_stage_words<T>() * 4));
-            const int n_el = min(TILE, q.lead + A.V - j * TILE);
+            T* tile = reinterpret_cast<T*>(smem + L.tiles + stage * kTileBytes);
+            const uint32_t* smask = reinterpret_cast<const uint32_t*>(smem + L.masks + stage * (mask_stage_words<T>() * 4));
+            const int n_el = min(TILE, rem);
             const int lo = max(0, q.lead - j * TILE);
             const int tok_tile0 = j * TILE - q.lead;          // token (within the virtual row) of element 0
             const int id_tile0 = sg.id0 + tok_tile0;
@@ -619,20 +762,37 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                 }
             }
             const bool first = (seen == 0);
+            bool patched = false;
+#ifdef BORN_PROFILE
+            const long long ph0 = clock64();
+#endif
+            if (hist_on && !failed) {
+                // (a bf16 segment's first tile: no threshold exists yet, and the values are gone from the
+                // tile when one does -- every finite one is offered; the finish drops what lies below its cut)
+                const float tau_h = !collect ? INFINITY : (first ? -INFINITY : current_tau(sg, sh));
+                patched = hist_apply<T, kMask, kLse>(hc, hlist, rp, tile, smask, mb_rel, j, q.lead, lo, n_el, pl.need_mass, 6, sg.id0,
+                                                     tau_h, pl.c2, st, wbuf, wcount, excl);
+            }
+#ifdef BORN_PROFILE
+            pf_hist += clock64() - ph0;
+#endif
             if (!failed && n_el > lo) {
                 if (pl.need_mass) {
                     // (rows of these routes are 16-byte aligned: the host sees to it)
                     const float tau = first ? INFINITY : current_tau(sg, sh);
                     mass_tile<T, kMask>(tile, smask, n_el, tok_tile0, id_tile0, tau, pl.inv_T, collect && !first, row_blocks, A.nblk,
-                                        st, sh, wbuf, wcount);
+                                        st, sh, wbuf, wcount, excl);
                 } else if (first) {
-                    if (full) fast_tile<T, kMask, kLse, true, false>(tile, smask, id_tile0, 0.0f, pl.c2, st, wbuf, wcount);
-                    else slow_tile<T, kMask, kLse>(tile, smask, mb_rel, lo, n_el, id_tile0, 0.0f, pl.c2, true, false, st, wbuf, wcount);
+                    // statistics only: the threshold does not exist yet (tau = +inf collects nothing)
+                    if (full) fast_tile<T, kMask, kLse>(tile, smask, id_tile0, INFINITY, pl.c2, st, wbuf, wcount, excl);
+                    else slow_tile<T, kMask, kLse>(tile, smask, mb_rel, lo, n_el, id_tile0, 0.0f, pl.c2, true, false, st, wbuf, wcount, excl);
                 } else {
+                    {
                     const float tau = collect ? current_tau(sg, sh) : INFINITY;
-                    if (full) fast_tile<T, kMask, kLse, true, true>(tile, smask, id_tile0, tau, pl.c2, st, wbuf, wcount);
-                    else slow_tile<T, kMask, kLse>(tile, smask, mb_rel, lo, n_el, id_tile0, tau, pl.c2, true, collect, st, wbuf, wcount);
+                    if (full) fast_tile<T, kMask, kLse>(tile, smask, id_tile0, tau, pl.c2, st, wbuf, wcount, excl);
+                    else slow_tile<T, kMask, kLse>(tile, smask, mb_rel, lo, n_el, id_tile0, tau, pl.c2, true, collect, st, wbuf, wcount, excl);
                     if (pl.use_max) publish_max(st, sh);
+                    }
                 }
             }
             if (first) {
@@ -652,32 +812,19 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                 }
                 if (!failed && collect && n_el > lo) {
                     const float tau = current_tau(sg, sh);
-                    if (pl.need_mass) {
-                        // collect only: the values are read again, no mass work
-                        slow_tile<T, kMask, false>(tile, smask, mb_rel, lo, n_el, id_tile0, tau, pl.c2, false, true, st, wbuf, wcount);
-                    } else if (full) {
-                        fast_tile<T, kMask, kLse, false, true>(tile, smask, id_tile0, tau, pl.c2, st, wbuf, wcount);
-                    } else {
-                        slow_tile<T, kMask, kLse>(tile, smask, mb_rel, lo, n_el, id_tile0, tau, pl.c2, false, true, st, wbuf, wcount);
-                    }
+                    // collect only: the values are read again
+                    if (full) collect_tile<T, kMask>(tile, smask, id_tile0, tau, st, wbuf, wcount, excl);
+                    else slow_tile<T, kMask, kLse>(tile, smask, mb_rel, lo, n_el, id_tile0, tau, pl.c2, false, true, st, wbuf, wcount, excl);
                 }
             } else if (pl.lane_bound && ((seen + 1) & seen) == 0) {
                 // tighten the bound when the number of tiles seen doubles (no barrier: values of
                 // warps that lag are older, hence lower, hence still valid)
                 sg.tau_fix = fmaxf(sg.tau_fix, lane_bound(sh, pl.k, st.mx));
             }
-            // a lane that lost a candidate to a full buffer raises the warp's exclusion level
-            if (collect && __any_sync(0xffffffffu, st.lost > -INFINITY)) {
-                float lw = st.lost;
-#pragma unroll
-                for (int d = 16; d > 0; d >>= 1) lw = fmaxf(lw, __shfl_xor_sync(0xffffffffu, lw, d));
-                const uint32_t kx = key_above(lw);
-                if (lane == 0) smem_red_max(&sh.excl_bits, kx);
-                sg.tau_fix = fmaxf(sg.tau_fix, zkey_to_float(kx));
-                st.lost = -INFINITY;
-            }
+            if (patched) fence_proxy_async();  // the stage is next written by a bulk copy
             __syncwarp();
             if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage]));  // tile back to the producer
+            if (++stage == kScanStages) { stage = 0; phase ^= 1u; }
 #ifdef BORN_PROFILE
             pf_proc += clock64() - pw1;
 #endif
@@ -695,16 +842,8 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
         }
         if (pl.lane_bound) lane_bound(sh, pl.k, st.mx);
         if (lane == 0) { sh.wmax[warp] = wm; sh.wsum[warp] = ws; }
-        uint32_t side_n = 0;
-        float side_m = -INFINITY, side_s = 0.0f;
-        if (sizeof(T) == 2 && use_ready) {
-            const ScanShared::Side& sd = sh.side[seg_ord % (kScanStages + 1)];
-            side_n = sd.n; side_m = sd.m; side_s = sd.s;
-            if (tid == 0) sh.rec_count = min(side_n, (uint32_t)A.rec_cap);
-            if (tid == 0 && side_n > (uint32_t)A.rec_cap) sh.excl_bits = zkey(INFINITY);  // cannot tell what was lost
-        }
         cta_sync();
-        float m_seg = max_nan(sh.wmax[0], side_m);
+        float m_seg = sh.wmax[0];
 #pragma unroll
         for (int w = 1; w < kScanWarps; ++w) m_seg = max_nan(m_seg, sh.wmax[w]);
         float s_seg = 0.0f;
@@ -714,7 +853,6 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                 const float x = sh.wsum[w];
                 if (x > 0.0f) s_seg += x * ex2_approx(__fmul_rn(sh.wmax[w] - m_seg, pl.c2));
             }
-            if (side_s > 0.0f) s_seg += side_s * ex2_approx(__fmul_rn(side_m - m_seg, pl.c2));
         }
         float bound_k = -INFINITY;
         if (pl.lane_bound) {
@@ -729,74 +867,103 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
             if (pl.window) excl_window = m_seg + pl.delta;
             cut = fmaxf(cut, m_seg + pl.delta);
         }
-        uint8_t* rec = A.records + (int64_t)(p0.row + (int)blockIdx.x) * A.rec_stride;
-        uint64_t* ent = reinterpret_cast<uint64_t*>(rec + kRecordHdrBytes);
-        if (!failed && collect) {
-            const uint32_t nw = min(*wcount, (uint32_t)kWarpCand);
-            float lost2 = -INFINITY;
-            for (uint32_t base = 0; base < nw; base += 32) {
-                const uint32_t i2 = base + lane;
-                uint64_t e = 0;
-                bool ok = false;
-                float z = -INFINITY;
-                if (i2 < nw) {
-                    e = wbuf[i2];
-                    z = __uint_as_float((uint32_t)(e >> 32));
-                    ok = z >= cut;
+        // A row that this CTA streamed from its first tile to its last needs no record and no
+        // ticket: it is finished straight from shared memory.
+        const bool whole = seg_begin == (long long)p0.row * A.tpr && seg_end == (long long)(p0.row + 1) * A.tpr;
+        RowSrc src;
+        src.b = q.b; src.g = q.g; src.u = u_row; src.rp = rp; src.plan = pl;
+        bool finish_here;
+        if (whole) {
+            if (cta_sync_or(*reinterpret_cast<const volatile int*>(&sh.fail))) { bad = 1; break; }
+            PROF(3 + 3 * min(seg_ord, 1));
+            src.direct = true;
+            src.m = m_seg; src.ls = s_seg; src.bk = bound_k;
+            src.taux = pl.no_bound ? INFINITY : fmaxf(zkey_to_float(sh.excl_bits), excl_window);
+            src.wbuf = reinterpret_cast<const uint64_t*>(smem + L.cand);
+            src.wcount = sh.wcount;
+            src.c_first = (int)blockIdx.x; src.nseg = 1;
+            finish_here = true;
+        } else {
+            uint8_t* rec = A.records + (int64_t)(p0.row + (int)blockIdx.x) * A.rec_stride;
+            uint64_t* ent = reinterpret_cast<uint64_t*>(rec + kRecordHdrBytes);
+            if (!failed && collect) {
+                const uint32_t nw = min(*wcount, (uint32_t)kWarpCand);
+                float lost2 = -INFINITY;
+                for (uint32_t base = 0; base < nw; base += 32) {
+                    const uint32_t i2 = base + lane;
+                    uint64_t e = 0;
+                    bool ok = false;
+                    float z = -INFINITY;
+                    if (i2 < nw) {
+                        e = wbuf[i2];
+                        z = __uint_as_float((uint32_t)(e >> 32));
+                        ok = z >= cut;
+                    }
+                    const uint32_t okb = __ballot_sync(0xffffffffu, ok);
+                    uint32_t basepos = 0;
+                    if (lane == 0 && okb) basepos = smem_atom_add(&sh.rec_count, (uint32_t)__popc(okb));
+                    basepos = __shfl_sync(0xffffffffu, basepos, 0);
+                    if (ok) {
+                        const uint32_t pos = basepos + __popc(okb & ((1u << lane) - 1u));
+                        if (pos < (uint32_t)A.rec_cap) ent[pos] = e;
+                        else lost2 = fmaxf(lost2, z);
+                    }
                 }
-                const uint32_t okb = __ballot_sync(0xffffffffu, ok);
-                uint32_t basepos = 0;
-                if (lane == 0 && okb) basepos = smem_atom_add(&sh.rec_count, (uint32_t)__popc(okb));
-                basepos = __shfl_sync(0xffffffffu, basepos, 0);
-                if (ok) {
-                    const uint32_t pos = basepos + __popc(okb & ((1u << lane) - 1u));
-                    if (pos < (uint32_t)A.rec_cap) ent[pos] = e;
-                    else lost2 = fmaxf(lost2, z);
-                }
-            }
 #pragma unroll
-            for (int d = 16; d > 0; d >>= 1) lost2 = fmaxf(lost2, __shfl_xor_sync(0xffffffffu, lost2, d));
-            if (lane == 0 && lost2 > -INFINITY) smem_red_max(&sh.excl_bits, key_above(lost2));
+                for (int d = 16; d > 0; d >>= 1) lost2 = fmaxf(lost2, __shfl_xor_sync(0xffffffffu, lost2, d));
+                if (lane == 0 && lost2 > -INFINITY) smem_red_max(&sh.excl_bits, key_above(lost2));
+            }
+            cta_sync();
+            if (tid == 0) {
+                SegHdr h;
+                h.m = m_seg;
+                h.lse_sum = s_seg;
+                float te = zkey_to_float(sh.excl_bits);
+                te = fmaxf(te, excl_window);
+                if (pl.no_bound) te = INFINITY;
+                h.tau_excl = te;
+                h.bound_k = bound_k;
+                h.count = min(sh.rec_count, (uint32_t)A.rec_cap);
+                h.pad[0] = h.pad[1] = h.pad[2] = 0;
+                *reinterpret_cast<SegHdr*>(rec) = h;
+            }
+            if (cta_sync_or(*reinterpret_cast<const volatile int*>(&sh.fail))) { bad = 1; break; }  // (the same answer in every thread)
+            if (tid == 0) {
+                // the barrier above has ordered every thread's record writes before this fence, which
+                // makes them visible to the CTA that draws the last ticket
+                __threadfence();
+                const int c_first = cta_of_tile((long long)p0.row * A.tpr, T_total, ncta);
+                const int c_last = cta_of_tile((long long)(p0.row + 1) * A.tpr - 1, T_total, ncta);
+                const uint32_t tk = atomicAdd(&A.tickets[p0.row], 1u);
+                sh.last = (tk == (uint32_t)(c_last - c_first));
+                if (sh.last) A.tickets[p0.row] = 0;  // ready for the next launch
+                sh.c_first = c_first;
+                sh.c_last = c_last;
+            }
+            cta_sync();
+            PROF(3 + 3 * min(seg_ord, 1));
+            finish_here = sh.last != 0;
+            if (finish_here) {
+                __threadfence();
+                src.direct = false;
+                src.m = src.ls = src.taux = src.bk = 0.0f;
+                src.wbuf = nullptr; src.wcount = nullptr;
+                src.c_first = sh.c_first; src.nseg = sh.c_last - sh.c_first + 1;
+            }
         }
-        cta_sync();
-        if (tid == 0) {
-            SegHdr h;
-            h.m = m_seg;
-            h.lse_sum = s_seg;
-            float te = zkey_to_float(sh.excl_bits);
-            te = fmaxf(te, excl_window);
-            if (pl.no_bound) te = INFINITY;
-            h.tau_excl = te;
-            h.bound_k = bound_k;
-            h.count = min(sh.rec_count, (uint32_t)A.rec_cap);
-            h.pad[0] = h.pad[1] = h.pad[2] = 0;
-            *reinterpret_cast<SegHdr*>(rec) = h;
-        }
-        if (cta_sync_or(*reinterpret_cast<const volatile int*>(&sh.fail))) { bad = 1; break; }  // (the same answer in every thread)
-        if (tid == 0) {
-            // the barrier above has ordered every thread's record writes before this fence, which
-            // makes them visible to the CTA that draws the last ticket
-            __threadfence();
-            const int c_first = cta_of_tile((long long)p0.row * A.tpr, T_total, ncta);
-            const int c_last = cta_of_tile((long long)(p0.row + 1) * A.tpr - 1, T_total, ncta);
-            const uint32_t tk = atomicAdd(&A.tickets[p0.row], 1u);
-            sh.last = (tk == (uint32_t)(c_last - c_first));
-            if (sh.last) A.tickets[p0.row] = 0;  // ready for the next launch
-            sh.c_first = c_first;
-            sh.c_last = c_last;
-        }
-        cta_sync();
-        PROF(3 + 3 * min(seg_ord, 1));
-        if (sh.last) {
-            __threadfence();
-            finish_row<T>(A, sh, smem + L.cand, p0.row, sh.c_first, sh.c_last);
-        }
+        // (one call site: the finish is inlined, its arguments stay in registers)
+        if (finish_here) finish_row<T>(A, sh, reinterpret_cast<uint64_t*>(smem + L.sel), reinterpret_cast<unsigned long long*>(smem + L.cand),
+                                       p0.row, src);
         PROF(4 + 3 * min(seg_ord, 1));
     }
     PROF(10);
 #ifdef BORN_PROFILE
+    if (A.prof && tid == 0) A.prof[(size_t)blockIdx.x * 32 + 12] = global_timer_ns();
+#endif
+#ifdef BORN_PROFILE
     PROF_ADD(8, pf_wait);
     PROF_ADD(9, pf_proc);
+    PROF_ADD(14, pf_hist);
 #endif
 
     if (!bad) bad = cta_sync_or(*reinterpret_cast<const volatile int*>(&sh.fail));
@@ -836,9 +1003,9 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
         const int r0 = (int)(t0 / A.tpr), r1 = (int)((t1 - 1) / A.tpr);
         for (int r = r0; r <= r1; ++r) {
             const uint32_t owner = __ldcg(&A.deferred[r]);
-            if (owner == (uint32_t)blockIdx.x + 1u) {
+            if ((owner & 0xFFFFFFu) == (uint32_t)blockIdx.x + 1u) {
                 cta_sync();
-                if (tid == 0) { A.deferred[r] = 0; atomicAdd(A.dev_error + 1, 1); }
+                if (tid == 0) { A.deferred[r] = 0; atomicAdd(A.dev_error + 1, 1); atomicAdd(A.dev_error + 8 + (owner >> 24), 1); }
                 fallback_row<T>(A, sh, smem, r);
                 cta_sync();
             }

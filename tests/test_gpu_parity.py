@@ -614,9 +614,9 @@ def test_whole_vocabulary_routes_with_history_penalties(sampler, oracle):
 
 
 def test_launch_counts(sampler):
-    # one launch for every parameter set; one more (the history dedupe) when a token history is
-    # given; two more instead (the clean fp32 copy and its penalty patch) when whole-vocabulary
-    # rows are bf16 with history penalties, or one more when they are not 16-byte aligned
+    # one launch for every parameter set, token history or not; two more (the clean fp32 copy and
+    # its penalty patch) when whole-vocabulary rows are bf16 with history penalties, one more
+    # when they are not 16-byte aligned
     from born_b200 import SamplingConfig
     torch = torch_mod()
     B, V = 4, 32000
@@ -631,7 +631,7 @@ def test_launch_counts(sampler):
         return sampler.launch_count - n0
 
     pen = dict(frequency_penalty=0.5, presence_penalty=0.3)
-    assert launches(SamplingConfig(temperature=0.7, min_p=0.05, top_p=0.9, **pen), hist) == 2
+    assert launches(SamplingConfig(temperature=0.7, min_p=0.05, top_p=0.9, **pen), hist) == 1
     assert launches(SamplingConfig(temperature=0.7, min_p=0.05, top_p=0.9)) == 1
     assert launches(SamplingConfig(temperature=0.7, top_k=50, top_p=0.9)) == 1
     assert launches(SamplingConfig(temperature=0.7, min_p=0.05)) == 1
@@ -639,10 +639,10 @@ def test_launch_counts(sampler):
     assert launches(SamplingConfig(temperature=0.7)) == 1
     assert launches(SamplingConfig(temperature=0.7, min_p=0.05, full_vocab=True)) == 1
     assert launches(SamplingConfig(temperature=0.7, top_p=0.9)) == 1
-    assert launches(SamplingConfig(temperature=0.7, **pen), hist) == 2
-    assert launches(SamplingConfig(temperature=0.7, top_p=0.9, **pen), hist) == 2
+    assert launches(SamplingConfig(temperature=0.7, **pen), hist) == 1
+    assert launches(SamplingConfig(temperature=0.7, top_p=0.9, **pen), hist) == 1
     zb = z.to(torch.bfloat16)
-    assert launches(SamplingConfig(temperature=0.7, top_k=50, **pen), hist, zb) == 2
+    assert launches(SamplingConfig(temperature=0.7, top_k=50, **pen), hist, zb) == 1
     assert launches(SamplingConfig(temperature=0.7, **pen), hist, zb) == 3
     odd = torch.randn((B, V + 1), device="cuda")[:, :V]  # rows of 32001 floats: not 16-byte aligned
     assert launches(SamplingConfig(temperature=0.7, top_k=50), None, odd) == 1

@@ -89,7 +89,8 @@ def test_random_configurations_match_the_oracle(sampler, oracle, seed):
             if rng.random() < 0.4:
                 hl = rng.integers(0, H + 1, B).astype(np.int32)
         seg = 1
-        if (not per_row and hist is None and 0 < params.get("top_k", 0) <= 128 and V >= 4096 and rng.random() < 0.3):
+        if (not per_row and hist is None and 0 < params.get("top_k", 0) <= 128 and "min_p" not in params and V >= 4096
+                and rng.random() < 0.3):
             for g in (2, 4, 8):
                 if V % g == 0 and params["top_k"] * g <= 1024:
                     seg = g

@@ -180,6 +180,7 @@ static_assert(kScanWarps * kWarpCand * 8 >= kSelCap * 8, "the selection's masses
 struct ScanShared {
     unsigned long long full_bar[kScanStages];
     unsigned long long empty_bar[kScanStages];
+    unsigned long long ready_bar[kScanStages];  // fp32 launches with token histories: the producer has patched the tile
     // segment state of the compute threads
     uint32_t maxbits;               // key of the running maximum (only ever raised)
     uint32_t excl_bits;             // key of the exclusion level (only ever raised)
@@ -188,6 +189,9 @@ struct ScanShared {
     uint32_t wcount[kScanWarps];    // candidates in each warp's buffer
     float wmax[kScanWarps], wsum[kScanWarps];
     int fail;
+    int hist_seq;                   // segments of this CTA whose history list is built (read by the producer warp)
+    int hist_n;                     // ... entries of the latest one
+    born_row_params hist_rp;        // ... and its row's parameters
     int prod_done;                  // the producer warp has left its loop
     long long issued;               // ... having issued the tiles below this one
     int last, c_first, c_last;

@@ -96,6 +96,28 @@ __device__ __forceinline__ void push_cand(uint64_t* wbuf, uint32_t* wcount, uint
     else smem_red_max(excl, key_above(z));
 }
 
+// A warp's buffer is half full: drop what lies below the threshold as it stands now.  Every
+// part of the threshold only rises, and the finish uses nothing below its final value, so what
+// goes is never missed -- while a buffer full of entries from the time the threshold was still
+// low would turn away the candidates that count.  Called by the whole warp.
+__device__ __forceinline__ void compact_cands(uint64_t* wbuf, uint32_t* wcount, float tau) {
+    const int lane = threadIdx.x & 31;
+    const uint32_t n = min(*reinterpret_cast<volatile uint32_t*>(wcount), (uint32_t)kWarpCand);
+    uint32_t kept = 0;
+    for (uint32_t base = 0; base < n; base += 32) {
+        const uint32_t i = base + lane;
+        const uint64_t e = i < n ? wbuf[i] : 0ull;
+        const bool keep = i < n && __uint_as_float((uint32_t)(e >> 32)) >= tau;
+        const uint32_t kb = __ballot_sync(0xffffffffu, keep);
+        __syncwarp();  // the chunk is in registers before any of it is overwritten
+        if (keep) wbuf[kept + __popc(kb & ((1u << lane) - 1u))] = e;
+        kept += __popc(kb);
+    }
+    __syncwarp();
+    if (lane == 0) *reinterpret_cast<volatile uint32_t*>(wcount) = kept;
+    __syncwarp();
+}
+
 struct SegCtx {   // what the compute threads know about the segment they are in (block-uniform)
     RowPlan plan;
     int row, id0;       // virtual row; token id of the row's token 0 as written to candidates
@@ -346,10 +368,8 @@ __device__ __forceinline__ TilePos tile_pos(long long t, int tpr) {
 
 template <typename T, bool kMask>
 __device__ __forceinline__ void producer_issue(const ScanArgs& A, ScanShared& sh, uint8_t* smem, const ScanSmem& L,
-                                               long long t, int stage) {
+                                               long long t, const TilePos& p, const RowGeom& q, int stage) {
     constexpr int TILE = TileOf<T>::n;
-    const TilePos p = tile_pos(t, A.tpr);
-    const RowGeom q = row_geom<T>(A, p.row);
     const int n_el = min(TILE, q.lead + A.V - p.j * TILE);
     const int lo = max(0, q.lead - p.j * TILE);
     uint64_t* bar = reinterpret_cast<uint64_t*>(&sh.full_bar[stage]);
@@ -376,30 +396,143 @@ __device__ __forceinline__ void producer_issue(const ScanArgs& A, ScanShared& sh
     }
 }
 
+// Cursor over the CTA's tiles: (row, tile within the row) advanced without divisions.
+template <typename T>
+struct TileCursor {
+    TilePos p;
+    RowGeom q;
+    __device__ __forceinline__ void start(const ScanArgs& A, long long t) {
+        p = tile_pos(t, A.tpr);
+        q = row_geom<T>(A, p.row);
+    }
+    // returns true when the next tile opens a new row
+    __device__ __forceinline__ bool next(const ScanArgs& A, bool more) {
+        if (++p.j < A.tpr) return false;
+        p.j = 0;
+        ++p.row;
+        if (more) q = row_geom<T>(A, p.row);
+        return true;
+    }
+};
+
 // The producer warp: keeps the ring full.  Step n waits (bounded) for the stage of tile n to be
 // handed back by the compute warps and issues its copy.
 template <typename T, bool kMask>
 __device__ __forceinline__ void producer_loop(const ScanArgs& A, ScanShared& sh, uint8_t* smem, const ScanSmem& L,
                                               long long t0, long long t1) {
     const int lane = threadIdx.x & 31;
-    long long issue_t = t0;
-    const long long n_tiles = t1 - t0;
+    const int n_tiles = (int)(t1 - t0);
+    int n = 0, stage = 0;
+    uint32_t round = 0;
     bool ok = true;
-    for (long long n = 0; n < n_tiles; ++n) {
-        const int stage = (int)(n % kScanStages);
+    TileCursor<T> ci;
+    ci.start(A, t0);
+    for (; n < n_tiles; ++n) {
         if (n >= kScanStages &&
-            !mbar_wait_limit(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage]), (uint32_t)((n / kScanStages) - 1) & 1u,
-                             A.timeout_ns, &sh.fail)) {
+            !mbar_wait_limit(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage]), (round - 1u) & 1u, A.timeout_ns, &sh.fail)) {
             ok = false;
             break;
         }
-        if (lane == 0) producer_issue<T, kMask>(A, sh, smem, L, t0 + n, stage);
-        issue_t = t0 + n + 1;
+        if (lane == 0) producer_issue<T, kMask>(A, sh, smem, L, t0 + n, ci.p, ci.q, stage);
+        ci.next(A, n + 1 < n_tiles);
+        if (++stage == kScanStages) { stage = 0; ++round; }
     }
     if (!ok) sh.fail = 1;
     // what the failure path of the compute threads needs to know (see the end of scan_kernel)
     if (lane == 0) {
-        sh.issued = issue_t;
+        sh.issued = t0 + n;
+        __threadfence_block();
+        *reinterpret_cast<volatile int*>(&sh.prod_done) = 1;
+    }
+}
+
+// The producer warp of an fp32 launch with token histories.  Besides keeping the ring full it
+// applies the history penalties to every tile once it has landed -- the penalised value is
+// written in place -- and only then hands the tile to the compute warps (`ready`), which so
+// never see an unpenalised logit and spend nothing on it.  The list of a segment's history
+// tokens is built by the compute threads (hist_build); `hist_seq` says for how many of the
+// CTA's segments it has been.  The warp never blocks on one thing while the other could move:
+// it alternates between "issue the next copy if its stage is free" and "patch and release the
+// next tile if it has landed", and sleeps a few dozen nanoseconds when neither can.
+template <typename T, bool kMask>
+__device__ __forceinline__ void producer_loop_patching(const ScanArgs& A, ScanShared& sh, uint8_t* smem, const ScanSmem& L,
+                                                       long long t0, long long t1) {
+    constexpr int TILE = TileOf<T>::n;
+    const int lane = threadIdx.x & 31;
+    const int n_tiles = (int)(t1 - t0);
+    int n_i = 0, stage_i = 0;   // next tile to issue
+    uint32_t round_i = 0;
+    int n_p = 0, stage_p = 0;   // next tile to patch and release
+    uint32_t round_p = 0;
+    TileCursor<T> ci, cp;
+    ci.start(A, t0);
+    cp.start(A, t0);
+    int seg_p = 0;              // ordinal of the segment the release cursor is in
+    bool seg_open = false;      // ... and whether its list has been taken over
+    int n_list = 0, pos = 0;
+    born_row_params rp = A.params;
+    const unsigned long long* list = reinterpret_cast<const unsigned long long*>(smem + L.hist);
+    unsigned long long idle_since = 0;
+    bool ok = true;
+    while (n_p < n_tiles) {
+        bool moved = false;
+        if (n_i < n_tiles &&
+            (n_i < kScanStages || mbar_test(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage_i]), (round_i - 1u) & 1u))) {
+            if (lane == 0) producer_issue<T, kMask>(A, sh, smem, L, t0 + n_i, ci.p, ci.q, stage_i);
+            ++n_i;
+            ci.next(A, n_i < n_tiles);
+            if (++stage_i == kScanStages) { stage_i = 0; ++round_i; }
+            moved = true;
+        }
+        if (n_p < n_i && mbar_test(reinterpret_cast<uint64_t*>(&sh.full_bar[stage_p]), round_p & 1u)) {
+            if (!seg_open && *reinterpret_cast<const volatile int*>(&sh.hist_seq) > seg_p) {
+                // (the compute threads' writes of the list are ordered before their write of hist_seq)
+                __threadfence_block();
+                n_list = *reinterpret_cast<const volatile int*>(&sh.hist_n);
+                rp = sh.hist_rp;
+                pos = 0;
+                seg_open = true;
+            }
+            if (seg_open) {
+                bool wrote = false;
+                if (n_list > 0) {
+                    float* tile = reinterpret_cast<float*>(smem + L.tiles + (size_t)stage_p * kTileBytes);
+                    for (;;) {
+                        const int idx = pos + lane;
+                        const unsigned long long e = idx < n_list ? list[idx] : ~0ull;
+                        const int off = (int)(uint32_t)e + cp.q.lead - cp.p.j * TILE;
+                        const bool in = idx < n_list && off >= 0 && off < TILE;
+                        const int c = __popc(__ballot_sync(0xffffffffu, in));
+                        if (in && (e >> 32) != 0) {  // (0: a repeat of a token listed before)
+                            tile[off] = penalise(rp, tile[off], (int)(e >> 32));
+                            wrote = true;
+                        }
+                        pos += c;
+                        if (c < 32) break;
+                    }
+                }
+                if (wrote) fence_proxy_async();  // the stage is next written by a bulk copy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(&sh.ready_bar[stage_p]));
+                ++n_p;
+                if (cp.next(A, n_p < n_tiles)) { ++seg_p; seg_open = false; }
+                if (++stage_p == kScanStages) { stage_p = 0; ++round_p; }
+                moved = true;
+            }
+        }
+        if (moved) {
+            idle_since = 0;
+        } else {
+            __nanosleep(40);
+            if (*reinterpret_cast<const volatile int*>(&sh.fail)) { ok = false; break; }
+            const unsigned long long now = global_timer_ns();
+            if (idle_since == 0) idle_since = now;
+            else if (now - idle_since > A.timeout_ns) { ok = false; break; }
+        }
+    }
+    if (!ok) sh.fail = 1;
+    if (lane == 0) {
+        sh.issued = t0 + n_i;
         __threadfence_block();
         *reinterpret_cast<volatile int*>(&sh.prod_done) = 1;
     }
@@ -441,7 +574,7 @@ __device__ __forceinline__ void hist_ids(const ScanArgs& A, int b, int (&ids)[kH
 }
 
 template <int TILE>
-__device__ __forceinline__ int hist_build(const ScanArgs& A, const int (&ids)[kHistPer], int g, int lead, int j_begin, int j_end,
+__device__ __noinline__ int hist_build_wide(const ScanArgs& A, const int (&ids)[kHistPer], int g, int lead, int j_begin, int j_end,
                                           uint32_t* keys, uint32_t* cnt32, unsigned long long* list, uint32_t* wscr) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int span = j_end - j_begin;
@@ -453,7 +586,6 @@ __device__ __forceinline__ int hist_build(const ScanArgs& A, const int (&ids)[kH
     uint32_t* mult = keys + slots;  // repeats, beside the keys
     const int P = span <= 128 ? kScanWarps : 1;
     const int nc = span * P;
-    PROF(25);
     {
         uint4* k4 = reinterpret_cast<uint4*>(keys);
         uint4* m4 = reinterpret_cast<uint4*>(mult);
@@ -464,7 +596,6 @@ __device__ __forceinline__ int hist_build(const ScanArgs& A, const int (&ids)[kH
         for (int i = tid; i < nc / 2 + 1; i += kThreads) cnt32[i] = 0;
     }
     cta_sync();
-    PROF(26);
     // (shared-memory atomics are what this build costs: one per id for the table, one per new
     // token to count it, one to place it)
     int ctr_of[kHistPer];  // the token's counter if this thread was the first to insert it, else -1
@@ -495,9 +626,7 @@ __device__ __forceinline__ int hist_build(const ScanArgs& A, const int (&ids)[kH
             slot = (slot + 1) & (slots - 1);
         }
     }
-    PROF(29);
     cta_sync();
-    PROF(27);
     // exclusive scan of the counters (a thread takes `per` consecutive ones)
     uint16_t* cnt16 = reinterpret_cast<uint16_t*>(cnt32);
     const int per = (nc + kThreads - 1) / kThreads;
@@ -538,7 +667,132 @@ __device__ __forceinline__ int hist_build(const ScanArgs& A, const int (&ids)[kH
         list[(old >> (16 * (c & 1))) & 0xFFFFu] = ((unsigned long long)(mult[slot] + 1u) << 32) | tok;
     }
     cta_sync();
+    return (int)n;
+}
+
+// The same list for a segment of at most kHistVoteTiles tiles -- every row below some 260 000
+// fp32 logits -- without one atomic: shared-memory atomics cost about two cycles per lane and SM,
+// and the build sits in front of the segment's first tile.  A warp finds, tile by tile, which of
+// its lanes hold a token of that tile (a vote per tile and id slot): the lane's rank among them
+// is its place in the warp's part of the tile's bucket, the count goes to the (tile, warp)
+// counter by a plain store.  After the scan every token is stored at start + rank.  Repeats are
+// found afterwards inside the tile's bucket (a handful of entries): the first occurrence gets
+// the multiplicity, the others get 0 and are skipped by whoever applies the list.
+constexpr int kHistVoteTiles = 64;
+template <int TILE>
+__device__ __forceinline__ int hist_build(const ScanArgs& A, const int (&ids)[kHistPer], int g, int lead, int j_begin, int j_end,
+                                          uint32_t* keys, uint32_t* cnt32, unsigned long long* list, uint32_t* wscr) {
+    const int span = j_end - j_begin;
+    if (span > kHistVoteTiles) return hist_build_wide<TILE>(A, ids, g, lead, j_begin, j_end, keys, cnt32, list, wscr);
+    static_assert(kHistPer == 4, "the vote loop is written for four ids per thread");
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t lt = (1u << lane) - 1u;
+    uint16_t* cnt16 = reinterpret_cast<uint16_t*>(cnt32);
+    const int nc = span * kScanWarps;
+    PROF(25);
+    int rel[kHistPer];
+    uint32_t tok[kHistPer];
+#pragma unroll
+    for (int r = 0; r < kHistPer; ++r) {
+        rel[r] = -1;
+        tok[r] = 0;
+        const int id = ids[r];
+        if (id < 0) continue;
+        int g2 = 0;
+        uint32_t tk = (uint32_t)id;
+        if (A.G > 1) { g2 = id / A.V; tk = (uint32_t)(id - g2 * A.V); }
+        if (g2 != g || tk >= (uint32_t)A.V) continue;  // another vocabulary segment's token, or an id beyond the vocabulary
+        const int tl = (int)((tk + (uint32_t)lead) / (uint32_t)TILE);
+        if (tl < j_begin || tl >= j_end) continue;
+        rel[r] = tl - j_begin;
+        tok[r] = tk;
+    }
+    // (population counts run on the slow pipe: the votes are parked in shared memory -- the
+    // candidate area is idle -- and only the lanes that need a count take one afterwards)
+    uint4* votes = reinterpret_cast<uint4*>(keys) + warp * kHistVoteTiles;
+    for (int t = 0; t < span; ++t) {
+        const uint32_t b0 = __ballot_sync(0xffffffffu, rel[0] == t), b1 = __ballot_sync(0xffffffffu, rel[1] == t);
+        const uint32_t b2 = __ballot_sync(0xffffffffu, rel[2] == t), b3 = __ballot_sync(0xffffffffu, rel[3] == t);
+        if (lane == 0) votes[t] = make_uint4(b0, b1, b2, b3);
+    }
+    __syncwarp();
+    int rank[kHistPer];
+#pragma unroll
+    for (int r = 0; r < kHistPer; ++r) {
+        rank[r] = 0;
+        if (rel[r] < 0) continue;
+        const uint4 v = votes[rel[r]];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int r2 = 0; r2 < r; ++r2) rank[r] += __popc(w[r2]);
+        rank[r] += __popc(w[r] & lt);
+    }
+#pragma unroll
+    for (int h = 0; h < kHistVoteTiles / 32; ++h) {
+        const int t = lane + 32 * h;
+        if (t < span) {
+            const uint4 v = votes[t];
+            cnt16[t * kScanWarps + warp] = (uint16_t)(__popc(v.x) + __popc(v.y) + __popc(v.z) + __popc(v.w));
+        }
+    }
+    cta_sync();
+    PROF(26);
+    // exclusive scan of the span * 8 counters (at most two per thread)
+    const int per = (nc + kThreads - 1) / kThreads;
+    const int lo = min(tid * per, nc), hi = min(lo + per, nc);
+    uint32_t loc = 0;
+    for (int i = lo; i < hi; ++i) loc += cnt16[i];
+    uint32_t incl = loc;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t up = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += up;
+    }
+    if (lane == 31) wscr[warp] = incl;
+    cta_sync();
+    uint32_t off = 0, n = 0;
+#pragma unroll
+    for (int w = 0; w < kScanWarps; ++w) {
+        const uint32_t x = wscr[w];
+        if (w < warp) off += x;
+        n += x;
+    }
+    uint32_t run = off + incl - loc;
+    for (int i = lo; i < hi; ++i) {
+        const uint32_t c = cnt16[i];
+        cnt16[i] = (uint16_t)run;  // where the counter's tokens start in the list
+        run += c;
+    }
+    cta_sync();
+    PROF(29);
+#pragma unroll
+    for (int r = 0; r < kHistPer; ++r)
+        if (rel[r] >= 0) list[cnt16[rel[r] * kScanWarps + warp] + rank[r]] = (1ull << 32) | tok[r];
+    cta_sync();
+    PROF(27);
+    // repeats: inside the tile's bucket
+    for (int i = tid; i < (int)n; i += kThreads) {
+        const uint32_t tk = (uint32_t)list[i];
+        const int t = (int)((tk + (uint32_t)lead) / (uint32_t)TILE) - j_begin;
+        const int b0 = cnt16[t * kScanWarps], b1 = t + 1 < span ? (int)cnt16[(t + 1) * kScanWarps] : (int)n;
+        int same = 0;
+        bool first = true;
+        int j = b0;
+        for (; j + 4 <= b1; j += 4) {  // (four loads in flight: the loop is bound by their latency otherwise)
+            uint32_t x[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) x[k] = (uint32_t)list[j + k];
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (x[k] == tk) { ++same; first = first && j + k >= i; }
+        }
+        for (; j < b1; ++j)
+            if ((uint32_t)list[j] == tk) { ++same; first = first && j >= i; }
+        if (same > 1) list[i] = ((unsigned long long)(first ? same : 0) << 32) | tk;
+    }
+    cta_sync();
     PROF(28);
+    (void)keys;
     return (int)n;
 }
 
@@ -561,7 +815,7 @@ __device__ __forceinline__ bool hist_apply(HistCursor& hc, const unsigned long l
         const int off = tok + lead - j * TILE;
         const bool in = idx < hc.n && off >= 0 && off < TILE;
         const int c = __popc(__ballot_sync(0xffffffffu, in));
-        if (in && off >= lo_el && off < n_el) {
+        if (in && off >= lo_el && off < n_el && (e >> 32) != 0) {  // (0: a repeat of a token listed before)
             const int vec = off / VEC;
             const int owner = slices ? (vec >> 7) : ((vec & (kThreads - 1)) >> 5);
             if (owner == warp) {
@@ -607,7 +861,9 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
         for (int s = 0; s < kScanStages; ++s) {
             mbar_init(reinterpret_cast<uint64_t*>(&sh.full_bar[s]), 1);
             mbar_init(reinterpret_cast<uint64_t*>(&sh.empty_bar[s]), kScanWarps);
+            mbar_init(reinterpret_cast<uint64_t*>(&sh.ready_bar[s]), 1);
         }
+        sh.hist_seq = 0;
         mbar_fence_init();
         sh.fail = 0;
         sh.prod_done = 0;
@@ -622,7 +878,8 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
     __syncthreads();  // the only barrier all 288 threads share
 
     if (tid >= kThreads) {
-        producer_loop<T, kMask>(A, sh, smem, L, t0, t1);
+        if (sizeof(T) == 4 && A.history != nullptr) producer_loop_patching<T, kMask>(A, sh, smem, L, t0, t1);
+        else producer_loop<T, kMask>(A, sh, smem, L, t0, t1);
         return;
     }
 
@@ -641,6 +898,9 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
 #endif
     bool failed = false;
     int bad = 0;
+    // fp32 launches with token histories: the producer warp patches the tiles and releases them
+    const bool prod_patch = sizeof(T) == 4 && A.history != nullptr;
+    unsigned long long* const wait_bar = prod_patch ? sh.ready_bar : sh.full_bar;
     int seg_ord = -1;
     long long t = t0;
     int stage = 0;         // ring stage of tile t
@@ -688,7 +948,13 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                                         reinterpret_cast<uint32_t*>(smem + L.sel), reinterpret_cast<unsigned long long*>(smem + L.hist),
                                         reinterpret_cast<uint32_t*>(sh.red64));
         }
-        const bool hist_on = hc.n > 0;
+        if (prod_patch && tid == 0) {  // (hist_build ended on a barrier: the list is complete)
+            sh.hist_n = hc.n;
+            sh.hist_rp = rp;
+            __threadfence_block();
+            *reinterpret_cast<volatile int*>(&sh.hist_seq) = seg_ord + 1;
+        }
+        const bool hist_on = hc.n > 0 && !prod_patch;
         const bool lean = A.fast && !pl.need_mass;
         for (; t < seg_end; ++t, ++seen, ++j, rem -= TILE) {
             // ---- steady state: the full tiles of an aligned row after the segment's first tile.
@@ -699,7 +965,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
 #ifdef BORN_PROFILE
                     const long long qw0 = clock64();
 #endif
-                    uint64_t* fb = reinterpret_cast<uint64_t*>(&sh.full_bar[stage]);
+                    uint64_t* fb = reinterpret_cast<uint64_t*>(&wait_bar[stage]);
                     bool here = mbar_try(fb, phase);
                     if (!here) here = mbar_wait_limit(fb, phase, A.timeout_ns, &sh.fail);
                     if (!__all_sync(0xffffffffu, here)) {
@@ -721,6 +987,8 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                     fast_tile<T, kMask, kLse>(tile, smask, sg.id0 + j * TILE, tau, pl.c2, st, wbuf, wcount, excl);
                     if (pl.use_max) publish_max(st, sh);
                     if (pl.lane_bound && ((seen + 1) & seen) == 0) sg.tau_fix = fmaxf(sg.tau_fix, lane_bound(sh, pl.k, st.mx));
+                    if (collect && *reinterpret_cast<volatile uint32_t*>(wcount) >= (uint32_t)(kWarpCand / 2))
+                        compact_cands(wbuf, wcount, current_tau(sg, sh));
                     if (patched) fence_proxy_async();  // the stage is next written by a bulk copy
                     __syncwarp();
                     if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage]));
@@ -736,7 +1004,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
             const long long pw0 = clock64();
 #endif
             if (!failed) {
-                const bool here = mbar_wait_limit(reinterpret_cast<uint64_t*>(&sh.full_bar[stage]), phase, A.timeout_ns, &sh.fail);
+                const bool here = mbar_wait_limit(reinterpret_cast<uint64_t*>(&wait_bar[stage]), phase, A.timeout_ns, &sh.fail);
                 if (!__all_sync(0xffffffffu, here)) {  // (the warp gives up as one: what follows votes and shuffles)
                     failed = true;
                     sh.fail = 1;
@@ -821,6 +1089,8 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                 // warps that lag are older, hence lower, hence still valid)
                 sg.tau_fix = fmaxf(sg.tau_fix, lane_bound(sh, pl.k, st.mx));
             }
+            if (collect && !failed && *reinterpret_cast<volatile uint32_t*>(wcount) >= (uint32_t)(kWarpCand / 2))
+                compact_cands(wbuf, wcount, current_tau(sg, sh));
             if (patched) fence_proxy_async();  // the stage is next written by a bulk copy
             __syncwarp();
             if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage]));  // tile back to the producer

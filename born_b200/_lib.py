@@ -13,7 +13,7 @@ ERR_UNSUPPORTED = 4
 ERR_NCCL = 5
 ERR_DEVICE_TIMEOUT = 6
 
-ROW_OK, ROW_ALL_MASKED, ROW_NAN, ROW_POS_INF, ROW_OVERFLOW, ROW_BAD_TOKEN = range(6)
+ROW_OK, ROW_ALL_MASKED, ROW_NAN, ROW_POS_INF, ROW_OVERFLOW, ROW_BAD_TOKEN, ROW_FINISHED = range(7)
 
 MAX_TOP_K = 1024
 MAX_HISTORY = 1024
@@ -121,6 +121,14 @@ SYMBOLS = {
     "born_check_error": (C.c_int32, [C.c_void_p]),
     "born_fallback_rows": (C.c_int64, [C.c_void_p]),
     "born_debug_expire_wait": (C.c_int32, [C.c_void_p, C.c_void_p]),
+    "born_history_create": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "born_history_reset": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_uint32, C.c_void_p]),
+    "born_history_set_stop_tokens": (C.c_int32, [C.c_void_p, C.POINTER(C.c_int32), C.c_int32]),
+    "born_history_read": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_uint32, C.c_void_p]),
+    "born_sample_next": (C.c_int32, [C.c_void_p, C.POINTER(SampleArgs), C.c_void_p]),
+    "born_mask_begin": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.POINTER(C.c_uint32))]),
+    "born_mask_commit": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "born_mask_wait": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "born_spec_verify": (C.c_int32, [C.c_void_p, C.POINTER(SpecArgs), C.c_void_p]),
     "born_shard_record_bytes": (C.c_int32, [C.c_int32]),
     "born_shard_unique_id": (C.c_int32, [C.c_void_p]),

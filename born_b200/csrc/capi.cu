@@ -64,6 +64,21 @@ struct Handle {
     float* clean_copy = nullptr;  // aligned fp32 copy of the rows (mask and penalties applied)
     size_t clean_copy_bytes = 0;
     Staging stage[16];
+    // device-resident history (born_history_*)
+    int32_t* ring = nullptr;       // [max_batch, ring_cap], then total / len / finished [max_batch] each
+    int ring_cap = 0;
+    int n_stop = 0;
+    int32_t stop_ids[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    bool use_ring = false;         // set by born_sample_next around its call of sample_device
+    // grammar-mask upload (born_mask_*)
+    uint32_t* mask_host[2] = {nullptr, nullptr};
+    uint32_t* mask_dev[2] = {nullptr, nullptr};
+    size_t mask_words = 0;         // words each of the four buffers holds
+    size_t mask_pending_words = 0; // words of the buffer handed out by born_mask_begin
+    int mask_next = 0;             // buffer the next born_mask_begin hands out
+    int mask_filled = -1;          // buffer handed out and not yet committed
+    cudaStream_t mask_stream = nullptr;
+    cudaEvent_t mask_event = nullptr;
     cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
     float timing[3] = {0, 0, 0};
     int64_t launches = 0;
@@ -364,6 +379,13 @@ int32_t born_sampler_destroy(void* handle) {
     if (!h) return BORN_OK;
     cudaSetDevice(h->device);
     if (h->comm && h->nccl.CommDestroy) h->nccl.CommDestroy(h->comm);
+    cudaFree(h->ring);
+    for (int i = 0; i < 2; ++i) {
+        if (h->mask_host[i]) cudaFreeHost(h->mask_host[i]);
+        cudaFree(h->mask_dev[i]);
+    }
+    if (h->mask_stream) cudaStreamDestroy(h->mask_stream);
+    if (h->mask_event) cudaEventDestroy(h->mask_event);
     cudaFree(h->records);
     cudaFree(h->blocks);
     cudaFree(h->tickets);
@@ -461,6 +483,16 @@ static int sample_device(Handle* h, const born_sample_args* a_in, cudaStream_t s
     A.history = a->history;
     A.history_len = a->history_len;
     A.history_stride = a->history_stride;
+    if (h->use_ring) {
+        int32_t* meta = h->ring + (size_t)h->max_batch * h->ring_cap;
+        A.ring = h->ring;
+        A.ring_total = meta;
+        A.ring_len = meta + h->max_batch;
+        A.ring_finished = meta + 2 * (size_t)h->max_batch;
+        A.ring_cap = h->ring_cap;
+        A.n_stop = h->n_stop;
+        memcpy(A.stop_ids, h->stop_ids, sizeof A.stop_ids);
+    }
     A.row_params = a->row_params;
     A.params = a->params;
     A.uniforms = a->uniforms;
@@ -655,6 +687,182 @@ int32_t born_sample(void* handle, const born_sample_args* a, void* stream) {
     cudaEventElapsedTime(&h->timing[1], h->ev[1], h->ev[2]);
     cudaEventElapsedTime(&h->timing[2], h->ev[2], h->ev[3]);
     return check_device_error(h);
+}
+
+// ---- device-resident history ------------------------------------------------------------
+int32_t born_history_create(void* handle, int32_t capacity) {
+    Handle* h = (Handle*)handle;
+    if (!h) return fail(nullptr, BORN_ERR_INVALID_ARGUMENT, "handle is NULL");
+    if (h->is_static) return fail(h, BORN_ERR_UNSUPPORTED, "the allocation-free entry point keeps no history");
+    if (capacity < 1 || capacity > BORN_MAX_HISTORY) return fail(h, BORN_ERR_INVALID_ARGUMENT, "history capacity must be 1..%d", BORN_MAX_HISTORY);
+    int rc = use_device(h);
+    if (rc) return rc;
+    cudaFree(h->ring);
+    h->ring = nullptr;
+    const size_t words = (size_t)h->max_batch * ((size_t)capacity + 3);
+    CUDA_TRY(h, cudaMalloc((void**)&h->ring, words * 4));
+    CUDA_TRY(h, cudaMemset(h->ring, 0, words * 4));
+    h->ring_cap = capacity;
+    h->workspace += (int64_t)words * 4;
+    return BORN_OK;
+}
+
+namespace {
+// ring[b][i] <- the i-th of the last min(len, cap) prompt tokens of row b; total = len = that count
+__global__ void history_load_kernel(const int32_t* tokens, const int32_t* lens, int stride, int cap, int max_batch, int batch,
+                                    int32_t* ring) {
+    const int b = blockIdx.x;
+    int32_t* meta = ring + (size_t)max_batch * cap;
+    int len = lens ? lens[b] : stride;
+    len = max(0, min(len, stride));
+    const int keep = min(len, cap);
+    for (int i = threadIdx.x; i < keep; i += blockDim.x) ring[(size_t)b * cap + i] = tokens[(size_t)b * stride + (len - keep) + i];
+    if (threadIdx.x == 0) {
+        meta[b] = keep;                          // total
+        meta[max_batch + b] = keep;              // len
+        meta[2 * (size_t)max_batch + b] = 0;     // finished
+    }
+    (void)batch;
+}
+}  // namespace
+
+int32_t born_history_reset(void* handle, const int32_t* tokens, const int32_t* lens, int32_t batch, int32_t stride,
+                           uint32_t memory, void* stream) {
+    Handle* h = (Handle*)handle;
+    if (!h) return fail(nullptr, BORN_ERR_INVALID_ARGUMENT, "handle is NULL");
+    if (!h->ring) return fail(h, BORN_ERR_INVALID_ARGUMENT, "born_history_create has not been called");
+    if (batch < 1 || batch > h->max_batch) return fail(h, BORN_ERR_INVALID_ARGUMENT, "batch %d outside 1..%d", batch, h->max_batch);
+    if (stride < 0 || (stride > 0 && !tokens)) return fail(h, BORN_ERR_INVALID_ARGUMENT, "tokens is NULL with stride %d", stride);
+    int rc = use_device(h);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int32_t* d_tok = tokens;
+    const int32_t* d_len = lens;
+    if (memory == BORN_MEM_HOST) {
+        if (stride > 0) {
+            if ((rc = stage_reserve(h, 7, (size_t)batch * stride * 4))) return rc;
+            CUDA_TRY(h, cudaMemcpyAsync(h->stage[7].p, tokens, (size_t)batch * stride * 4, cudaMemcpyHostToDevice, st));
+            d_tok = (const int32_t*)h->stage[7].p;
+        }
+        if (lens) {
+            if ((rc = stage_reserve(h, 8, (size_t)batch * 4))) return rc;
+            CUDA_TRY(h, cudaMemcpyAsync(h->stage[8].p, lens, (size_t)batch * 4, cudaMemcpyHostToDevice, st));
+            d_len = (const int32_t*)h->stage[8].p;
+        }
+    } else if (memory != BORN_MEM_DEVICE) {
+        return fail(h, BORN_ERR_INVALID_ARGUMENT, "memory must be BORN_MEM_DEVICE or BORN_MEM_HOST");
+    }
+    history_load_kernel<<<batch, 128, 0, st>>>(d_tok, d_len, stride, h->ring_cap, h->max_batch, batch, h->ring);
+    CUDA_TRY(h, cudaGetLastError());
+    h->launches++;
+    if (memory == BORN_MEM_HOST) CUDA_TRY(h, cudaStreamSynchronize(st));  // (the caller may reuse its buffers)
+    return BORN_OK;
+}
+
+int32_t born_history_set_stop_tokens(void* handle, const int32_t* ids, int32_t n) {
+    Handle* h = (Handle*)handle;
+    if (!h) return fail(nullptr, BORN_ERR_INVALID_ARGUMENT, "handle is NULL");
+    if (n < 0 || n > 8 || (n > 0 && !ids)) return fail(h, BORN_ERR_INVALID_ARGUMENT, "0..8 stop tokens");
+    h->n_stop = n;
+    for (int i = 0; i < n; ++i) h->stop_ids[i] = ids[i];
+    return BORN_OK;
+}
+
+int32_t born_history_read(void* handle, int32_t* tokens, int32_t* total, int32_t* finished, int32_t batch, uint32_t memory,
+                          void* stream) {
+    Handle* h = (Handle*)handle;
+    if (!h) return fail(nullptr, BORN_ERR_INVALID_ARGUMENT, "handle is NULL");
+    if (!h->ring) return fail(h, BORN_ERR_INVALID_ARGUMENT, "born_history_create has not been called");
+    if (batch < 1 || batch > h->max_batch) return fail(h, BORN_ERR_INVALID_ARGUMENT, "batch %d outside 1..%d", batch, h->max_batch);
+    int rc = use_device(h);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const cudaMemcpyKind kind = memory == BORN_MEM_HOST ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice;
+    const int32_t* meta = h->ring + (size_t)h->max_batch * h->ring_cap;
+    if (tokens) CUDA_TRY(h, cudaMemcpyAsync(tokens, h->ring, (size_t)batch * h->ring_cap * 4, kind, st));
+    if (total) CUDA_TRY(h, cudaMemcpyAsync(total, meta, (size_t)batch * 4, kind, st));
+    if (finished) CUDA_TRY(h, cudaMemcpyAsync(finished, meta + 2 * (size_t)h->max_batch, (size_t)batch * 4, kind, st));
+    CUDA_TRY(h, cudaStreamSynchronize(st));
+    return BORN_OK;
+}
+
+int32_t born_sample_next(void* handle, const born_sample_args* a, void* stream) {
+    Handle* h = (Handle*)handle;
+    if (!h) return fail(nullptr, BORN_ERR_INVALID_ARGUMENT, "handle is NULL");
+    if (!h->ring) return fail(h, BORN_ERR_INVALID_ARGUMENT, "born_history_create has not been called");
+    if (!a || a->struct_size != sizeof(born_sample_args)) return fail(h, BORN_ERR_INVALID_ARGUMENT, "args is NULL or of another version");
+    if (a->history || a->history_len) return fail(h, BORN_ERR_INVALID_ARGUMENT, "born_sample_next reads the handle's history: args->history must be NULL");
+    if (a->memory != BORN_MEM_DEVICE) return fail(h, BORN_ERR_UNSUPPORTED, "born_sample_next takes device memory");
+    if (a->vocab_segments > 1) return fail(h, BORN_ERR_UNSUPPORTED, "born_sample_next does not take vocab_segments");
+    born_sample_args d = *a;
+    const int32_t* meta = h->ring + (size_t)h->max_batch * h->ring_cap;
+    d.history = h->ring;
+    d.history_len = meta + h->max_batch;
+    d.history_stride = h->ring_cap;
+    h->use_ring = true;
+    const int32_t rc = born_sample(h, &d, stream);
+    h->use_ring = false;
+    return rc;
+}
+
+// ---- grammar-mask upload -----------------------------------------------------------------
+int32_t born_mask_begin(void* handle, int32_t batch, int32_t words_per_row, uint32_t** host_buffer) {
+    Handle* h = (Handle*)handle;
+    if (!h) return fail(nullptr, BORN_ERR_INVALID_ARGUMENT, "handle is NULL");
+    if (h->is_static) return fail(h, BORN_ERR_UNSUPPORTED, "the allocation-free entry point owns no mask buffers");
+    if (!host_buffer || batch < 1 || words_per_row < 1) return fail(h, BORN_ERR_INVALID_ARGUMENT, "born_mask_begin: bad arguments");
+    if (h->mask_filled >= 0) return fail(h, BORN_ERR_INVALID_ARGUMENT, "born_mask_begin: the previous buffer has not been committed");
+    int rc = use_device(h);
+    if (rc) return rc;
+    const size_t words = ((size_t)batch * (size_t)words_per_row + 3) / 4 * 4;
+    if (!h->mask_stream) {
+        CUDA_TRY(h, cudaStreamCreateWithFlags(&h->mask_stream, cudaStreamNonBlocking));
+        CUDA_TRY(h, cudaEventCreateWithFlags(&h->mask_event, cudaEventDisableTiming));
+    }
+    if (words > h->mask_words) {
+        CUDA_TRY(h, cudaStreamSynchronize(h->mask_stream));
+        CUDA_TRY(h, cudaDeviceSynchronize());  // (a kernel may still be reading the buffers about to be freed)
+        for (int i = 0; i < 2; ++i) {
+            if (h->mask_host[i]) cudaFreeHost(h->mask_host[i]);
+            cudaFree(h->mask_dev[i]);
+            h->mask_host[i] = nullptr;
+            h->mask_dev[i] = nullptr;
+            CUDA_TRY(h, cudaMallocHost((void**)&h->mask_host[i], words * 4));
+            CUDA_TRY(h, cudaMalloc((void**)&h->mask_dev[i], words * 4));
+        }
+        h->mask_words = words;
+    }
+    // the pinned buffer may still feed the copy committed two steps ago
+    CUDA_TRY(h, cudaStreamSynchronize(h->mask_stream));
+    h->mask_filled = h->mask_next;
+    h->mask_pending_words = words;
+    *host_buffer = h->mask_host[h->mask_filled];
+    return BORN_OK;
+}
+
+int32_t born_mask_commit(void* handle, const uint32_t** device_mask) {
+    Handle* h = (Handle*)handle;
+    if (!h) return fail(nullptr, BORN_ERR_INVALID_ARGUMENT, "handle is NULL");
+    if (h->mask_filled < 0 || !device_mask) return fail(h, BORN_ERR_INVALID_ARGUMENT, "born_mask_commit without born_mask_begin");
+    int rc = use_device(h);
+    if (rc) return rc;
+    const int i = h->mask_filled;
+    CUDA_TRY(h, cudaMemcpyAsync(h->mask_dev[i], h->mask_host[i], h->mask_pending_words * 4, cudaMemcpyHostToDevice, h->mask_stream));
+    CUDA_TRY(h, cudaEventRecord(h->mask_event, h->mask_stream));
+    *device_mask = h->mask_dev[i];
+    h->mask_filled = -1;
+    h->mask_next = i ^ 1;
+    return BORN_OK;
+}
+
+int32_t born_mask_wait(void* handle, void* stream) {
+    Handle* h = (Handle*)handle;
+    if (!h) return fail(nullptr, BORN_ERR_INVALID_ARGUMENT, "handle is NULL");
+    if (!h->mask_event) return fail(h, BORN_ERR_INVALID_ARGUMENT, "born_mask_wait before any born_mask_commit");
+    int rc = use_device(h);
+    if (rc) return rc;
+    CUDA_TRY(h, cudaStreamWaitEvent((cudaStream_t)stream, h->mask_event, 0));
+    return BORN_OK;
 }
 
 int32_t born_debug_expire_wait(void* handle, void* stream) {

@@ -58,6 +58,13 @@ struct ScanArgs {
     const int32_t* history;
     const int32_t* history_len;
     int history_stride;
+    // device-resident history (born_history_*): the finished row appends its token here
+    int32_t* ring;            // [rows, ring_cap] the last ring_cap tokens of every row; NULL: off
+    int32_t* ring_total;      // [rows] tokens appended since the reset
+    int32_t* ring_len;        // [rows] min(total, ring_cap): what the next call reads as history_len
+    int32_t* ring_finished;   // [rows] non-zero once the row has sampled a stop token
+    int ring_cap, n_stop;
+    int32_t stop_ids[8];
     const born_row_params* row_params;
     born_row_params params;
     const float* uniforms;

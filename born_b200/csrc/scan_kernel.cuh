@@ -845,6 +845,28 @@ __device__ __forceinline__ bool hist_apply(HistCursor& hc, const unsigned long l
     return __any_sync(0xffffffffu, wrote);
 }
 
+// Device-resident history: the CTA that finished caller row b appends the sampled token to the
+// row's ring (the next call reads the ring as its history), marks the row finished when the
+// token is a stop token, and blanks the outputs of a row that had finished before.  One thread,
+// after a barrier that follows the row's output writes.
+__device__ __forceinline__ void ring_append(const ScanArgs& A, int b) {
+    if (A.ring_finished[b]) {
+        A.out_token[b] = -1;
+        A.out_status[b] = BORN_ROW_FINISHED;
+        if (A.out_prob) A.out_prob[b] = 0.0f;
+        if (A.out_kept_count) A.out_kept_count[b] = 0;
+        return;
+    }
+    const int tok = A.out_token[b];
+    if (A.out_status[b] != BORN_ROW_OK || tok < 0) return;
+    const int total = A.ring_total[b];
+    A.ring[(int64_t)b * A.ring_cap + total % A.ring_cap] = tok;
+    A.ring_total[b] = total + 1;
+    A.ring_len[b] = min(total + 1, A.ring_cap);
+    for (int i = 0; i < A.n_stop; ++i)
+        if (A.stop_ids[i] == tok) A.ring_finished[b] = 1;
+}
+
 // ---- the kernel -------------------------------------------------------------------------------
 template <typename T, bool kMask, bool kLse>
 __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_constant__ ScanArgs A) {
@@ -1222,8 +1244,14 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
             }
         }
         // (one call site: the finish is inlined, its arguments stay in registers)
-        if (finish_here) finish_row<T>(A, sh, reinterpret_cast<uint64_t*>(smem + L.sel), reinterpret_cast<unsigned long long*>(smem + L.cand),
-                                       p0.row, src);
+        if (finish_here) {
+            finish_row<T>(A, sh, reinterpret_cast<uint64_t*>(smem + L.sel), reinterpret_cast<unsigned long long*>(smem + L.cand),
+                          p0.row, src);
+            if (A.ring != nullptr && A.mode == kScanFull) {
+                cta_sync();  // the row's outputs are written (or the row is handed to the exact search)
+                if (tid == 0 && A.deferred[p0.row] == 0) ring_append(A, q.b);
+            }
+        }
         PROF(4 + 3 * min(seg_ord, 1));
     }
     PROF(10);
@@ -1278,6 +1306,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                 if (tid == 0) { A.deferred[r] = 0; atomicAdd(A.dev_error + 1, 1); atomicAdd(A.dev_error + 8 + (owner >> 24), 1); }
                 fallback_row<T>(A, sh, smem, r);
                 cta_sync();
+                if (A.ring != nullptr && A.mode == kScanFull && tid == 0) ring_append(A, r / A.G);
             }
         }
     }

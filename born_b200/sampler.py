@@ -208,7 +208,7 @@ class Sampler:
     # -- sampling -------------------------------------------------------------------------
     def sample(self, logits, uniforms=None, config=None, row_params=None, mask=None, history=None,
                history_len=None, want_prob=True, want_lse=False, want_kept=0, vocab_segments=0, stream=None,
-               bf16=False, out=None, want_kept_count=False):
+               bf16=False, out=None, want_kept_count=False, uploaded_mask=None):
         """Sample one token per row of `logits` [batch, vocab].
 
         row_params: optional per-row array (numpy structured `ROW_PARAMS_DTYPE` on the host, or a
@@ -240,6 +240,11 @@ class Sampler:
                 raise InvalidArgument("mask must be [batch, ceil(vocab/32)] uint32")
             a.mask = _ptr(mask)
             a.mask_row_stride = int(mask.shape[1])
+        if uploaded_mask is not None:  # (device pointer from mask_commit, words per row)
+            if mask is not None or not dev:
+                raise InvalidArgument("uploaded_mask goes with device logits and without `mask`")
+            a.mask = int(uploaded_mask[0])
+            a.mask_row_stride = int(uploaded_mask[1])
         if history is not None:
             if history.ndim != 2 or int(history.shape[0]) != B:
                 raise InvalidArgument("history must be [batch, n] int32")
@@ -276,10 +281,79 @@ class Sampler:
         if getattr(self, "_marshal", None) is not None:
             self._marshal.args = a
             return res
-        rc = self._lib.born_sample(self._h, C.byref(a), stream)
+        entry = self._lib.born_sample_next if getattr(self, "_next", False) else self._lib.born_sample
+        rc = entry(self._h, C.byref(a), stream)
         if rc != L.BORN_OK:
             self._raise(rc)
         return res
+
+    # -- the autoregressive loop: device-resident history, stop tokens --------------------------
+    def history_create(self, capacity):
+        """Allocate the device-resident token history: the last `capacity` tokens of every row."""
+        rc = self._lib.born_history_create(self._h, int(capacity))
+        if rc != L.BORN_OK:
+            self._raise(rc)
+
+    def history_reset(self, tokens, lens=None, stream=None):
+        """Load prompts [batch, n] (int32, host or device) with optional per-row lengths; clears the finished flags."""
+        dev = _on_device(tokens)
+        if lens is not None and _on_device(lens) != dev:
+            raise InvalidArgument("lens must live on the same side (host/device) as tokens")
+        B, n = int(tokens.shape[0]), int(tokens.shape[1])
+        rc = self._lib.born_history_reset(self._h, _ptr(tokens) if n else None, _ptr(lens), B, n,
+                                          L.MEM_DEVICE if dev else L.MEM_HOST, stream)
+        if rc != L.BORN_OK:
+            self._raise(rc)
+
+    def history_set_stop_tokens(self, ids):
+        ids = [int(i) for i in ids]
+        arr = (C.c_int32 * max(1, len(ids)))(*ids)
+        rc = self._lib.born_history_set_stop_tokens(self._h, arr, len(ids))
+        if rc != L.BORN_OK:
+            self._raise(rc)
+
+    def history_read(self, batch, capacity, stream=None):
+        """(tokens [batch, capacity] in ring order, total [batch], finished [batch]) as numpy arrays."""
+        tok = np.zeros((batch, capacity), dtype=np.int32)
+        total = np.zeros(batch, dtype=np.int32)
+        fin = np.zeros(batch, dtype=np.int32)
+        rc = self._lib.born_history_read(self._h, tok.ctypes.data, total.ctypes.data, fin.ctypes.data, int(batch), L.MEM_HOST, stream)
+        if rc != L.BORN_OK:
+            self._raise(rc)
+        return tok, total, fin
+
+    def sample_next(self, logits, **kw):
+        """`sample` over the device-resident history: the kernel appends every row's token to it."""
+        if kw.get("history") is not None or kw.get("history_len") is not None:
+            raise InvalidArgument("sample_next reads the sampler's own history")
+        self._next = True
+        try:
+            return self.sample(logits, **kw)
+        finally:
+            self._next = False
+
+    # -- grammar masks: double-buffered upload ----------------------------------------------------
+    def mask_begin(self, batch, words_per_row):
+        """The pinned host buffer to fill for the next step, as a numpy uint32 array [batch, words_per_row]."""
+        p = C.POINTER(C.c_uint32)()
+        rc = self._lib.born_mask_begin(self._h, int(batch), int(words_per_row), C.byref(p))
+        if rc != L.BORN_OK:
+            self._raise(rc)
+        return np.ctypeslib.as_array(p, shape=(int(batch), int(words_per_row)))
+
+    def mask_commit(self):
+        """Start the copy of the buffer from `mask_begin` to the device; returns the device pointer."""
+        d = C.c_void_p()
+        rc = self._lib.born_mask_commit(self._h, C.byref(d))
+        if rc != L.BORN_OK:
+            self._raise(rc)
+        return int(d.value)
+
+    def mask_wait(self, stream=None):
+        """Make `stream` wait for the committed mask (no host synchronisation)."""
+        rc = self._lib.born_mask_wait(self._h, stream)
+        if rc != L.BORN_OK:
+            self._raise(rc)
 
     def prepare(self, logits, **kw):
         """Marshal a `sample` call once and return a `PreparedCall`: `run(stream)` then costs one

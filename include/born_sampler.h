@@ -58,6 +58,7 @@ extern "C" {
 #define BORN_ROW_POS_INF 3    /* +inf logit among the allowed tokens: token = -1 */
 #define BORN_ROW_OVERFLOW 4   /* only from the vocab-sharded path: a shard record could not be made exact */
 #define BORN_ROW_BAD_TOKEN 5  /* speculative verify: draft token outside [0, vocab) */
+#define BORN_ROW_FINISHED 6   /* born_sample_next: the row sampled a stop token in an earlier step; token = -1 */
 
 /* ---- limits ---- */
 #define BORN_MAX_TOP_K 1024
@@ -255,6 +256,53 @@ const char* born_version(void);
  * the kernel reported the expiry and came back (the expected outcome), BORN_OK when it did
  * not expire.  The handle stays usable.  Synchronises the stream. */
 int32_t born_debug_expire_wait(void* handle, void* stream);
+
+/* ---- the autoregressive loop around the sampler ---------------------------------------
+ * The reference's only call site of this path is a per-batch loop on the host that takes the
+ * arg-max of the model's output and compares it (examples/mnist/main.go:229-245); a language
+ * model's generate loop does the same once per token, and feeds the token back.  The entry
+ * points below keep what that loop carries from step to step on the device, so that step t+1
+ * needs no host round trip for it.  None has a counterpart in the reference. */
+
+/* Device-resident token history: per row the last `capacity` (<= BORN_MAX_HISTORY) tokens, a
+ * count, and a finished flag.  Allocates for the handle's max_batch rows; calling it again
+ * re-allocates.  Returns BORN_ERR_UNSUPPORTED for the handle of born_sample_static. */
+int32_t born_history_create(void* handle, int32_t capacity);
+
+/* Loads prompts: tokens [batch, stride] with lens [batch] valid ids per row (NULL: stride); only
+ * the last `capacity` ids of a row are kept.  `memory` says where tokens/lens live.  Clears the
+ * finished flags.  Ordered on `stream`. */
+int32_t born_history_reset(void* handle, const int32_t* tokens, const int32_t* lens, int32_t batch, int32_t stride,
+                           uint32_t memory, void* stream);
+
+/* Up to 8 stop token ids (n = 0: none).  A row that samples one is reported normally in that
+ * step and is finished from the next step on: token -1, status BORN_ROW_FINISHED, nothing
+ * appended. */
+int32_t born_history_set_stop_tokens(void* handle, const int32_t* ids, int32_t n);
+
+/* Copies the state out (any pointer may be NULL): tokens [batch, capacity] in ring order (slot
+ * i holds the (i mod capacity)-th token appended since the reset), total [batch] tokens
+ * appended since the reset (prompt included), finished [batch].  Synchronises `stream`. */
+int32_t born_history_read(void* handle, int32_t* tokens, int32_t* total, int32_t* finished, int32_t batch, uint32_t memory,
+                          void* stream);
+
+/* born_sample over the device-resident history: args->history and args->history_len must be
+ * NULL, args->memory BORN_MEM_DEVICE, vocab_segments off.  The kernel that finishes a row
+ * appends the sampled token to the row's history before it exits, so the next call sees it
+ * with no host step in between. */
+int32_t born_sample_next(void* handle, const born_sample_args* args, void* stream);
+
+/* Grammar-mask producer interface (absent in the reference): two pinned host buffers and two
+ * device buffers owned by the handle.  born_mask_begin hands out the pinned buffer to fill for
+ * the next step ([batch, words_per_row] words, rows tight) while the previous step's kernel
+ * may still be reading the other device buffer; born_mask_commit starts the copy to the
+ * device on the handle's own copy stream and returns the device pointer to pass as
+ * args->mask (mask_row_stride = words_per_row); born_mask_wait makes `stream` wait for that
+ * copy (an event, no host synchronisation).  The first begin allocates; later ones re-allocate
+ * only when batch * words_per_row grows. */
+int32_t born_mask_begin(void* handle, int32_t batch, int32_t words_per_row, uint32_t** host_buffer);
+int32_t born_mask_commit(void* handle, const uint32_t** device_mask);
+int32_t born_mask_wait(void* handle, void* stream);
 
 /* Test hooks: run the library's deterministic exp / fixed-point mass on device arrays. */
 int32_t born_debug_exp(const float* x_dev, float* y_dev, int64_t n, void* stream);

@@ -13,7 +13,7 @@ ERR_UNSUPPORTED = 4
 ERR_NCCL = 5
 ERR_DEVICE_TIMEOUT = 6
 
-ROW_OK, ROW_ALL_MASKED, ROW_NAN, ROW_POS_INF, ROW_OVERFLOW, ROW_BAD_TOKEN, ROW_FINISHED = range(7)
+ROW_OK, ROW_ALL_MASKED, ROW_NAN, ROW_POS_INF, ROW_OVERFLOW, ROW_BAD_TOKEN, ROW_FINISHED, ROW_BAD_PARAMS = range(8)
 
 MAX_TOP_K = 1024
 MAX_HISTORY = 1024

@@ -556,6 +556,7 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
     o.token = A.out_token; o.prob = A.out_prob; o.lse = A.out_lse; o.status = A.out_status;
     o.kept_ids = A.out_kept_ids; o.kept_count = A.out_kept_count; o.kept_stride = A.kept_stride;
     o.row = b;
+    if (A.row_params != nullptr && !row_params_ok(rp)) status = BORN_ROW_BAD_PARAMS;  // (device arrays are not checked on the host)
     if (status != BORN_ROW_OK) {
         if (tid == 0 && A.out_lse) A.out_lse[b] = NAN;
         row_fail(o, status);

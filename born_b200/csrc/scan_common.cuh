@@ -280,6 +280,14 @@ __device__ __forceinline__ float penalise(const born_row_params& rp, float z, in
     }
     return z;
 }
+// The range check that the host applies to uniform parameters (params_ok in capi.cu), for
+// per-row parameter arrays that live on the device and so reach the kernel unchecked.
+__device__ __forceinline__ bool row_params_ok(const born_row_params& p) {
+    const bool fin = isfinite(p.temperature) && isfinite(p.top_p) && isfinite(p.repetition_penalty) &&
+                     isfinite(p.frequency_penalty) && isfinite(p.presence_penalty);
+    return fin && p.temperature >= 0.0f && (p.temperature == 0.0f || p.temperature >= 1e-4f) && p.top_p >= 0.0f &&
+           p.min_p >= 0.0f && p.min_p <= 1.0f && p.top_k >= 0 && p.top_k <= BORN_MAX_TOP_K && p.repetition_penalty >= 0.0f;
+}
 __device__ __forceinline__ bool penalties_on(const born_row_params& rp) {
     return (rp.repetition_penalty != 1.0f && rp.repetition_penalty != 0.0f) || rp.frequency_penalty != 0.0f ||
            rp.presence_penalty != 0.0f;

@@ -58,6 +58,7 @@ extern "C" {
 #define BORN_ROW_POS_INF 3    /* +inf logit among the allowed tokens: token = -1 */
 #define BORN_ROW_OVERFLOW 4   /* only from the vocab-sharded path: a shard record could not be made exact */
 #define BORN_ROW_BAD_TOKEN 5  /* speculative verify: draft token outside [0, vocab) */
+#define BORN_ROW_BAD_PARAMS 7 /* a row of a device-resident row_params array is out of range: token = -1 */
 #define BORN_ROW_FINISHED 6   /* born_sample_next: the row sampled a stop token in an earlier step; token = -1 */
 
 /* ---- limits ---- */

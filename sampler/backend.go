@@ -22,6 +22,14 @@ type binding interface {
 	shardLocal(handle uintptr, a *ShardArgs, stream uintptr) int32
 	shardMerge(handle uintptr, a *ShardArgs, stream uintptr) int32
 	sampleSharded(handle uintptr, a *ShardArgs, stream uintptr) int32
+	historyCreate(handle uintptr, capacity int32) int32
+	historyReset(handle uintptr, tokens, lens uintptr, batch, stride int32, memory uint32, stream uintptr) int32
+	historySetStopTokens(handle uintptr, ids *int32, n int32) int32
+	historyRead(handle uintptr, tokens, total, finished uintptr, batch int32, memory uint32, stream uintptr) int32
+	sampleNext(handle uintptr, a *SampleArgs, stream uintptr) int32
+	maskBegin(handle uintptr, batch, wordsPerRow int32, host *uintptr) int32
+	maskCommit(handle uintptr, device *uintptr) int32
+	maskWait(handle uintptr, stream uintptr) int32
 	lastError(handle uintptr) string
 	version() string
 }

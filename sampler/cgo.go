@@ -55,5 +55,29 @@ func (cgoBinding) shardMerge(h uintptr, a *ShardArgs, st uintptr) int32 {
 func (cgoBinding) sampleSharded(h uintptr, a *ShardArgs, st uintptr) int32 {
 	return int32(C.born_sample_sharded(h2p(h), (*C.born_shard_args)(unsafe.Pointer(a)), h2p(st)))
 }
+func (cgoBinding) historyCreate(h uintptr, capacity int32) int32 {
+	return int32(C.born_history_create(h2p(h), C.int32_t(capacity)))
+}
+func (cgoBinding) historyReset(h uintptr, tokens, lens uintptr, batch, stride int32, memory uint32, st uintptr) int32 {
+	return int32(C.born_history_reset(h2p(h), (*C.int32_t)(h2p(tokens)), (*C.int32_t)(h2p(lens)), C.int32_t(batch),
+		C.int32_t(stride), C.uint32_t(memory), h2p(st)))
+}
+func (cgoBinding) historySetStopTokens(h uintptr, ids *int32, n int32) int32 {
+	return int32(C.born_history_set_stop_tokens(h2p(h), (*C.int32_t)(unsafe.Pointer(ids)), C.int32_t(n)))
+}
+func (cgoBinding) historyRead(h uintptr, tokens, total, finished uintptr, batch int32, memory uint32, st uintptr) int32 {
+	return int32(C.born_history_read(h2p(h), (*C.int32_t)(h2p(tokens)), (*C.int32_t)(h2p(total)), (*C.int32_t)(h2p(finished)),
+		C.int32_t(batch), C.uint32_t(memory), h2p(st)))
+}
+func (cgoBinding) sampleNext(h uintptr, a *SampleArgs, st uintptr) int32 {
+	return int32(C.born_sample_next(h2p(h), (*C.born_sample_args)(unsafe.Pointer(a)), h2p(st)))
+}
+func (cgoBinding) maskBegin(h uintptr, batch, wordsPerRow int32, host *uintptr) int32 {
+	return int32(C.born_mask_begin(h2p(h), C.int32_t(batch), C.int32_t(wordsPerRow), (**C.uint32_t)(unsafe.Pointer(host))))
+}
+func (cgoBinding) maskCommit(h uintptr, device *uintptr) int32 {
+	return int32(C.born_mask_commit(h2p(h), (**C.uint32_t)(unsafe.Pointer(device))))
+}
+func (cgoBinding) maskWait(h uintptr, st uintptr) int32 { return int32(C.born_mask_wait(h2p(h), h2p(st))) }
 func (cgoBinding) lastError(h uintptr) string { return C.GoString(C.born_last_error(h2p(h))) }
 func (cgoBinding) version() string            { return C.GoString(C.born_version()) }

@@ -19,6 +19,8 @@ const (
 	RowPosInf    = 3
 	RowOverflow  = 4
 	RowBadToken  = 5
+	RowFinished  = 6 // SampleNext: the row sampled a stop token in an earlier step
+	RowBadParams = 7 // a row of a device-resident parameter array is out of range
 )
 
 const (

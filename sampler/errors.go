@@ -20,7 +20,8 @@ type RowError struct {
 
 func (e *RowError) Error() string {
 	names := map[int32]string{RowAllMasked: "every token masked", RowNaN: "NaN logit", RowPosInf: "+inf logit",
-		RowOverflow: "shard record not exact", RowBadToken: "draft token out of range"}
+		RowOverflow: "shard record not exact", RowBadToken: "draft token out of range",
+		RowFinished: "row finished at a stop token", RowBadParams: "sampling parameters out of range"}
 	if e.Status == 100+ErrDeviceTimeout {
 		return fmt.Sprintf("born sampler: row %d: a bounded on-device wait gave up", e.Row)
 	}

@@ -30,6 +30,14 @@ type puregoBinding struct {
 	fShardLocal    func(h uintptr, a *ShardArgs, stream uintptr) int32
 	fShardMerge    func(h uintptr, a *ShardArgs, stream uintptr) int32
 	fSampleSharded func(h uintptr, a *ShardArgs, stream uintptr) int32
+	fHistCreate    func(h uintptr, capacity int32) int32
+	fHistReset     func(h uintptr, tokens, lens uintptr, batch, stride int32, memory uint32, stream uintptr) int32
+	fHistStop      func(h uintptr, ids *int32, n int32) int32
+	fHistRead      func(h uintptr, tokens, total, finished uintptr, batch int32, memory uint32, stream uintptr) int32
+	fSampleNext    func(h uintptr, a *SampleArgs, stream uintptr) int32
+	fMaskBegin     func(h uintptr, batch, words int32, host *uintptr) int32
+	fMaskCommit    func(h uintptr, device *uintptr) int32
+	fMaskWait      func(h uintptr, stream uintptr) int32
 	fLastError     func(h uintptr) *byte
 	fVersion       func() *byte
 }
@@ -66,6 +74,14 @@ func load() (binding, error) {
 		purego.RegisterLibFunc(&b.fShardLocal, lib, "born_shard_local")
 		purego.RegisterLibFunc(&b.fShardMerge, lib, "born_shard_merge")
 		purego.RegisterLibFunc(&b.fSampleSharded, lib, "born_sample_sharded")
+		purego.RegisterLibFunc(&b.fHistCreate, lib, "born_history_create")
+		purego.RegisterLibFunc(&b.fHistReset, lib, "born_history_reset")
+		purego.RegisterLibFunc(&b.fHistStop, lib, "born_history_set_stop_tokens")
+		purego.RegisterLibFunc(&b.fHistRead, lib, "born_history_read")
+		purego.RegisterLibFunc(&b.fSampleNext, lib, "born_sample_next")
+		purego.RegisterLibFunc(&b.fMaskBegin, lib, "born_mask_begin")
+		purego.RegisterLibFunc(&b.fMaskCommit, lib, "born_mask_commit")
+		purego.RegisterLibFunc(&b.fMaskWait, lib, "born_mask_wait")
 		purego.RegisterLibFunc(&b.fLastError, lib, "born_last_error")
 		purego.RegisterLibFunc(&b.fVersion, lib, "born_version")
 		loaded = b
@@ -111,3 +127,17 @@ func (b *puregoBinding) shardInit(h uintptr, id *[128]byte, rank, nranks int32) 
 func (b *puregoBinding) sampleSharded(h uintptr, a *ShardArgs, st uintptr) int32 {
 	return b.fSampleSharded(h, a, st)
 }
+func (b *puregoBinding) historyCreate(h uintptr, capacity int32) int32 { return b.fHistCreate(h, capacity) }
+func (b *puregoBinding) historyReset(h uintptr, tokens, lens uintptr, batch, stride int32, memory uint32, st uintptr) int32 {
+	return b.fHistReset(h, tokens, lens, batch, stride, memory, st)
+}
+func (b *puregoBinding) historySetStopTokens(h uintptr, ids *int32, n int32) int32 { return b.fHistStop(h, ids, n) }
+func (b *puregoBinding) historyRead(h uintptr, tokens, total, finished uintptr, batch int32, memory uint32, st uintptr) int32 {
+	return b.fHistRead(h, tokens, total, finished, batch, memory, st)
+}
+func (b *puregoBinding) sampleNext(h uintptr, a *SampleArgs, st uintptr) int32 { return b.fSampleNext(h, a, st) }
+func (b *puregoBinding) maskBegin(h uintptr, batch, words int32, host *uintptr) int32 {
+	return b.fMaskBegin(h, batch, words, host)
+}
+func (b *puregoBinding) maskCommit(h uintptr, device *uintptr) int32 { return b.fMaskCommit(h, device) }
+func (b *puregoBinding) maskWait(h uintptr, st uintptr) int32        { return b.fMaskWait(h, st) }

@@ -15,12 +15,14 @@ def _worker(rank, world, port, q):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"  # plain peer transfers: a rank that failed would otherwise fault its peers' links
     import torch
     import torch.distributed as dist
     from born_b200 import Sampler, parallel as P, workloads as W
     from oracle import born_oracle as O
     torch.cuda.set_device(rank)
     dist.init_process_group("gloo", rank=rank, world_size=world)  # set-up only; the data path is the library's NCCL
+    s = None
     try:
         B, V, k = 64, 64000, 16
         c = W.config5(seed=3, batch=B, vocab=V, shards=world)
@@ -41,12 +43,13 @@ def _worker(rank, world, port, q):
         z = W.bf16_bits_to_f32(c["logits_bf16"]).astype(np.float64)
         truth = np.log(np.exp(z - z.max(1, keepdims=True)).sum(1)) + z.max(1)
         assert np.max(np.abs(out["lse"].cpu().numpy() - truth)) <= 2e-5
-        s.close()
         q.put((rank, "ok"))
     except Exception:
         import traceback
         q.put((rank, traceback.format_exc()))
     finally:
+        if s is not None:
+            s.close()  # (also on a failed assertion: the communicator is destroyed between steps, nothing in flight)
         dist.destroy_process_group()
 
 

@@ -711,3 +711,30 @@ def test_config5_full_batch_on_one_gpu(sampler, oracle):
     c = W.config5(seed=0, batch=1024)
     got, ref = run_both(sampler, oracle, c["logits_bf16"], c["params"], c["uniforms"], segments=c["shards"], want_kept=0)
     assert_parity(got, ref, check_kept=False)
+
+
+def test_out_of_range_row_params_on_the_device_fail_their_row_only(sampler, oracle):
+    # a per-row parameter array in device memory is not seen by the host-side range check: the kernel
+    # reports the row (token -1, BORN_ROW_BAD_PARAMS) and samples the others as usual
+    from born_b200 import SamplingConfig, _lib as L
+    from born_b200.sampler import row_params_array
+    torch = torch_mod()
+    B, V = 6, 9000
+    z = (W.normal(77, 1, B * V) * 3.0).astype(np.float32).reshape(B, V)
+    u = W.uniform_f32(77, 2, B)
+    rows = [dict(temperature=0.8, top_k=30) for _ in range(B)]
+    good = row_params_array([SamplingConfig(**r) for r in rows])
+    bad = good.copy()
+    bad["temperature"][1] = np.nan
+    bad["min_p"][3] = 1.5
+    bad["top_k"][4] = 5000
+    rp = torch.from_numpy(bad.view(np.uint8).copy()).cuda()
+    out = sampler.sample(torch.from_numpy(z).cuda(), uniforms=torch.from_numpy(u).cuda(), row_params=rp)
+    torch.cuda.synchronize()
+    ref = oracle.sample(z, oracle.params_from_rows(rows), uniforms=u, want_kept=1)
+    tok, st = out["token"].cpu().numpy(), out["status"].cpu().numpy()
+    for b in range(B):
+        if b in (1, 3, 4):
+            assert tok[b] == -1 and st[b] == L.ROW_BAD_PARAMS, b
+        else:
+            assert tok[b] == ref["token"][b] and st[b] == L.ROW_OK, b

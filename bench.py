@@ -403,7 +403,7 @@ def run_sharded(torch, dist, sampler, w, rank, world, device, steps, warmup, bar
     # parity: rank 0 gathers the shards of buffer 0 once, outside the timed region
     calls[0](stream.cuda_stream)
     torch.cuda.synchronize()
-    shard = bufs[0]["logits"].view(torch.int16)
+    shard = bufs[0]["logits"].contiguous().view(torch.uint8)  # (bytes: the collective takes no 16-bit integer type)
     gathered = [torch.empty_like(shard) for _ in range(world)] if rank == 0 else None
     dist.gather(shard, gathered, dst=0)
     toks = [torch.empty_like(out["token"]) for _ in range(world)] if rank == 0 else None
@@ -412,7 +412,7 @@ def run_sharded(torch, dist, sampler, w, rank, world, device, steps, warmup, bar
     if rank == 0:
         from oracle import born_oracle as O
         O.build()
-        full = torch.cat(gathered, dim=1).cpu().numpy().view(np.uint16)
+        full = torch.cat([g.view(torch.int16) for g in gathered], dim=1).cpu().numpy().view(np.uint16)
         u = bufs[0]["uniforms"].cpu().numpy()
         ref = O.sample(np.ascontiguousarray(full), O.make_params(**p), uniforms=u, segments=world,
                        nthreads=os.cpu_count() or 1)

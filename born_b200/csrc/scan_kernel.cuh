@@ -670,32 +670,31 @@ __device__ __noinline__ int hist_build_wide(const ScanArgs& A, const int (&ids)[
     return (int)n;
 }
 
-// The same list for a segment of at most kHistVoteTiles tiles -- every row below some 260 000
-// fp32 logits -- without one atomic: shared-memory atomics cost about two cycles per lane and SM,
-// and the build sits in front of the segment's first tile.  A warp finds, tile by tile, which of
-// its lanes hold a token of that tile (a vote per tile and id slot): the lane's rank among them
-// is its place in the warp's part of the tile's bucket, the count goes to the (tile, warp)
-// counter by a plain store.  After the scan every token is stored at start + rank.  Repeats are
-// found afterwards inside the tile's bucket (a handful of entries): the first occurrence gets
-// the multiplicity, the others get 0 and are skipped by whoever applies the list.
-constexpr int kHistVoteTiles = 64;
+// The same list for a segment of at most kHistNarrowTiles tiles -- every row below some 260 000
+// fp32 logits.  The build sits in front of the segment's first tile, and shared-memory atomics
+// cost about two cycles per lane and SM, so there is one per id and nothing else that
+// serialises: the atomic on the (tile, warp) counter (zeroed by the segment set-up) counts the
+// token and returns its place among the warp's tokens of that tile; after one barrier every
+// warp works out the starts of all (tile, warp) runs for itself -- a lane per tile, eight
+// counters each, a shuffle scan -- and stores its tokens.  Repeats of a token are resolved
+// afterwards inside the tile's bucket (a handful of entries): the first occurrence gets the
+// multiplicity, the others 0, and whoever applies the list skips those.
+constexpr int kHistNarrowTiles = 64;
 template <int TILE>
 __device__ __forceinline__ int hist_build(const ScanArgs& A, const int (&ids)[kHistPer], int g, int lead, int j_begin, int j_end,
                                           uint32_t* keys, uint32_t* cnt32, unsigned long long* list, uint32_t* wscr) {
     const int span = j_end - j_begin;
-    if (span > kHistVoteTiles) return hist_build_wide<TILE>(A, ids, g, lead, j_begin, j_end, keys, cnt32, list, wscr);
-    static_assert(kHistPer == 4, "the vote loop is written for four ids per thread");
+    if (span > kHistNarrowTiles) return hist_build_wide<TILE>(A, ids, g, lead, j_begin, j_end, keys, cnt32, list, wscr);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t lt = (1u << lane) - 1u;
-    uint16_t* cnt16 = reinterpret_cast<uint16_t*>(cnt32);
-    const int nc = span * kScanWarps;
+    uint16_t* tstart = reinterpret_cast<uint16_t*>(keys);  // (the candidate area is idle) start of every tile's bucket
     PROF(25);
     int rel[kHistPer];
-    uint32_t tok[kHistPer];
+    uint32_t tok[kHistPer], rank[kHistPer];
 #pragma unroll
     for (int r = 0; r < kHistPer; ++r) {
         rel[r] = -1;
         tok[r] = 0;
+        rank[r] = 0;
         const int id = ids[r];
         if (id < 0) continue;
         int g2 = 0;
@@ -706,93 +705,72 @@ __device__ __forceinline__ int hist_build(const ScanArgs& A, const int (&ids)[kH
         if (tl < j_begin || tl >= j_end) continue;
         rel[r] = tl - j_begin;
         tok[r] = tk;
-    }
-    // (population counts run on the slow pipe: the votes are parked in shared memory -- the
-    // candidate area is idle -- and only the lanes that need a count take one afterwards)
-    uint4* votes = reinterpret_cast<uint4*>(keys) + warp * kHistVoteTiles;
-    for (int t = 0; t < span; ++t) {
-        const uint32_t b0 = __ballot_sync(0xffffffffu, rel[0] == t), b1 = __ballot_sync(0xffffffffu, rel[1] == t);
-        const uint32_t b2 = __ballot_sync(0xffffffffu, rel[2] == t), b3 = __ballot_sync(0xffffffffu, rel[3] == t);
-        if (lane == 0) votes[t] = make_uint4(b0, b1, b2, b3);
-    }
-    __syncwarp();
-    int rank[kHistPer];
-#pragma unroll
-    for (int r = 0; r < kHistPer; ++r) {
-        rank[r] = 0;
-        if (rel[r] < 0) continue;
-        const uint4 v = votes[rel[r]];
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int r2 = 0; r2 < r; ++r2) rank[r] += __popc(w[r2]);
-        rank[r] += __popc(w[r] & lt);
-    }
-#pragma unroll
-    for (int h = 0; h < kHistVoteTiles / 32; ++h) {
-        const int t = lane + 32 * h;
-        if (t < span) {
-            const uint4 v = votes[t];
-            cnt16[t * kScanWarps + warp] = (uint16_t)(__popc(v.x) + __popc(v.y) + __popc(v.z) + __popc(v.w));
-        }
+        const int c = rel[r] * kScanWarps + warp;
+        rank[r] = (smem_atom_add(&cnt32[c >> 1], 1u << (16 * (c & 1))) >> (16 * (c & 1))) & 0xFFFFu;
     }
     cta_sync();
     PROF(26);
-    // exclusive scan of the span * 8 counters (at most two per thread)
-    const int per = (nc + kThreads - 1) / kThreads;
-    const int lo = min(tid * per, nc), hi = min(lo + per, nc);
-    uint32_t loc = 0;
-    for (int i = lo; i < hi; ++i) loc += cnt16[i];
-    uint32_t incl = loc;
+    // lane l: tiles l and l + 32 -- the tile's total, and what the warps below this one hold of it
+    uint32_t tot[2] = {0, 0}, below[2] = {0, 0};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int t = lane + 32 * h;
+        if (t < span) {
+            const uint4 v = reinterpret_cast<const uint4*>(cnt32)[t];  // eight 16-bit counters
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < kScanWarps; ++i) {
+                const uint32_t c = (w[i >> 1] >> (16 * (i & 1))) & 0xFFFFu;
+                tot[h] += c;
+                if (i < warp) below[h] += c;
+            }
+        }
+    }
+    uint32_t incl0 = tot[0], incl1 = tot[1];
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
-        const uint32_t up = __shfl_up_sync(0xffffffffu, incl, d);
-        if (lane >= d) incl += up;
+        const uint32_t u0 = __shfl_up_sync(0xffffffffu, incl0, d), u1 = __shfl_up_sync(0xffffffffu, incl1, d);
+        if (lane >= d) { incl0 += u0; incl1 += u1; }
     }
-    if (lane == 31) wscr[warp] = incl;
-    cta_sync();
-    uint32_t off = 0, n = 0;
+    const uint32_t sum0 = __shfl_sync(0xffffffffu, incl0, 31);
+    const uint32_t n = sum0 + __shfl_sync(0xffffffffu, incl1, 31);
+    const uint32_t base0 = incl0 - tot[0], base1 = sum0 + incl1 - tot[1];
 #pragma unroll
-    for (int w = 0; w < kScanWarps; ++w) {
-        const uint32_t x = wscr[w];
-        if (w < warp) off += x;
-        n += x;
+    for (int r = 0; r < kHistPer; ++r) {
+        const int src = rel[r] >= 0 ? (rel[r] & 31) : 0;
+        const uint32_t v0 = __shfl_sync(0xffffffffu, base0 + below[0], src), v1 = __shfl_sync(0xffffffffu, base1 + below[1], src);
+        if (rel[r] >= 0) list[((rel[r] >> 5) ? v1 : v0) + rank[r]] = (1ull << 32) | tok[r];
     }
-    uint32_t run = off + incl - loc;
-    for (int i = lo; i < hi; ++i) {
-        const uint32_t c = cnt16[i];
-        cnt16[i] = (uint16_t)run;  // where the counter's tokens start in the list
-        run += c;
+    if (warp == 0) {
+        if (lane < span) tstart[lane] = (uint16_t)base0;
+        if (lane + 32 < span) tstart[lane + 32] = (uint16_t)base1;
+        if (lane == 0) tstart[span] = (uint16_t)n;
     }
-    cta_sync();
-    PROF(29);
-#pragma unroll
-    for (int r = 0; r < kHistPer; ++r)
-        if (rel[r] >= 0) list[cnt16[rel[r] * kScanWarps + warp] + rank[r]] = (1ull << 32) | tok[r];
     cta_sync();
     PROF(27);
-    // repeats: inside the tile's bucket
-    for (int i = tid; i < (int)n; i += kThreads) {
-        const uint32_t tk = (uint32_t)list[i];
-        const int t = (int)((tk + (uint32_t)lead) / (uint32_t)TILE) - j_begin;
-        const int b0 = cnt16[t * kScanWarps], b1 = t + 1 < span ? (int)cnt16[(t + 1) * kScanWarps] : (int)n;
-        int same = 0;
-        bool first = true;
-        int j = b0;
-        for (; j + 4 <= b1; j += 4) {  // (four loads in flight: the loop is bound by their latency otherwise)
-            uint32_t x[4];
+    {
+        for (int i = tid; i < (int)n; i += kThreads) {
+            const uint32_t tk = (uint32_t)list[i];
+            const int t = (int)((tk + (uint32_t)lead) / (uint32_t)TILE) - j_begin;
+            const int b0 = tstart[t], b1 = tstart[t + 1];
+            int same = 0;
+            bool first = true;
+            int j = b0;
+            for (; j + 4 <= b1; j += 4) {  // (four loads in flight: the loop is bound by their latency otherwise)
+                uint32_t x[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) x[k] = (uint32_t)list[j + k];
+                for (int k = 0; k < 4; ++k) x[k] = (uint32_t)list[j + k];
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-                if (x[k] == tk) { ++same; first = first && j + k >= i; }
+                for (int k = 0; k < 4; ++k)
+                    if (x[k] == tk) { ++same; first = first && j + k >= i; }
+            }
+            for (; j < b1; ++j)
+                if ((uint32_t)list[j] == tk) { ++same; first = first && j >= i; }
+            if (same > 1) list[i] = ((unsigned long long)(first ? same : 0) << 32) | tk;
         }
-        for (; j < b1; ++j)
-            if ((uint32_t)list[j] == tk) { ++same; first = first && j >= i; }
-        if (same > 1) list[i] = ((unsigned long long)(first ? same : 0) << 32) | tk;
+        cta_sync();
     }
-    cta_sync();
     PROF(28);
-    (void)keys;
     return (int)n;
 }
 
@@ -951,6 +929,8 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
         // the row's uniform is wanted at the very end: fetch it now
         const float u_row = (A.uniforms != nullptr && A.mode == kScanFull) ? __ldg(A.uniforms + q.b) : 0.0f;
         if (tid < kScanWarps) { sh.wbound[tid] = -INFINITY; sh.wcount[tid] = 0; }
+        if (A.history != nullptr)  // the (tile, warp) counters of the history build: kHistNarrowTiles x 8 of 16 bits
+            reinterpret_cast<uint32_t*>(smem + L.sel)[tid] = 0;
         cta_sync();
         ThreadStats st;
         stats_reset(st, pl.c2);

@@ -246,9 +246,6 @@ int fill_scan(Handle* h, ScanArgs& A, int B, int G, int V, int dtype, const void
     // When a whole number S of equal slices per row nearly fills the GPU, every CTA gets exactly
     // one slice: no CTA meets a row boundary in mid-stream, and with S = 1 a row is finished from
     // the shared memory of the CTA that streamed it.
-#if defined(BORN_EXP) || defined(BORN_PROFILE)
-    if (!getenv("BORN_NO_SLICES"))
-#endif
     for (int S = 1; S <= 64 && rows * S <= h->max_grid; ++S)
         if (A.tpr % S == 0 && rows * S * 20 >= (int64_t)h->max_grid * 17) { *grid = (int)(rows * S); break; }
     // entries per segment record: as many as the record area gives every (row + cta) slot
@@ -261,10 +258,6 @@ int fill_scan(Handle* h, ScanArgs& A, int B, int G, int V, int dtype, const void
     A.dev_error = h->dev_error;
     A.timeout_ns = h->timeout_ns;
     A.debug_skip_tile = -1;
-#ifdef BORN_PROFILE
-    A.prof = nullptr;
-    if (const char* pp = getenv("BORN_PROF_PTR")) A.prof = (unsigned long long*)strtoull(pp, nullptr, 0);
-#endif
     return BORN_OK;
 }
 

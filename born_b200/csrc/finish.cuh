@@ -78,13 +78,11 @@ __device__ __forceinline__ bool select_small(const SelectIn& in, uint64_t* sel, 
         q = (x < -30.0f) ? 0ull : mass_of(x);
         if (in.Qa && q < in.Qa) { q = 0; ck &= (uint64_t)kIdxMask; }  // min-p: a dead entry keeps its index only
     }
-    PROFG(15);
     cta_sync();  // every thread has read sel[] for its rank
     const int nk = min(n, k_eff);
     if (mine && rank < nk) { sel[rank] = ck; selq[rank] = q; }
     if (tid == 0) { sh.acc[0] = 0; sh.nw = 0; }
     cta_sync();
-    PROFG(16);
     // the entry of rank `tid`, and the mass ahead of it
     const uint64_t c2 = tid < nk ? sel[tid] : 0ull;
     const uint64_t q2 = tid < nk ? (uint64_t)selq[tid] : 0ull;
@@ -119,7 +117,6 @@ __device__ __forceinline__ bool select_small(const SelectIn& in, uint64_t* sel, 
     }
     cta_sync();
     const int R = sh.nw;
-    PROFG(17);
     const uint64_t S = sh.acc[0];
     if (topp && in.S_ext && !in.complete && S < Tp) return false;  // (uniform)
     if (S == 0) {  // cannot happen while the row maximum is finite; never divide by it
@@ -148,7 +145,6 @@ __device__ __forceinline__ bool select_small(const SelectIn& in, uint64_t* sel, 
         if (o.kept_ids && tid < o.kept_stride) o.kept_ids[(int64_t)o.row * o.kept_stride + tid] = ck_idx(c2);
     }
     if (o.kept_count && tid == 0) o.kept_count[o.row] = R;
-    PROFG(18);
     return true;
 }
 
@@ -520,7 +516,6 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
             }
         }
     };
-    PROF(20);
     int status = BORN_ROW_OK;
     if (m != m) status = BORN_ROW_NAN;
     else if (m == INFINITY) status = BORN_ROW_POS_INF;
@@ -592,7 +587,6 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
     }
 
     const float u = src.u;
-    PROF(21);
     unsigned long long S_tot = 0;
     if (pl.need_mass) {
         // row total from the mass blocks; log-sum-exp from it
@@ -667,7 +661,6 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
         return (int)sh.nl;
     };
     int n = gather(lowest);
-    PROF(23);
     if (n > kSelCap && !pl.no_bound) {
         // More candidates than the selection takes (a wide nucleus window, many ties).  Use only
         // the part above a higher level -- the lowest of a fixed ladder (in scaled-logit units
@@ -729,7 +722,6 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
         else defer = !select_and_draw(in, sel, selq, sh, o);
         if (defer) why = 7;                        // the nucleus reaches below the candidates
     }
-    PROF(24);
     if (defer && tid == 0) A.deferred[row] = (why << 24) | (blockIdx.x + 1u);
 }
 

@@ -96,20 +96,7 @@ struct ScanArgs {
     int* dev_error;                 // [0] error word, [1] rows that took the exact search, [8..16] ... by reason
     unsigned long long timeout_ns;  // limit of every on-device wait
     long long debug_skip_tile;      // test hook: the bulk copy of this tile is never issued (-1: none)
-#ifdef BORN_PROFILE
-    unsigned long long* prof;
-#endif
 };
-#ifdef BORN_PROFILE
-#define PROF(i) do { if (A.prof && threadIdx.x == 0) A.prof[(size_t)blockIdx.x * 32 + (i)] = (unsigned long long)clock64(); } while (0)
-__device__ unsigned long long* g_prof_ptr;
-#define PROFG(i) do { if (g_prof_ptr && threadIdx.x == 0) g_prof_ptr[(size_t)blockIdx.x * 32 + (i)] = (unsigned long long)clock64(); } while (0)
-#define PROF_ADD(i, v) do { if (A.prof && threadIdx.x == 0) A.prof[(size_t)blockIdx.x * 32 + (i)] += (unsigned long long)(v); } while (0)
-#else
-#define PROF(i) do { } while (0)
-#define PROFG(i) do { } while (0)
-#define PROF_ADD(i, v) do { } while (0)
-#endif
 
 // ---- geometry -----------------------------------------------------------------------------
 struct RowGeom {

@@ -5,16 +5,25 @@
 // the selection and the inverse-CDF draw (finish.cuh).  Every logit crosses HBM once.
 //
 // A CTA is 8 compute warps and one producer warp and streams a contiguous range of 16 KB
-// tiles (scan_common.cuh).  The producer keeps kScanStages tiles in flight with 1-D bulk
-// copies (TMA, no multicast) that complete on `full` mbarriers, applies the token-history
-// penalties to each tile once it has landed (fp32: the penalised value is written in place;
-// bf16: the token is taken out of the tile and its penalised value goes to the segment record
-// directly) and releases it on a `ready` mbarrier.  It never blocks: it alternates between
-// "issue the next copy if a stage is free" and "patch the next tile if it has landed".
-// A compute warp owns a fixed 2 KB slice of every tile (512 fp32 / 1024 bf16 logits), waits
-// for the tile, runs its slice and hands the tile back with one arrival on the `empty`
-// mbarrier.  Inside a segment the warps never meet; they meet at segment boundaries only
-// (threshold bootstrap after the first tile, record at the end).
+// tiles (scan_common.cuh): all tiles of all rows form one sequence, cut evenly over the CTAs,
+// so a CTA may stream part of a row, a whole row, or several.  The part of a row inside one
+// CTA is a segment.  The producer keeps kScanStages tiles in flight with 1-D bulk copies (TMA,
+// no multicast) that complete on `full` mbarriers; the compute warps hand a tile back with one
+// arrival each on its `empty` mbarrier.  Every thread reads a fixed share of each tile (16
+// values in four 16-byte vectors).  Inside a segment the warps meet only after its first tile
+// (threshold bootstrap) and at its end (statistics, record or finish).
+//
+// Token histories.  At the start of a segment the compute threads build, in shared memory, the
+// list of the row's distinct history tokens grouped by tile (hist_build).  In fp32 launches the
+// producer warp then writes the penalised value over the logit in every tile that has landed
+// and releases the tile on a second barrier (`ready`), so the compute warps never see an
+// unpenalised logit; in bf16 launches (a bf16 tile cannot hold the value) the compute warps
+// take the token out of the tile and feed its penalised value to the statistics and the
+// candidates themselves (hist_apply).
+//
+// Full tiles of an aligned row after the segment's first run through a short steady-state loop
+// (wait, one read of the thresholds, the straight-line tile body, the hand-back); everything
+// that is decided once per segment stays outside it.
 //
 // Candidates.  A value reaches the slow path only when it is at or above the warp's
 // threshold tau (one compare per 16 values).  tau is the maximum of
@@ -23,7 +32,8 @@
 //     minimised over the 8 warps, has at least k tokens at or above it;
 //   * running maximum + delta (greedy: delta 0; min-p: T * (ln min_p - 0.05); top-p alone: a
 //     window that the finish verifies against the exact row total);
-//   * the exclusion level of a warp whose 256-entry buffer overflowed.
+//   * the CTA's exclusion level, raised when a candidate finds its warp's 256-entry buffer full
+//     (the buffers are compacted against the current threshold when half full).
 // The first two never exclude a token the row can keep.  The third (and the nucleus window)
 // may; they are recorded as tau_excl, and a row whose kept set is not provably inside the
 // complete part of its candidates takes the exact fallback instead (fallback.cuh).
@@ -541,18 +551,15 @@ __device__ __forceinline__ void producer_loop_patching(const ScanArgs& A, ScanSh
 // ---- token history -----------------------------------------------------------------------------
 // Penalties touch at most BORN_MAX_HISTORY tokens of a row.  At the start of a segment the
 // compute threads turn the row's history into a list of its distinct tokens with their
-// multiplicities, grouped by the tile they fall into (only the tiles of this segment): a hash
-// table in the candidate area (empty at that point) removes the repeats, counters in the
-// selection area -- per (tile, warp) while the tiles are few, so that the warps do not meet on
-// the same word -- drive a counting sort into the list.  The global read of the ids is the only
-// memory round trip; it leaves before the CTA's first copies.
+// multiplicities, grouped by the tile they fall into (only the tiles of this segment), in shared
+// memory: hist_build for segments of up to kHistNarrowTiles tiles, hist_build_wide beyond.  The
+// global read of the ids is the only memory round trip; for a CTA's first row it leaves before
+// the CTA's first copies.
 //
-// While streaming, every warp walks the list in step with the tiles: the entries of tile j sit
-// at the cursor, a warp applies those that fall into its own share of the tile -- the warp that
-// reads an element is the only one that ever touches it, so a warp-level sync is all it takes.
-// fp32: the penalised value replaces the logit in the tile.  bf16 (a bf16 tile cannot hold it):
-// the token is taken out of the tile (-inf) and its penalised value goes to the statistics and
-// the candidates directly.
+// The list is applied tile by tile, in step with the stream: by the producer warp in fp32
+// launches (producer_loop_patching), by the compute warps in bf16 launches (hist_apply: a warp
+// applies the entries that fall into its own share of the tile -- the warp that reads an
+// element is the only one that ever touches it, so a warp-level sync is all it takes).
 constexpr int kHistPer = BORN_MAX_HISTORY / kThreads;  // history ids per compute thread
 struct HistCursor {
     int n, pos;
@@ -573,6 +580,10 @@ __device__ __forceinline__ void hist_ids(const ScanArgs& A, int b, int (&ids)[kH
         if ((int)threadIdx.x + r * kThreads >= len) ids[r] = -1;
 }
 
+// Segments of more than kHistNarrowTiles tiles (rows beyond some 260 000 fp32 logits): a hash table
+// in the candidate area (empty at that point) removes the repeats; counters in the selection area
+// -- per (tile, warp) up to 128 tiles, so that the warps do not meet on the same word -- drive a
+// counting sort into the list.
 template <int TILE>
 __device__ __noinline__ int hist_build_wide(const ScanArgs& A, const int (&ids)[kHistPer], int g, int lead, int j_begin, int j_end,
                                           uint32_t* keys, uint32_t* cnt32, unsigned long long* list, uint32_t* wscr) {
@@ -687,7 +698,6 @@ __device__ __forceinline__ int hist_build(const ScanArgs& A, const int (&ids)[kH
     if (span > kHistNarrowTiles) return hist_build_wide<TILE>(A, ids, g, lead, j_begin, j_end, keys, cnt32, list, wscr);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     uint16_t* tstart = reinterpret_cast<uint16_t*>(keys);  // (the candidate area is idle) start of every tile's bucket
-    PROF(25);
     int rel[kHistPer];
     uint32_t tok[kHistPer], rank[kHistPer];
 #pragma unroll
@@ -709,7 +719,6 @@ __device__ __forceinline__ int hist_build(const ScanArgs& A, const int (&ids)[kH
         rank[r] = (smem_atom_add(&cnt32[c >> 1], 1u << (16 * (c & 1))) >> (16 * (c & 1))) & 0xFFFFu;
     }
     cta_sync();
-    PROF(26);
     // lane l: tiles l and l + 32 -- the tile's total, and what the warps below this one hold of it
     uint32_t tot[2] = {0, 0}, below[2] = {0, 0};
 #pragma unroll
@@ -747,7 +756,6 @@ __device__ __forceinline__ int hist_build(const ScanArgs& A, const int (&ids)[kH
         if (lane == 0) tstart[span] = (uint16_t)n;
     }
     cta_sync();
-    PROF(27);
     {
         for (int i = tid; i < (int)n; i += kThreads) {
             const uint32_t tk = (uint32_t)list[i];
@@ -770,7 +778,6 @@ __device__ __forceinline__ int hist_build(const ScanArgs& A, const int (&ids)[kH
         }
         cta_sync();
     }
-    PROF(28);
     return (int)n;
 }
 
@@ -884,18 +891,10 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
     }
 
     // ------------------------------------------------------------------------ compute threads
-    PROF(0);
-#ifdef BORN_PROFILE
-    if (tid == 0) g_prof_ptr = A.prof;
-    if (A.prof && tid == 0) A.prof[(size_t)blockIdx.x * 32 + 11] = global_timer_ns();
-#endif
     const int lane = tid & 31, warp = tid >> 5;
     uint64_t* wbuf = reinterpret_cast<uint64_t*>(smem + L.cand) + warp * kWarpCand;
     uint32_t* wcount = &sh.wcount[warp];
     uint32_t* excl = &sh.excl_bits;
-#ifdef BORN_PROFILE
-    long long pf_wait = 0, pf_proc = 0, pf_hist = 0;
-#endif
     bool failed = false;
     int bad = 0;
     // fp32 launches with token histories: the producer warp patches the tiles and releases them
@@ -964,9 +963,6 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
             // wait, one read of the thresholds, the straight-line tile body and the hand-back.
             if (lean && seen > 0 && !failed) {
                 while (t < seg_end && rem >= TILE) {
-#ifdef BORN_PROFILE
-                    const long long qw0 = clock64();
-#endif
                     uint64_t* fb = reinterpret_cast<uint64_t*>(&wait_bar[stage]);
                     bool here = mbar_try(fb, phase);
                     if (!here) here = mbar_wait_limit(fb, phase, A.timeout_ns, &sh.fail);
@@ -975,10 +971,6 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                         sh.fail = 1;
                         break;
                     }
-#ifdef BORN_PROFILE
-                    const long long qw1 = clock64();
-                    pf_wait += qw1 - qw0;
-#endif
                     T* tile = reinterpret_cast<T*>(smem + L.tiles + stage * kTileBytes);
                     const uint32_t* smask = reinterpret_cast<const uint32_t*>(smem + L.masks + stage * (mask_stage_words<T>() * 4));
                     const float tau = collect ? current_tau(sg, sh) : INFINITY;
@@ -996,15 +988,9 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                     if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage]));
                     if (++stage == kScanStages) { stage = 0; phase ^= 1u; }
                     ++t; ++seen; ++j; rem -= TILE;
-#ifdef BORN_PROFILE
-                    pf_proc += clock64() - qw1;
-#endif
                 }
                 if (t >= seg_end) break;
             }
-#ifdef BORN_PROFILE
-            const long long pw0 = clock64();
-#endif
             if (!failed) {
                 const bool here = mbar_wait_limit(reinterpret_cast<uint64_t*>(&wait_bar[stage]), phase, A.timeout_ns, &sh.fail);
                 if (!__all_sync(0xffffffffu, here)) {  // (the warp gives up as one: what follows votes and shuffles)
@@ -1012,11 +998,6 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                     sh.fail = 1;
                 }
             }
-#ifdef BORN_PROFILE
-            const long long pw1 = clock64();
-            pf_wait += pw1 - pw0;
-            if (t == t0) PROF(1);
-#endif
             T* tile = reinterpret_cast<T*>(smem + L.tiles + stage * kTileBytes);
             const uint32_t* smask = reinterpret_cast<const uint32_t*>(smem + L.masks + stage * (mask_stage_words<T>() * 4));
             const int n_el = min(TILE, rem);
@@ -1033,9 +1014,6 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
             }
             const bool first = (seen == 0);
             bool patched = false;
-#ifdef BORN_PROFILE
-            const long long ph0 = clock64();
-#endif
             if (hist_on && !failed) {
                 // (a bf16 segment's first tile: no threshold exists yet, and the values are gone from the
                 // tile when one does -- every finite one is offered; the finish drops what lies below its cut)
@@ -1043,9 +1021,6 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                 patched = hist_apply<T, kMask, kLse>(hc, hlist, rp, tile, smask, mb_rel, j, q.lead, lo, n_el, pl.need_mass, 6, sg.id0,
                                                      tau_h, pl.c2, st, wbuf, wcount, excl);
             }
-#ifdef BORN_PROFILE
-            pf_hist += clock64() - ph0;
-#endif
             if (!failed && n_el > lo) {
                 if (pl.need_mass) {
                     // (rows of these routes are 16-byte aligned: the host sees to it)
@@ -1097,11 +1072,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage]));  // tile back to the producer
             if (++stage == kScanStages) { stage = 0; phase ^= 1u; }
-#ifdef BORN_PROFILE
-            pf_proc += clock64() - pw1;
-#endif
         }
-        PROF(2 + 3 * min(seg_ord, 1));
 
         // ---- segment record (block-synchronous)
         const float wm = warp_max_nan(st.mx);
@@ -1147,7 +1118,6 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
         bool finish_here;
         if (whole) {
             if (cta_sync_or(*reinterpret_cast<const volatile int*>(&sh.fail))) { bad = 1; break; }
-            PROF(3 + 3 * min(seg_ord, 1));
             src.direct = true;
             src.m = m_seg; src.ls = s_seg; src.bk = bound_k;
             src.taux = pl.no_bound ? INFINITY : fmaxf(zkey_to_float(sh.excl_bits), excl_window);
@@ -1213,7 +1183,6 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                 sh.c_last = c_last;
             }
             cta_sync();
-            PROF(3 + 3 * min(seg_ord, 1));
             finish_here = sh.last != 0;
             if (finish_here) {
                 __threadfence();
@@ -1232,17 +1201,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                 if (tid == 0 && A.deferred[p0.row] == 0) ring_append(A, q.b);
             }
         }
-        PROF(4 + 3 * min(seg_ord, 1));
     }
-    PROF(10);
-#ifdef BORN_PROFILE
-    if (A.prof && tid == 0) A.prof[(size_t)blockIdx.x * 32 + 12] = global_timer_ns();
-#endif
-#ifdef BORN_PROFILE
-    PROF_ADD(8, pf_wait);
-    PROF_ADD(9, pf_proc);
-    PROF_ADD(14, pf_hist);
-#endif
 
     if (!bad) bad = cta_sync_or(*reinterpret_cast<const volatile int*>(&sh.fail));
     if (bad) {

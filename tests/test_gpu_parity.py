@@ -738,3 +738,33 @@ def test_out_of_range_row_params_on_the_device_fail_their_row_only(sampler, orac
             assert tok[b] == -1 and st[b] == L.ROW_BAD_PARAMS, b
         else:
             assert tok[b] == ref["token"][b] and st[b] == L.ROW_OK, b
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_history_penalties_on_rows_of_more_than_64_tiles(oracle, dtype):
+    # beyond 64 tiles per row the history list is built by the hash-table path
+    from born_b200 import Sampler, SamplingConfig
+    torch = torch_mod()
+    B, V, H = 3, 300000 if dtype == "f32" else 600000, 700
+    params = dict(temperature=0.9, top_k=64, top_p=0.95, repetition_penalty=1.2, frequency_penalty=0.3, presence_penalty=0.1)
+    z = (W.normal(91, 1, B * V) * 3.0).astype(np.float32).reshape(B, V)
+    hist = W.randint(91, 3, B * H, V).astype(np.int32).reshape(B, H)
+    hist[:, 100:200] = hist[:, 0:100]          # repeats
+    hist[1, 300:] = hist[1, 300]               # one token many times
+    top = np.argsort(-z, axis=1)[:, :40]
+    hist[:, 600:640] = top                      # tokens that matter
+    u = W.uniform_f32(91, 2, B)
+    logits = W.f32_to_bf16_bits(z).reshape(B, V) if dtype == "bf16" else z
+    ld = torch.from_numpy(logits.view(np.int16).copy()).cuda().view(torch.bfloat16) if dtype == "bf16" else torch.from_numpy(z).cuda()
+    s = Sampler(device=0, max_batch=4, max_vocab=V)
+    try:
+        out = s.sample(ld, uniforms=torch.from_numpy(u).cuda(), config=SamplingConfig(**params),
+                       history=torch.from_numpy(hist).cuda(), want_lse=True, want_kept=64)
+        torch.cuda.synchronize()
+        ref = oracle.sample(logits, oracle.make_params(**params), uniforms=u, history=hist, want_kept=64)
+        assert np.array_equal(out["status"].cpu().numpy(), ref["status"])
+        assert np.array_equal(out["token"].cpu().numpy(), ref["token"])
+        assert np.array_equal(out["prob"].cpu().numpy().view(np.uint32), ref["prob"].view(np.uint32))
+        assert np.array_equal(out["kept_ids"].cpu().numpy(), ref["kept_ids"][:, :64])
+    finally:
+        s.close()

@@ -22,7 +22,8 @@ constexpr int kFbBins = 4096;    // bins per radix pass (12 bits)
 struct FbCtx {
     const ScanArgs* A;
     ScanShared* sh;
-    float* chunk;                  // kFbChunk logits as the sampler sees them
+    float* chunk;                  // kFbChunk logits as the sampler sees them (the buffer in use)
+    float* chunk2[2];              // the two buffers that take turns
     unsigned long long* hlist;     // distinct history tokens of the row: (count << 32) | token
     uint32_t* bcnt;                // kFbBins counts
     unsigned long long* bwt;       // kFbBins masses (also: the masses of one chunk for the draw)
@@ -72,35 +73,65 @@ __device__ __forceinline__ void fb_history(FbCtx& c) {
     c.nlist = c.sh->nl;
 }
 
-// Chunk ci of the row into shared memory, as the sampler sees it.
+// Chunk ci of the row, as the sampler sees it apart from the penalties: the thread's 16 elements
+// (element tid + 256 * j), into registers.  The loads leave together; nothing waits for them here.
+constexpr int kFbPer = kFbChunk / kThreads;
 template <typename T>
-__device__ __forceinline__ void fb_load(const FbCtx& c, int ci) {
+__device__ __forceinline__ void fb_fetch(const FbCtx& c, int ci, float (&v)[kFbPer]) {
+    const int c0 = ci * kFbChunk;
+    bool ok[kFbPer];
+#pragma unroll
+    for (int j = 0; j < kFbPer; ++j) {
+        const int tok = c0 + (int)threadIdx.x + kThreads * j;
+        ok[j] = tok < c.V && fb_allowed(c, tok);
+    }
+#pragma unroll
+    for (int j = 0; j < kFbPer; ++j) {
+        const int tok = c0 + (int)threadIdx.x + kThreads * j;
+        v[j] = tok < c.V ? fb_raw<T>(c, tok) : -INFINITY;
+    }
+#pragma unroll
+    for (int j = 0; j < kFbPer; ++j)
+        if (!ok[j]) v[j] = -INFINITY;
+}
+// ... from the registers into the buffer whose turn it is, with the history penalties on top.
+template <typename T>
+__device__ __forceinline__ void fb_store(FbCtx& c, int ci, const float (&v)[kFbPer]) {
     const int tid = threadIdx.x;
     const int c0 = ci * kFbChunk;
-    cta_sync();  // the previous chunk has been used
-    for (int e = tid; e < kFbChunk; e += kThreads) {
-        const int tok = c0 + e;
-        float z = -INFINITY;
-        if (tok < c.V && fb_allowed(c, tok)) z = fb_raw<T>(c, tok);
-        c.chunk[e] = z;
+    c.chunk = c.chunk2[ci & 1];
+#pragma unroll
+    for (int j = 0; j < kFbPer; ++j) c.chunk[tid + kThreads * j] = v[j];
+    cta_sync();  // (also: every thread is done with the chunk before last, whose buffer the next store takes)
+    if (c.nlist > 0) {
+        for (int i = tid; i < c.nlist; i += kThreads) {
+            const unsigned long long e = c.hlist[i];
+            const int tok = (int)(uint32_t)e;
+            if (tok >= c0 && tok < c0 + kFbChunk && fb_allowed(c, tok)) c.chunk[tok - c0] = penalise(c.rp, fb_raw<T>(c, tok), (int)(e >> 32));
+        }
+        cta_sync();
     }
-    cta_sync();
-    for (int i = tid; i < c.nlist; i += kThreads) {
-        const unsigned long long e = c.hlist[i];
-        const int tok = (int)(uint32_t)e;
-        if (tok >= c0 && tok < c0 + kFbChunk && fb_allowed(c, tok)) c.chunk[tok - c0] = penalise(c.rp, fb_raw<T>(c, tok), (int)(e >> 32));
-    }
-    cta_sync();
+}
+template <typename T>
+__device__ __forceinline__ void fb_load(FbCtx& c, int ci) {
+    float v[kFbPer];
+    fb_fetch<T>(c, ci, v);
+    fb_store<T>(c, ci, v);
 }
 
-// One pass over the row: f(token, z) for every token above -inf, by the thread that owns it.
+// One pass over the row: f(token, z) for every token above -inf, by the thread that owns it.  The
+// next chunk's loads are in flight while the current chunk is worked on.
 template <typename T, typename F>
-__device__ __forceinline__ void fb_pass(const FbCtx& c, F f) {
+__device__ __forceinline__ void fb_pass(FbCtx& c, F f) {
     const int nchunks = (c.V + kFbChunk - 1) / kFbChunk;
+    float v[kFbPer];
+    fb_fetch<T>(c, 0, v);
     for (int ci = 0; ci < nchunks; ++ci) {
-        fb_load<T>(c, ci);
+        fb_store<T>(c, ci, v);
+        if (ci + 1 < nchunks) fb_fetch<T>(c, ci + 1, v);
+        const float* ch = c.chunk;
         for (int e = threadIdx.x; e < kFbChunk; e += kThreads) {
-            const float z = c.chunk[e];
+            const float z = ch[e];
             if (z > -INFINITY) f(ci * kFbChunk + e, z);
         }
     }
@@ -116,15 +147,24 @@ __device__ __forceinline__ unsigned long long fb_mass(const FbCtx& c, float z) {
 // running weight (1 per token, or its mass) first exceeds `target`.  Returns 0 when the total
 // weight does not exceed target (the caller keeps everything).
 template <typename T, bool kWeighted>
-__device__ __noinline__ unsigned long long fb_search(const FbCtx& c, unsigned long long lowkey, unsigned long long target) {
+__device__ __noinline__ unsigned long long fb_search(FbCtx& c, unsigned long long lowkey, unsigned long long target) {
     const int tid = threadIdx.x;
     ScanShared& sh = *c.sh;
     unsigned long long prefix = 0, pmask = 0;
     const int shifts[5] = {44, 32, 20, 8, 0};
+    // Masses are summed per bin as three 14-bit limbs in 32-bit words: 32-bit shared-memory atomics
+    // are native, 64-bit ones are compare-and-swap loops.  A limb sum stays below 2^32 for rows of
+    // up to 2^17 tokens; longer rows use the 64-bit words.
+    uint32_t* limb = reinterpret_cast<uint32_t*>(c.bwt);  // [3][kFbBins], over the mass and count areas
+    const bool limbs = kWeighted && c.V <= (1 << 17);
     for (int lvl = 0; lvl < 5; ++lvl) {
         const int shift = shifts[lvl];
         const int nb = (lvl == 4) ? 256 : kFbBins;
-        for (int i = tid; i < nb; i += kThreads) { c.bcnt[i] = 0; c.bwt[i] = 0; }
+        if (limbs) {
+            for (int i = tid; i < 3 * kFbBins; i += kThreads) limb[i] = 0;
+        } else {
+            for (int i = tid; i < nb; i += kThreads) { c.bcnt[i] = 0; c.bwt[i] = 0; }
+        }
         cta_sync();
         fb_pass<T>(c, [&](int tok, float z) {
             const unsigned long long ck = make_ck(z, c.id0 + tok);
@@ -132,11 +172,31 @@ __device__ __noinline__ unsigned long long fb_search(const FbCtx& c, unsigned lo
             const uint32_t d = (uint32_t)(ck >> shift) & (uint32_t)(nb - 1);
             if (kWeighted) {
                 const unsigned long long w = fb_mass(c, z);
-                if (w) atomicAdd(&c.bwt[d], w);
+                if (!w) return;
+                if (limbs) {
+                    smem_red_add(&limb[d], (uint32_t)w & 0x3FFFu);
+                    smem_red_add(&limb[kFbBins + d], (uint32_t)(w >> 14) & 0x3FFFu);
+                    smem_red_add(&limb[2 * kFbBins + d], (uint32_t)(w >> 28));
+                } else {
+                    atomicAdd(&c.bwt[d], w);
+                }
             } else {
                 smem_red_add(&c.bcnt[d], 1u);
             }
         });
+        if (limbs) {  // fold the limbs into the 64-bit words the scan below reads
+            unsigned long long w[kFbBins / kThreads];
+#pragma unroll
+            for (int j = 0; j < kFbBins / kThreads; ++j) {
+                const int bin = tid + kThreads * j;
+                w[j] = (unsigned long long)limb[bin] + ((unsigned long long)limb[kFbBins + bin] << 14) +
+                       ((unsigned long long)limb[2 * kFbBins + bin] << 28);
+            }
+            cta_sync();
+#pragma unroll
+            for (int j = 0; j < kFbBins / kThreads; ++j) c.bwt[tid + kThreads * j] = w[j];
+            cta_sync();
+        }
         // block scan over the bins in walk order (descending digit): thread t owns nb/256 of them
         const int per = nb / kThreads;
         unsigned long long loc = 0;
@@ -184,7 +244,7 @@ __device__ __noinline__ unsigned long long fb_search(const FbCtx& c, unsigned lo
 
 // The (at most kSelCap) tokens with rank key >= lowkey, gathered and written in rank order.
 template <typename T>
-__device__ __forceinline__ int fb_gather(const FbCtx& c, unsigned long long lowkey, uint64_t* sel) {
+__device__ __forceinline__ int fb_gather(FbCtx& c, unsigned long long lowkey, uint64_t* sel) {
     if (threadIdx.x == 0) c.sh->nl = 0;
     cta_sync();
     fb_pass<T>(c, [&](int tok, float z) {
@@ -203,10 +263,16 @@ __device__ __noinline__ void fallback_row(const ScanArgs& A, ScanShared& sh, uin
     FbCtx c;
     c.A = &A;
     c.sh = &sh;
-    c.chunk = reinterpret_cast<float*>(smem);
-    c.hlist = reinterpret_cast<unsigned long long*>(smem + kFbChunk * 4);
-    c.bwt = reinterpret_cast<unsigned long long*>(smem + kFbChunk * 4 + BORN_MAX_HISTORY * 8);
-    c.bcnt = reinterpret_cast<uint32_t*>(smem + kFbChunk * 4 + BORN_MAX_HISTORY * 8 + kFbBins * 8);
+    // 88 KB of the CTA's dynamic shared memory (no variant of the kernel has less):
+    // two chunk buffers | history list | mass bins | count bins
+    c.chunk2[0] = reinterpret_cast<float*>(smem);
+    c.chunk2[1] = reinterpret_cast<float*>(smem + kFbChunk * 4);
+    c.chunk = c.chunk2[0];
+    c.hlist = reinterpret_cast<unsigned long long*>(smem + 2 * kFbChunk * 4);
+    c.bwt = reinterpret_cast<unsigned long long*>(smem + 2 * kFbChunk * 4 + BORN_MAX_HISTORY * 8);
+    c.bcnt = reinterpret_cast<uint32_t*>(smem + 2 * kFbChunk * 4 + BORN_MAX_HISTORY * 8 + kFbBins * 8);
+    static_assert(2 * kFbChunk * 4 + BORN_MAX_HISTORY * 8 + kFbBins * 12 <= kScanStages * kTileBytes + kScanWarps * kWarpCand * 8 + kSelCap * 8,
+                  "the exact search lives in the streaming kernel's shared memory");
     uint64_t* sel = reinterpret_cast<uint64_t*>(c.bwt);  // gathers happen when no search is in flight
     c.b = row / A.G;
     c.g = row - c.b * A.G;

@@ -173,8 +173,11 @@ bool host_need_mass(const born_row_params& p) {
 
 template <typename T, bool M, bool Lse>
 cudaError_t scan_attr() {
-    return cudaFuncSetAttribute(scan_kernel<T, M, Lse>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                scan_smem_layout((int)sizeof(T), M, true).total);
+    const int bytes = scan_smem_layout((int)sizeof(T), M, true).total;
+    cudaError_t e = cudaFuncSetAttribute(scan_kernel<T, M, Lse, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess && sizeof(T) == 4)
+        e = cudaFuncSetAttribute(scan_kernel<T, M, Lse, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    return e;
 }
 // The dynamic shared-memory limit of every variant is raised once (at create / first static call).
 cudaError_t scan_attrs_all() {
@@ -192,7 +195,9 @@ cudaError_t scan_attrs_all() {
 
 template <typename T, bool M, bool Lq>
 cudaError_t launch_scan_variant(const ScanArgs& A, int grid, size_t smem, cudaStream_t st) {
-    scan_kernel<T, M, Lq><<<grid, kScanThreads, smem, st>>>(A);
+    // fp32 launches without token histories take the instantiation whose loop pairs tiles
+    if (sizeof(T) == 4 && A.history == nullptr) scan_kernel<T, M, Lq, true><<<grid, kScanThreads, smem, st>>>(A);
+    else scan_kernel<T, M, Lq, false><<<grid, kScanThreads, smem, st>>>(A);
     return cudaGetLastError();
 }
 

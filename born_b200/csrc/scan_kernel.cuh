@@ -257,6 +257,63 @@ __device__ __forceinline__ void fast_tile(const T* tile, const uint32_t* smask, 
     __syncwarp();
 }
 
+// Two full fp32 tiles at once: their loads, maxima and exponentials are independent, which gives
+// the warp twice the work in flight per dependent step -- with 18 warps per SM that, not issue
+// slots, is what the tile loop runs out of -- and the per-tile overhead of the loop once.
+template <bool kMask, bool kLse>
+__device__ __forceinline__ void fast_tile_pair(const float* tile_a, const uint32_t* smask_a, const float* tile_b,
+                                               const uint32_t* smask_b, int id_tile0, float tau, float c2, ThreadStats& st,
+                                               uint64_t* wbuf, uint32_t* wcount, uint32_t* excl) {
+    constexpr int TILE = TileOf<float>::n;
+    float va[16], vb[16];
+    int e0[4];
+    load16<float, kMask, false>(tile_a, smask_a, 0, va, e0);
+    load16<float, kMask, false>(tile_b, smask_b, 0, vb, e0);
+    float ma[4], mb[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        ma[i] = max_nan(max3_nan(va[4 * i], va[4 * i + 1], va[4 * i + 2]), va[4 * i + 3]);
+        mb[i] = max_nan(max3_nan(vb[4 * i], vb[4 * i + 1], vb[4 * i + 2]), vb[4 * i + 3]);
+    }
+    const float mta = max_nan(max3_nan(ma[0], ma[1], ma[2]), ma[3]);
+    const float mtb = max_nan(max3_nan(mb[0], mb[1], mb[2]), mb[3]);
+    const float mt = max_nan(mta, mtb);
+    st.mx = max_nan(st.mx, mt);
+    if constexpr (kLse) {
+        if (mt > st.R && mt < INFINITY) {
+            const float f = ex2_approx(__fmul_rn(st.R - mt, c2));
+            st.s = __fmul2_rn(st.s, make_float2(f, f));
+            st.R = mt;
+            st.nRc = -mt * c2;
+        }
+        const float2 cc = make_float2(c2, c2), rr = make_float2(st.nRc, st.nRc);
+        float2 s1 = make_float2(0.0f, 0.0f), s2 = s1, s3 = s1;
+#pragma unroll
+        for (int i = 0; i < 16; i += 4) {
+            const float2 a0 = __ffma2_rn(make_float2(va[i], va[i + 1]), cc, rr), a1 = __ffma2_rn(make_float2(va[i + 2], va[i + 3]), cc, rr);
+            const float2 b0 = __ffma2_rn(make_float2(vb[i], vb[i + 1]), cc, rr), b1 = __ffma2_rn(make_float2(vb[i + 2], vb[i + 3]), cc, rr);
+            st.s = __fadd2_rn(st.s, make_float2(ex2_approx(a0.x), ex2_approx(a0.y)));
+            s1 = __fadd2_rn(s1, make_float2(ex2_approx(a1.x), ex2_approx(a1.y)));
+            s2 = __fadd2_rn(s2, make_float2(ex2_approx(b0.x), ex2_approx(b0.y)));
+            s3 = __fadd2_rn(s3, make_float2(ex2_approx(b1.x), ex2_approx(b1.y)));
+        }
+        st.s = __fadd2_rn(__fadd2_rn(st.s, s1), __fadd2_rn(s2, s3));
+    }
+    if (mta >= tau) {  // rare per lane
+        uint32_t hits = 0;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) hits |= (va[i] >= tau && va[i] > -INFINITY) ? (1u << i) : 0u;
+        push_hits<float>(hits, tile_a, 0, id_tile0, st, wbuf, wcount, excl);
+    }
+    if (mtb >= tau) {
+        uint32_t hits = 0;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) hits |= (vb[i] >= tau && vb[i] > -INFINITY) ? (1u << i) : 0u;
+        push_hits<float>(hits, tile_b, 0, id_tile0 + TILE, st, wbuf, wcount, excl);
+    }
+    __syncwarp();
+}
+
 // Candidates of a full tile whose statistics were taken before (the first tile of a segment,
 // once its threshold exists): compact code, run once per segment.
 template <typename T, bool kMask>
@@ -853,7 +910,9 @@ __device__ __forceinline__ void ring_append(const ScanArgs& A, int b) {
 }
 
 // ---- the kernel -------------------------------------------------------------------------------
-template <typename T, bool kMask, bool kLse>
+// kPair: the steady-state loop may take two tiles at a time (fp32 launches without token
+// histories; a separate instantiation so that the other launches keep their register allocation).
+template <typename T, bool kMask, bool kLse, bool kPair>
 __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_constant__ ScanArgs A) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ ScanShared sh;
@@ -978,16 +1037,45 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                     if (hist_on)
                         patched = hist_apply<T, kMask, kLse>(hc, hlist, rp, tile, smask, 0, j, 0, 0, TILE, false, 6, sg.id0, tau, pl.c2, st,
                                                              wbuf, wcount, excl);
-                    fast_tile<T, kMask, kLse>(tile, smask, sg.id0 + j * TILE, tau, pl.c2, st, wbuf, wcount, excl);
-                    if (pl.use_max) publish_max(st, sh);
-                    if (pl.lane_bound && ((seen + 1) & seen) == 0) sg.tau_fix = fmaxf(sg.tau_fix, lane_bound(sh, pl.k, st.mx));
-                    if (collect && *reinterpret_cast<volatile uint32_t*>(wcount) >= (uint32_t)(kWarpCand / 2))
-                        compact_cands(wbuf, wcount, current_tau(sg, sh));
-                    if (patched) fence_proxy_async();  // the stage is next written by a bulk copy
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage]));
-                    if (++stage == kScanStages) { stage = 0; phase ^= 1u; }
-                    ++t; ++seen; ++j; rem -= TILE;
+                    if constexpr (kPair && sizeof(T) == 4) {
+                        // fp32: when the tile after this one has landed as well, the two are taken together
+                        bool pair = false;
+                        if (t + 1 < seg_end && rem >= 2 * TILE) {
+                            const int s2 = stage + 1 == kScanStages ? 0 : stage + 1;
+                            const uint32_t p2 = stage + 1 == kScanStages ? phase ^ 1u : phase;
+                            pair = __all_sync(0xffffffffu, mbar_test(reinterpret_cast<uint64_t*>(&wait_bar[s2]), p2));  // (a probe that never suspends)
+                            if (pair) {
+                                const float* tile2 = reinterpret_cast<const float*>(smem + L.tiles + s2 * kTileBytes);
+                                const uint32_t* smask2 = reinterpret_cast<const uint32_t*>(smem + L.masks + s2 * (mask_stage_words<T>() * 4));
+                                fast_tile_pair<kMask, kLse>(reinterpret_cast<const float*>(tile), smask, tile2, smask2, sg.id0 + j * TILE, tau,
+                                                            pl.c2, st, wbuf, wcount, excl);
+                            }
+                        }
+                        if (!pair) fast_tile<T, kMask, kLse>(tile, smask, sg.id0 + j * TILE, tau, pl.c2, st, wbuf, wcount, excl);
+                        if (pl.use_max) publish_max(st, sh);
+                        const int n_done = pair ? 2 : 1;
+                        if (pl.lane_bound && (((seen + 1) & seen) == 0 || (pair && ((seen + 2) & (seen + 1)) == 0)))
+                            sg.tau_fix = fmaxf(sg.tau_fix, lane_bound(sh, pl.k, st.mx));
+                        if (collect && *reinterpret_cast<volatile uint32_t*>(wcount) >= (uint32_t)(kWarpCand / 2))
+                            compact_cands(wbuf, wcount, current_tau(sg, sh));
+                        __syncwarp();
+                        for (int d = 0; d < n_done; ++d) {
+                            if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage]));
+                            if (++stage == kScanStages) { stage = 0; phase ^= 1u; }
+                        }
+                        t += n_done; seen += n_done; j += n_done; rem -= n_done * TILE;
+                    } else {
+                        fast_tile<T, kMask, kLse>(tile, smask, sg.id0 + j * TILE, tau, pl.c2, st, wbuf, wcount, excl);
+                        if (pl.use_max) publish_max(st, sh);
+                        if (pl.lane_bound && ((seen + 1) & seen) == 0) sg.tau_fix = fmaxf(sg.tau_fix, lane_bound(sh, pl.k, st.mx));
+                        if (collect && *reinterpret_cast<volatile uint32_t*>(wcount) >= (uint32_t)(kWarpCand / 2))
+                            compact_cands(wbuf, wcount, current_tau(sg, sh));
+                        if (patched) fence_proxy_async();  // the stage is next written by a bulk copy
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage]));
+                        if (++stage == kScanStages) { stage = 0; phase ^= 1u; }
+                        ++t; ++seen; ++j; rem -= TILE;
+                    }
                 }
                 if (t >= seg_end) break;
             }

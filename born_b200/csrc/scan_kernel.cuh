@@ -740,13 +740,13 @@ __device__ __noinline__ int hist_build_wide(const ScanArgs& A, const int (&ids)[
 
 // The same list for a segment of at most kHistNarrowTiles tiles -- every row below some 260 000
 // fp32 logits.  The build sits in front of the segment's first tile, and shared-memory atomics
-// cost about two cycles per lane and SM, so there is one per id and nothing else that
-// serialises: the atomic on the (tile, warp) counter (zeroed by the segment set-up) counts the
-// token and returns its place among the warp's tokens of that tile; after one barrier every
-// warp works out the starts of all (tile, warp) runs for itself -- a lane per tile, eight
-// counters each, a shuffle scan -- and stores its tokens.  Repeats of a token are resolved
-// afterwards inside the tile's bucket (a handful of entries): the first occurrence gets the
-// multiplicity, the others 0, and whoever applies the list skips those.
+// cost about two cycles per lane and SM, so there are two per id and nothing else that
+// serialises: a compare-and-swap into a hash table tells a token's first occurrence from its
+// repeats (which only count themselves beside the key), and for a first occurrence the atomic on
+// the (tile, warp) counter counts the token and returns its place among the warp's tokens of that
+// tile.  After one barrier every warp works out the starts of all (tile, warp) runs for itself
+// -- a lane per tile, eight counters each, a shuffle scan -- and stores its tokens with their
+// multiplicities.  Table and counters are cleared by the segment set-up.
 constexpr int kHistNarrowTiles = 64;
 template <int TILE>
 __device__ __forceinline__ int hist_build(const ScanArgs& A, const int (&ids)[kHistPer], int g, int lead, int j_begin, int j_end,
@@ -754,7 +754,7 @@ __device__ __forceinline__ int hist_build(const ScanArgs& A, const int (&ids)[kH
     const int span = j_end - j_begin;
     if (span > kHistNarrowTiles) return hist_build_wide<TILE>(A, ids, g, lead, j_begin, j_end, keys, cnt32, list, wscr);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    uint16_t* tstart = reinterpret_cast<uint16_t*>(keys);  // (the candidate area is idle) start of every tile's bucket
+    uint32_t* mult = keys + kHashSlots;  // repeats, beside the keys
     int rel[kHistPer];
     uint32_t tok[kHistPer], rank[kHistPer];
 #pragma unroll
@@ -770,6 +770,15 @@ __device__ __forceinline__ int hist_build(const ScanArgs& A, const int (&ids)[kH
         if (g2 != g || tk >= (uint32_t)A.V) continue;  // another vocabulary segment's token, or an id beyond the vocabulary
         const int tl = (int)((tk + (uint32_t)lead) / (uint32_t)TILE);
         if (tl < j_begin || tl >= j_end) continue;
+        uint32_t slot = (tk * 2654435761u) >> (32 - 11);
+        bool fresh = false;
+        for (int probe = 0; probe < kHashSlots; ++probe) {
+            const uint32_t old = atomicCAS(&keys[slot], 0xFFFFFFFFu, tk);
+            if (old == 0xFFFFFFFFu) { fresh = true; break; }
+            if (old == tk) { smem_red_add(&mult[slot], 1u); break; }  // a repeat
+            slot = (slot + 1) & (kHashSlots - 1);
+        }
+        if (!fresh) continue;
         rel[r] = tl - j_begin;
         tok[r] = tk;
         const int c = rel[r] * kScanWarps + warp;
@@ -805,36 +814,13 @@ __device__ __forceinline__ int hist_build(const ScanArgs& A, const int (&ids)[kH
     for (int r = 0; r < kHistPer; ++r) {
         const int src = rel[r] >= 0 ? (rel[r] & 31) : 0;
         const uint32_t v0 = __shfl_sync(0xffffffffu, base0 + below[0], src), v1 = __shfl_sync(0xffffffffu, base1 + below[1], src);
-        if (rel[r] >= 0) list[((rel[r] >> 5) ? v1 : v0) + rank[r]] = (1ull << 32) | tok[r];
-    }
-    if (warp == 0) {
-        if (lane < span) tstart[lane] = (uint16_t)base0;
-        if (lane + 32 < span) tstart[lane + 32] = (uint16_t)base1;
-        if (lane == 0) tstart[span] = (uint16_t)n;
+        if (rel[r] >= 0) {
+            uint32_t slot = (tok[r] * 2654435761u) >> (32 - 11);  // (found again: cheaper than carried along)
+            while (keys[slot] != tok[r]) slot = (slot + 1) & (kHashSlots - 1);
+            list[((rel[r] >> 5) ? v1 : v0) + rank[r]] = ((unsigned long long)(mult[slot] + 1u) << 32) | tok[r];
+        }
     }
     cta_sync();
-    {
-        for (int i = tid; i < (int)n; i += kThreads) {
-            const uint32_t tk = (uint32_t)list[i];
-            const int t = (int)((tk + (uint32_t)lead) / (uint32_t)TILE) - j_begin;
-            const int b0 = tstart[t], b1 = tstart[t + 1];
-            int same = 0;
-            bool first = true;
-            int j = b0;
-            for (; j + 4 <= b1; j += 4) {  // (four loads in flight: the loop is bound by their latency otherwise)
-                uint32_t x[4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) x[k] = (uint32_t)list[j + k];
-#pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    if (x[k] == tk) { ++same; first = first && j + k >= i; }
-            }
-            for (; j < b1; ++j)
-                if ((uint32_t)list[j] == tk) { ++same; first = first && j >= i; }
-            if (same > 1) list[i] = ((unsigned long long)(first ? same : 0) << 32) | tk;
-        }
-        cta_sync();
-    }
     return (int)n;
 }
 
@@ -987,8 +973,16 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
         // the row's uniform is wanted at the very end: fetch it now
         const float u_row = (A.uniforms != nullptr && A.mode == kScanFull) ? __ldg(A.uniforms + q.b) : 0.0f;
         if (tid < kScanWarps) { sh.wbound[tid] = -INFINITY; sh.wcount[tid] = 0; }
-        if (A.history != nullptr)  // the (tile, warp) counters of the history build: kHistNarrowTiles x 8 of 16 bits
+        if (A.history != nullptr) {
+            // the history build's (tile, warp) counters (kHistNarrowTiles x 8 of 16 bits) and its hash
+            // table in the candidate area (keys empty, repeat counts zero)
             reinterpret_cast<uint32_t*>(smem + L.sel)[tid] = 0;
+            uint4* k4 = reinterpret_cast<uint4*>(smem + L.cand);
+            k4[tid] = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu);
+            k4[tid + kThreads] = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu);
+            k4[tid + 2 * kThreads] = make_uint4(0u, 0u, 0u, 0u);
+            k4[tid + 3 * kThreads] = make_uint4(0u, 0u, 0u, 0u);
+        }
         cta_sync();
         ThreadStats st;
         stats_reset(st, pl.c2);

@@ -314,6 +314,47 @@ __device__ __forceinline__ void fast_tile_pair(const float* tile_a, const uint32
     __syncwarp();
 }
 
+// The thread's maximum over its share of a full tile, nothing else: what the threshold bootstrap
+// of a segment's first tile needs before the tile is processed like any other.
+template <typename T, bool kMask>
+__device__ __forceinline__ float tile_max(const T* tile, const uint32_t* smask) {
+    constexpr int VEC = VecOf<T>::n, NV = 16 / VEC, NB = TileOf<T>::n / (kThreads * 16);
+    float pm = -INFINITY;
+#pragma unroll
+    for (int h = 0; h < NB; ++h) {
+        float v[16];
+        int e0[NV];
+        load16<T, kMask, false>(tile, smask, h, v, e0);
+        float m4[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) m4[i] = max_nan(max3_nan(v[4 * i], v[4 * i + 1], v[4 * i + 2]), v[4 * i + 3]);
+        pm = max_nan(pm, max_nan(max3_nan(m4[0], m4[1], m4[2]), m4[3]));
+    }
+    return pm;
+}
+
+// The last tile of an aligned row is partial: the copy brought n_el elements and left the rest
+// of the stage as it was.  Every thread blanks its own elements from n_el on (-inf), after
+// which the tile is a full one.  (The caller orders these writes before the stage's next copy.)
+template <typename T>
+__device__ __forceinline__ void pad_tile(T* tile, int n_el) {
+    constexpr int VEC = VecOf<T>::n, ITER = TileOf<T>::n / (kThreads * VEC);
+#pragma unroll
+    for (int jj = 0; jj < ITER; ++jj) {
+        const int e0 = ((int)threadIdx.x + kThreads * jj) * VEC;
+        if (e0 + VEC <= n_el) continue;
+        if (e0 >= n_el) {
+            if constexpr (sizeof(T) == 4) reinterpret_cast<float4*>(tile)[e0 / VEC] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            else reinterpret_cast<uint4*>(tile)[e0 / VEC] = make_uint4(0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u);
+        } else {
+            for (int i = n_el - e0; i < VEC; ++i) {
+                if constexpr (sizeof(T) == 4) reinterpret_cast<float*>(tile)[e0 + i] = -INFINITY;
+                else reinterpret_cast<uint16_t*>(tile)[e0 + i] = 0xFF80u;
+            }
+        }
+    }
+}
+
 // Candidates of a full tile whose statistics were taken before (the first tile of a segment,
 // once its threshold exists): compact code, run once per segment.
 template <typename T, bool kMask>
@@ -1086,7 +1127,13 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
             const int lo = max(0, q.lead - j * TILE);
             const int tok_tile0 = j * TILE - q.lead;          // token (within the virtual row) of element 0
             const int id_tile0 = sg.id0 + tok_tile0;
-            const bool full = A.fast && n_el == TILE;
+            bool full = A.fast && n_el == TILE;
+            bool patched = false;
+            if (A.fast && !full && n_el > 0 && !failed && !pl.need_mass) {
+                pad_tile<T>(tile, n_el);
+                full = true;
+                patched = true;
+            }
             int64_t mb_rel = 0;
             if constexpr (kMask) {
                 if (!full && n_el > lo) {
@@ -1095,24 +1142,28 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                 }
             }
             const bool first = (seen == 0);
-            bool patched = false;
             if (hist_on && !failed) {
                 // (a bf16 segment's first tile: no threshold exists yet, and the values are gone from the
                 // tile when one does -- every finite one is offered; the finish drops what lies below its cut)
                 const float tau_h = !collect ? INFINITY : (first ? -INFINITY : current_tau(sg, sh));
-                patched = hist_apply<T, kMask, kLse>(hc, hlist, rp, tile, smask, mb_rel, j, q.lead, lo, n_el, pl.need_mass, 6, sg.id0,
-                                                     tau_h, pl.c2, st, wbuf, wcount, excl);
+                patched |= hist_apply<T, kMask, kLse>(hc, hlist, rp, tile, smask, mb_rel, j, q.lead, lo, n_el, pl.need_mass, 6, sg.id0,
+                                                      tau_h, pl.c2, st, wbuf, wcount, excl);
             }
+            // A segment's first tile, when it is a full one: the threshold is bootstrapped from the
+            // threads' maxima alone, then the tile is processed like any other.
+            const bool quick_first = first && full && !pl.need_mass && !failed;
+            if (quick_first) st.mx = max_nan(st.mx, tile_max<T, kMask>(tile, smask));
             if (!failed && n_el > lo) {
                 if (pl.need_mass) {
                     // (rows of these routes are 16-byte aligned: the host sees to it)
                     const float tau = first ? INFINITY : current_tau(sg, sh);
                     mass_tile<T, kMask>(tile, smask, n_el, tok_tile0, id_tile0, tau, pl.inv_T, collect && !first, row_blocks, A.nblk,
                                         st, sh, wbuf, wcount, excl);
+                } else if (quick_first) {
+                    // (processed below, once the threshold exists)
                 } else if (first) {
                     // statistics only: the threshold does not exist yet (tau = +inf collects nothing)
-                    if (full) fast_tile<T, kMask, kLse>(tile, smask, id_tile0, INFINITY, pl.c2, st, wbuf, wcount, excl);
-                    else slow_tile<T, kMask, kLse>(tile, smask, mb_rel, lo, n_el, id_tile0, 0.0f, pl.c2, true, false, st, wbuf, wcount, excl);
+                    slow_tile<T, kMask, kLse>(tile, smask, mb_rel, lo, n_el, id_tile0, 0.0f, pl.c2, true, false, st, wbuf, wcount, excl);
                 } else {
                     {
                     const float tau = collect ? current_tau(sg, sh) : INFINITY;
@@ -1137,7 +1188,11 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                     cta_sync();
                     sg.tau_fix = fmaxf(sg.tau_fix, lane_bound(sh, pl.k, st.mx));
                 }
-                if (!failed && collect && n_el > lo) {
+                if (quick_first) {
+                    const float tau = collect ? current_tau(sg, sh) : INFINITY;
+                    fast_tile<T, kMask, kLse>(tile, smask, id_tile0, tau, pl.c2, st, wbuf, wcount, excl);
+                    if (pl.use_max) publish_max(st, sh);
+                } else if (!failed && collect && n_el > lo) {
                     const float tau = current_tau(sg, sh);
                     // collect only: the values are read again
                     if (full) collect_tile<T, kMask>(tile, smask, id_tile0, tau, st, wbuf, wcount, excl);

@@ -1052,11 +1052,15 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
         const bool hist_on = hc.n > 0 && !prod_patch;
         const bool lean = A.fast && !pl.need_mass;
         for (; t < seg_end; ++t, ++seen, ++j, rem -= TILE) {
-            // ---- steady state: the full tiles of an aligned row after the segment's first tile.
-            // Everything that is decided per segment stays outside; what is left per tile is the
-            // wait, one read of the thresholds, the straight-line tile body and the hand-back.
-            if (lean && seen > 0 && !failed) {
-                while (t < seg_end && rem >= TILE) {
+            // ---- the tiles of an aligned row.  Everything that is decided per segment stays outside;
+            // what is left per tile is the wait, one read of the thresholds, the straight-line tile
+            // body and the hand-back (plus the threshold bootstrap on a segment's first tile and the
+            // padding of a row's partial last one).
+            // (kPair instantiations also take a segment's first tile and a row's partial last tile in this
+            // loop; the others leave those two to the general body below -- measured: the extra branches
+            // cost the history launches more than the general body costs them)
+            if (lean && !failed && (kPair || seen > 0)) {
+                while (t < seg_end && (kPair || rem >= TILE)) {
                     uint64_t* fb = reinterpret_cast<uint64_t*>(&wait_bar[stage]);
                     bool here = mbar_try(fb, phase);
                     if (!here) here = mbar_wait_limit(fb, phase, A.timeout_ns, &sh.fail);
@@ -1067,11 +1071,37 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                     }
                     T* tile = reinterpret_cast<T*>(smem + L.tiles + stage * kTileBytes);
                     const uint32_t* smask = reinterpret_cast<const uint32_t*>(smem + L.masks + stage * (mask_stage_words<T>() * 4));
-                    const float tau = collect ? current_tau(sg, sh) : INFINITY;
                     bool patched = false;
-                    if (hist_on)
-                        patched = hist_apply<T, kMask, kLse>(hc, hlist, rp, tile, smask, 0, j, 0, 0, TILE, false, 6, sg.id0, tau, pl.c2, st,
-                                                             wbuf, wcount, excl);
+                    if (kPair && rem < TILE) {  // the row's last tile: blank what the copy did not bring
+                        pad_tile<T>(tile, rem);
+                        patched = true;
+                    }
+                    if (kPair && seen == 0) {
+                        // The segment's first tile.  bf16 history tokens are offered whatever their value (no
+                        // threshold exists yet, and they are gone from the tile when one does; the finish drops
+                        // what lies below its cut).  Then the threshold is bootstrapped from the threads' maxima:
+                        // the warp's maximum opens the running-maximum threshold; for top-k the warps meet once
+                        // and take the lane-maxima bound.
+                        if (hist_on)
+                            patched |= hist_apply<T, kMask, kLse>(hc, hlist, rp, tile, smask, 0, j, 0, 0, min(rem, TILE), false, 6, sg.id0,
+                                                                  collect ? -INFINITY : INFINITY, pl.c2, st, wbuf, wcount, excl);
+                        st.mx = max_nan(st.mx, tile_max<T, kMask>(tile, smask));
+                        if (pl.use_max) {
+                            const float wm = warp_max_nan(st.mx);
+                            if (lane == 0 && wm == wm) smem_red_max(&sh.maxbits, zkey(wm));
+                            st.pub = fmaxf(st.pub, (wm == wm) ? wm : -INFINITY);
+                            __syncwarp();
+                        }
+                        if (pl.lane_bound) {
+                            lane_bound(sh, pl.k, st.mx);
+                            cta_sync();
+                            sg.tau_fix = fmaxf(sg.tau_fix, lane_bound(sh, pl.k, st.mx));
+                        }
+                    }
+                    const float tau = collect ? current_tau(sg, sh) : INFINITY;
+                    if (hist_on && (!kPair || seen > 0))
+                        patched |= hist_apply<T, kMask, kLse>(hc, hlist, rp, tile, smask, 0, j, 0, 0, kPair ? min(rem, TILE) : TILE, false, 6, sg.id0, tau,
+                                                              pl.c2, st, wbuf, wcount, excl);
                     if constexpr (kPair && sizeof(T) == 4) {
                         // fp32: when the tile after this one has landed as well, the two are taken together
                         bool pair = false;
@@ -1089,10 +1119,11 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                         if (!pair) fast_tile<T, kMask, kLse>(tile, smask, sg.id0 + j * TILE, tau, pl.c2, st, wbuf, wcount, excl);
                         if (pl.use_max) publish_max(st, sh);
                         const int n_done = pair ? 2 : 1;
-                        if (pl.lane_bound && (((seen + 1) & seen) == 0 || (pair && ((seen + 2) & (seen + 1)) == 0)))
+                        if (pl.lane_bound && ((seen > 0 && ((seen + 1) & seen) == 0) || (pair && ((seen + 2) & (seen + 1)) == 0)))
                             sg.tau_fix = fmaxf(sg.tau_fix, lane_bound(sh, pl.k, st.mx));
                         if (collect && *reinterpret_cast<volatile uint32_t*>(wcount) >= (uint32_t)(kWarpCand / 2))
                             compact_cands(wbuf, wcount, current_tau(sg, sh));
+                        if (patched) fence_proxy_async();  // (a padded last tile) the stage is next written by a bulk copy
                         __syncwarp();
                         for (int d = 0; d < n_done; ++d) {
                             if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage]));
@@ -1102,7 +1133,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                     } else {
                         fast_tile<T, kMask, kLse>(tile, smask, sg.id0 + j * TILE, tau, pl.c2, st, wbuf, wcount, excl);
                         if (pl.use_max) publish_max(st, sh);
-                        if (pl.lane_bound && ((seen + 1) & seen) == 0) sg.tau_fix = fmaxf(sg.tau_fix, lane_bound(sh, pl.k, st.mx));
+                        if (pl.lane_bound && seen > 0 && ((seen + 1) & seen) == 0) sg.tau_fix = fmaxf(sg.tau_fix, lane_bound(sh, pl.k, st.mx));
                         if (collect && *reinterpret_cast<volatile uint32_t*>(wcount) >= (uint32_t)(kWarpCand / 2))
                             compact_cands(wbuf, wcount, current_tau(sg, sh));
                         if (patched) fence_proxy_async();  // the stage is next written by a bulk copy

@@ -1049,7 +1049,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
             __threadfence_block();
             *reinterpret_cast<volatile int*>(&sh.hist_seq) = seg_ord + 1;
         }
-        const bool hist_on = hc.n > 0 && !prod_patch;
+        const bool hist_on = sizeof(T) == 2 && hc.n > 0;  // (fp32: the producer warp applies the list)
         const bool lean = A.fast && !pl.need_mass;
         for (; t < seg_end; ++t, ++seen, ++j, rem -= TILE) {
             // ---- the tiles of an aligned row.  Everything that is decided per segment stays outside;

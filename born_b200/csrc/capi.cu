@@ -195,7 +195,8 @@ cudaError_t scan_attrs_all() {
 
 template <typename T, bool M, bool Lq>
 cudaError_t launch_scan_variant(const ScanArgs& A, int grid, size_t smem, cudaStream_t st) {
-    // fp32 launches without token histories take the instantiation whose loop pairs tiles
+    // fp32 launches without token histories take the instantiation whose loop pairs tiles (and
+    // that carries no history code); fp32 launches with one take the other (which always has one)
     if (sizeof(T) == 4 && A.history == nullptr) scan_kernel<T, M, Lq, true><<<grid, kScanThreads, smem, st>>>(A);
     else scan_kernel<T, M, Lq, false><<<grid, kScanThreads, smem, st>>>(A);
     return cudaGetLastError();

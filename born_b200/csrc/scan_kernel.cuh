@@ -945,7 +945,13 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
     __shared__ ScanShared sh;
     constexpr int TILE = TileOf<T>::n;
     const int tid = threadIdx.x;
-    const ScanSmem L = scan_smem_layout((int)sizeof(T), kMask, A.history != nullptr);
+    // What the instantiation knows about token histories: fp32 launches come in two instantiations --
+    // kPair without a history, the other with one (the producer warp applies it) -- bf16 launches in
+    // one that finds out at run time (the compute warps apply it).
+    constexpr bool kFp32 = sizeof(T) == 4;
+    const bool has_hist = kFp32 ? !kPair : (A.history != nullptr);
+    constexpr bool prod_patch = kFp32 && !kPair;
+    const ScanSmem L = scan_smem_layout((int)sizeof(T), kMask, has_hist);
     const long long rows = (long long)A.B * A.G;
     const long long T_total = rows * A.tpr;
     const long long ncta = gridDim.x;
@@ -967,11 +973,11 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
     int ids[kHistPer];
 #pragma unroll
     for (int r = 0; r < kHistPer; ++r) ids[r] = -1;
-    if (A.history != nullptr && tid < kThreads && t0 < t1) hist_ids(A, (int)(t0 / A.tpr) / A.G, ids);
+    if (has_hist && tid < kThreads && t0 < t1) hist_ids(A, (int)(t0 / A.tpr) / A.G, ids);
     __syncthreads();  // the only barrier all 288 threads share
 
     if (tid >= kThreads) {
-        if (sizeof(T) == 4 && A.history != nullptr) producer_loop_patching<T, kMask>(A, sh, smem, L, t0, t1);
+        if constexpr (prod_patch) producer_loop_patching<T, kMask>(A, sh, smem, L, t0, t1);
         else producer_loop<T, kMask>(A, sh, smem, L, t0, t1);
         return;
     }
@@ -984,7 +990,6 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
     bool failed = false;
     int bad = 0;
     // fp32 launches with token histories: the producer warp patches the tiles and releases them
-    const bool prod_patch = sizeof(T) == 4 && A.history != nullptr;
     unsigned long long* const wait_bar = prod_patch ? sh.ready_bar : sh.full_bar;
     int seg_ord = -1;
     long long t = t0;
@@ -1014,7 +1019,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
         // the row's uniform is wanted at the very end: fetch it now
         const float u_row = (A.uniforms != nullptr && A.mode == kScanFull) ? __ldg(A.uniforms + q.b) : 0.0f;
         if (tid < kScanWarps) { sh.wbound[tid] = -INFINITY; sh.wcount[tid] = 0; }
-        if (A.history != nullptr) {
+        if (has_hist) {
             // the history build's (tile, warp) counters (kHistNarrowTiles x 8 of 16 bits) and its hash
             // table in the candidate area (keys empty, repeat counts zero)
             reinterpret_cast<uint32_t*>(smem + L.sel)[tid] = 0;
@@ -1036,7 +1041,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
         HistCursor hc;
         hc.n = 0; hc.pos = 0;
         const unsigned long long* hlist = reinterpret_cast<const unsigned long long*>(smem + L.hist);
-        if (A.history != nullptr) {
+        if (has_hist) {
             if (seg_ord > 0) hist_ids(A, q.b, ids);  // (those of the CTA's first row were fetched before the first copy)
             if (penalties_on(rp))
                 hc.n = hist_build<TILE>(A, ids, q.g, q.lead, j, j_end, reinterpret_cast<uint32_t*>(smem + L.cand),

@@ -171,13 +171,26 @@ bool host_need_mass(const born_row_params& p) {
     return !greedy && p.top_k <= 0 && !(p.min_p > 0.0f);
 }
 
+template <typename T, bool M, bool Lse, int R>
+cudaError_t scan_attr_route() {
+    const int bytes = scan_smem_layout((int)sizeof(T), M, true).total;
+    cudaError_t e = cudaFuncSetAttribute(scan_kernel<T, M, Lse, false, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess && sizeof(T) == 4)
+        e = cudaFuncSetAttribute(scan_kernel<T, M, Lse, true, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    return e;
+}
+// (the route classes 1 and 2 exist for launches without a mask that want the log-sum-exp -- the
+// serving configurations; the others take the general instantiation: every instantiation costs
+// half a minute of compile time)
 template <typename T, bool M, bool Lse>
 cudaError_t scan_attr() {
-    const int bytes = scan_smem_layout((int)sizeof(T), M, true).total;
-    cudaError_t e = cudaFuncSetAttribute(scan_kernel<T, M, Lse, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e == cudaSuccess && sizeof(T) == 4)
-        e = cudaFuncSetAttribute(scan_kernel<T, M, Lse, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    return e;
+    cudaError_t e;
+    if ((e = scan_attr_route<T, M, Lse, 0>()) != cudaSuccess) return e;
+    if constexpr (!M && Lse) {
+        if ((e = scan_attr_route<T, M, Lse, 1>()) != cudaSuccess) return e;
+        if ((e = scan_attr_route<T, M, Lse, 2>()) != cudaSuccess) return e;
+    }
+    return cudaSuccess;
 }
 // The dynamic shared-memory limit of every variant is raised once (at create / first static call).
 cudaError_t scan_attrs_all() {
@@ -193,21 +206,38 @@ cudaError_t scan_attrs_all() {
     return cudaSuccess;
 }
 
-template <typename T, bool M, bool Lq>
-cudaError_t launch_scan_variant(const ScanArgs& A, int grid, size_t smem, cudaStream_t st) {
+template <typename T, bool M, bool Lq, int R>
+cudaError_t launch_scan_route(const ScanArgs& A, int grid, size_t smem, cudaStream_t st) {
     // fp32 launches without token histories take the instantiation whose loop pairs tiles (and
     // that carries no history code); fp32 launches with one take the other (which always has one)
-    if (sizeof(T) == 4 && A.history == nullptr) scan_kernel<T, M, Lq, true><<<grid, kScanThreads, smem, st>>>(A);
-    else scan_kernel<T, M, Lq, false><<<grid, kScanThreads, smem, st>>>(A);
+    if (sizeof(T) == 4 && A.history == nullptr) scan_kernel<T, M, Lq, true, R><<<grid, kScanThreads, smem, st>>>(A);
+    else scan_kernel<T, M, Lq, false, R><<<grid, kScanThreads, smem, st>>>(A);
     return cudaGetLastError();
+}
+template <typename T, bool M, bool Lq>
+cudaError_t launch_scan_variant(const ScanArgs& A, int grid, size_t smem, cudaStream_t st, int route) {
+    if constexpr (!M && Lq) {
+        if (route == 1) return launch_scan_route<T, M, Lq, 1>(A, grid, smem, st);
+        if (route == 2) return launch_scan_route<T, M, Lq, 2>(A, grid, smem, st);
+    }
+    return launch_scan_route<T, M, Lq, 0>(A, grid, smem, st);
+}
+
+// The route class of a launch (RouteOf in scan_common.cuh): uniform parameters tell it on the host.
+static int route_of(const born_row_params* row_params, const born_row_params& p) {
+    if (row_params) return 0;
+    if (host_need_mass(p)) return 0;
+    const bool greedy = (p.flags & BORN_FLAG_GREEDY) || p.temperature == 0.0f;
+    return (!greedy && p.top_k > 0) ? 2 : 1;
 }
 
 int launch_scan(Handle* h, const ScanArgs& A, int dtype, int grid, cudaStream_t st) {
+    const int route = route_of(A.row_params, A.params);
     const bool has_mask = A.mask != nullptr;
     const bool lse = A.out_lse != nullptr || A.want_lse;
     const size_t smem = (size_t)scan_smem_layout(dtype == BORN_DTYPE_F32 ? 4 : 2, has_mask, A.history != nullptr).total;
     cudaError_t e;
-#define V_(T, M, Lq) e = launch_scan_variant<T, M, Lq>(A, grid, smem, st)
+#define V_(T, M, Lq) e = launch_scan_variant<T, M, Lq>(A, grid, smem, st, route)
     if (dtype == BORN_DTYPE_F32) {
         if (has_mask) { if (lse) V_(float, true, true); else V_(float, true, false); }
         else { if (lse) V_(float, false, true); else V_(float, false, false); }

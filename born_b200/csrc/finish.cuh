@@ -446,7 +446,7 @@ struct RowSrc {
 };
 
 // A row is complete: merge its statistics, select, draw.
-template <typename T>
+template <typename T, int kRoute>
 __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, uint64_t* sel, unsigned long long* selq, int row,
                                            const RowSrc& src) {
     const int tid = threadIdx.x;
@@ -476,7 +476,7 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
                 taux = fmaxf(taux, h.z);
                 bk = fmaxf(bk, h.w);
             }
-            if (!pl.need_mass)
+            if (!(RouteOf<kRoute>::mass && pl.need_mass))
                 for (int s = 0; s < nseg; ++s) {
                     const float4 h = sh.hdr[s];
                     if (h.y > 0.0f) ls += h.y * ex2_approx(__fmul_rn(h.x - m, pl.c2));
@@ -491,7 +491,7 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
             m = block_max_nan(m, sh.redf);
             taux = block_max_nan(taux, sh.redf2);
             bk = block_max_nan(bk, sh.redf3);
-            if (!pl.need_mass) {
+            if (!(RouteOf<kRoute>::mass && pl.need_mass)) {
                 for (int s = tid; s < nseg; s += kThreads) {
                     const float4 h = __ldcg(reinterpret_cast<const float4*>(rec_of(s)));
                     if (h.y > 0.0f) ls += h.y * ex2_approx(__fmul_rn(h.x - m, pl.c2));
@@ -537,7 +537,7 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
             cta_sync();
             n = sh.nl;
             // complete above max(bk, taux); the k best are inside iff there are k of them (or nothing was excluded)
-            if (n > kSelCap || (taux > bk && n < pl.k) || pl.no_bound) {
+            if (n > kSelCap || (taux > bk && n < pl.k) || (RouteOf<kRoute>::lane && pl.no_bound)) {
                 // the exact search over the row writes the record instead
                 if (tid == 0) A.deferred[row] = (8u << 24) | (blockIdx.x + 1u);
                 return;
@@ -557,7 +557,7 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
         row_fail(o, status);
         return;
     }
-    if (!pl.need_mass && A.out_lse && tid == 0) A.out_lse[b] = m * pl.inv_T + __log2f(ls) * 0.69314718f;
+    if (!(RouteOf<kRoute>::mass && pl.need_mass) && A.out_lse && tid == 0) A.out_lse[b] = m * pl.inv_T + __log2f(ls) * 0.69314718f;
 
     if (pl.greedy) {
         if (taux > m) {  // a token equal to the maximum may have been lost to a full buffer
@@ -588,7 +588,7 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
 
     const float u = src.u;
     unsigned long long S_tot = 0;
-    if (pl.need_mass) {
+    if ((RouteOf<kRoute>::mass && pl.need_mass)) {
         // row total from the mass blocks; log-sum-exp from it
         const MassBlock* blocks = A.blocks + (int64_t)row * A.nblk;
         unsigned long long part = 0;
@@ -606,7 +606,7 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
         }
         if (A.out_lse && tid == 0)
             A.out_lse[b] = (float)((double)m * (double)pl.inv_T + log(__ull2double_rn(S_tot) * (1.0 / 1099511627776.0)));
-        if (!pl.window) {
+        if (!(RouteOf<kRoute>::mass && pl.window)) {
             if (A.out_kept_count && tid == 0) A.out_kept_count[b] = nfin;
             if (A.out_kept_ids) {  // the kept set is the whole row: no list of a useful size exists
                 if (tid == 0) A.deferred[row] = (2u << 24) | (blockIdx.x + 1u);
@@ -619,9 +619,9 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
 
     // ---- candidates at or above the valid cut
     float cut = -INFINITY;
-    if (pl.lane_bound) cut = bk;
+    if ((RouteOf<kRoute>::lane && pl.lane_bound)) cut = bk;
     if (rp.min_p > 0.0f) cut = fmaxf(cut, m + pl.delta);
-    if (pl.window) {
+    if ((RouteOf<kRoute>::mass && pl.window)) {
         // tokens lighter than (1 - P) * S / V weigh less than (1 - P) * S together: outside the nucleus
         const float s_all = (float)S_tot * (1.0f / 1099511627776.0f);
         cut = m + (__logf((1.0f - rp.top_p) * s_all / (float)A.V) - 0.05f) * rp.temperature;
@@ -661,7 +661,7 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
         return (int)sh.nl;
     };
     int n = gather(lowest);
-    if (n > kSelCap && !pl.no_bound) {
+    if (n > kSelCap && !(RouteOf<kRoute>::lane && pl.no_bound)) {
         // More candidates than the selection takes (a wide nucleus window, many ties).  Use only
         // the part above a higher level -- the lowest of a fixed ladder (in scaled-logit units
         // below the row maximum) that leaves at most kSelCap entries; that part is complete, and
@@ -702,11 +702,11 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
     }
     // why a row goes to the exact search (kept in the upper byte of its `deferred` word)
     uint32_t why = 0;
-    if (pl.no_bound) why = 4;
+    if ((RouteOf<kRoute>::lane && pl.no_bound)) why = 4;
     else if (n > kSelCap) why = 3;
     else if (!complete) {
         if (pl.k > 0) { if (n < pl.k) why = 5; }   // the k best are all at or above taux iff k tokens are
-        else if (!pl.window) why = 6;              // min-p survivors may lie below taux
+        else if (!(RouteOf<kRoute>::mass && pl.window)) why = 6;              // min-p survivors may lie below taux
     }
     bool defer = why != 0;
     if (!defer) {
@@ -715,7 +715,7 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
         in.k = pl.k;
         in.Qa = (rp.min_p > 0.0f) ? __double2ull_ru((double)rp.min_p * 1099511627776.0) : 0ull;
         in.top_p = rp.top_p;
-        in.S_ext = pl.window ? S_tot : 0ull;
+        in.S_ext = (RouteOf<kRoute>::mass && pl.window) ? S_tot : 0ull;
         in.complete = complete;
         in.m_row = m; in.inv_T = pl.inv_T; in.u = u;
         if (n <= kThreads) defer = !select_small(in, sel, selq, sh, o);

@@ -280,6 +280,17 @@ __device__ __forceinline__ bool penalties_on(const born_row_params& rp) {
            rp.presence_penalty != 0.0f;
 }
 
+// Route classes the streaming kernel is instantiated for, so that a launch whose rows all take
+// the same kind of route does not carry (and pay, in registers and instruction fetches) the code
+// of the others: 0 any route (decided per row at run time: per-row parameter arrays, and the
+// whole-vocabulary routes), 1 running-maximum thresholds only (greedy, min-p with or without
+// top-p), 2 top-k (lane-maxima bound, with or without min-p).
+template <int kRoute>
+struct RouteOf {
+    static constexpr bool mass = kRoute == 0;  // rows may take their total from the mass blocks
+    static constexpr bool lane = kRoute != 1;  // rows may use the lane-maxima bound
+};
+
 // What a row's parameters ask of the streaming pass.
 struct RowPlan {
     bool greedy;

@@ -939,7 +939,7 @@ __device__ __forceinline__ void ring_append(const ScanArgs& A, int b) {
 // ---- the kernel -------------------------------------------------------------------------------
 // kPair: the steady-state loop may take two tiles at a time (fp32 launches without token
 // histories; a separate instantiation so that the other launches keep their register allocation).
-template <typename T, bool kMask, bool kLse, bool kPair>
+template <typename T, bool kMask, bool kLse, bool kPair, int kRoute>
 __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_constant__ ScanArgs A) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ ScanShared sh;
@@ -1007,7 +1007,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
         sg.plan = row_plan(rp);
         sg.row = p0.row;
         sg.id0 = A.idx_base + q.g * A.V;
-        sg.tau_fix = sg.plan.no_bound ? INFINITY : -INFINITY;
+        sg.tau_fix = (RouteOf<kRoute>::lane && sg.plan.no_bound) ? INFINITY : -INFINITY;
         const RowPlan& pl = sg.plan;
         cta_sync();
         if (tid == 0) {
@@ -1033,7 +1033,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
         ThreadStats st;
         stats_reset(st, pl.c2);
         MassBlock* row_blocks = A.blocks + (int64_t)p0.row * A.nblk;
-        const bool collect = pl.collect && !pl.no_bound;
+        const bool collect = pl.collect && !(RouteOf<kRoute>::lane && pl.no_bound);
         int seen = 0;  // tiles of this segment done
         int j = (int)(t - (long long)p0.row * A.tpr);       // tile within the row
         int rem = q.lead + A.V - j * TILE;                  // elements of the row from this tile on
@@ -1055,7 +1055,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
             *reinterpret_cast<volatile int*>(&sh.hist_seq) = seg_ord + 1;
         }
         const bool hist_on = sizeof(T) == 2 && hc.n > 0;  // (fp32: the producer warp applies the list)
-        const bool lean = A.fast && !pl.need_mass;
+        const bool lean = A.fast && !(RouteOf<kRoute>::mass && pl.need_mass);
         for (; t < seg_end; ++t, ++seen, ++j, rem -= TILE) {
             // ---- the tiles of an aligned row.  Everything that is decided per segment stays outside;
             // what is left per tile is the wait, one read of the thresholds, the straight-line tile
@@ -1097,7 +1097,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                             st.pub = fmaxf(st.pub, (wm == wm) ? wm : -INFINITY);
                             __syncwarp();
                         }
-                        if (pl.lane_bound) {
+                        if ((RouteOf<kRoute>::lane && pl.lane_bound)) {
                             lane_bound(sh, pl.k, st.mx);
                             cta_sync();
                             sg.tau_fix = fmaxf(sg.tau_fix, lane_bound(sh, pl.k, st.mx));
@@ -1124,7 +1124,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                         if (!pair) fast_tile<T, kMask, kLse>(tile, smask, sg.id0 + j * TILE, tau, pl.c2, st, wbuf, wcount, excl);
                         if (pl.use_max) publish_max(st, sh);
                         const int n_done = pair ? 2 : 1;
-                        if (pl.lane_bound && ((seen > 0 && ((seen + 1) & seen) == 0) || (pair && ((seen + 2) & (seen + 1)) == 0)))
+                        if ((RouteOf<kRoute>::lane && pl.lane_bound) && ((seen > 0 && ((seen + 1) & seen) == 0) || (pair && ((seen + 2) & (seen + 1)) == 0)))
                             sg.tau_fix = fmaxf(sg.tau_fix, lane_bound(sh, pl.k, st.mx));
                         if (collect && *reinterpret_cast<volatile uint32_t*>(wcount) >= (uint32_t)(kWarpCand / 2))
                             compact_cands(wbuf, wcount, current_tau(sg, sh));
@@ -1138,7 +1138,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                     } else {
                         fast_tile<T, kMask, kLse>(tile, smask, sg.id0 + j * TILE, tau, pl.c2, st, wbuf, wcount, excl);
                         if (pl.use_max) publish_max(st, sh);
-                        if (pl.lane_bound && seen > 0 && ((seen + 1) & seen) == 0) sg.tau_fix = fmaxf(sg.tau_fix, lane_bound(sh, pl.k, st.mx));
+                        if ((RouteOf<kRoute>::lane && pl.lane_bound) && seen > 0 && ((seen + 1) & seen) == 0) sg.tau_fix = fmaxf(sg.tau_fix, lane_bound(sh, pl.k, st.mx));
                         if (collect && *reinterpret_cast<volatile uint32_t*>(wcount) >= (uint32_t)(kWarpCand / 2))
                             compact_cands(wbuf, wcount, current_tau(sg, sh));
                         if (patched) fence_proxy_async();  // the stage is next written by a bulk copy
@@ -1165,7 +1165,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
             const int id_tile0 = sg.id0 + tok_tile0;
             bool full = A.fast && n_el == TILE;
             bool patched = false;
-            if (A.fast && !full && n_el > 0 && !failed && !pl.need_mass) {
+            if (A.fast && !full && n_el > 0 && !failed && !(RouteOf<kRoute>::mass && pl.need_mass)) {
                 pad_tile<T>(tile, n_el);
                 full = true;
                 patched = true;
@@ -1182,15 +1182,15 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                 // (a bf16 segment's first tile: no threshold exists yet, and the values are gone from the
                 // tile when one does -- every finite one is offered; the finish drops what lies below its cut)
                 const float tau_h = !collect ? INFINITY : (first ? -INFINITY : current_tau(sg, sh));
-                patched |= hist_apply<T, kMask, kLse>(hc, hlist, rp, tile, smask, mb_rel, j, q.lead, lo, n_el, pl.need_mass, 6, sg.id0,
+                patched |= hist_apply<T, kMask, kLse>(hc, hlist, rp, tile, smask, mb_rel, j, q.lead, lo, n_el, (RouteOf<kRoute>::mass && pl.need_mass), 6, sg.id0,
                                                       tau_h, pl.c2, st, wbuf, wcount, excl);
             }
             // A segment's first tile, when it is a full one: the threshold is bootstrapped from the
             // threads' maxima alone, then the tile is processed like any other.
-            const bool quick_first = first && full && !pl.need_mass && !failed;
+            const bool quick_first = first && full && !(RouteOf<kRoute>::mass && pl.need_mass) && !failed;
             if (quick_first) st.mx = max_nan(st.mx, tile_max<T, kMask>(tile, smask));
             if (!failed && n_el > lo) {
-                if (pl.need_mass) {
+                if ((RouteOf<kRoute>::mass && pl.need_mass)) {
                     // (rows of these routes are 16-byte aligned: the host sees to it)
                     const float tau = first ? INFINITY : current_tau(sg, sh);
                     mass_tile<T, kMask>(tile, smask, n_el, tok_tile0, id_tile0, tau, pl.inv_T, collect && !first, row_blocks, A.nblk,
@@ -1219,7 +1219,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                     st.pub = fmaxf(st.pub, (wm == wm) ? wm : -INFINITY);
                     __syncwarp();
                 }
-                if (pl.lane_bound) {
+                if ((RouteOf<kRoute>::lane && pl.lane_bound)) {
                     lane_bound(sh, pl.k, st.mx);
                     cta_sync();
                     sg.tau_fix = fmaxf(sg.tau_fix, lane_bound(sh, pl.k, st.mx));
@@ -1234,7 +1234,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                     if (full) collect_tile<T, kMask>(tile, smask, id_tile0, tau, st, wbuf, wcount, excl);
                     else slow_tile<T, kMask, kLse>(tile, smask, mb_rel, lo, n_el, id_tile0, tau, pl.c2, false, true, st, wbuf, wcount, excl);
                 }
-            } else if (pl.lane_bound && ((seen + 1) & seen) == 0) {
+            } else if ((RouteOf<kRoute>::lane && pl.lane_bound) && ((seen + 1) & seen) == 0) {
                 // tighten the bound when the number of tiles seen doubles (no barrier: values of
                 // warps that lag are older, hence lower, hence still valid)
                 sg.tau_fix = fmaxf(sg.tau_fix, lane_bound(sh, pl.k, st.mx));
@@ -1250,20 +1250,20 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
         // ---- segment record (block-synchronous)
         const float wm = warp_max_nan(st.mx);
         float ws = 0.0f;
-        if (kLse && !pl.need_mass) {
+        if (kLse && !(RouteOf<kRoute>::mass && pl.need_mass)) {
             const float ssum = st.s.x + st.s.y;
             ws = (ssum > 0.0f && wm == wm) ? ssum * ex2_approx(__fmul_rn(st.R - wm, pl.c2)) : 0.0f;
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) ws += __shfl_xor_sync(0xffffffffu, ws, d);
         }
-        if (pl.lane_bound) lane_bound(sh, pl.k, st.mx);
+        if ((RouteOf<kRoute>::lane && pl.lane_bound)) lane_bound(sh, pl.k, st.mx);
         if (lane == 0) { sh.wmax[warp] = wm; sh.wsum[warp] = ws; }
         cta_sync();
         float m_seg = sh.wmax[0];
 #pragma unroll
         for (int w = 1; w < kScanWarps; ++w) m_seg = max_nan(m_seg, sh.wmax[w]);
         float s_seg = 0.0f;
-        if (kLse && !pl.need_mass) {
+        if (kLse && !(RouteOf<kRoute>::mass && pl.need_mass)) {
 #pragma unroll
             for (int w = 0; w < kScanWarps; ++w) {
                 const float x = sh.wsum[w];
@@ -1271,7 +1271,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
             }
         }
         float bound_k = -INFINITY;
-        if (pl.lane_bound) {
+        if ((RouteOf<kRoute>::lane && pl.lane_bound)) {
             bound_k = sh.wbound[0];
 #pragma unroll
             for (int w = 1; w < kScanWarps; ++w) bound_k = fminf(bound_k, sh.wbound[w]);
@@ -1280,7 +1280,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
         float cut = bound_k;
         float excl_window = -INFINITY;
         if (pl.use_max && m_seg == m_seg) {
-            if (pl.window) excl_window = m_seg + pl.delta;
+            if ((RouteOf<kRoute>::mass && pl.window)) excl_window = m_seg + pl.delta;
             cut = fmaxf(cut, m_seg + pl.delta);
         }
         // A row that this CTA streamed from its first tile to its last needs no record and no
@@ -1293,7 +1293,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
             if (cta_sync_or(*reinterpret_cast<const volatile int*>(&sh.fail))) { bad = 1; break; }
             src.direct = true;
             src.m = m_seg; src.ls = s_seg; src.bk = bound_k;
-            src.taux = pl.no_bound ? INFINITY : fmaxf(zkey_to_float(sh.excl_bits), excl_window);
+            src.taux = (RouteOf<kRoute>::lane && pl.no_bound) ? INFINITY : fmaxf(zkey_to_float(sh.excl_bits), excl_window);
             src.wbuf = reinterpret_cast<const uint64_t*>(smem + L.cand);
             src.wcount = sh.wcount;
             src.c_first = (int)blockIdx.x; src.nseg = 1;
@@ -1335,7 +1335,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                 h.lse_sum = s_seg;
                 float te = zkey_to_float(sh.excl_bits);
                 te = fmaxf(te, excl_window);
-                if (pl.no_bound) te = INFINITY;
+                if ((RouteOf<kRoute>::lane && pl.no_bound)) te = INFINITY;
                 h.tau_excl = te;
                 h.bound_k = bound_k;
                 h.count = min(sh.rec_count, (uint32_t)A.rec_cap);
@@ -1367,7 +1367,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
         }
         // (one call site: the finish is inlined, its arguments stay in registers)
         if (finish_here) {
-            finish_row<T>(A, sh, reinterpret_cast<uint64_t*>(smem + L.sel), reinterpret_cast<unsigned long long*>(smem + L.cand),
+            finish_row<T, kRoute>(A, sh, reinterpret_cast<uint64_t*>(smem + L.sel), reinterpret_cast<unsigned long long*>(smem + L.cand),
                           p0.row, src);
             if (A.ring != nullptr && A.mode == kScanFull) {
                 cta_sync();  // the row's outputs are written (or the row is handed to the exact search)

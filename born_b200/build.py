@@ -12,10 +12,14 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
-SRC = os.path.join(HERE, "csrc", "capi.cu")
-DEPS = [os.path.join(HERE, "csrc", f) for f in ("capi.cu", "spec.cuh", "scan_common.cuh", "scan_kernel.cuh", "finish.cuh", "fallback.cuh", "merge_kernel.cuh",
-                                                   "prepass.cuh", "spec_kernel.cuh")]
+CSRC = os.path.join(HERE, "csrc")
+# translation units (compiled side by side: the streaming kernel's instantiations take minutes)
+UNITS = ["capi.cu", "scan_f32_pair.cu", "scan_f32_hist.cu", "scan_bf16.cu"]
+HEADERS = ["spec.cuh", "scan_common.cuh", "scan_kernel.cuh", "scan_inst.cuh", "scan_launch.cuh", "finish.cuh", "fallback.cuh",
+           "merge_kernel.cuh", "prepass.cuh", "spec_kernel.cuh"]
+DEPS = [os.path.join(CSRC, f) for f in UNITS + HEADERS]
 DEPS.append(os.path.join(ROOT, "include", "born_sampler.h"))
+OBJ_DIR = os.path.join(HERE, "build")
 OUT = os.path.join(HERE, "libborn_sampler.so")
 
 
@@ -36,18 +40,30 @@ def up_to_date():
 def build(verbose=False, force=False):
     if not force and up_to_date():
         return OUT
-    cmd = [
-        nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-        "--fmad=false", "-Xcompiler", "-fPIC", "-shared", "-o", OUT, SRC, "-ldl",
-    ]
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    flags = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--fmad=false", "-Xcompiler", "-fPIC"]
     if verbose:
-        cmd += ["-Xptxas", "-v"]
-    res = subprocess.run(cmd, capture_output=True, text=True)
+        flags += ["-Xptxas", "-v"]
+    procs = []
+    for u in UNITS:
+        obj = os.path.join(OBJ_DIR, u[:-3] + ".o")
+        cmd = [nvcc_path()] + flags + ["-c", os.path.join(CSRC, u), "-o", obj]
+        procs.append((u, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)))
+    objs, failed = [], False
+    for u, obj, p in procs:
+        out, err = p.communicate()
+        if p.returncode != 0:
+            sys.stderr.write("nvcc failed on %s\n" % u + out + err)
+            failed = True
+        elif verbose:
+            sys.stderr.write(err)
+        objs.append(obj)
+    if failed:
+        raise RuntimeError("nvcc failed")
+    res = subprocess.run([nvcc_path(), "-shared", "-o", OUT] + objs + ["-ldl"], capture_output=True, text=True)
     if res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)
-        raise RuntimeError("nvcc failed")
-    if verbose:
-        sys.stderr.write(res.stderr)
+        raise RuntimeError("nvcc link failed")
     return OUT
 
 

@@ -14,8 +14,8 @@
 #include <string.h>
 
 #include "../../include/born_sampler.h"
-#include "scan_kernel.cuh"
-#include "fallback.cuh"
+#include "scan_common.cuh"
+#include "scan_launch.cuh"
 #include "merge_kernel.cuh"
 #include "prepass.cuh"
 #include "spec_kernel.cuh"
@@ -171,56 +171,12 @@ bool host_need_mass(const born_row_params& p) {
     return !greedy && p.top_k <= 0 && !(p.min_p > 0.0f);
 }
 
-template <typename T, bool M, bool Lse, int R>
-cudaError_t scan_attr_route() {
-    const int bytes = scan_smem_layout((int)sizeof(T), M, true).total;
-    cudaError_t e = cudaFuncSetAttribute(scan_kernel<T, M, Lse, false, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e == cudaSuccess && sizeof(T) == 4)
-        e = cudaFuncSetAttribute(scan_kernel<T, M, Lse, true, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    return e;
-}
-// (the route classes 1 and 2 exist for launches without a mask that want the log-sum-exp -- the
-// serving configurations; the others take the general instantiation: every instantiation costs
-// half a minute of compile time)
-template <typename T, bool M, bool Lse>
-cudaError_t scan_attr() {
-    cudaError_t e;
-    if ((e = scan_attr_route<T, M, Lse, 0>()) != cudaSuccess) return e;
-    if constexpr (!M && Lse) {
-        if ((e = scan_attr_route<T, M, Lse, 1>()) != cudaSuccess) return e;
-        if ((e = scan_attr_route<T, M, Lse, 2>()) != cudaSuccess) return e;
-    }
-    return cudaSuccess;
-}
-// The dynamic shared-memory limit of every variant is raised once (at create / first static call).
+// The dynamic shared-memory limit of every instantiation is raised once (at create / first static call).
 cudaError_t scan_attrs_all() {
     cudaError_t e;
-    if ((e = scan_attr<float, false, false>()) != cudaSuccess) return e;
-    if ((e = scan_attr<float, false, true>()) != cudaSuccess) return e;
-    if ((e = scan_attr<float, true, false>()) != cudaSuccess) return e;
-    if ((e = scan_attr<float, true, true>()) != cudaSuccess) return e;
-    if ((e = scan_attr<uint16_t, false, false>()) != cudaSuccess) return e;
-    if ((e = scan_attr<uint16_t, false, true>()) != cudaSuccess) return e;
-    if ((e = scan_attr<uint16_t, true, false>()) != cudaSuccess) return e;
-    if ((e = scan_attr<uint16_t, true, true>()) != cudaSuccess) return e;
-    return cudaSuccess;
-}
-
-template <typename T, bool M, bool Lq, int R>
-cudaError_t launch_scan_route(const ScanArgs& A, int grid, size_t smem, cudaStream_t st) {
-    // fp32 launches without token histories take the instantiation whose loop pairs tiles (and
-    // that carries no history code); fp32 launches with one take the other (which always has one)
-    if (sizeof(T) == 4 && A.history == nullptr) scan_kernel<T, M, Lq, true, R><<<grid, kScanThreads, smem, st>>>(A);
-    else scan_kernel<T, M, Lq, false, R><<<grid, kScanThreads, smem, st>>>(A);
-    return cudaGetLastError();
-}
-template <typename T, bool M, bool Lq>
-cudaError_t launch_scan_variant(const ScanArgs& A, int grid, size_t smem, cudaStream_t st, int route) {
-    if constexpr (!M && Lq) {
-        if (route == 1) return launch_scan_route<T, M, Lq, 1>(A, grid, smem, st);
-        if (route == 2) return launch_scan_route<T, M, Lq, 2>(A, grid, smem, st);
-    }
-    return launch_scan_route<T, M, Lq, 0>(A, grid, smem, st);
+    if ((e = scan_attrs_f32_pair()) != cudaSuccess) return e;
+    if ((e = scan_attrs_f32_hist()) != cudaSuccess) return e;
+    return scan_attrs_bf16();
 }
 
 // The route class of a launch (RouteOf in scan_common.cuh): uniform parameters tell it on the host.
@@ -236,16 +192,12 @@ int launch_scan(Handle* h, const ScanArgs& A, int dtype, int grid, cudaStream_t 
     const bool has_mask = A.mask != nullptr;
     const bool lse = A.out_lse != nullptr || A.want_lse;
     const size_t smem = (size_t)scan_smem_layout(dtype == BORN_DTYPE_F32 ? 4 : 2, has_mask, A.history != nullptr).total;
+    // fp32 launches without a token history take the instantiations whose loop pairs tiles (and
+    // that carry no history code); fp32 launches with one take the others (which always have one)
     cudaError_t e;
-#define V_(T, M, Lq) e = launch_scan_variant<T, M, Lq>(A, grid, smem, st, route)
-    if (dtype == BORN_DTYPE_F32) {
-        if (has_mask) { if (lse) V_(float, true, true); else V_(float, true, false); }
-        else { if (lse) V_(float, false, true); else V_(float, false, false); }
-    } else {
-        if (has_mask) { if (lse) V_(uint16_t, true, true); else V_(uint16_t, true, false); }
-        else { if (lse) V_(uint16_t, false, true); else V_(uint16_t, false, false); }
-    }
-#undef V_
+    if (dtype != BORN_DTYPE_F32) e = scan_launch_bf16(A, has_mask, lse, route, grid, smem, st);
+    else if (A.history == nullptr) e = scan_launch_f32_pair(A, has_mask, lse, route, grid, smem, st);
+    else e = scan_launch_f32_hist(A, has_mask, lse, route, grid, smem, st);
     if (e != cudaSuccess) return fail(h, BORN_ERR_CUDA, "scan kernel launch failed: %s", cudaGetErrorString(e));
     h->launches++;
     return BORN_OK;

@@ -150,7 +150,7 @@ __device__ __forceinline__ bool select_small(const SelectIn& in, uint64_t* sel, 
 
 // Selection and draw over kThreads < n <= kSelCap candidates: radix select, then mass-weighted
 // radix threshold searches.  Same rules, same answer convention as select_small.
-__device__ __noinline__ bool select_and_draw(const SelectIn in, uint64_t* sel, unsigned long long* selq, ScanShared& sh,
+static __device__ __noinline__ bool select_and_draw(const SelectIn in, uint64_t* sel, unsigned long long* selq, ScanShared& sh,
                                              const RowOut o) {
     const int tid = threadIdx.x;
     const int n = in.n;

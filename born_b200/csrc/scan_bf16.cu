@@ -1,0 +1,7 @@
+// scan_kernel for bf16 launches (a token history, if any, is applied by the compute warps).
+#include <cstdint>
+#define SCAN_INST_T uint16_t
+#define SCAN_INST_PAIR false
+#define SCAN_INST_ATTRS scan_attrs_bf16
+#define SCAN_INST_LAUNCH scan_launch_bf16
+#include "scan_inst.cuh"

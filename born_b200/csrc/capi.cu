@@ -175,8 +175,11 @@ bool host_need_mass(const born_row_params& p) {
 cudaError_t scan_attrs_all() {
     cudaError_t e;
     if ((e = scan_attrs_f32_pair()) != cudaSuccess) return e;
+    if ((e = scan_attrs_f32_pair_row()) != cudaSuccess) return e;
     if ((e = scan_attrs_f32_hist()) != cudaSuccess) return e;
-    return scan_attrs_bf16();
+    if ((e = scan_attrs_f32_hist_row()) != cudaSuccess) return e;
+    if ((e = scan_attrs_bf16()) != cudaSuccess) return e;
+    return scan_attrs_bf16_row();
 }
 
 // The route class of a launch (RouteOf in scan_common.cuh): uniform parameters tell it on the host.
@@ -194,10 +197,18 @@ int launch_scan(Handle* h, const ScanArgs& A, int dtype, int grid, cudaStream_t 
     const size_t smem = (size_t)scan_smem_layout(dtype == BORN_DTYPE_F32 ? 4 : 2, has_mask, A.history != nullptr).total;
     // fp32 launches without a token history take the instantiations whose loop pairs tiles (and
     // that carry no history code); fp32 launches with one take the others (which always have one)
+    // A sampling launch whose grid is one CTA per row (the tile ranges of range_begin are then the
+    // rows themselves) takes the instantiations without the segment-record path.
+    const bool one_row = A.mode == kScanFull && A.G == 1 && grid == A.B;
     cudaError_t e;
-    if (dtype != BORN_DTYPE_F32) e = scan_launch_bf16(A, has_mask, lse, route, grid, smem, st);
-    else if (A.history == nullptr) e = scan_launch_f32_pair(A, has_mask, lse, route, grid, smem, st);
-    else e = scan_launch_f32_hist(A, has_mask, lse, route, grid, smem, st);
+    if (dtype != BORN_DTYPE_F32)
+        e = one_row ? scan_launch_bf16_row(A, has_mask, lse, route, grid, smem, st) : scan_launch_bf16(A, has_mask, lse, route, grid, smem, st);
+    else if (A.history == nullptr)
+        e = one_row ? scan_launch_f32_pair_row(A, has_mask, lse, route, grid, smem, st)
+                    : scan_launch_f32_pair(A, has_mask, lse, route, grid, smem, st);
+    else
+        e = one_row ? scan_launch_f32_hist_row(A, has_mask, lse, route, grid, smem, st)
+                    : scan_launch_f32_hist(A, has_mask, lse, route, grid, smem, st);
     if (e != cudaSuccess) return fail(h, BORN_ERR_CUDA, "scan kernel launch failed: %s", cudaGetErrorString(e));
     h->launches++;
     return BORN_OK;

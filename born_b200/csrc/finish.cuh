@@ -446,10 +446,24 @@ struct RowSrc {
 };
 
 // A row is complete: merge its statistics, select, draw.
-template <typename T, int kRoute>
+// Hands row `row` to the exact search that its CTA runs once the ring is idle.  The reason goes in
+// the upper byte.  A CTA that streams exactly one row keeps the word in shared memory (and spares
+// every CTA a round trip to global memory at its end).
+template <bool kOneRow>
+__device__ __forceinline__ void defer_row(const ScanArgs& A, ScanShared& sh, int row, uint32_t why) {
+    const uint32_t word = (why << 24) | (blockIdx.x + 1u);
+    if constexpr (kOneRow) sh.defer = word;
+    else A.deferred[row] = word;
+}
+
+// kOneRow: the instantiation only ever finishes rows straight from the shared memory of the CTA
+// that streamed them, in sampling mode -- the record path and the k-best mode are left out of it.
+template <typename T, int kRoute, bool kOneRow>
 __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, uint64_t* sel, unsigned long long* selq, int row,
                                            const RowSrc& src) {
     const int tid = threadIdx.x;
+    const bool direct = kOneRow || src.direct;
+    const bool local_mode = !kOneRow && A.mode == kScanLocal;
     const int nseg = src.nseg, c_first = src.c_first;
     const int b = src.b, g = src.g;
     const born_row_params& rp = src.rp;
@@ -459,7 +473,7 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
     // statistics: row maximum, exclusion level, best lane-maxima bound, log-sum-exp sum
     float m = src.m, taux = src.taux, bk = src.bk, ls = src.ls;
     const bool cached = nseg <= kHdrCache;
-    if (!src.direct) {
+    if (!direct) {
         m = -INFINITY; taux = -INFINITY; bk = -INFINITY; ls = 0.0f;
         if (cached) {  // the headers are fetched once (one round trip to L2) and shared
             cta_sync();
@@ -503,7 +517,7 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
     auto count_of = [&](int s) { return cached ? (int)sh.hdr_cnt[s] : (int)__ldcg(reinterpret_cast<const uint32_t*>(rec_of(s)) + 4); };
     // every raw entry (value bits << 32 | token id) of the row, dealt over the threads
     auto for_entries = [&](auto f) {
-        if (src.direct) {
+        if (direct) {
             for (int idx = tid; idx < kScanWarps * kWarpCand; idx += kThreads) {
                 const int w = idx / kWarpCand, i = idx - w * kWarpCand;
                 if (i < (int)min(src.wcount[w], (uint32_t)kWarpCand)) f(src.wbuf[idx]);
@@ -521,7 +535,7 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
     else if (m == INFINITY) status = BORN_ROW_POS_INF;
     else if (m == -INFINITY) status = BORN_ROW_ALL_MASKED;
 
-    if (A.mode == kScanLocal) {
+    if (local_mode) {
         // ---- the k best of the virtual row, in rank order
         int n = 0;
         if (status == BORN_ROW_OK) {
@@ -539,7 +553,7 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
             // complete above max(bk, taux); the k best are inside iff there are k of them (or nothing was excluded)
             if (n > kSelCap || (taux > bk && n < pl.k) || (RouteOf<kRoute>::lane && pl.no_bound)) {
                 // the exact search over the row writes the record instead
-                if (tid == 0) A.deferred[row] = (8u << 24) | (blockIdx.x + 1u);
+                if (tid == 0) defer_row<kOneRow>(A, sh, row, 8u);
                 return;
             }
         }
@@ -561,7 +575,7 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
 
     if (pl.greedy) {
         if (taux > m) {  // a token equal to the maximum may have been lost to a full buffer
-            if (tid == 0) A.deferred[row] = (1u << 24) | (blockIdx.x + 1u);
+            if (tid == 0) defer_row<kOneRow>(A, sh, row, 1u);
             return;
         }
         uint64_t best = 0;
@@ -609,7 +623,7 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
         if (!(RouteOf<kRoute>::mass && pl.window)) {
             if (A.out_kept_count && tid == 0) A.out_kept_count[b] = nfin;
             if (A.out_kept_ids) {  // the kept set is the whole row: no list of a useful size exists
-                if (tid == 0) A.deferred[row] = (2u << 24) | (blockIdx.x + 1u);
+                if (tid == 0) defer_row<kOneRow>(A, sh, row, 2u);
                 return;
             }
             draw_whole_row<T>(A, sh, nullptr, o, rp, b, g, row, m, pl.inv_T, S_tot, u);
@@ -630,7 +644,7 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
     float lowest = complete ? cut : taux;  // below it the entries are not all there: not used
     // (sh.nl is zero on entry: the caller's last barrier saw to it)
     auto gather = [&](float low) {
-        if (src.direct) {
+        if (direct) {
             // a warp compacts its own buffer: one reservation per 32 entries
             const int lane = tid & 31, w = tid >> 5;
             const uint32_t cnt = min(src.wcount[w], (uint32_t)kWarpCand);
@@ -722,7 +736,7 @@ __device__ __forceinline__ void finish_row(const ScanArgs& A, ScanShared& sh, ui
         else defer = !select_and_draw(in, sel, selq, sh, o);
         if (defer) why = 7;                        // the nucleus reaches below the candidates
     }
-    if (defer && tid == 0) A.deferred[row] = (why << 24) | (blockIdx.x + 1u);
+    if (defer && tid == 0) defer_row<kOneRow>(A, sh, row, why);
 }
 
 }  // namespace born

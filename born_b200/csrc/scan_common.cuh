@@ -104,11 +104,12 @@ struct RowGeom {
     int lead;              // elements between the 16-byte boundary below the row and its first logit
     const uint8_t* abase;  // that boundary
 };
-template <typename T>
+// kOneSeg: the launch has no vocabulary segments (G == 1)
+template <typename T, bool kOneSeg = false>
 __device__ __forceinline__ RowGeom row_geom(const ScanArgs& A, int r) {
     RowGeom q;
-    q.b = r / A.G;
-    q.g = r - q.b * A.G;
+    q.b = kOneSeg ? r : r / A.G;
+    q.g = kOneSeg ? 0 : r - q.b * A.G;
     const uint8_t* base = reinterpret_cast<const uint8_t*>(A.logits) +
                           ((int64_t)q.b * A.row_stride + (int64_t)q.g * A.V) * (int64_t)sizeof(T);
     const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(base) & 15u);
@@ -179,6 +180,7 @@ struct ScanShared {
     uint32_t maxbits;               // key of the running maximum (only ever raised)
     uint32_t excl_bits;             // key of the exclusion level (only ever raised)
     uint32_t rec_count;
+    uint32_t defer;             // one-row launches: the row's `deferred` word (0: finished)
     float wbound[kScanWarps];       // per warp: its share of the lane-maxima bound
     uint32_t wcount[kScanWarps];    // candidates in each warp's buffer
     float wmax[kScanWarps], wsum[kScanWarps];

@@ -1,7 +1,8 @@
-// scan_kernel for fp32 launches without a token history (paired tiles, no history code).
+// scan_kernel for fp32 launches without a token history (paired tiles, no history code); any grid and mode.
 #include <cstdint>
 #define SCAN_INST_T float
 #define SCAN_INST_PAIR true
+#define SCAN_INST_ONEROW false
 #define SCAN_INST_ATTRS scan_attrs_f32_pair
 #define SCAN_INST_LAUNCH scan_launch_f32_pair
 #include "scan_inst.cuh"

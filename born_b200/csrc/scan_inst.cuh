@@ -2,6 +2,7 @@
 // included by scan_f32_pair.cu, scan_f32_hist.cu and scan_bf16.cu after they have defined
 //   SCAN_INST_T      the element type (float or uint16_t)
 //   SCAN_INST_PAIR   true: fp32 without a token history (paired tiles); false otherwise
+//   SCAN_INST_ONEROW true: sampling launches whose grid gives every CTA one whole row
 //   SCAN_INST_ATTRS  / SCAN_INST_LAUNCH   the names of the two functions of scan_launch.cuh
 #include <cuda_runtime.h>
 #include <math.h>
@@ -18,7 +19,7 @@ namespace {
 
 template <bool M, bool Lse, int R>
 cudaError_t attr_one() {
-    return cudaFuncSetAttribute(scan_kernel<SCAN_INST_T, M, Lse, SCAN_INST_PAIR, R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    return cudaFuncSetAttribute(scan_kernel<SCAN_INST_T, M, Lse, SCAN_INST_PAIR, R, SCAN_INST_ONEROW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 scan_smem_layout((int)sizeof(SCAN_INST_T), M, true).total);
 }
 // (the route classes 1 and 2 exist for launches without a mask that want the log-sum-exp -- the
@@ -37,10 +38,10 @@ cudaError_t attr_all_routes() {
 template <bool M, bool Lse>
 cudaError_t launch_route(const ScanArgs& A, int route, int grid, size_t smem, cudaStream_t st) {
     if constexpr (!M && Lse) {
-        if (route == 1) { scan_kernel<SCAN_INST_T, M, Lse, SCAN_INST_PAIR, 1><<<grid, kScanThreads, smem, st>>>(A); return cudaGetLastError(); }
-        if (route == 2) { scan_kernel<SCAN_INST_T, M, Lse, SCAN_INST_PAIR, 2><<<grid, kScanThreads, smem, st>>>(A); return cudaGetLastError(); }
+        if (route == 1) { scan_kernel<SCAN_INST_T, M, Lse, SCAN_INST_PAIR, 1, SCAN_INST_ONEROW><<<grid, kScanThreads, smem, st>>>(A); return cudaGetLastError(); }
+        if (route == 2) { scan_kernel<SCAN_INST_T, M, Lse, SCAN_INST_PAIR, 2, SCAN_INST_ONEROW><<<grid, kScanThreads, smem, st>>>(A); return cudaGetLastError(); }
     }
-    scan_kernel<SCAN_INST_T, M, Lse, SCAN_INST_PAIR, 0><<<grid, kScanThreads, smem, st>>>(A);
+    scan_kernel<SCAN_INST_T, M, Lse, SCAN_INST_PAIR, 0, SCAN_INST_ONEROW><<<grid, kScanThreads, smem, st>>>(A);
     return cudaGetLastError();
 }
 

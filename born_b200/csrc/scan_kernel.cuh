@@ -513,6 +513,12 @@ struct TileCursor {
         p = tile_pos(t, A.tpr);
         q = row_geom<T>(A, p.row);
     }
+    // the CTA streams exactly row `row` (no divisions on the way to the first copy)
+    __device__ __forceinline__ void start_row(const ScanArgs& A, int row) {
+        p.row = row;
+        p.j = 0;
+        q = row_geom<T, true>(A, row);
+    }
     // returns true when the next tile opens a new row
     __device__ __forceinline__ bool next(const ScanArgs& A, bool more) {
         if (++p.j < A.tpr) return false;
@@ -525,7 +531,7 @@ struct TileCursor {
 
 // The producer warp: keeps the ring full.  Step n waits (bounded) for the stage of tile n to be
 // handed back by the compute warps and issues its copy.
-template <typename T, bool kMask>
+template <typename T, bool kMask, bool kOneRow>
 __device__ __forceinline__ void producer_loop(const ScanArgs& A, ScanShared& sh, uint8_t* smem, const ScanSmem& L,
                                               long long t0, long long t1) {
     const int lane = threadIdx.x & 31;
@@ -534,7 +540,8 @@ __device__ __forceinline__ void producer_loop(const ScanArgs& A, ScanShared& sh,
     uint32_t round = 0;
     bool ok = true;
     TileCursor<T> ci;
-    ci.start(A, t0);
+    if constexpr (kOneRow) ci.start_row(A, (int)blockIdx.x);
+    else ci.start(A, t0);
     for (; n < n_tiles; ++n) {
         if (n >= kScanStages &&
             !mbar_wait_limit(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage]), (round - 1u) & 1u, A.timeout_ns, &sh.fail)) {
@@ -562,7 +569,7 @@ __device__ __forceinline__ void producer_loop(const ScanArgs& A, ScanShared& sh,
 // CTA's segments it has been.  The warp never blocks on one thing while the other could move:
 // it alternates between "issue the next copy if its stage is free" and "patch and release the
 // next tile if it has landed", and sleeps a few dozen nanoseconds when neither can.
-template <typename T, bool kMask>
+template <typename T, bool kMask, bool kOneRow>
 __device__ __forceinline__ void producer_loop_patching(const ScanArgs& A, ScanShared& sh, uint8_t* smem, const ScanSmem& L,
                                                        long long t0, long long t1) {
     constexpr int TILE = TileOf<T>::n;
@@ -573,8 +580,8 @@ __device__ __forceinline__ void producer_loop_patching(const ScanArgs& A, ScanSh
     int n_p = 0, stage_p = 0;   // next tile to patch and release
     uint32_t round_p = 0;
     TileCursor<T> ci, cp;
-    ci.start(A, t0);
-    cp.start(A, t0);
+    if constexpr (kOneRow) { ci.start_row(A, (int)blockIdx.x); cp = ci; }
+    else { ci.start(A, t0); cp.start(A, t0); }
     int seg_p = 0;              // ordinal of the segment the release cursor is in
     bool seg_open = false;      // ... and whether its list has been taken over
     int n_list = 0, pos = 0;
@@ -939,7 +946,10 @@ __device__ __forceinline__ void ring_append(const ScanArgs& A, int b) {
 // ---- the kernel -------------------------------------------------------------------------------
 // kPair: the steady-state loop may take two tiles at a time (fp32 launches without token
 // histories; a separate instantiation so that the other launches keep their register allocation).
-template <typename T, bool kMask, bool kLse, bool kPair, int kRoute>
+// kOneRow: a sampling launch whose grid gives every CTA exactly one whole row (the host checks
+// grid == rows and the mode), so the segment records, the tickets and the k-best mode are left
+// out of the instantiation -- code that is never run still costs registers and instruction cache.
+template <typename T, bool kMask, bool kLse, bool kPair, int kRoute, bool kOneRow>
 __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_constant__ ScanArgs A) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ ScanShared sh;
@@ -955,7 +965,9 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
     const long long rows = (long long)A.B * A.G;
     const long long T_total = rows * A.tpr;
     const long long ncta = gridDim.x;
-    const long long t0 = range_begin(blockIdx.x, T_total, ncta), t1 = range_begin(blockIdx.x + 1, T_total, ncta);
+    // (one row per CTA: the tile range is the row's, known without the 64-bit divisions)
+    const long long t0 = kOneRow ? (long long)blockIdx.x * A.tpr : range_begin(blockIdx.x, T_total, ncta);
+    const long long t1 = kOneRow ? t0 + A.tpr : range_begin(blockIdx.x + 1, T_total, ncta);
     if (tid == 0) {
         for (int s = 0; s < kScanStages; ++s) {
             mbar_init(reinterpret_cast<uint64_t*>(&sh.full_bar[s]), 1);
@@ -973,12 +985,12 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
     int ids[kHistPer];
 #pragma unroll
     for (int r = 0; r < kHistPer; ++r) ids[r] = -1;
-    if (has_hist && tid < kThreads && t0 < t1) hist_ids(A, (int)(t0 / A.tpr) / A.G, ids);
+    if (has_hist && tid < kThreads && t0 < t1) hist_ids(A, kOneRow ? (int)blockIdx.x : (int)(t0 / A.tpr) / A.G, ids);
     __syncthreads();  // the only barrier all 288 threads share
 
     if (tid >= kThreads) {
-        if constexpr (prod_patch) producer_loop_patching<T, kMask>(A, sh, smem, L, t0, t1);
-        else producer_loop<T, kMask>(A, sh, smem, L, t0, t1);
+        if constexpr (prod_patch) producer_loop_patching<T, kMask, kOneRow>(A, sh, smem, L, t0, t1);
+        else producer_loop<T, kMask, kOneRow>(A, sh, smem, L, t0, t1);
         return;
     }
 
@@ -997,11 +1009,13 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
     uint32_t phase = 0;    // ... and the parity of its use
     while (t < t1) {
         // ---- segment set-up (block-synchronous)
-        const TilePos p0 = tile_pos(t, A.tpr);
+        TilePos p0;
+        if constexpr (kOneRow) { p0.row = (int)blockIdx.x; p0.j = 0; }
+        else p0 = tile_pos(t, A.tpr);
         const long long seg_begin = t;
         const long long seg_end = min(t1, (long long)(p0.row + 1) * A.tpr);
         ++seg_ord;
-        const RowGeom q = row_geom<T>(A, p0.row);
+        const RowGeom q = row_geom<T, kOneRow>(A, p0.row);
         const born_row_params rp = A.row_params ? A.row_params[q.b] : A.params;
         SegCtx sg;
         sg.plan = row_plan(rp);
@@ -1014,10 +1028,11 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
             sh.maxbits = zkey(-INFINITY);
             sh.excl_bits = zkey(-INFINITY);
             sh.rec_count = 0;
+            if constexpr (kOneRow) sh.defer = 0;
             sh.nl = 0;  // (the row's finish counts its candidates here)
         }
         // the row's uniform is wanted at the very end: fetch it now
-        const float u_row = (A.uniforms != nullptr && A.mode == kScanFull) ? __ldg(A.uniforms + q.b) : 0.0f;
+        const float u_row = (A.uniforms != nullptr && (kOneRow || A.mode == kScanFull)) ? __ldg(A.uniforms + q.b) : 0.0f;
         if (tid < kScanWarps) { sh.wbound[tid] = -INFINITY; sh.wcount[tid] = 0; }
         if (has_hist) {
             // the history build's (tile, warp) counters (kHistNarrowTiles x 8 of 16 bits) and its hash
@@ -1285,7 +1300,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
         }
         // A row that this CTA streamed from its first tile to its last needs no record and no
         // ticket: it is finished straight from shared memory.
-        const bool whole = seg_begin == (long long)p0.row * A.tpr && seg_end == (long long)(p0.row + 1) * A.tpr;
+        const bool whole = kOneRow || seg_begin == (long long)p0.row * A.tpr && seg_end == (long long)(p0.row + 1) * A.tpr;
         RowSrc src;
         src.b = q.b; src.g = q.g; src.u = u_row; src.rp = rp; src.plan = pl;
         bool finish_here;
@@ -1367,13 +1382,14 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
         }
         // (one call site: the finish is inlined, its arguments stay in registers)
         if (finish_here) {
-            finish_row<T, kRoute>(A, sh, reinterpret_cast<uint64_t*>(smem + L.sel), reinterpret_cast<unsigned long long*>(smem + L.cand),
+            finish_row<T, kRoute, kOneRow>(A, sh, reinterpret_cast<uint64_t*>(smem + L.sel), reinterpret_cast<unsigned long long*>(smem + L.cand),
                           p0.row, src);
-            if (A.ring != nullptr && A.mode == kScanFull) {
+            if (A.ring != nullptr && (kOneRow || A.mode == kScanFull)) {
                 cta_sync();  // the row's outputs are written (or the row is handed to the exact search)
-                if (tid == 0 && A.deferred[p0.row] == 0) ring_append(A, q.b);
+                if (tid == 0 && (kOneRow ? sh.defer : A.deferred[p0.row]) == 0) ring_append(A, q.b);
             }
         }
+        if constexpr (kOneRow) break;  // (the CTA's only row)
     }
 
     if (!bad) bad = cta_sync_or(*reinterpret_cast<const volatile int*>(&sh.fail));
@@ -1396,9 +1412,9 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                 }
             }
         }
-        const int r0 = (int)(t0 / A.tpr), r1 = (int)((t1 - 1) / A.tpr);
+        const int r0 = kOneRow ? (int)blockIdx.x : (int)(t0 / A.tpr), r1 = kOneRow ? r0 : (int)((t1 - 1) / A.tpr);
         for (int r = r0 + tid; r <= r1; r += kThreads) {
-            if (A.mode == kScanFull) {
+            if ((kOneRow || A.mode == kScanFull)) {
                 A.out_status[r / A.G] = 100 + BORN_ERR_DEVICE_TIMEOUT;
                 A.out_token[r / A.G] = -1;
             }
@@ -1410,15 +1426,19 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
     // ---- rows whose kept set could not be proven complete: exact fallback, now that the ring is idle
     cta_sync();
     {
-        const int r0 = (int)(t0 / A.tpr), r1 = (int)((t1 - 1) / A.tpr);
+        const int r0 = kOneRow ? (int)blockIdx.x : (int)(t0 / A.tpr), r1 = kOneRow ? r0 : (int)((t1 - 1) / A.tpr);
         for (int r = r0; r <= r1; ++r) {
-            const uint32_t owner = __ldcg(&A.deferred[r]);
+            const uint32_t owner = kOneRow ? sh.defer : __ldcg(&A.deferred[r]);
             if ((owner & 0xFFFFFFu) == (uint32_t)blockIdx.x + 1u) {
                 cta_sync();
-                if (tid == 0) { A.deferred[r] = 0; atomicAdd(A.dev_error + 1, 1); atomicAdd(A.dev_error + 8 + (owner >> 24), 1); }
+                if (tid == 0) {
+                    if constexpr (!kOneRow) A.deferred[r] = 0;
+                    atomicAdd(A.dev_error + 1, 1);
+                    atomicAdd(A.dev_error + 8 + (owner >> 24), 1);
+                }
                 fallback_row<T>(A, sh, smem, r);
                 cta_sync();
-                if (A.ring != nullptr && A.mode == kScanFull && tid == 0) ring_append(A, r / A.G);
+                if (A.ring != nullptr && (kOneRow || A.mode == kScanFull) && tid == 0) ring_append(A, r / A.G);
             }
         }
     }

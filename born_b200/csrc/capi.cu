@@ -178,6 +178,8 @@ cudaError_t scan_attrs_all() {
     if ((e = scan_attrs_f32_pair_row()) != cudaSuccess) return e;
     if ((e = scan_attrs_f32_hist()) != cudaSuccess) return e;
     if ((e = scan_attrs_f32_hist_row()) != cudaSuccess) return e;
+    if ((e = scan_attrs_bf16_pair()) != cudaSuccess) return e;
+    if ((e = scan_attrs_bf16_pair_row()) != cudaSuccess) return e;
     if ((e = scan_attrs_bf16()) != cudaSuccess) return e;
     return scan_attrs_bf16_row();
 }
@@ -195,13 +197,16 @@ int launch_scan(Handle* h, const ScanArgs& A, int dtype, int grid, cudaStream_t 
     const bool has_mask = A.mask != nullptr;
     const bool lse = A.out_lse != nullptr || A.want_lse;
     const size_t smem = (size_t)scan_smem_layout(dtype == BORN_DTYPE_F32 ? 4 : 2, has_mask, A.history != nullptr).total;
-    // fp32 launches without a token history take the instantiations whose loop pairs tiles (and
-    // that carry no history code); fp32 launches with one take the others (which always have one)
+    // Launches without a token history take the instantiations that carry no history code (fp32:
+    // their loop pairs tiles); launches with one take the others.
     // A sampling launch whose grid is one CTA per row (the tile ranges of range_begin are then the
     // rows themselves) takes the instantiations without the segment-record path.
     const bool one_row = A.mode == kScanFull && A.G == 1 && grid == A.B;
     cudaError_t e;
-    if (dtype != BORN_DTYPE_F32)
+    if (dtype != BORN_DTYPE_F32 && A.history == nullptr)
+        e = one_row ? scan_launch_bf16_pair_row(A, has_mask, lse, route, grid, smem, st)
+                    : scan_launch_bf16_pair(A, has_mask, lse, route, grid, smem, st);
+    else if (dtype != BORN_DTYPE_F32)
         e = one_row ? scan_launch_bf16_row(A, has_mask, lse, route, grid, smem, st) : scan_launch_bf16(A, has_mask, lse, route, grid, smem, st);
     else if (A.history == nullptr)
         e = one_row ? scan_launch_f32_pair_row(A, has_mask, lse, route, grid, smem, st)

@@ -1,4 +1,4 @@
-// scan_kernel for bf16 launches (the token history, if any, is applied by the compute warps); any grid and mode.
+// scan_kernel for bf16 launches with a token history (applied by the compute warps); any grid and mode.
 #include <cstdint>
 #define SCAN_INST_T uint16_t
 #define SCAN_INST_PAIR false

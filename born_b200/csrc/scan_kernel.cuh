@@ -944,8 +944,10 @@ __device__ __forceinline__ void ring_append(const ScanArgs& A, int b) {
 }
 
 // ---- the kernel -------------------------------------------------------------------------------
-// kPair: the steady-state loop may take two tiles at a time (fp32 launches without token
-// histories; a separate instantiation so that the other launches keep their register allocation).
+// kPair: a launch without token histories -- no history code in the instantiation, the segment's
+// first and last tile are taken inside the steady-state loop, and (fp32) that loop may take two
+// tiles at a time; a separate instantiation so that the other launches keep their register
+// allocation.
 // kOneRow: a sampling launch whose grid gives every CTA exactly one whole row (the host checks
 // grid == rows and the mode), so the segment records, the tickets and the k-best mode are left
 // out of the instantiation -- code that is never run still costs registers and instruction cache.
@@ -955,11 +957,11 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
     __shared__ ScanShared sh;
     constexpr int TILE = TileOf<T>::n;
     const int tid = threadIdx.x;
-    // What the instantiation knows about token histories: fp32 launches come in two instantiations --
-    // kPair without a history, the other with one (the producer warp applies it) -- bf16 launches in
-    // one that finds out at run time (the compute warps apply it).
+    // What the instantiation knows about token histories: kPair instantiations serve the launches
+    // without one; of the others, the fp32 ones always have one (the producer warp applies it), the
+    // bf16 ones look at run time (a launch with a history pointer; the compute warps apply it).
     constexpr bool kFp32 = sizeof(T) == 4;
-    const bool has_hist = kFp32 ? !kPair : (A.history != nullptr);
+    const bool has_hist = kPair ? false : (kFp32 ? true : (A.history != nullptr));
     constexpr bool prod_patch = kFp32 && !kPair;
     const ScanSmem L = scan_smem_layout((int)sizeof(T), kMask, has_hist);
     const long long rows = (long long)A.B * A.G;
@@ -1069,7 +1071,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
             __threadfence_block();
             *reinterpret_cast<volatile int*>(&sh.hist_seq) = seg_ord + 1;
         }
-        const bool hist_on = sizeof(T) == 2 && hc.n > 0;  // (fp32: the producer warp applies the list)
+        const bool hist_on = !kPair && sizeof(T) == 2 && hc.n > 0;  // (fp32: the producer warp applies the list)
         const bool lean = A.fast && !(RouteOf<kRoute>::mass && pl.need_mass);
         for (; t < seg_end; ++t, ++seen, ++j, rem -= TILE) {
             // ---- the tiles of an aligned row.  Everything that is decided per segment stays outside;

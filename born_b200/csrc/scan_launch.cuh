@@ -1,7 +1,7 @@
 // Host-side entry points of the streaming kernel's instantiations.  The kernel is instantiated
-// in six translation units that compile side by side -- fp32 launches without a token history
-// (scan_f32_pair*.cu), fp32 launches with one (scan_f32_hist*.cu), bf16 launches (scan_bf16*.cu),
-// each once for any grid and mode and once (*_row.cu) for sampling launches whose grid gives
+// in eight translation units that compile side by side -- fp32 launches without a token history
+// (scan_f32_pair*.cu) and with one (scan_f32_hist*.cu), bf16 launches without (scan_bf16_pair*.cu)
+// and with one (scan_bf16*.cu), each once for any grid and mode and once (*_row.cu) for sampling launches whose grid gives
 // every CTA exactly one whole row -- each for mask x log-sum-exp and, without a mask and with
 // the log-sum-exp, per route class (RouteOf in scan_common.cuh).  capi.cu only calls these.
 #pragma once
@@ -20,6 +20,8 @@ SCAN_UNIT(f32_pair)
 SCAN_UNIT(f32_pair_row)
 SCAN_UNIT(f32_hist)
 SCAN_UNIT(f32_hist_row)
+SCAN_UNIT(bf16_pair)
+SCAN_UNIT(bf16_pair_row)
 SCAN_UNIT(bf16)
 SCAN_UNIT(bf16_row)
 #undef SCAN_UNIT

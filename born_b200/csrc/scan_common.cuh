@@ -16,7 +16,11 @@
 
 namespace born {
 
-constexpr int kScanStages = 4;              // bulk-copy stages in flight per CTA
+constexpr int kScanStages = 4;              // bulk-copy stages in flight per CTA: what every instantiation has ...
+constexpr int kScanStagesMax = 5;           // ... and what those without a mask and without a token history have: their
+                                            // shared memory has room for one more at two CTAs per SM, and the stream is
+                                            // bound by the bytes a CTA keeps in flight
+__host__ __device__ constexpr int scan_stages(bool has_mask, bool has_hist) { return (!has_mask && !has_hist) ? kScanStagesMax : kScanStages; }
 constexpr int kScanWarps = kThreads / 32;   // compute warps
 constexpr int kScanThreads = kThreads + 32; // compute threads + the producer warp
 constexpr int kWarpCand = 256;              // candidate slots per compute warp and segment
@@ -160,8 +164,9 @@ struct ScanSmem {
 __host__ __device__ inline ScanSmem scan_smem_layout(int elem_bytes, bool has_mask, bool has_hist) {
     ScanSmem L;
     int off = 0;
-    L.tiles = off; off += kScanStages * kTileBytes;
-    L.masks = off; off += has_mask ? kScanStages * ((kTileBytes / elem_bytes / 32 + 8) * 4) : 0;
+    const int stages = scan_stages(has_mask, has_hist);
+    L.tiles = off; off += stages * kTileBytes;
+    L.masks = off; off += has_mask ? stages * ((kTileBytes / elem_bytes / 32 + 8) * 4) : 0;
     off = (off + 127) & ~127;
     L.cand = off; off += kScanWarps * kWarpCand * 8;  // the warps' candidate buffers; the selection's masses once they are read
     L.sel = off; off += kSelCap * 8;                   // the selection's rank keys
@@ -173,9 +178,9 @@ static_assert(kScanWarps * kWarpCand * 8 >= kSelCap * 8, "the selection's masses
 
 // Static shared state of a CTA of scan_kernel (and of merge_kernel, which uses the selection part).
 struct ScanShared {
-    unsigned long long full_bar[kScanStages];
-    unsigned long long empty_bar[kScanStages];
-    unsigned long long ready_bar[kScanStages];  // fp32 launches with token histories: the producer has patched the tile
+    unsigned long long full_bar[kScanStagesMax];
+    unsigned long long empty_bar[kScanStagesMax];
+    unsigned long long ready_bar[kScanStagesMax];  // fp32 launches with token histories: the producer has patched the tile
     // segment state of the compute threads
     uint32_t maxbits;               // key of the running maximum (only ever raised)
     uint32_t excl_bits;             // key of the exclusion level (only ever raised)

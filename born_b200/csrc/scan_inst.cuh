@@ -20,7 +20,7 @@ namespace {
 template <bool M, bool Lse, int R>
 cudaError_t attr_one() {
     return cudaFuncSetAttribute(scan_kernel<SCAN_INST_T, M, Lse, SCAN_INST_PAIR, R, SCAN_INST_ONEROW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                scan_smem_layout((int)sizeof(SCAN_INST_T), M, true).total);
+                                scan_smem_layout((int)sizeof(SCAN_INST_T), M, !SCAN_INST_PAIR).total);
 }
 // (the route classes 1 and 2 exist for launches without a mask that want the log-sum-exp -- the
 // serving configurations; the others take the general instantiation: every instantiation costs

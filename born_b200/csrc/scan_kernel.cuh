@@ -531,7 +531,7 @@ struct TileCursor {
 
 // The producer warp: keeps the ring full.  Step n waits (bounded) for the stage of tile n to be
 // handed back by the compute warps and issues its copy.
-template <typename T, bool kMask, bool kOneRow>
+template <typename T, bool kMask, bool kOneRow, int kStages>
 __device__ __forceinline__ void producer_loop(const ScanArgs& A, ScanShared& sh, uint8_t* smem, const ScanSmem& L,
                                               long long t0, long long t1) {
     const int lane = threadIdx.x & 31;
@@ -543,14 +543,14 @@ __device__ __forceinline__ void producer_loop(const ScanArgs& A, ScanShared& sh,
     if constexpr (kOneRow) ci.start_row(A, (int)blockIdx.x);
     else ci.start(A, t0);
     for (; n < n_tiles; ++n) {
-        if (n >= kScanStages &&
+        if (n >= kStages &&
             !mbar_wait_limit(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage]), (round - 1u) & 1u, A.timeout_ns, &sh.fail)) {
             ok = false;
             break;
         }
         if (lane == 0) producer_issue<T, kMask>(A, sh, smem, L, t0 + n, ci.p, ci.q, stage);
         ci.next(A, n + 1 < n_tiles);
-        if (++stage == kScanStages) { stage = 0; ++round; }
+        if (++stage == kStages) { stage = 0; ++round; }
     }
     if (!ok) sh.fail = 1;
     // what the failure path of the compute threads needs to know (see the end of scan_kernel)
@@ -956,6 +956,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ ScanShared sh;
     constexpr int TILE = TileOf<T>::n;
+    constexpr int kStages = scan_stages(kMask, !kPair);  // (launches with a history never take a kPair instantiation)
     const int tid = threadIdx.x;
     // What the instantiation knows about token histories: kPair instantiations serve the launches
     // without one; of the others, the fp32 ones always have one (the producer warp applies it), the
@@ -971,7 +972,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
     const long long t0 = kOneRow ? (long long)blockIdx.x * A.tpr : range_begin(blockIdx.x, T_total, ncta);
     const long long t1 = kOneRow ? t0 + A.tpr : range_begin(blockIdx.x + 1, T_total, ncta);
     if (tid == 0) {
-        for (int s = 0; s < kScanStages; ++s) {
+        for (int s = 0; s < kStages; ++s) {
             mbar_init(reinterpret_cast<uint64_t*>(&sh.full_bar[s]), 1);
             mbar_init(reinterpret_cast<uint64_t*>(&sh.empty_bar[s]), kScanWarps);
             mbar_init(reinterpret_cast<uint64_t*>(&sh.ready_bar[s]), 1);
@@ -992,7 +993,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
 
     if (tid >= kThreads) {
         if constexpr (prod_patch) producer_loop_patching<T, kMask, kOneRow>(A, sh, smem, L, t0, t1);
-        else producer_loop<T, kMask, kOneRow>(A, sh, smem, L, t0, t1);
+        else producer_loop<T, kMask, kOneRow, kStages>(A, sh, smem, L, t0, t1);
         return;
     }
 
@@ -1128,8 +1129,8 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                         // fp32: when the tile after this one has landed as well, the two are taken together
                         bool pair = false;
                         if (t + 1 < seg_end && rem >= 2 * TILE) {
-                            const int s2 = stage + 1 == kScanStages ? 0 : stage + 1;
-                            const uint32_t p2 = stage + 1 == kScanStages ? phase ^ 1u : phase;
+                            const int s2 = stage + 1 == kStages ? 0 : stage + 1;
+                            const uint32_t p2 = stage + 1 == kStages ? phase ^ 1u : phase;
                             pair = __all_sync(0xffffffffu, mbar_test(reinterpret_cast<uint64_t*>(&wait_bar[s2]), p2));  // (a probe that never suspends)
                             if (pair) {
                                 const float* tile2 = reinterpret_cast<const float*>(smem + L.tiles + s2 * kTileBytes);
@@ -1149,7 +1150,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                         __syncwarp();
                         for (int d = 0; d < n_done; ++d) {
                             if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage]));
-                            if (++stage == kScanStages) { stage = 0; phase ^= 1u; }
+                            if (++stage == kStages) { stage = 0; phase ^= 1u; }
                         }
                         t += n_done; seen += n_done; j += n_done; rem -= n_done * TILE;
                     } else {
@@ -1161,7 +1162,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
                         if (patched) fence_proxy_async();  // the stage is next written by a bulk copy
                         __syncwarp();
                         if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage]));
-                        if (++stage == kScanStages) { stage = 0; phase ^= 1u; }
+                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
                         ++t; ++seen; ++j; rem -= TILE;
                     }
                 }
@@ -1261,7 +1262,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
             if (patched) fence_proxy_async();  // the stage is next written by a bulk copy
             __syncwarp();
             if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage]));  // tile back to the producer
-            if (++stage == kScanStages) { stage = 0; phase ^= 1u; }
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
 
         // ---- segment record (block-synchronous)
@@ -1406,10 +1407,10 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
             while (!*reinterpret_cast<const volatile int*>(&sh.prod_done) && global_timer_ns() - w0 < 4 * A.timeout_ns) { }
             if (*reinterpret_cast<const volatile int*>(&sh.prod_done)) {
                 const long long issued = sh.issued;
-                for (long long tt = max(t0, issued - kScanStages); tt < issued; ++tt) {
+                for (long long tt = max(t0, issued - kStages); tt < issued; ++tt) {
                     if (tt == A.debug_skip_tile) continue;
                     const long long i = tt - t0;
-                    mbar_wait_limit(reinterpret_cast<uint64_t*>(&sh.full_bar[i % kScanStages]), (uint32_t)(i / kScanStages) & 1u,
+                    mbar_wait_limit(reinterpret_cast<uint64_t*>(&sh.full_bar[i % kStages]), (uint32_t)(i / kStages) & 1u,
                                     A.timeout_ns, nullptr);
                 }
             }

@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 # translation units (compiled side by side: the streaming kernel's instantiations take minutes)
-UNITS = ["capi.cu", "scan_f32_pair.cu", "scan_f32_pair_row.cu", "scan_f32_hist.cu", "scan_f32_hist_row.cu", "scan_bf16_pair.cu",
+UNITS = ["capi.cu", "scan_f32_pair.cu", "scan_f32_pair_row.cu", "scan_f32_hist.cu", "scan_f32_hist_row.cu", "scan_f32_hist_short_row.cu", "scan_bf16_pair.cu",
          "scan_bf16_pair_row.cu", "scan_bf16.cu", "scan_bf16_row.cu"]
 HEADERS = ["spec.cuh", "scan_common.cuh", "scan_kernel.cuh", "scan_inst.cuh", "scan_launch.cuh", "finish.cuh", "fallback.cuh",
            "merge_kernel.cuh", "prepass.cuh", "spec_kernel.cuh"]

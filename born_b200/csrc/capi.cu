@@ -178,6 +178,7 @@ cudaError_t scan_attrs_all() {
     if ((e = scan_attrs_f32_pair_row()) != cudaSuccess) return e;
     if ((e = scan_attrs_f32_hist()) != cudaSuccess) return e;
     if ((e = scan_attrs_f32_hist_row()) != cudaSuccess) return e;
+    if ((e = scan_attrs_f32_hist_short_row()) != cudaSuccess) return e;
     if ((e = scan_attrs_bf16_pair()) != cudaSuccess) return e;
     if ((e = scan_attrs_bf16_pair_row()) != cudaSuccess) return e;
     if ((e = scan_attrs_bf16()) != cudaSuccess) return e;
@@ -196,12 +197,16 @@ int launch_scan(Handle* h, const ScanArgs& A, int dtype, int grid, cudaStream_t 
     const int route = route_of(A.row_params, A.params);
     const bool has_mask = A.mask != nullptr;
     const bool lse = A.out_lse != nullptr || A.want_lse;
-    const size_t smem = (size_t)scan_smem_layout(dtype == BORN_DTYPE_F32 ? 4 : 2, has_mask, A.history != nullptr).total;
+
     // Launches without a token history take the instantiations that carry no history code (fp32:
     // their loop pairs tiles); launches with one take the others.
     // A sampling launch whose grid is one CTA per row (the tile ranges of range_begin are then the
     // rows themselves) takes the instantiations without the segment-record path.
     const bool one_row = A.mode == kScanFull && A.G == 1 && grid == A.B;
+    // ... and, fp32 with histories of at most kHistShort ids per row, the one whose list takes half the room
+    const bool short_hist = one_row && dtype == BORN_DTYPE_F32 && A.history != nullptr && A.history_stride <= kHistShort;
+    const size_t smem = (size_t)scan_smem_layout(dtype == BORN_DTYPE_F32 ? 4 : 2, has_mask, A.history != nullptr,
+                                                 short_hist ? kHistShort : (int)BORN_MAX_HISTORY).total;
     cudaError_t e;
     if (dtype != BORN_DTYPE_F32 && A.history == nullptr)
         e = one_row ? scan_launch_bf16_pair_row(A, has_mask, lse, route, grid, smem, st)
@@ -212,8 +217,9 @@ int launch_scan(Handle* h, const ScanArgs& A, int dtype, int grid, cudaStream_t 
         e = one_row ? scan_launch_f32_pair_row(A, has_mask, lse, route, grid, smem, st)
                     : scan_launch_f32_pair(A, has_mask, lse, route, grid, smem, st);
     else
-        e = one_row ? scan_launch_f32_hist_row(A, has_mask, lse, route, grid, smem, st)
-                    : scan_launch_f32_hist(A, has_mask, lse, route, grid, smem, st);
+        e = short_hist ? scan_launch_f32_hist_short_row(A, has_mask, lse, route, grid, smem, st)
+            : one_row  ? scan_launch_f32_hist_row(A, has_mask, lse, route, grid, smem, st)
+                       : scan_launch_f32_hist(A, has_mask, lse, route, grid, smem, st);
     if (e != cudaSuccess) return fail(h, BORN_ERR_CUDA, "scan kernel launch failed: %s", cudaGetErrorString(e));
     h->launches++;
     return BORN_OK;

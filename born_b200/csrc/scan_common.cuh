@@ -17,17 +17,21 @@
 namespace born {
 
 constexpr int kScanStages = 4;              // bulk-copy stages in flight per CTA: what every instantiation has ...
-constexpr int kScanStagesMax = 5;           // ... and what those without a mask and without a token history have: their
-                                            // shared memory has room for one more at two CTAs per SM, and the stream is
-                                            // bound by the bytes a CTA keeps in flight
-__host__ __device__ constexpr int scan_stages(bool has_mask, bool has_hist) { return (!has_mask && !has_hist) ? kScanStagesMax : kScanStages; }
+constexpr int kScanStagesMax = 5;           // ... and what those without a mask have whose token-history list is absent or short:
+                                            // their shared memory has room for one more at two CTAs per SM, and the stream
+                                            // is bound by the bytes a CTA keeps in flight
+constexpr int kHistShort = 512;             // history ids per row up to which the list counts as short
+// hist_cap: entries the history list has room for (kHistShort or BORN_MAX_HISTORY; ignored without a history)
+__host__ __device__ constexpr int scan_stages(bool has_mask, bool has_hist, int hist_cap) {
+    return (!has_mask && (!has_hist || hist_cap <= kHistShort)) ? kScanStagesMax : kScanStages;
+}
 constexpr int kScanWarps = kThreads / 32;   // compute warps
 constexpr int kScanThreads = kThreads + 32; // compute threads + the producer warp
 constexpr int kWarpCand = 256;              // candidate slots per compute warp and segment
 constexpr int kMassBlock = 512;             // tokens per mass block of the whole-vocabulary routes
 constexpr int kSelCap = 1024;               // candidates the in-shared-memory selection handles
 constexpr int kHashSlots = 2048;            // open-addressing table for the distinct history ids
-constexpr int kHdrCache = 64;                // segment headers of a row that the finish keeps in shared memory
+constexpr int kHdrCache = 32;                // segment headers of a row that the finish keeps in shared memory
 constexpr float kNucleusWindow = 10.0f;     // top-p alone: candidates are collected this far (in units of
                                             // scaled logits) below the running maximum, then verified
 
@@ -161,16 +165,16 @@ __host__ __device__ inline int cta_of_tile(long long t, long long T, long long G
 struct ScanSmem {
     int tiles, masks, cand, sel, hist, total;
 };
-__host__ __device__ inline ScanSmem scan_smem_layout(int elem_bytes, bool has_mask, bool has_hist) {
+__host__ __device__ inline ScanSmem scan_smem_layout(int elem_bytes, bool has_mask, bool has_hist, int hist_cap = BORN_MAX_HISTORY) {
     ScanSmem L;
     int off = 0;
-    const int stages = scan_stages(has_mask, has_hist);
+    const int stages = scan_stages(has_mask, has_hist, hist_cap);
     L.tiles = off; off += stages * kTileBytes;
     L.masks = off; off += has_mask ? stages * ((kTileBytes / elem_bytes / 32 + 8) * 4) : 0;
     off = (off + 127) & ~127;
     L.cand = off; off += kScanWarps * kWarpCand * 8;  // the warps' candidate buffers; the selection's masses once they are read
     L.sel = off; off += kSelCap * 8;                   // the selection's rank keys
-    L.hist = off; off += has_hist ? BORN_MAX_HISTORY * 8 : 0;  // the segment's distinct history tokens, by tile
+    L.hist = off; off += has_hist ? hist_cap * 8 : 0;  // the segment's distinct history tokens, by tile
     L.total = off;
     return L;
 }

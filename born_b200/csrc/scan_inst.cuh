@@ -3,6 +3,7 @@
 //   SCAN_INST_T      the element type (float or uint16_t)
 //   SCAN_INST_PAIR   true: launches without a token history (fp32: paired tiles); false: with one
 //   SCAN_INST_ONEROW true: sampling launches whose grid gives every CTA one whole row
+//   SCAN_INST_SHORT  (optional) true: histories of at most kHistShort ids per row
 //   SCAN_INST_ATTRS  / SCAN_INST_LAUNCH   the names of the two functions of scan_launch.cuh
 #include <cuda_runtime.h>
 #include <math.h>
@@ -14,13 +15,17 @@
 #include "fallback.cuh"
 #include "scan_launch.cuh"
 
+#ifndef SCAN_INST_SHORT
+#define SCAN_INST_SHORT false
+#endif
+
 namespace born {
 namespace {
 
 template <bool M, bool Lse, int R>
 cudaError_t attr_one() {
-    return cudaFuncSetAttribute(scan_kernel<SCAN_INST_T, M, Lse, SCAN_INST_PAIR, R, SCAN_INST_ONEROW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                scan_smem_layout((int)sizeof(SCAN_INST_T), M, !SCAN_INST_PAIR).total);
+    return cudaFuncSetAttribute(scan_kernel<SCAN_INST_T, M, Lse, SCAN_INST_PAIR, R, SCAN_INST_ONEROW, SCAN_INST_SHORT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                scan_smem_layout((int)sizeof(SCAN_INST_T), M, !SCAN_INST_PAIR, SCAN_INST_SHORT ? kHistShort : (int)BORN_MAX_HISTORY).total);
 }
 // (the route classes 1 and 2 exist for launches without a mask that want the log-sum-exp -- the
 // serving configurations; the others take the general instantiation: every instantiation costs
@@ -38,10 +43,10 @@ cudaError_t attr_all_routes() {
 template <bool M, bool Lse>
 cudaError_t launch_route(const ScanArgs& A, int route, int grid, size_t smem, cudaStream_t st) {
     if constexpr (!M && Lse) {
-        if (route == 1) { scan_kernel<SCAN_INST_T, M, Lse, SCAN_INST_PAIR, 1, SCAN_INST_ONEROW><<<grid, kScanThreads, smem, st>>>(A); return cudaGetLastError(); }
-        if (route == 2) { scan_kernel<SCAN_INST_T, M, Lse, SCAN_INST_PAIR, 2, SCAN_INST_ONEROW><<<grid, kScanThreads, smem, st>>>(A); return cudaGetLastError(); }
+        if (route == 1) { scan_kernel<SCAN_INST_T, M, Lse, SCAN_INST_PAIR, 1, SCAN_INST_ONEROW, SCAN_INST_SHORT><<<grid, kScanThreads, smem, st>>>(A); return cudaGetLastError(); }
+        if (route == 2) { scan_kernel<SCAN_INST_T, M, Lse, SCAN_INST_PAIR, 2, SCAN_INST_ONEROW, SCAN_INST_SHORT><<<grid, kScanThreads, smem, st>>>(A); return cudaGetLastError(); }
     }
-    scan_kernel<SCAN_INST_T, M, Lse, SCAN_INST_PAIR, 0, SCAN_INST_ONEROW><<<grid, kScanThreads, smem, st>>>(A);
+    scan_kernel<SCAN_INST_T, M, Lse, SCAN_INST_PAIR, 0, SCAN_INST_ONEROW, SCAN_INST_SHORT><<<grid, kScanThreads, smem, st>>>(A);
     return cudaGetLastError();
 }
 

@@ -569,7 +569,7 @@ __device__ __forceinline__ void producer_loop(const ScanArgs& A, ScanShared& sh,
 // CTA's segments it has been.  The warp never blocks on one thing while the other could move:
 // it alternates between "issue the next copy if its stage is free" and "patch and release the
 // next tile if it has landed", and sleeps a few dozen nanoseconds when neither can.
-template <typename T, bool kMask, bool kOneRow>
+template <typename T, bool kMask, bool kOneRow, int kStages>
 __device__ __forceinline__ void producer_loop_patching(const ScanArgs& A, ScanShared& sh, uint8_t* smem, const ScanSmem& L,
                                                        long long t0, long long t1) {
     constexpr int TILE = TileOf<T>::n;
@@ -592,11 +592,11 @@ __device__ __forceinline__ void producer_loop_patching(const ScanArgs& A, ScanSh
     while (n_p < n_tiles) {
         bool moved = false;
         if (n_i < n_tiles &&
-            (n_i < kScanStages || mbar_test(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage_i]), (round_i - 1u) & 1u))) {
+            (n_i < kStages || mbar_test(reinterpret_cast<uint64_t*>(&sh.empty_bar[stage_i]), (round_i - 1u) & 1u))) {
             if (lane == 0) producer_issue<T, kMask>(A, sh, smem, L, t0 + n_i, ci.p, ci.q, stage_i);
             ++n_i;
             ci.next(A, n_i < n_tiles);
-            if (++stage_i == kScanStages) { stage_i = 0; ++round_i; }
+            if (++stage_i == kStages) { stage_i = 0; ++round_i; }
             moved = true;
         }
         if (n_p < n_i && mbar_test(reinterpret_cast<uint64_t*>(&sh.full_bar[stage_p]), round_p & 1u)) {
@@ -631,7 +631,7 @@ __device__ __forceinline__ void producer_loop_patching(const ScanArgs& A, ScanSh
                 if (lane == 0) mbar_arrive(reinterpret_cast<uint64_t*>(&sh.ready_bar[stage_p]));
                 ++n_p;
                 if (cp.next(A, n_p < n_tiles)) { ++seg_p; seg_open = false; }
-                if (++stage_p == kScanStages) { stage_p = 0; ++round_p; }
+                if (++stage_p == kStages) { stage_p = 0; ++round_p; }
                 moved = true;
             }
         }
@@ -948,15 +948,18 @@ __device__ __forceinline__ void ring_append(const ScanArgs& A, int b) {
 // first and last tile are taken inside the steady-state loop, and (fp32) that loop may take two
 // tiles at a time; a separate instantiation so that the other launches keep their register
 // allocation.
+// kShortHist: the launch's histories have at most kHistShort ids per row (the host checks the
+// stride): the list takes half the room, which without a mask buys a fifth stage.
 // kOneRow: a sampling launch whose grid gives every CTA exactly one whole row (the host checks
 // grid == rows and the mode), so the segment records, the tickets and the k-best mode are left
 // out of the instantiation -- code that is never run still costs registers and instruction cache.
-template <typename T, bool kMask, bool kLse, bool kPair, int kRoute, bool kOneRow>
+template <typename T, bool kMask, bool kLse, bool kPair, int kRoute, bool kOneRow, bool kShortHist>
 __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_constant__ ScanArgs A) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ ScanShared sh;
     constexpr int TILE = TileOf<T>::n;
-    constexpr int kStages = scan_stages(kMask, !kPair);  // (launches with a history never take a kPair instantiation)
+    constexpr int kHistCap = kShortHist ? kHistShort : (int)BORN_MAX_HISTORY;
+    constexpr int kStages = scan_stages(kMask, !kPair, kHistCap);  // (launches with a history never take a kPair instantiation)
     const int tid = threadIdx.x;
     // What the instantiation knows about token histories: kPair instantiations serve the launches
     // without one; of the others, the fp32 ones always have one (the producer warp applies it), the
@@ -964,7 +967,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
     constexpr bool kFp32 = sizeof(T) == 4;
     const bool has_hist = kPair ? false : (kFp32 ? true : (A.history != nullptr));
     constexpr bool prod_patch = kFp32 && !kPair;
-    const ScanSmem L = scan_smem_layout((int)sizeof(T), kMask, has_hist);
+    const ScanSmem L = scan_smem_layout((int)sizeof(T), kMask, has_hist, kHistCap);
     const long long rows = (long long)A.B * A.G;
     const long long T_total = rows * A.tpr;
     const long long ncta = gridDim.x;
@@ -992,7 +995,7 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
     __syncthreads();  // the only barrier all 288 threads share
 
     if (tid >= kThreads) {
-        if constexpr (prod_patch) producer_loop_patching<T, kMask, kOneRow>(A, sh, smem, L, t0, t1);
+        if constexpr (prod_patch) producer_loop_patching<T, kMask, kOneRow, kStages>(A, sh, smem, L, t0, t1);
         else producer_loop<T, kMask, kOneRow, kStages>(A, sh, smem, L, t0, t1);
         return;
     }

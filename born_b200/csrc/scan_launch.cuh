@@ -1,8 +1,9 @@
 // Host-side entry points of the streaming kernel's instantiations.  The kernel is instantiated
-// in eight translation units that compile side by side -- fp32 launches without a token history
+// in nine translation units that compile side by side -- fp32 launches without a token history
 // (scan_f32_pair*.cu) and with one (scan_f32_hist*.cu), bf16 launches without (scan_bf16_pair*.cu)
 // and with one (scan_bf16*.cu), each once for any grid and mode and once (*_row.cu) for sampling launches whose grid gives
-// every CTA exactly one whole row -- each for mask x log-sum-exp and, without a mask and with
+// every CTA exactly one whole row (for fp32 with a history: once more for histories of at most
+// kHistShort ids per row, scan_f32_hist_short_row.cu) -- each for mask x log-sum-exp and, without a mask and with
 // the log-sum-exp, per route class (RouteOf in scan_common.cuh).  capi.cu only calls these.
 #pragma once
 #include <cuda_runtime.h>
@@ -20,6 +21,7 @@ SCAN_UNIT(f32_pair)
 SCAN_UNIT(f32_pair_row)
 SCAN_UNIT(f32_hist)
 SCAN_UNIT(f32_hist_row)
+SCAN_UNIT(f32_hist_short_row)
 SCAN_UNIT(bf16_pair)
 SCAN_UNIT(bf16_pair_row)
 SCAN_UNIT(bf16)

@@ -768,3 +768,23 @@ def test_history_penalties_on_rows_of_more_than_64_tiles(oracle, dtype):
         assert np.array_equal(out["kept_ids"].cpu().numpy(), ref["kept_ids"][:, :64])
     finally:
         s.close()
+
+
+@pytest.mark.parametrize("H", [512, 513, 1024])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_history_lengths_either_side_of_the_short_list(sampler, oracle, H, dtype):
+    # 256 rows give one CTA per row; fp32 launches with at most 512 history ids per row take the
+    # instantiation with the short list and five stages, longer histories the one with four
+    B, V = 256, 20000
+    params = dict(temperature=0.8, min_p=0.02, top_p=0.95, repetition_penalty=1.3, frequency_penalty=0.4, presence_penalty=0.2)
+    z = (W.normal(123, 1, B * V) * 3.0).astype(np.float32).reshape(B, V)
+    hist = W.randint(123, 3, B * H, V).astype(np.int32).reshape(B, H)
+    hist[:, 40:80] = hist[:, 0:40]                              # repeats
+    hist[:, H - 24:] = np.argsort(-z, axis=1)[:, :24]           # the tokens that matter, at the end of the list
+    hist_len = np.full(B, H, np.int32)
+    hist_len[::7] = H // 2                                      # ragged lengths
+    u = W.uniform_f32(123, 2, B)
+    logits = W.f32_to_bf16_bits(z).reshape(B, V) if dtype == "bf16" else z
+    got, ref = run_both(sampler, oracle, logits, params, u, hist=hist, hist_len=hist_len, want_kept=32)
+    assert_parity(got, ref)
+    assert (ref["status"] == 0).all()

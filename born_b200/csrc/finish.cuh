@@ -445,7 +445,6 @@ struct RowSrc {
     RowPlan plan;
 };
 
-// A row is complete: merge its statistics, select, draw.
 // Hands row `row` to the exact search that its CTA runs once the ring is idle.  The reason goes in
 // the upper byte.  A CTA that streams exactly one row keeps the word in shared memory (and spares
 // every CTA a round trip to global memory at its end).
@@ -456,6 +455,7 @@ __device__ __forceinline__ void defer_row(const ScanArgs& A, ScanShared& sh, int
     else A.deferred[row] = word;
 }
 
+// A row is complete: merge its statistics, select, draw.
 // kOneRow: the instantiation only ever finishes rows straight from the shared memory of the CTA
 // that streamed them, in sampling mode -- the record path and the k-best mode are left out of it.
 template <typename T, int kRoute, bool kOneRow>

@@ -124,3 +124,51 @@ def test_uploaded_masks_alternate_buffers_and_match_a_direct_mask(sampler, oracl
         assert np.array_equal(out["token"].cpu().numpy(), ref["token"])
         assert np.array_equal(out["status"].cpu().numpy(), ref["status"])
     assert ptrs[0] == ptrs[2] and ptrs[1] == ptrs[3] and ptrs[0] != ptrs[1]
+
+
+@pytest.mark.parametrize("cap,top_k", [(32, 40), (600, 40), (32, 300)], ids=["short-ring", "long-ring", "exact-search"])
+def test_device_history_with_one_cta_per_row(sampler, oracle, cap, top_k):
+    # 256 rows: every CTA streams one whole row (the instantiations without segment records), the
+    # CTA that finishes a row -- from its candidates or, for top-k above 256, by the exact search --
+    # appends the token to the ring; rings of at most 512 ids take the short history list
+    import torch
+    from born_b200 import SamplingConfig, _lib as L
+    B, V, steps, P = 256, 9000, 5, 20
+    params = dict(temperature=0.9, top_k=top_k, top_p=0.97, repetition_penalty=1.2, frequency_penalty=0.3, presence_penalty=0.1)
+    cfg, op = SamplingConfig(**params), oracle.make_params(**params)
+    prompts = W.randint(11, 1, B * P, V).astype(np.int32).reshape(B, P)
+    lens = (W.randint(11, 2, B, P + 1)).astype(np.int32)
+    stop = [int(x) for x in W.randint(11, 3, 2, V)]
+    sampler.history_create(cap)
+    sampler.history_set_stop_tokens(stop)
+    sampler.history_reset(_dev(prompts), _dev(lens))
+    hist = [list(prompts[b, :lens[b]]) for b in range(B)]
+    finished = np.zeros(B, dtype=bool)
+    for t in range(steps):
+        z = (W.normal(500 + t, 1, B * V) * 2.5).astype(np.float32).reshape(B, V)
+        z[(7 * t) % B, stop[t % 2]] += 30.0
+        u = W.uniform_f32(500 + t, 2, B)
+        out = sampler.sample_next(_dev(z), uniforms=_dev(u), config=cfg, want_lse=True)
+        torch.cuda.synchronize()
+        got_tok, got_st = out["token"].cpu().numpy(), out["status"].cpu().numpy()
+        H = max(1, max(min(len(h), cap) for h in hist))
+        hw = np.zeros((B, H), dtype=np.int32)
+        hl = np.zeros(B, dtype=np.int32)
+        for b in range(B):
+            tail = hist[b][-cap:]
+            hw[b, :len(tail)] = tail
+            hl[b] = len(tail)
+        ref = oracle.sample(z, op, uniforms=u, history=hw, history_len=hl, want_kept=1, nthreads=8)
+        for b in range(B):
+            if finished[b]:
+                assert got_tok[b] == -1 and got_st[b] == L.ROW_FINISHED, (t, b)
+                continue
+            assert got_tok[b] == ref["token"][b] and got_st[b] == ref["status"][b], (t, b)
+            hist[b].append(int(got_tok[b]))
+            if int(got_tok[b]) in stop:
+                finished[b] = True
+    tok, total, fin = sampler.history_read(B, cap)
+    assert finished.any() and not finished.all()
+    assert np.array_equal(fin.astype(bool), finished)
+    for b in range(B):
+        assert total[b] == len(hist[b])

@@ -417,9 +417,11 @@ __device__ __forceinline__ void mass_tile(const T* tile, const uint32_t* smask, 
         float v[16];
         int e0[NV];
         load16<T, kMask, true>(tile, smask, h, v, e0);
+        if (hi < TileOf<T>::n) {  // (a row's partial last tile: block-uniform)
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-            if (e0[i / VEC] + (i % VEC) >= hi) v[i] = -INFINITY;
+            for (int i = 0; i < 16; ++i)
+                if (e0[i / VEC] + (i % VEC) >= hi) v[i] = -INFINITY;
+        }
         float mt = v[0];
 #pragma unroll
         for (int i = 1; i < 16; ++i) mt = max_nan(mt, v[i]);

@@ -143,13 +143,13 @@ struct DrawCtx {
 };
 __device__ __forceinline__ uint64_t draw_weight(const DrawCtx& D, float zp, float zq) {
     if (D.residual) {
-        float pi = __fmul_rn(exp_det(scaled_shift(zp, D.mp, D.inv_T)), D.invSp);
-        float qi = __fmul_rn(exp_det(scaled_shift(zq, D.mq, D.inv_T)), D.invSq);
+        float pi = __fmul_rn(exp_det<false>(scaled_shift(zp, D.mp, D.inv_T)), D.invSp);
+        float qi = __fmul_rn(exp_det<false>(scaled_shift(zq, D.mq, D.inv_T)), D.invSq);
         float r = __fsub_rn(pi, qi);
         r = r > 0.0f ? r : 0.0f;
         return __float2ull_rn(__fmul_rn(r, 1099511627776.0f));
     }
-    return mass_of(scaled_shift(zp, D.mp, D.inv_T));
+    return mass_of<false>(scaled_shift(zp, D.mp, D.inv_T));
 }
 
 // ------------------------------------------------------------------ launch 1: block masses
@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(kSpecThreads, 2) spec_mass_kernel(const SpecKe
             for (int d = 16; d > 0; d >>= 1) mc = max_nan(mc, __shfl_xor_sync(0xffffffffu, mc, d));
             uint64_t Mc = 0;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) Mc += mass_of(scaled_shift(v[i], mc, A.inv_T));
+            for (int i = 0; i < 32; ++i) Mc += mass_of<false>(scaled_shift(v[i], mc, A.inv_T));
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) Mc += shfl_xor_u64(Mc, d);
             if (lane == 0 && !sh.fail) {
@@ -304,7 +304,7 @@ __global__ void __launch_bounds__(kSpecThreads, 2) spec_draw_kernel(const SpecKe
 #pragma unroll
                 for (int q = 0; q < kPerLane; ++q) {
                     if (bm[q] == -INFINITY) continue;
-                    const float ef = exp_det(scaled_shift(bm[q], m, A.inv_T));
+                    const float ef = exp_det<false>(scaled_shift(bm[q], m, A.inv_T));
                     S += __double2ull_rn(__dmul_rn(__ull2double_rn(bM[q]), (double)ef));
                 }
 #pragma unroll
@@ -338,8 +338,8 @@ __global__ void __launch_bounds__(kSpecThreads, 2) spec_draw_kernel(const SpecKe
             else {
                 const float* rowp = A.target + ((int64_t)b * R + j) * (int64_t)V;
                 const float* rowq = A.draft + ((int64_t)b * K + j) * (int64_t)V;
-                const uint64_t wp = mass_of(scaled_shift(rowp[x], zkey_to_float(sh.rowkey[j]), A.inv_T));
-                const uint64_t wq = mass_of(scaled_shift(rowq[x], zkey_to_float(sh.rowkey[R + j]), A.inv_T));
+                const uint64_t wp = mass_of<false>(scaled_shift(rowp[x], zkey_to_float(sh.rowkey[j]), A.inv_T));
+                const uint64_t wq = mass_of<false>(scaled_shift(rowq[x], zkey_to_float(sh.rowkey[R + j]), A.inv_T));
                 const double u = (double)A.u_accept[(int64_t)b * K + j];
                 const double lhs = __dmul_rn(__dmul_rn(u, __ull2double_rn(wq)), __ull2double_rn(sh.rowS[j]));
                 const double rhs = __dmul_rn(__ull2double_rn(wp), __ull2double_rn(sh.rowS[R + j]));

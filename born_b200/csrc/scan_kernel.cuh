@@ -231,6 +231,23 @@ __device__ __forceinline__ void push_hits(uint32_t hits, const T* tile, int h, i
     }
 }
 
+// Which of a thread's 16 values are candidates (at or above tau, and not -inf): only the groups of
+// four whose maximum m4[g] reaches tau are looked at, with one compare per value -- a threshold of
+// -inf is replaced by the lowest finite value, which every value above -inf reaches and -inf does
+// not.  The warp runs this whenever any of its lanes has a hit, which for top-k is most of the time.
+__device__ __forceinline__ uint32_t hit_mask(const float (&v)[16], const float (&m4)[4], float tau) {
+    const float tf = fmaxf(tau, -3.402823466e38f);
+    uint32_t hits = 0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        if (m4[g] >= tf) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) hits |= (v[4 * g + i] >= tf) ? (1u << (4 * g + i)) : 0u;
+        }
+    }
+    return hits;
+}
+
 // A full tile of a 16-byte-aligned row: straight-line code, one compare per 16 values.
 template <typename T, bool kMask, bool kLse>
 __device__ __forceinline__ void fast_tile(const T* tile, const uint32_t* smask, int id_tile0, float tau, float c2,
@@ -248,10 +265,7 @@ __device__ __forceinline__ void fast_tile(const T* tile, const uint32_t* smask, 
         st.mx = max_nan(st.mx, mt);
         if constexpr (kLse) lse16(st, v, mt, c2);
         if (mt >= tau) {  // rare per lane
-            uint32_t hits = 0;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) hits |= (v[i] >= tau && v[i] > -INFINITY) ? (1u << i) : 0u;
-            push_hits<T>(hits, tile, h, id_tile0, st, wbuf, wcount, excl);
+            push_hits<T>(hit_mask(v, m4, tau), tile, h, id_tile0, st, wbuf, wcount, excl);
         }
     }
     __syncwarp();
@@ -299,18 +313,8 @@ __device__ __forceinline__ void fast_tile_pair(const float* tile_a, const uint32
         }
         st.s = __fadd2_rn(__fadd2_rn(st.s, s1), __fadd2_rn(s2, s3));
     }
-    if (mta >= tau) {  // rare per lane
-        uint32_t hits = 0;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) hits |= (va[i] >= tau && va[i] > -INFINITY) ? (1u << i) : 0u;
-        push_hits<float>(hits, tile_a, 0, id_tile0, st, wbuf, wcount, excl);
-    }
-    if (mtb >= tau) {
-        uint32_t hits = 0;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) hits |= (vb[i] >= tau && vb[i] > -INFINITY) ? (1u << i) : 0u;
-        push_hits<float>(hits, tile_b, 0, id_tile0 + TILE, st, wbuf, wcount, excl);
-    }
+    if (mta >= tau) push_hits<float>(hit_mask(va, ma, tau), tile_a, 0, id_tile0, st, wbuf, wcount, excl);  // rare per lane
+    if (mtb >= tau) push_hits<float>(hit_mask(vb, mb, tau), tile_b, 0, id_tile0 + TILE, st, wbuf, wcount, excl);
     __syncwarp();
 }
 

@@ -49,16 +49,31 @@ def _rand_params(rng):
     return p
 
 
+SMALL_BATCHES = [1, 2, 3, 5, 16, 33, 64]
+ALL_VOCABS = [1, 7, 33, 1000, 4096, 4097, 8192, 8200, 32000, 50257, 65536, 128256, 151936, 200003]
+
+
 @pytest.mark.parametrize("seed", [11, 12, 13])
 def test_random_configurations_match_the_oracle(sampler, oracle, seed):
+    _random_configurations(sampler, oracle, seed, 80, SMALL_BATCHES, ALL_VOCABS)
+
+
+@pytest.mark.parametrize("seed", [21, 22])
+def test_random_configurations_with_one_cta_per_row(sampler, oracle, seed):
+    # batches that fill the GPU with one CTA per row (the instantiations without segment records),
+    # rows of one to a dozen tiles
+    _random_configurations(sampler, oracle, seed, 40, [252, 256, 280, 296], [1000, 4097, 8200, 20000, 32000, 50257])
+
+
+def _random_configurations(sampler, oracle, seed, iterations, batches, vocabs):
     import torch
     from born_b200 import SamplingConfig
     from born_b200.sampler import row_params_array
     rng = np.random.default_rng(seed)
     limit_rows = 0
-    for it in range(80):
-        B = int(rng.choice([1, 2, 3, 5, 16, 33, 64]))
-        V = int(rng.choice([1, 7, 33, 1000, 4096, 4097, 8192, 8200, 32000, 50257, 65536, 128256, 151936, 200003]))
+    for it in range(iterations):
+        B = int(rng.choice(batches))
+        V = int(rng.choice(vocabs))
         bf = rng.random() < 0.4
         z = (W.normal(seed * 1000 + it, 1, B * V) * float(rng.choice([0.5, 2.0, 3.0, 6.0]))).astype(np.float32).reshape(B, V)
         kind = int(rng.integers(0, 5))

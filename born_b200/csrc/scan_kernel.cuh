@@ -7,8 +7,8 @@
 // A CTA is 8 compute warps and one producer warp and streams a contiguous range of 16 KB
 // tiles (scan_common.cuh): all tiles of all rows form one sequence, cut evenly over the CTAs,
 // so a CTA may stream part of a row, a whole row, or several.  The part of a row inside one
-// CTA is a segment.  The producer keeps kScanStages tiles in flight with 1-D bulk copies (TMA,
-// no multicast) that complete on `full` mbarriers; the compute warps hand a tile back with one
+// CTA is a segment.  The producer keeps four tiles in flight (five where the instantiation's
+// shared memory has the room: scan_stages) with 1-D bulk copies (TMA, no multicast) that complete on `full` mbarriers; the compute warps hand a tile back with one
 // arrival each on its `empty` mbarrier.  Every thread reads a fixed share of each tile (16
 // values in four 16-byte vectors).  Inside a segment the warps meet only after its first tile
 // (threshold bootstrap) and at its end (statistics, record or finish).
@@ -426,9 +426,10 @@ __device__ __forceinline__ void mass_tile(const T* tile, const uint32_t* smask, 
             for (int i = 0; i < 16; ++i)
                 if (e0[i / VEC] + (i % VEC) >= hi) v[i] = -INFINITY;
         }
-        float mt = v[0];
+        float m4[4];
 #pragma unroll
-        for (int i = 1; i < 16; ++i) mt = max_nan(mt, v[i]);
+        for (int i = 0; i < 4; ++i) m4[i] = max_nan(max3_nan(v[4 * i], v[4 * i + 1], v[4 * i + 2]), v[4 * i + 3]);
+        const float mt = max_nan(max3_nan(m4[0], m4[1], m4[2]), m4[3]);
         st.mx = max_nan(st.mx, mt);
         const float mb = warp_max_nan(mt);
         unsigned long long q = 0;
@@ -453,9 +454,7 @@ __device__ __forceinline__ void mass_tile(const T* tile, const uint32_t* smask, 
         if (collect) {
             publish_max(st, sh);
             if (mt >= tau) {
-                uint32_t hits = 0;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) hits |= (v[i] >= tau && v[i] > -INFINITY) ? (1u << i) : 0u;
+                uint32_t hits = hit_mask(v, m4, tau);
 #pragma unroll 1
                 while (hits) {
                     const int i = __ffs(hits) - 1;

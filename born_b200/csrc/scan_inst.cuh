@@ -1,5 +1,5 @@
 // Body of a translation unit that instantiates scan_kernel for one (element type, history form):
-// included by scan_f32_pair.cu, scan_f32_hist.cu and scan_bf16.cu after they have defined
+// included by the scan_*.cu units after they have defined
 //   SCAN_INST_T      the element type (float or uint16_t)
 //   SCAN_INST_PAIR   true: launches without a token history (fp32: paired tiles); false: with one
 //   SCAN_INST_ONEROW true: sampling launches whose grid gives every CTA one whole row

@@ -474,7 +474,9 @@ struct TilePos {   // where global tile t lies
 };
 __device__ __forceinline__ TilePos tile_pos(long long t, int tpr) {
     TilePos p;
-    p.row = (int)(t / tpr);
+    // (a 64-bit division is a subroutine of a hundred instructions on the way to a CTA's first copy)
+    if (t <= 0x7FFFFFFFll) p.row = (int)((uint32_t)t / (uint32_t)tpr);
+    else p.row = (int)(t / tpr);
     p.j = (int)(t - (long long)p.row * tpr);
     return p;
 }
@@ -977,8 +979,17 @@ __global__ void __launch_bounds__(kScanThreads, 2) scan_kernel(const __grid_cons
     const long long T_total = rows * A.tpr;
     const long long ncta = gridDim.x;
     // (one row per CTA: the tile range is the row's, known without the 64-bit divisions)
-    const long long t0 = kOneRow ? (long long)blockIdx.x * A.tpr : range_begin(blockIdx.x, T_total, ncta);
-    const long long t1 = kOneRow ? t0 + A.tpr : range_begin(blockIdx.x + 1, T_total, ncta);
+    long long t0, t1;
+    if constexpr (kOneRow) {
+        t0 = (long long)blockIdx.x * A.tpr;
+        t1 = t0 + A.tpr;
+    } else if (T_total * (ncta + 1) <= 0xFFFFFFFFll) {  // (the products fit 32 bits: the same quotients, cheaply)
+        t0 = (long long)(((uint32_t)blockIdx.x * (uint32_t)T_total) / (uint32_t)ncta);
+        t1 = (long long)((((uint32_t)blockIdx.x + 1u) * (uint32_t)T_total) / (uint32_t)ncta);
+    } else {
+        t0 = range_begin(blockIdx.x, T_total, ncta);
+        t1 = range_begin(blockIdx.x + 1, T_total, ncta);
+    }
     if (tid == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(reinterpret_cast<uint64_t*>(&sh.full_bar[s]), 1);
